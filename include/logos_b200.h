@@ -1,0 +1,238 @@
+/*
+ * logos_b200.h — C ABI of liblogos_b200.so: the Q8 LLM-decode hot path as
+ * hand-written sm_100a CUDA kernels behind logicaffeine's native-operator /
+ * "Universal ABI" conventions.
+ *
+ * The reference (logicaffeine v0.10.1) ships no GPU operators; what it does
+ * fix, and what this header follows, is the shape of its C boundary:
+ *   - every exported symbol is `logos_<name>`
+ *       (crates/logicaffeine_compile/src/codegen/marshal.rs:143-146)
+ *   - every fallible entry returns a LogosStatus with these exact codes
+ *       (crates/logicaffeine_compile/src/codegen/ffi.rs:196-209, C mirror :1364-1375)
+ *   - the message of the last failure on the calling thread is read with
+ *     logos_last_error() / logos_get_last_error() and dropped with
+ *     logos_clear_error()            (ffi.rs:214-264)
+ *   - logos_abi_version() / logos_version()            (ffi.rs:275-285)
+ *   - objects cross as opaque logos_handle_t ids held in a mutex-guarded
+ *     registry; a stale or double-freed id is InvalidHandle, never UB
+ *                                                       (ffi.rs:212,288-324,368-388)
+ *   - out-parameters are null-checked before any work   (marshal.rs:355-358)
+ *   - LOGOS `Int` is i64, so extents are int64_t
+ *       (crates/logicaffeine_compile/src/codegen/types.rs:277)
+ * A Rust host binds these with one `extern "C"` block inside a
+ * `logicaffeine_system::llm` module shaped like `logicaffeine_system::ntt`
+ * (crates/logicaffeine_system/src/ntt.rs:330-335) and reaches them from LOGOS
+ * through rows in `map_native_function`
+ * (crates/logicaffeine_compile/src/codegen/program.rs:1936-2003).
+ *
+ * Threading: error state is per thread; the registry is behind a mutex; one
+ * model handle is driven by one host thread at a time.  `stream` arguments
+ * take a cudaStream_t cast to void* (NULL = the legacy default stream).
+ * There is no CPU fallback: without a CUDA device every compute entry
+ * returns LOGOS_ERROR.
+ */
+#ifndef LOGOS_B200_H
+#define LOGOS_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ffi.rs:196-209 */
+typedef enum {
+  LOGOS_OK = 0,
+  LOGOS_ERROR = 1,
+  LOGOS_REFINEMENT_VIOLATION = 2,
+  LOGOS_NULL_POINTER = 3,
+  LOGOS_OUT_OF_BOUNDS = 4,
+  LOGOS_DESERIALIZATION_FAILED = 5,
+  LOGOS_INVALID_HANDLE = 6,
+  LOGOS_CONTAINS_NULL_BYTE = 7,
+  LOGOS_THREAD_PANIC = 8,
+  LOGOS_MEMORY_EXHAUSTED = 9
+} logos_status_t;
+
+/* ffi.rs:212 — an id, not an address */
+typedef void* logos_handle_t;
+
+#define LOGOS_ABI_VERSION 1u
+
+#if defined(__GNUC__)
+#define LOGOS_API __attribute__((visibility("default")))
+#else
+#define LOGOS_API
+#endif
+
+/* element types of device buffers named in operator signatures */
+typedef enum {
+  LOGOS_F32 = 0,
+  LOGOS_F16 = 1,
+  LOGOS_BF16 = 2,
+  LOGOS_I8 = 3,
+  LOGOS_I32 = 4
+} logos_dtype_t;
+
+/* ---- runtime (names identical to the reference preamble, ffi.rs:1377-1384) ---- */
+LOGOS_API const char* logos_last_error(void);
+LOGOS_API const char* logos_get_last_error(void);
+LOGOS_API void logos_clear_error(void);
+LOGOS_API uint32_t logos_abi_version(void);
+LOGOS_API const char* logos_version(void);
+/* number of CUDA devices visible to the library; 0 when there is none */
+LOGOS_API int32_t logos_device_count(void);
+
+/* ---- device buffers (handles, ffi.rs:288-324; create/free pairs, ffi.rs:368-388) ---- */
+LOGOS_API logos_status_t logos_dev_alloc(int64_t bytes, int32_t device, logos_handle_t* out);
+LOGOS_API logos_status_t logos_dev_upload(logos_handle_t dst, int64_t dst_offset, const void* src_host, int64_t bytes);
+LOGOS_API logos_status_t logos_dev_download(void* dst_host, logos_handle_t src, int64_t src_offset, int64_t bytes);
+LOGOS_API logos_status_t logos_dev_memset(logos_handle_t dst, int32_t byte_value, int64_t bytes);
+/* raw device address and size of a buffer, for hosts that share it with other CUDA code */
+LOGOS_API logos_status_t logos_dev_ptr(logos_handle_t h, void** out_ptr, int64_t* out_bytes);
+LOGOS_API logos_status_t logos_dev_sync(int32_t device);
+LOGOS_API logos_status_t logos_dev_free(logos_handle_t h);
+/* Every device-side wait in the library is bounded; a kernel that gives up
+ * stores a non-zero code in a per-device status word instead of hanging.  This
+ * reads and clears it (0 = nothing reported).  Call after a synchronisation. */
+LOGOS_API logos_status_t logos_kernel_status(int32_t device, int32_t* out_code);
+
+/* ---- seeded synthetic inputs, generated on the device ----
+ * One counter-based generator (SplitMix64 finaliser over seed/stream/index, the
+ * mixer the reference seeds with: crates/logicaffeine_runtime/src/seed.rs:15-28)
+ * gives every element of every tensor from (seed, stream, index) alone, so a
+ * shard can be produced on the rank that owns it.
+ *   kind 0: int8 uniform in [-127,127]           (dst i8)
+ *   kind 1: f32 uniform in [a,b)                 (dst f32)
+ *   kind 2: normal, mean a, std b                (dst f32 / f16 / bf16 by `dtype`)
+ *   kind 3: int32 uniform in [0,(int)b)          (dst i32)
+ * `first_index` offsets the counter (element i uses first_index+i). */
+LOGOS_API logos_status_t logos_synth_fill(logos_handle_t dst, int64_t dst_offset_bytes, int32_t dtype, int32_t kind,
+                                uint64_t seed, uint64_t stream, int64_t first_index, int64_t count,
+                                float a, float b, void* stream_or_null);
+
+/* Weight prep: per 32-element block along K, s = max|w|/127, q = rint(w/s).
+ * w f32 [N][K] -> q i8 [N][K], s f32 [N][K/32]. */
+LOGOS_API logos_status_t logos_q8_quantize(logos_handle_t w, logos_handle_t q, logos_handle_t s,
+                                 int64_t n, int64_t k, void* stream_or_null);
+/* Generate w ~ N(0,std) with the generator above (element (r,c) of the full
+ * [rows_total][K] matrix uses index r*K+c) and quantise rows [row0,row0+n) in
+ * one pass, never holding f32 weights in memory. */
+LOGOS_API logos_status_t logos_q8_synth_weights(logos_handle_t q, logos_handle_t s, int64_t n, int64_t k,
+                                      int64_t row0, uint64_t seed, uint64_t stream, float std,
+                                      void* stream_or_null);
+
+/* ---- single operators ---- */
+
+/* y[n] = sum_kb s[n,kb] * sum_{k in kb} q[n,k] * x[k]   (f32 x, f32 accumulate, f32 y) */
+LOGOS_API logos_status_t logos_q8_gemv(logos_handle_t q /*i8 [N][K]*/, logos_handle_t s /*f32 [N][K/32]*/,
+                             logos_handle_t x /*f32 [K]*/, logos_handle_t y /*f32 [N]*/,
+                             int64_t n, int64_t k, void* stream_or_null);
+
+/* C[m,n] = bf16( sum_kb s[n,kb] * sum_k A[m,k] * q[n,k] )  (bf16 A, f32 accumulate)
+ * epilogue 0: plain.  1: C = bf16(acc + aux[m,n]) with aux bf16 [M][N] (residual).
+ * 2: rows of q interleave gate (even) and up (odd); C is [M][N/2] =
+ *    bf16( silu(acc_gate) * acc_up ).
+ * Uses the library's per-device scratch when the shape asks for split-K. */
+LOGOS_API logos_status_t logos_q8_gemm(logos_handle_t a /*bf16 [M][K]*/, logos_handle_t q, logos_handle_t s,
+                             logos_handle_t c /*bf16*/, int64_t m, int64_t n, int64_t k,
+                             int32_t epilogue, logos_handle_t aux_or_null, void* stream_or_null);
+
+/* Same contract as logos_q8_gemm, always on the plain SIMT kernel (no tensor
+ * cores, no split-K): the on-device cross-check the tests hold the tcgen05
+ * kernel against, and the path for shapes the tcgen05 kernel does not take. */
+LOGOS_API logos_status_t logos_q8_gemm_simt(logos_handle_t a, logos_handle_t q, logos_handle_t s,
+                                  logos_handle_t c, int64_t m, int64_t n, int64_t k,
+                                  int32_t epilogue, logos_handle_t aux_or_null, void* stream_or_null);
+
+/* cos/sin table for rotary embedding, computed on the host in double and
+ * rounded to f32: tab[pos][i] = {cos,sin}(pos * theta^(-2i/d)), i < d/2.
+ * `out_host` holds l_max*(d/2)*2 floats. */
+LOGOS_API logos_status_t logos_rope_table(float* out_host, int64_t l_max, int64_t d, double theta);
+
+/* Rotate k_new by its position (= seq_len[b]) and write k,v rows at that index;
+ * then seq_len[b] += 1.  f32 multiply and add rounded separately, fp16 store. */
+LOGOS_API logos_status_t logos_kv_append_rope(logos_handle_t k_cache, logos_handle_t v_cache /*f16 [B][Hkv][Lmax][D]*/,
+                                    logos_handle_t k_new, logos_handle_t v_new /*f16 [B][Hkv][D]*/,
+                                    logos_handle_t rope_table /*f32 [Lmax][D/2][2]*/,
+                                    logos_handle_t seq_len /*i32 [B]*/,
+                                    int64_t b, int64_t h_kv, int64_t d, int64_t l_max, void* stream_or_null);
+
+/* o = softmax(scale * q K^T) V over positions [0, seq_len[b]) for each of h_q
+ * query heads (h_q/h_kv query heads share a KV head); q is used as given (already
+ * rotated), f32 softmax.  q, o: f16 [B][Hq][D]. */
+LOGOS_API logos_status_t logos_gqa_decode_attn(logos_handle_t q, logos_handle_t k_cache, logos_handle_t v_cache,
+                                     logos_handle_t seq_len, logos_handle_t o,
+                                     int64_t b, int64_t h_q, int64_t h_kv, int64_t d, int64_t l_max,
+                                     float softmax_scale, void* stream_or_null);
+
+/* The fused form the decode step uses: rotate q and k_new at position seq_len[b],
+ * append k,v, attend over [0, seq_len[b]] including the new row, then
+ * seq_len[b] += 1.  q_raw / k_new / v_new are un-rotated f16. */
+LOGOS_API logos_status_t logos_gqa_decode_attn_fused(logos_handle_t q_raw, logos_handle_t k_new, logos_handle_t v_new,
+                                           logos_handle_t k_cache, logos_handle_t v_cache,
+                                           logos_handle_t rope_table, logos_handle_t seq_len, logos_handle_t o,
+                                           int64_t b, int64_t h_q, int64_t h_kv, int64_t d, int64_t l_max,
+                                           float softmax_scale, void* stream_or_null);
+
+/* y = x * rsqrt(mean(x^2) + eps) * g, rows of length h.  x,y f32 [rows][h], g f32 [h]. */
+LOGOS_API logos_status_t logos_rmsnorm(logos_handle_t x, logos_handle_t g, logos_handle_t y,
+                             int64_t rows, int64_t h, float eps, void* stream_or_null);
+/* y = silu(gate) * up, f32 element-wise over `count` elements. */
+LOGOS_API logos_status_t logos_swiglu(logos_handle_t gate, logos_handle_t up, logos_handle_t y,
+                            int64_t count, void* stream_or_null);
+
+/* ---- model level: batched Qwen-architecture greedy decode ---- */
+typedef struct {
+  int64_t layers, hidden, h_q, h_kv, head_dim, ffn, vocab, l_max, batch;
+  float   rms_eps, rope_theta;
+  int32_t tied_embeddings;   /* 1: lm_head shares the embedding matrix */
+  int32_t tp_degree, tp_rank; /* tensor-parallel group size and this rank */
+  int32_t device;
+  int32_t act_dtype;         /* precision of GEMM inputs: LOGOS_F32 (default: no rounding), LOGOS_F16 or LOGOS_BF16 */
+  uint64_t seed;             /* random-init weights: N(0, init_std) -> Q8 blocks of 32 */
+  float   init_std;
+  int32_t reserved;
+} logos_llm_config_t;
+
+/* 128-byte NCCL unique id for the tensor-parallel group (rank 0 makes it, the
+ * host carries it to the other ranks).  Not needed when tp_degree == 1. */
+LOGOS_API logos_status_t logos_tp_unique_id(void* out_128_bytes);
+LOGOS_API logos_status_t logos_llm_create(const logos_llm_config_t* cfg, const void* nccl_unique_id_or_null,
+                                logos_handle_t* out);
+/* Process t prompt tokens per sequence ([B][T] row-major, host) and fill the KV
+ * cache; sequence lengths become t.  Starts from an empty cache. */
+LOGOS_API logos_status_t logos_llm_prefill(logos_handle_t model, const int32_t* tokens_host, int64_t t);
+/* Fill the KV cache for positions [0,t) with seeded N(0,1) fp16 values instead
+ * of running a prompt (measurement of decode at a given context length). */
+LOGOS_API logos_status_t logos_llm_synth_kv(logos_handle_t model, int64_t t, uint64_t seed);
+/* Set the tokens the next decode step consumes ([B], host). */
+LOGOS_API logos_status_t logos_llm_set_tokens(logos_handle_t model, const int32_t* tokens_host);
+/* One greedy step for every sequence: consumes the current tokens, appends to the
+ * KV cache, writes argmax ids (lowest index wins ties) to next_tokens_host [B]
+ * and keeps them as the next step's input. */
+LOGOS_API logos_status_t logos_llm_decode_step(logos_handle_t model, int32_t* next_tokens_host);
+/* `steps` greedy steps without a host round trip in between; tokens_host
+ * receives [steps][B].  May be NULL to skip the read-back. */
+LOGOS_API logos_status_t logos_llm_decode_steps(logos_handle_t model, int64_t steps, int32_t* tokens_host_or_null);
+/* Parity-test accessors. K/V of one layer as stored on this rank:
+ * f16 [B][Hkv/tp][Lmax][D]; logits of the last step f32 [B][vocab]; lengths [B]. */
+LOGOS_API logos_status_t logos_llm_read_kv(logos_handle_t model, int64_t layer, void* k_host, void* v_host);
+LOGOS_API logos_status_t logos_llm_read_logits(logos_handle_t model, float* logits_host);
+LOGOS_API logos_status_t logos_llm_read_seq_len(logos_handle_t model, int32_t* seq_len_host);
+/* Rewind every sequence to length t (t <= current length): decode can be re-run
+ * from a prefilled state. */
+LOGOS_API logos_status_t logos_llm_set_seq_len(logos_handle_t model, int64_t t);
+/* Device-side time of the last logos_llm_decode_steps call, milliseconds
+ * (CUDA events on the model's stream), and kernels launched per step. */
+LOGOS_API logos_status_t logos_llm_last_timing(logos_handle_t model, double* ms_out, int64_t* launches_per_step_out);
+/* One greedy step with CUDA events around every launch group; ms_by_class_out
+ * receives 4 doubles: Q8 GEMMs, attention (+merge), norms/element-wise, and
+ * tensor-parallel exchange.  Advances the model like logos_llm_decode_step. */
+LOGOS_API logos_status_t logos_llm_profile_step(logos_handle_t model, double* ms_by_class_out);
+LOGOS_API logos_status_t logos_llm_free(logos_handle_t model);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LOGOS_B200_H */

@@ -1,0 +1,621 @@
+// GQA decode attention over an fp16 KV cache, with the rotary embedding and
+// the KV-cache append fused in.
+//
+// HBM-bound: every step streams the whole K and V history once (512 bytes per
+// position per KV head at D=128), so the kernel is built around that stream:
+//   * a (sequence, KV head) pair is cut into units of `unit_len` positions;
+//     one CTA per unit, sized so the grid is several waves of the SM count;
+//   * a producer thread moves 64-position K and V tiles into a 3-stage shared
+//     memory ring with TMA tile loads (128-byte swizzle, no multicast) signalled
+//     on mbarriers; four consumer warps each own 16 positions of every tile;
+//   * all query heads that share the KV head (up to 16) form the M side of
+//     m16n8k16 tensor-core MMAs, so a K/V tile is read from shared memory once
+//     for the whole group; scores, softmax and the running output stay in f32
+//     registers; the probabilities enter the second MMA as an fp16 high part
+//     plus an fp16 residual so the product keeps f32-class accuracy;
+//   * the CTA that owns the position being appended rotates the new key
+//     (f32 multiply and add rounded separately, fp16 store), writes the new
+//     K/V row to the cache and patches it into its own shared-memory tile;
+//   * units are merged by a second small kernel in a fixed order.
+#include "ops.cuh"
+#include "ptx.cuh"
+
+#include <math.h>
+
+namespace logos {
+
+namespace {
+
+using namespace ptx;
+
+constexpr int ATT_TILE = 64;
+constexpr int ATT_STAGES = 3;
+constexpr int ATT_CWARPS = 4;
+constexpr int ATT_THREADS = (ATT_CWARPS + 1) * 32;
+constexpr int ATT_BOX_BYTES = 64 * 128;  // 64 rows x 128 bytes
+
+struct AttnParams {
+  const __half* q_f16;
+  const float*  q_f32;
+  int64_t       q_ld;
+  int           rotate_q;
+  const __half* k_new_f16;
+  const __half* v_new_f16;
+  const float*  k_new_f32;
+  const float*  v_new_f32;
+  int64_t       kv_ld;
+  int           fused;
+  __half*       k_cache;
+  __half*       v_cache;
+  const float*  rope;
+  const int32_t* seq_len;
+  float*        part_o;   // [B][Hq][max_splits][D]
+  float*        part_ml;  // [B][Hq][max_splits][2]
+  int           b, h_q, h_kv, l_max, unit_len, max_splits;
+  float         scale_log2;
+  int*          status;
+};
+
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS)
+gqa_decode_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const AttnParams p) {
+  constexpr int NBOX = D / 64;
+  constexpr int STAGE_BYTES = 2 * NBOX * ATT_BOX_BYTES;
+  constexpr int QS_STRIDE = D + 8;  // halfs; +16 bytes keeps ldmatrix rows on distinct banks
+  constexpr int KSTEPS = D / 16;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stages = smem;                                            // ATT_STAGES * STAGE_BYTES
+  __half* qs = reinterpret_cast<__half*>(stages + ATT_STAGES * STAGE_BYTES);  // [16][QS_STRIDE]
+  __half* new_k = qs + 16 * QS_STRIDE;                               // [D]
+  __half* new_v = new_k + D;                                         // [D]
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(new_v + D);
+  uint64_t* bar_empty = bar_full + ATT_STAGES;
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int G = p.h_q / p.h_kv;
+
+  const int len0 = p.seq_len[b];
+  const bool append = p.fused && len0 < p.l_max;
+  int len_eff = p.fused ? len0 + 1 : len0;
+  if (len_eff > p.l_max) len_eff = p.l_max;
+  const int unit_start = split * p.unit_len;
+  if (unit_start >= len_eff) return;
+  const int unit_end = min(unit_start + p.unit_len, len_eff);
+  const int ntiles = (unit_end - unit_start + ATT_TILE - 1) / ATT_TILE;
+  const int64_t row_base = ((int64_t)b * p.h_kv + kvh) * p.l_max;
+  const int pos_new = len0;  // where the appended row goes
+  const bool owns_new = append && pos_new >= unit_start && pos_new < unit_start + p.unit_len;
+
+  if (tid == 0) {
+    for (int i = 0; i < ATT_STAGES; ++i) {
+      mbar_init(&bar_full[i], 1);
+      mbar_init(&bar_empty[i], ATT_CWARPS);
+    }
+    fence_barrier_init();
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v);
+  }
+
+  // ---- stage the query heads (rotated when asked), zero the padding rows
+  {
+    const int half_d = D / 2;
+    int pos_q = len0 < p.l_max ? len0 : p.l_max - 1;
+    if (pos_q < 0) pos_q = 0;
+    const float* tab = p.rope + (int64_t)pos_q * half_d * 2;
+    for (int i = tid; i < 16 * half_d; i += ATT_THREADS) {
+      int g = i / half_d, e = i - g * half_d;
+      float x1 = 0.f, x2 = 0.f;
+      if (g < G) {
+        int hq = kvh * G + g;
+        if (p.q_f16) {
+          const __half* qp = p.q_f16 + ((int64_t)b * p.h_q + hq) * D;
+          x1 = __half2float(qp[e]);
+          x2 = __half2float(qp[e + half_d]);
+        } else {
+          const float* qp = p.q_f32 + (int64_t)b * p.q_ld + (int64_t)hq * D;
+          x1 = qp[e];
+          x2 = qp[e + half_d];
+        }
+        if (p.rotate_q) {
+          float c = tab[2 * e], s = tab[2 * e + 1];
+          float r1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s));
+          float r2 = __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s));
+          x1 = r1;
+          x2 = r2;
+        }
+      }
+      qs[g * QS_STRIDE + e] = __float2half_rn(x1);
+      qs[g * QS_STRIDE + e + half_d] = __float2half_rn(x2);
+    }
+    // ---- the appended row: rotate k, round to fp16, write the cache, keep a copy
+    if (owns_new) {
+      const float* tabn = p.rope + (int64_t)pos_new * half_d * 2;
+      for (int e = tid; e < half_d; e += ATT_THREADS) {
+        float k1, k2, v1, v2;
+        if (p.k_new_f16) {
+          const __half* kp = p.k_new_f16 + ((int64_t)b * p.h_kv + kvh) * D;
+          const __half* vp = p.v_new_f16 + ((int64_t)b * p.h_kv + kvh) * D;
+          k1 = __half2float(kp[e]); k2 = __half2float(kp[e + half_d]);
+          v1 = __half2float(vp[e]); v2 = __half2float(vp[e + half_d]);
+        } else {
+          const float* kp = p.k_new_f32 + (int64_t)b * p.kv_ld + (int64_t)kvh * D;
+          const float* vp = p.v_new_f32 + (int64_t)b * p.kv_ld + (int64_t)kvh * D;
+          k1 = kp[e]; k2 = kp[e + half_d];
+          v1 = vp[e]; v2 = vp[e + half_d];
+        }
+        float c = tabn[2 * e], s = tabn[2 * e + 1];
+        __half r1 = __float2half_rn(__fsub_rn(__fmul_rn(k1, c), __fmul_rn(k2, s)));
+        __half r2 = __float2half_rn(__fadd_rn(__fmul_rn(k2, c), __fmul_rn(k1, s)));
+        __half h1 = __float2half_rn(v1), h2 = __float2half_rn(v2);
+        new_k[e] = r1; new_k[e + half_d] = r2;
+        new_v[e] = h1; new_v[e + half_d] = h2;
+        __half* kd = p.k_cache + (row_base + pos_new) * D;
+        __half* vd = p.v_cache + (row_base + pos_new) * D;
+        kd[e] = r1; kd[e + half_d] = r2;
+        vd[e] = h1; vd[e + half_d] = h2;
+      }
+    }
+  }
+  __syncthreads();
+
+  bool ok = true;
+
+  if (warp == ATT_CWARPS) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      for (int t = 0; t < ntiles && ok; ++t) {
+        int st = t % ATT_STAGES;
+        uint32_t ph = (uint32_t)(t / ATT_STAGES) & 1u;
+        ok = mbar_wait(&bar_empty[st], ph ^ 1u);
+        if (!ok) break;
+        uint8_t* sb = stages + st * STAGE_BYTES;
+        mbar_arrive_expect_tx(&bar_full[st], STAGE_BYTES);
+        int y = (int)(row_base + unit_start + t * ATT_TILE);
+#pragma unroll
+        for (int j = 0; j < NBOX; ++j) {
+          tma_load_2d(sb + j * ATT_BOX_BYTES, &map_k, &bar_full[st], j * 64, y);
+          tma_load_2d(sb + (NBOX + j) * ATT_BOX_BYTES, &map_v, &bar_full[st], j * 64, y);
+        }
+      }
+      if (!ok) atomicExch(p.status, 101);
+    }
+  } else {
+    // ---------------------------------------------------------------- consumers
+    const int g4 = lane >> 2, t4 = lane & 3;
+    uint32_t qa[KSTEPS][4];
+    {
+      int row = (lane & 7) + 8 * ((lane >> 3) & 1);
+      int colh = 8 * (lane >> 4);
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        uint32_t addr = smem_u32(qs + row * QS_STRIDE + ks * 16 + colh);
+        ldmatrix_x4(qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], addr);
+      }
+    }
+    float m_run[2] = {-INFINITY, -INFINITY};
+    float l_run[2] = {0.f, 0.f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+    for (int t = 0; t < ntiles; ++t) {
+      int st = t % ATT_STAGES;
+      uint32_t ph = (uint32_t)(t / ATT_STAGES) & 1u;
+      if (!mbar_wait(&bar_full[st], ph)) {
+        ok = false;
+        break;
+      }
+      uint8_t* kb = stages + st * STAGE_BYTES;
+      uint8_t* vb = kb + NBOX * ATT_BOX_BYTES;
+      const int tile_pos0 = unit_start + t * ATT_TILE;
+      const int my_pos0 = tile_pos0 + 16 * warp;
+
+      // patch the appended row / clear rows past the end (only this warp reads its 16 rows)
+      if (my_pos0 + 16 > len_eff || (owns_new && pos_new >= my_pos0 && pos_new < my_pos0 + 16)) {
+        for (int r = 0; r < 16; ++r) {
+          int pos = my_pos0 + r;
+          uint32_t row = 16 * warp + r;
+          if (owns_new && pos == pos_new) {
+            for (int c = lane; c < 2 * (D / 8); c += 32) {
+              bool is_v = c >= D / 8;
+              int cc = is_v ? c - D / 8 : c;
+              const uint4 val = *reinterpret_cast<const uint4*>((is_v ? new_v : new_k) + cc * 8);
+              uint8_t* base = (is_v ? vb : kb) + (cc >> 3) * ATT_BOX_BYTES;
+              *reinterpret_cast<uint4*>(base + swz128(row, cc & 7)) = val;
+            }
+          } else if (pos >= len_eff) {
+            for (int c = lane; c < D / 8; c += 32) {
+              uint8_t* base = vb + (c >> 3) * ATT_BOX_BYTES;
+              *reinterpret_cast<uint4*>(base + swz128(row, c & 7)) = make_uint4(0, 0, 0, 0);
+            }
+          }
+        }
+        __syncwarp();
+      }
+
+      // ---- S = Q K^T for 16 positions
+      float s[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+      {
+        uint32_t row = 16 * warp + (lane & 7) + 8 * (lane >> 4);
+        int ch = (lane >> 3) & 1;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+          int chunk = ks * 2 + ch;
+          uint32_t addr = smem_u32(kb + (chunk >> 3) * ATT_BOX_BYTES + swz128(row, chunk & 7));
+          uint32_t r0, r1, r2, r3;
+          ldmatrix_x4(r0, r1, r2, r3, addr);
+          mma_f16_16816(s[0], qa[ks], r0, r1);
+          mma_f16_16816(s[1], qa[ks], r2, r3);
+        }
+      }
+      // ---- mask, scale, online softmax
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          int pos = my_pos0 + nt * 8 + 2 * t4 + (j & 1);
+          float v = (pos < len_eff) ? s[nt][j] * p.scale_log2 : -INFINITY;
+          s[nt][j] = v;
+          mx[j >> 1] = fmaxf(mx[j >> 1], v);
+        }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      }
+      float corr[2], m_use[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        float m_new = fmaxf(m_run[r], mx[r]);
+        m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;
+        corr[r] = exp2f(m_run[r] - m_use[r]);
+        m_run[r] = m_new;
+      }
+      float pr[2][4];
+      float psum[2] = {0.f, 0.f};
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float e = exp2f(s[nt][j] - m_use[j >> 1]);
+          pr[nt][j] = e;
+          psum[j >> 1] += e;
+        }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * corr[r] + psum[r];
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        o[i][0] *= corr[0]; o[i][1] *= corr[0];
+        o[i][2] *= corr[1]; o[i][3] *= corr[1];
+      }
+      // ---- P as fp16 high part + fp16 residual
+      uint32_t a_hi[4], a_lo[4];
+      {
+        const float (*q)[4] = pr;
+        float h[8] = {q[0][0], q[0][1], q[0][2], q[0][3], q[1][0], q[1][1], q[1][2], q[1][3]};
+        float lo[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float hi = __half2float(__float2half_rn(h[i]));
+          lo[i] = h[i] - hi;
+        }
+        a_hi[0] = pack_half2(h[0], h[1]); a_hi[1] = pack_half2(h[2], h[3]);
+        a_hi[2] = pack_half2(h[4], h[5]); a_hi[3] = pack_half2(h[6], h[7]);
+        a_lo[0] = pack_half2(lo[0], lo[1]); a_lo[1] = pack_half2(lo[2], lo[3]);
+        a_lo[2] = pack_half2(lo[4], lo[5]); a_lo[3] = pack_half2(lo[6], lo[7]);
+      }
+      // ---- O += P V
+      {
+        uint32_t row = 16 * warp + (lane & 7) + 8 * ((lane >> 3) & 1);
+        int ch = lane >> 4;
+#pragma unroll
+        for (int dn = 0; dn < D / 16; ++dn) {
+          int chunk = dn * 2 + ch;
+          uint32_t addr = smem_u32(vb + (chunk >> 3) * ATT_BOX_BYTES + swz128(row, chunk & 7));
+          uint32_t r0, r1, r2, r3;
+          ldmatrix_x4_trans(r0, r1, r2, r3, addr);
+          mma_f16_16816(o[2 * dn], a_hi, r0, r1);
+          mma_f16_16816(o[2 * dn], a_lo, r0, r1);
+          mma_f16_16816(o[2 * dn + 1], a_hi, r2, r3);
+          mma_f16_16816(o[2 * dn + 1], a_lo, r2, r3);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_empty[st]);
+    }
+    if (!ok && lane == 0) atomicExch(p.status, 102);
+
+    // ---- combine the four warps (stage memory is free now: every load landed and was read)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(ATT_CWARPS * 32));
+    float* mo = reinterpret_cast<float*>(stages);            // [warp][16][D]
+    float* mml = mo + ATT_CWARPS * 16 * D;                   // [warp][16][2]
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      int col = i * 8 + 2 * t4;
+      float* r0p = mo + ((warp * 16 + g4) * D) + col;
+      float* r1p = mo + ((warp * 16 + g4 + 8) * D) + col;
+      r0p[0] = o[i][0]; r0p[1] = o[i][1];
+      r1p[0] = o[i][2]; r1p[1] = o[i][3];
+    }
+    if (t4 == 0) {
+      mml[(warp * 16 + g4) * 2 + 0] = m_run[0];
+      mml[(warp * 16 + g4) * 2 + 1] = l_run[0];
+      mml[(warp * 16 + g4 + 8) * 2 + 0] = m_run[1];
+      mml[(warp * 16 + g4 + 8) * 2 + 1] = l_run[1];
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(ATT_CWARPS * 32));
+    for (int e = tid; e < G * D; e += ATT_CWARPS * 32) {
+      int r = e / D, d = e - r * D;
+      float mstar = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < ATT_CWARPS; ++w) mstar = fmaxf(mstar, mml[(w * 16 + r) * 2]);
+      float muse = (mstar == -INFINITY) ? 0.f : mstar;
+      float acc = 0.f, L = 0.f;
+#pragma unroll
+      for (int w = 0; w < ATT_CWARPS; ++w) {
+        float wgt = exp2f(mml[(w * 16 + r) * 2] - muse);
+        acc = fmaf(mo[(w * 16 + r) * D + d], wgt, acc);
+        L = fmaf(mml[(w * 16 + r) * 2 + 1], wgt, L);
+      }
+      int hq = kvh * G + r;
+      int64_t pi = ((int64_t)b * p.h_q + hq) * p.max_splits + split;
+      p.part_o[pi * D + d] = acc;
+      if (d == 0) {
+        p.part_ml[pi * 2 + 0] = mstar;
+        p.part_ml[pi * 2 + 1] = L;
+      }
+    }
+  }
+  __syncthreads();
+}
+
+// One CTA per (sequence, query head): fold the units in ascending order.
+template <int D>
+__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                  const int32_t* __restrict__ seq_len, void* __restrict__ o, int o_dtype, int h_q,
+                                  int l_max, int unit_len, int max_splits, int fused) {
+  const int hq = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  int len_eff = seq_len[b] + (fused ? 1 : 0);
+  if (len_eff > l_max) len_eff = l_max;
+  int ns = len_eff > 0 ? (len_eff + unit_len - 1) / unit_len : 0;
+  int64_t base = ((int64_t)b * h_q + hq) * max_splits;
+  float mstar = -INFINITY;
+  for (int s = 0; s < ns; ++s) mstar = fmaxf(mstar, part_ml[(base + s) * 2]);
+  float muse = (mstar == -INFINITY) ? 0.f : mstar;
+  float acc = 0.f, L = 0.f;
+  for (int s = 0; s < ns; ++s) {
+    float wgt = exp2f(part_ml[(base + s) * 2] - muse);
+    acc = fmaf(part_o[(base + s) * D + d], wgt, acc);
+    L = fmaf(part_ml[(base + s) * 2 + 1], wgt, L);
+  }
+  float v = (ns > 0) ? __fdiv_rn(acc, L) : 0.f;
+  int64_t oi = ((int64_t)b * h_q + hq) * D + d;
+  if (o_dtype == LOGOS_F16) reinterpret_cast<__half*>(o)[oi] = __float2half_rn(v);
+  else if (o_dtype == LOGOS_BF16) reinterpret_cast<__nv_bfloat16*>(o)[oi] = __float2bfloat16_rn(v);
+  else reinterpret_cast<float*>(o)[oi] = v;
+}
+
+__global__ void bump_seq_len_kernel(int32_t* seq_len, int b, int l_max) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < b && seq_len[i] < l_max) seq_len[i] += 1;
+}
+
+// Stand-alone append (no attention): one CTA per (sequence, KV head).
+__global__ void kv_append_rope_kernel(__half* k_cache, __half* v_cache, const __half* k_new, const __half* v_new,
+                                      const float* rope, const int32_t* seq_len, int h_kv, int d, int l_max) {
+  const int kvh = blockIdx.x, b = blockIdx.y;
+  const int pos = seq_len[b];
+  if (pos < 0 || pos >= l_max) return;
+  const int half_d = d / 2;
+  const float* tab = rope + (int64_t)pos * half_d * 2;
+  const __half* kp = k_new + ((int64_t)b * h_kv + kvh) * d;
+  const __half* vp = v_new + ((int64_t)b * h_kv + kvh) * d;
+  __half* kd = k_cache + (((int64_t)b * h_kv + kvh) * l_max + pos) * d;
+  __half* vd = v_cache + (((int64_t)b * h_kv + kvh) * l_max + pos) * d;
+  for (int e = threadIdx.x; e < half_d; e += blockDim.x) {
+    float k1 = __half2float(kp[e]), k2 = __half2float(kp[e + half_d]);
+    float c = tab[2 * e], s = tab[2 * e + 1];
+    kd[e] = __float2half_rn(__fsub_rn(__fmul_rn(k1, c), __fmul_rn(k2, s)));
+    kd[e + half_d] = __float2half_rn(__fadd_rn(__fmul_rn(k2, c), __fmul_rn(k1, s)));
+    vd[e] = vp[e];
+    vd[e + half_d] = vp[e + half_d];
+  }
+}
+
+template <int D>
+constexpr size_t attn_smem_bytes() {
+  return 1024 + (size_t)ATT_STAGES * 2 * (D / 64) * ATT_BOX_BYTES + (size_t)16 * (D + 8) * 2 + (size_t)2 * D * 2 +
+         2 * ATT_STAGES * 8 + 64;
+}
+
+template <int D>
+logos_status_t launch_attn_t(const AttnArgs& a, cudaStream_t st) {
+  const int64_t rows_total = a.b * a.h_kv * a.l_max;
+  CUtensorMap mk, mv;
+  LOGOS_TRY(make_tensor_map_2d(&mk, a.k_cache, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, D, rows_total, D * 2, 64, ATT_TILE,
+                               CU_TENSOR_MAP_SWIZZLE_128B));
+  LOGOS_TRY(make_tensor_map_2d(&mv, a.v_cache, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, D, rows_total, D * 2, 64, ATT_TILE,
+                               CU_TENSOR_MAP_SWIZZLE_128B));
+  // unit length: aim at ~16 units per SM over the whole (sequence, KV head, position) space
+  int sms = sm_count(a.device);
+  int64_t total_pos = a.b * a.h_kv * a.l_max;
+  int64_t ul = (total_pos + (int64_t)sms * 16 - 1) / ((int64_t)sms * 16);
+  ul = ((ul + ATT_TILE - 1) / ATT_TILE) * ATT_TILE;
+  if (ul < 2 * ATT_TILE) ul = 2 * ATT_TILE;
+  int max_splits = (int)((a.l_max + ul - 1) / ul);
+
+  void* scratch = nullptr;
+  int64_t po_bytes = a.b * a.h_q * max_splits * D * (int64_t)sizeof(float);
+  int64_t pml_bytes = a.b * a.h_q * max_splits * 2 * (int64_t)sizeof(float);
+  LOGOS_TRY(scratch_get(a.device, 1, po_bytes + pml_bytes, &scratch));
+
+  AttnParams p{};
+  p.q_f16 = a.q_f16; p.q_f32 = a.q_f32; p.q_ld = a.q_ld; p.rotate_q = a.rotate_q;
+  p.k_new_f16 = a.k_new_f16; p.v_new_f16 = a.v_new_f16; p.k_new_f32 = a.k_new_f32; p.v_new_f32 = a.v_new_f32;
+  p.kv_ld = a.kv_ld;
+  p.fused = (a.k_new_f16 || a.k_new_f32) ? 1 : 0;
+  p.k_cache = a.k_cache; p.v_cache = a.v_cache; p.rope = a.rope; p.seq_len = a.seq_len;
+  p.part_o = reinterpret_cast<float*>(scratch);
+  p.part_ml = reinterpret_cast<float*>(static_cast<char*>(scratch) + po_bytes);
+  p.b = (int)a.b; p.h_q = (int)a.h_q; p.h_kv = (int)a.h_kv; p.l_max = (int)a.l_max;
+  p.unit_len = (int)ul; p.max_splits = max_splits;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.status = kernel_status_ptr(a.device);
+  if (!p.status) return fail(LOGOS_ERROR, "attention: no kernel status word");
+
+  constexpr size_t smem = attn_smem_bytes<D>();
+  LOGOS_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_attn_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(max_splits, (unsigned)a.h_kv, (unsigned)a.b);
+  gqa_decode_attn_kernel<D><<<grid, ATT_THREADS, smem, st>>>(mk, mv, p);
+  LOGOS_TRY(check_launch("gqa_decode_attn_kernel"));
+  dim3 mgrid((unsigned)a.h_q, (unsigned)a.b);
+  attn_merge_kernel<D><<<mgrid, D, 0, st>>>(p.part_o, p.part_ml, a.seq_len, a.o, a.o_dtype, (int)a.h_q, (int)a.l_max,
+                                            (int)ul, max_splits, p.fused);
+  LOGOS_TRY(check_launch("attn_merge_kernel"));
+  if (a.bump_seq_len) {
+    bump_seq_len_kernel<<<(unsigned)((a.b + 127) / 128), 128, 0, st>>>(a.seq_len, (int)a.b, (int)a.l_max);
+    LOGOS_TRY(check_launch("bump_seq_len_kernel"));
+  }
+  return LOGOS_OK;
+}
+
+}  // namespace
+
+void rope_table_host(float* out, int64_t l_max, int64_t d, double theta) {
+  int64_t half = d / 2;
+  for (int64_t pos = 0; pos < l_max; ++pos)
+    for (int64_t i = 0; i < half; ++i) {
+      double inv = pow(theta, -2.0 * (double)i / (double)d);
+      double ang = (double)pos * inv;
+      out[(pos * half + i) * 2 + 0] = (float)cos(ang);
+      out[(pos * half + i) * 2 + 1] = (float)sin(ang);
+    }
+}
+
+logos_status_t launch_gqa_decode_attn(const AttnArgs& a, cudaStream_t st) {
+  if (a.b == 0 || a.h_q == 0) return LOGOS_OK;
+  if (a.h_kv <= 0 || a.h_q % a.h_kv) return fail(LOGOS_ERROR, "attention: h_q must be a multiple of h_kv");
+  if (a.h_q / a.h_kv > 16) return fail(LOGOS_ERROR, "attention: at most 16 query heads per KV head");
+  if (a.l_max <= 0) return fail(LOGOS_OUT_OF_BOUNDS, "attention: l_max must be positive");
+  if (a.d == 128) return launch_attn_t<128>(a, st);
+  if (a.d == 64) return launch_attn_t<64>(a, st);
+  return fail(LOGOS_ERROR, "attention: head_dim %lld is not supported (64 or 128)", (long long)a.d);
+}
+
+logos_status_t launch_kv_append_rope(__half* k_cache, __half* v_cache, const __half* k_new, const __half* v_new,
+                                     const float* rope, int32_t* seq_len, int64_t b, int64_t h_kv, int64_t d,
+                                     int64_t l_max, int device, cudaStream_t st) {
+  (void)device;
+  if (b == 0 || h_kv == 0) return LOGOS_OK;
+  dim3 grid((unsigned)h_kv, (unsigned)b);
+  kv_append_rope_kernel<<<grid, 64, 0, st>>>(k_cache, v_cache, k_new, v_new, rope, seq_len, (int)h_kv, (int)d, (int)l_max);
+  LOGOS_TRY(check_launch("kv_append_rope_kernel"));
+  bump_seq_len_kernel<<<(unsigned)((b + 127) / 128), 128, 0, st>>>(seq_len, (int)b, (int)l_max);
+  return check_launch("bump_seq_len_kernel");
+}
+
+}  // namespace logos
+
+using namespace logos;
+
+extern "C" {
+
+logos_status_t logos_rope_table(float* out_host, int64_t l_max, int64_t d, double theta) {
+  return guarded([&]() -> logos_status_t {
+    if (!out_host) return fail(LOGOS_NULL_POINTER, "logos_rope_table: out_host is null");
+    if (l_max < 0 || d <= 0 || (d & 1)) return fail(LOGOS_OUT_OF_BOUNDS, "logos_rope_table: bad extents");
+    rope_table_host(out_host, l_max, d, theta);
+    return LOGOS_OK;
+  });
+}
+
+logos_status_t logos_kv_append_rope(logos_handle_t k_cache, logos_handle_t v_cache, logos_handle_t k_new,
+                                    logos_handle_t v_new, logos_handle_t rope_table, logos_handle_t seq_len,
+                                    int64_t b, int64_t h_kv, int64_t d, int64_t l_max, void* stream_or_null) {
+  return guarded([&]() -> logos_status_t {
+    if (b < 0 || h_kv < 0 || d <= 0 || l_max <= 0 || (d & 1))
+      return fail(LOGOS_OUT_OF_BOUNDS, "logos_kv_append_rope: bad extents");
+    __half *kc, *vc, *kn, *vn;
+    float* rt;
+    int32_t* sl;
+    int32_t dev = 0;
+    LOGOS_TRY(buf_ptr<__half>(k_cache, b * h_kv * l_max * d, "k_cache", &kc, &dev));
+    LOGOS_TRY(buf_ptr<__half>(v_cache, b * h_kv * l_max * d, "v_cache", &vc));
+    LOGOS_TRY(buf_ptr<__half>(k_new, b * h_kv * d, "k_new", &kn));
+    LOGOS_TRY(buf_ptr<__half>(v_new, b * h_kv * d, "v_new", &vn));
+    LOGOS_TRY(buf_ptr<float>(rope_table, l_max * d, "rope_table", &rt));
+    LOGOS_TRY(buf_ptr<int32_t>(seq_len, b, "seq_len", &sl));
+    LOGOS_CUDA_TRY(cudaSetDevice(dev));
+    return launch_kv_append_rope(kc, vc, kn, vn, rt, sl, b, h_kv, d, l_max, dev, as_stream(stream_or_null));
+  });
+}
+
+static logos_status_t attn_abi(bool fused, logos_handle_t q, logos_handle_t k_new, logos_handle_t v_new,
+                               logos_handle_t k_cache, logos_handle_t v_cache, logos_handle_t rope_table,
+                               logos_handle_t seq_len, logos_handle_t o, int64_t b, int64_t h_q, int64_t h_kv,
+                               int64_t d, int64_t l_max, float scale, void* stream) {
+  if (b < 0 || h_q < 0 || h_kv <= 0 || d <= 0 || l_max <= 0)
+    return fail(LOGOS_OUT_OF_BOUNDS, "gqa_decode_attn: bad extents");
+  AttnArgs a;
+  __half *qp, *kc, *vc, *op;
+  int32_t* sl;
+  int32_t dev = 0;
+  LOGOS_TRY(buf_ptr<__half>(q, b * h_q * d, "q", &qp, &dev));
+  LOGOS_TRY(buf_ptr<__half>(k_cache, b * h_kv * l_max * d, "k_cache", &kc));
+  LOGOS_TRY(buf_ptr<__half>(v_cache, b * h_kv * l_max * d, "v_cache", &vc));
+  LOGOS_TRY(buf_ptr<int32_t>(seq_len, b, "seq_len", &sl));
+  LOGOS_TRY(buf_ptr<__half>(o, b * h_q * d, "o", &op));
+  a.q_f16 = qp; a.k_cache = kc; a.v_cache = vc; a.seq_len = sl; a.o = op; a.o_dtype = LOGOS_F16;
+  if (fused) {
+    __half *kn, *vn;
+    float* rt;
+    LOGOS_TRY(buf_ptr<__half>(k_new, b * h_kv * d, "k_new", &kn));
+    LOGOS_TRY(buf_ptr<__half>(v_new, b * h_kv * d, "v_new", &vn));
+    LOGOS_TRY(buf_ptr<float>(rope_table, l_max * d, "rope_table", &rt));
+    a.k_new_f16 = kn; a.v_new_f16 = vn; a.rope = rt; a.rotate_q = 1; a.bump_seq_len = 1;
+  }
+  a.b = b; a.h_q = h_q; a.h_kv = h_kv; a.d = d; a.l_max = l_max; a.scale = scale; a.device = dev;
+  LOGOS_CUDA_TRY(cudaSetDevice(dev));
+  return launch_gqa_decode_attn(a, as_stream(stream));
+}
+
+logos_status_t logos_gqa_decode_attn(logos_handle_t q, logos_handle_t k_cache, logos_handle_t v_cache,
+                                     logos_handle_t seq_len, logos_handle_t o, int64_t b, int64_t h_q, int64_t h_kv,
+                                     int64_t d, int64_t l_max, float softmax_scale, void* stream_or_null) {
+  return guarded([&]() -> logos_status_t {
+    return attn_abi(false, q, nullptr, nullptr, k_cache, v_cache, nullptr, seq_len, o, b, h_q, h_kv, d, l_max,
+                    softmax_scale, stream_or_null);
+  });
+}
+
+logos_status_t logos_gqa_decode_attn_fused(logos_handle_t q_raw, logos_handle_t k_new, logos_handle_t v_new,
+                                           logos_handle_t k_cache, logos_handle_t v_cache, logos_handle_t rope_table,
+                                           logos_handle_t seq_len, logos_handle_t o, int64_t b, int64_t h_q,
+                                           int64_t h_kv, int64_t d, int64_t l_max, float softmax_scale,
+                                           void* stream_or_null) {
+  return guarded([&]() -> logos_status_t {
+    return attn_abi(true, q_raw, k_new, v_new, k_cache, v_cache, rope_table, seq_len, o, b, h_q, h_kv, d, l_max,
+                    softmax_scale, stream_or_null);
+  });
+}
+
+}  // extern "C"

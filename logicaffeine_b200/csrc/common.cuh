@@ -1,0 +1,93 @@
+// Shared internals of liblogos_b200: status/error plumbing, the handle
+// registry, and small device helpers.  Nothing here is part of the C ABI.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <string>
+
+#include "../../include/logos_b200.h"
+
+namespace logos {
+
+// ---------------------------------------------------------------- errors
+// Per-thread message store, read through logos_last_error(); same contract as
+// the reference's thread-keyed store (crates/logicaffeine_compile/src/codegen/ffi.rs:214-251).
+void set_last_error(const std::string& msg);
+logos_status_t fail(logos_status_t code, const char* fmt, ...);
+logos_status_t cuda_fail(cudaError_t e, const char* what);
+
+#define LOGOS_CUDA_TRY(expr)                                            \
+  do {                                                                  \
+    cudaError_t _e = (expr);                                            \
+    if (_e != cudaSuccess) return ::logos::cuda_fail(_e, #expr);        \
+  } while (0)
+
+#define LOGOS_TRY(expr)                                                 \
+  do {                                                                  \
+    logos_status_t _s = (expr);                                         \
+    if (_s != LOGOS_OK) return _s;                                      \
+  } while (0)
+
+// Every extern "C" body runs inside this guard: a C++ exception never crosses
+// the ABI (the reference wraps each export in catch_unwind, ffi.rs:329-345).
+template <class F>
+logos_status_t guarded(F&& f) {
+  try {
+    return f();
+  } catch (const std::bad_alloc&) {
+    return fail(LOGOS_MEMORY_EXHAUSTED, "host allocation failed");
+  } catch (const std::exception& e) {
+    return fail(LOGOS_THREAD_PANIC, "internal exception: %s", e.what());
+  } catch (...) {
+    return fail(LOGOS_THREAD_PANIC, "internal exception");
+  }
+}
+
+// ---------------------------------------------------------------- handles
+enum class ObjKind : uint32_t { DevBuf = 1, Model = 2 };
+
+struct DevBuf {
+  void*   ptr = nullptr;
+  int64_t bytes = 0;
+  int32_t device = 0;
+};
+
+// Registers an object and returns its id (never 0).  The id packs a slot
+// counter; a freed id is never reused, so stale handles stay invalid.
+logos_handle_t registry_put(ObjKind kind, void* obj);
+// Looks an id up; nullptr when unknown or of another kind.
+void* registry_get(logos_handle_t h, ObjKind kind);
+// Removes the id and returns the object, nullptr when unknown.
+void* registry_take(logos_handle_t h, ObjKind kind);
+
+// Resolves a device buffer handle, checking that [offset, offset+need) fits.
+logos_status_t buf_resolve(logos_handle_t h, int64_t offset, int64_t need, const char* name, DevBuf** out);
+
+template <class T>
+logos_status_t buf_ptr(logos_handle_t h, int64_t elems, const char* name, T** out, int32_t* device = nullptr) {
+  DevBuf* b = nullptr;
+  LOGOS_TRY(buf_resolve(h, 0, elems * (int64_t)sizeof(T), name, &b));
+  *out = reinterpret_cast<T*>(b->ptr);
+  if (device) *device = b->device;
+  return LOGOS_OK;
+}
+
+// Per-device scratch the library owns (split-K partials, attention partials).
+// Grows on demand, outside any stream capture; freed at process exit.
+logos_status_t scratch_get(int32_t device, int slot, int64_t bytes, void** out);
+
+int sm_count(int device);
+
+// Device-visible status word (mapped host memory): kernels store a non-zero
+// code when a bounded wait gives up.  0 = fine.
+int* kernel_status_ptr(int device);
+
+// ---------------------------------------------------------------- launch helpers
+logos_status_t check_launch(const char* kernel);
+
+static inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+}  // namespace logos

@@ -1,0 +1,212 @@
+// Norms and element-wise pieces of the decode step.
+//   rmsnorm            y = x * rsqrt(mean(x^2) + eps) * g
+//   swiglu             y = silu(gate) * up
+//   embed              h[row] = dequantised Q8 row of the token
+//   residual_rmsnorm   h += delta (split-K partials summed in ascending order),
+//                      xn = 16-bit( rmsnorm(h) )  — one pass over the row
+//   argmax             lowest index wins ties
+// Row reductions run in a fixed shape (per-thread strided partials, shuffle
+// tree, then warps in ascending order), so results do not depend on timing.
+#include "ops.cuh"
+
+namespace logos {
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Sum over the CTA; every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  v = warp_sum(v);
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  __syncthreads();
+  return t;
+}
+
+__device__ __forceinline__ void store_act(void* dst, int dtype, int64_t i, float v) {
+  if (dtype == LOGOS_F16) reinterpret_cast<__half*>(dst)[i] = __float2half_rn(v);
+  else if (dtype == LOGOS_BF16) reinterpret_cast<__nv_bfloat16*>(dst)[i] = __float2bfloat16_rn(v);
+  else reinterpret_cast<float*>(dst)[i] = v;
+}
+
+__global__ void rmsnorm_f32_kernel(const float* __restrict__ x, const float* __restrict__ g, float* __restrict__ y,
+                                   int64_t h, float eps) {
+  __shared__ float red[32];
+  const float* xr = x + (int64_t)blockIdx.x * h;
+  float* yr = y + (int64_t)blockIdx.x * h;
+  float ss = 0.f;
+  for (int64_t i = threadIdx.x; i < h; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+  ss = block_sum(ss, red);
+  float inv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)h), eps)));
+  for (int64_t i = threadIdx.x; i < h; i += blockDim.x) yr[i] = __fmul_rn(__fmul_rn(xr[i], inv), g[i]);
+}
+
+__global__ void swiglu_f32_kernel(const float* __restrict__ gate, const float* __restrict__ up,
+                                  float* __restrict__ y, int64_t count) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < count; i += step) {
+    float g = gate[i];
+    float sg = __fdiv_rn(g, 1.0f + expf(-g));
+    y[i] = __fmul_rn(sg, up[i]);
+  }
+}
+
+__global__ void embed_kernel(const int32_t* __restrict__ tokens, const int8_t* __restrict__ q,
+                             const float* __restrict__ s, float* __restrict__ h, int64_t hidden) {
+  int64_t row = blockIdx.x;
+  int64_t t = tokens[row];
+  const int8_t* qr = q + t * hidden;
+  const float* sr = s + t * (hidden / 32);
+  for (int64_t e = threadIdx.x; e < hidden; e += blockDim.x)
+    h[row * hidden + e] = __fmul_rn(sr[e >> 5], (float)qr[e]);
+}
+
+__global__ void residual_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int parts,
+                                        int64_t part_stride, const float* __restrict__ g, void* __restrict__ xn,
+                                        int xn_dtype, int64_t hidden, float eps) {
+  __shared__ float red[32];
+  extern __shared__ float row_cache[];  // hidden floats
+  const int64_t row = blockIdx.x;
+  float* hr = h + row * hidden;
+  float ss = 0.f;
+  for (int64_t i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = hr[i];
+    for (int p = 0; p < parts; ++p) v = __fadd_rn(v, delta[(int64_t)p * part_stride + row * hidden + i]);
+    if (parts > 0) hr[i] = v;
+    row_cache[i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, red);
+  float inv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hidden), eps)));
+  for (int64_t i = threadIdx.x; i < hidden; i += blockDim.x)
+    store_act(xn, xn_dtype, row * hidden + i, __fmul_rn(__fmul_rn(row_cache[i], inv), g[i]));
+}
+
+__global__ void argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ tokens,
+                              int32_t* __restrict__ history, int64_t vocab) {
+  __shared__ float bv[32];
+  __shared__ int bi[32];
+  const int64_t row = blockIdx.x;
+  const float* lr = logits + row * vocab;
+  float best = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int64_t i = threadIdx.x; i < vocab; i += blockDim.x) {
+    float v = lr[i];
+    if (v > best || (v == best && (int)i < idx)) {
+      best = v;
+      idx = (int)i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > best || (ov == best && oi < idx)) {
+      best = ov;
+      idx = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if (lane == 0) {
+    bv[warp] = best;
+    bi[warp] = idx;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < nw; ++w)
+      if (bv[w] > best || (bv[w] == best && bi[w] < idx)) {
+        best = bv[w];
+        idx = bi[w];
+      }
+    if (idx == 0x7fffffff) idx = 0;  // all NaN / empty row
+    tokens[row] = idx;
+    if (history) history[row] = idx;
+  }
+}
+
+}  // namespace
+
+logos_status_t launch_rmsnorm_f32(const float* x, const float* g, float* y, int64_t rows, int64_t h, float eps,
+                                  cudaStream_t st) {
+  if (rows == 0 || h == 0) return LOGOS_OK;
+  rmsnorm_f32_kernel<<<(unsigned)rows, 256, 0, st>>>(x, g, y, h, eps);
+  return check_launch("rmsnorm_f32_kernel");
+}
+
+logos_status_t launch_swiglu_f32(const float* gate, const float* up, float* y, int64_t count, cudaStream_t st) {
+  if (count == 0) return LOGOS_OK;
+  int64_t want = (count + 255) / 256;
+  int grid = (int)(want < 148 * 8 ? want : 148 * 8);
+  swiglu_f32_kernel<<<grid, 256, 0, st>>>(gate, up, y, count);
+  return check_launch("swiglu_f32_kernel");
+}
+
+logos_status_t launch_embed(const int32_t* tokens, const int8_t* q, const float* s, float* h, int64_t rows,
+                            int64_t hidden, cudaStream_t st) {
+  if (rows == 0) return LOGOS_OK;
+  embed_kernel<<<(unsigned)rows, 256, 0, st>>>(tokens, q, s, h, hidden);
+  return check_launch("embed_kernel");
+}
+
+logos_status_t launch_residual_rmsnorm(float* h, const float* delta, int parts, int64_t part_stride,
+                                       const float* g, void* xn, int xn_dtype, int64_t rows, int64_t hidden,
+                                       float eps, cudaStream_t st) {
+  if (rows == 0) return LOGOS_OK;
+  size_t smem = sizeof(float) * (size_t)hidden;
+  if (smem > 48 * 1024)
+    LOGOS_CUDA_TRY(cudaFuncSetAttribute(residual_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  residual_rmsnorm_kernel<<<(unsigned)rows, 256, smem, st>>>(h, delta, parts, part_stride, g, xn, xn_dtype, hidden, eps);
+  return check_launch("residual_rmsnorm_kernel");
+}
+
+logos_status_t launch_argmax(const float* logits, int32_t* tokens, int32_t* history_or_null, int64_t rows,
+                             int64_t vocab, cudaStream_t st) {
+  if (rows == 0) return LOGOS_OK;
+  argmax_kernel<<<(unsigned)rows, 1024, 0, st>>>(logits, tokens, history_or_null, vocab);
+  return check_launch("argmax_kernel");
+}
+
+}  // namespace logos
+
+using namespace logos;
+
+extern "C" {
+
+logos_status_t logos_rmsnorm(logos_handle_t x, logos_handle_t g, logos_handle_t y, int64_t rows, int64_t h,
+                             float eps, void* stream_or_null) {
+  return guarded([&]() -> logos_status_t {
+    if (rows < 0 || h < 0) return fail(LOGOS_OUT_OF_BOUNDS, "logos_rmsnorm: negative extent");
+    float *xp, *gp, *yp;
+    int32_t dev = 0;
+    LOGOS_TRY(buf_ptr<float>(x, rows * h, "x", &xp, &dev));
+    LOGOS_TRY(buf_ptr<float>(g, h, "g", &gp));
+    LOGOS_TRY(buf_ptr<float>(y, rows * h, "y", &yp));
+    LOGOS_CUDA_TRY(cudaSetDevice(dev));
+    return launch_rmsnorm_f32(xp, gp, yp, rows, h, eps, as_stream(stream_or_null));
+  });
+}
+
+logos_status_t logos_swiglu(logos_handle_t gate, logos_handle_t up, logos_handle_t y, int64_t count,
+                            void* stream_or_null) {
+  return guarded([&]() -> logos_status_t {
+    if (count < 0) return fail(LOGOS_OUT_OF_BOUNDS, "logos_swiglu: negative extent");
+    float *gp, *up_p, *yp;
+    int32_t dev = 0;
+    LOGOS_TRY(buf_ptr<float>(gate, count, "gate", &gp, &dev));
+    LOGOS_TRY(buf_ptr<float>(up, count, "up", &up_p));
+    LOGOS_TRY(buf_ptr<float>(y, count, "y", &yp));
+    LOGOS_CUDA_TRY(cudaSetDevice(dev));
+    return launch_swiglu_f32(gp, up_p, yp, count, as_stream(stream_or_null));
+  });
+}
+
+}  // extern "C"

@@ -1,0 +1,587 @@
+// Batched Qwen-architecture greedy decode on Q8 weights.
+//
+// One step, per layer (all sequences in lock step):
+//   residual add + RMSNorm -> 16-bit x          (one kernel; also folds split-K partials)
+//   Q8 GEMM  x -> [q | k | v]  (f32)
+//   RoPE + KV append + GQA attention           (one kernel + merge) -> 16-bit
+//   Q8 GEMM  o_proj  -> f32 partials           [all-reduce when tensor parallel]
+//   residual add + RMSNorm -> 16-bit x
+//   Q8 GEMM  gate/up with the SwiGLU epilogue -> 16-bit
+//   Q8 GEMM  down_proj -> f32 partials         [all-reduce when tensor parallel]
+// then final norm, lm_head GEMM (f32 logits), argmax.
+//
+// Memory: weights are int8 [N][K] + f32 [N][K/32]; the residual stream is f32;
+// GEMM inputs keep f32 precision by default (cfg.act_dtype = LOGOS_F32) or are
+// rounded to fp16 / bf16 when the configuration asks; the KV cache is fp16
+// [B][Hkv][Lmax][D] per layer.  Tensor parallelism shards q/k/v/gate/up by
+// output rows (heads, FFN columns) and o_proj/down_proj by input columns, so
+// the only exchanges are the two sum all-reduces per layer.
+#include "ops.cuh"
+#include "tp.cuh"
+
+#include <vector>
+
+namespace logos {
+
+namespace {
+
+struct Q8Mat {
+  int8_t* q = nullptr;
+  float*  s = nullptr;
+  int64_t n = 0, k = 0;
+};
+
+struct Layer {
+  Q8Mat wqkv, wo, wgu, wd;
+  __half *kc = nullptr, *vc = nullptr;
+};
+
+struct Model {
+  logos_llm_config_t cfg;
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  TpGroup tp;
+  int64_t nq = 0, nkv = 0, nqkv = 0, f_local = 0, hkv_local = 0, hq_local = 0;
+  std::vector<Layer> layers;
+  Q8Mat embed, head;
+  float* ones = nullptr;
+  float* rope = nullptr;
+  float* h = nullptr;        // [B][H] residual stream
+  void*  xn = nullptr;       // [B][H] 16-bit
+  float* qkv = nullptr;      // [B][nqkv]
+  void*  att = nullptr;      // [B][nq] 16-bit
+  void*  ffn = nullptr;      // [B][f_local] 16-bit
+  float* partials = nullptr; // [max_splits][B][H]
+  int    max_splits = 1;
+  float* logits = nullptr;   // [B][V]
+  int32_t* tokens = nullptr; // [B] current input / last output
+  int32_t* seq_len = nullptr;
+  int32_t* history = nullptr; // [history_cap][B]
+  int64_t  history_cap = 0;
+  int32_t* prompt = nullptr;  // [T][B]
+  int64_t  prompt_cap = 0;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  double last_ms = 0.0;
+  int64_t launches_per_step = 0;
+  int64_t launch_counter = 0;
+  std::vector<void*> allocs;
+  // per-class device timing of one step (logos_llm_profile_step)
+  bool profiling = false;
+  std::vector<cudaEvent_t> prof_events;
+  std::vector<int> prof_class;
+  size_t prof_used = 0;
+};
+
+enum ProfClass : int { PROF_GEMM = 0, PROF_ATTN = 1, PROF_ELEMWISE = 2, PROF_COMM = 3, PROF_CLASSES = 4 };
+
+// Brackets a group of launches with an event pair when a profiled step is running.
+struct ProfScope {
+  Model* m;
+  bool on;
+  ProfScope(Model* model, int cls) : m(model), on(model->profiling) {
+    if (!on) return;
+    if (m->prof_used + 2 > m->prof_events.size()) {
+      for (int i = 0; i < 2; ++i) {
+        cudaEvent_t e;
+        cudaEventCreate(&e);
+        m->prof_events.push_back(e);
+      }
+    }
+    m->prof_class.push_back(cls);
+    cudaEventRecord(m->prof_events[m->prof_used], m->stream);
+  }
+  ~ProfScope() {
+    if (!on) return;
+    cudaEventRecord(m->prof_events[m->prof_used + 1], m->stream);
+    m->prof_used += 2;
+  }
+};
+
+logos_status_t dmalloc(Model* m, void** p, int64_t bytes) {
+  *p = nullptr;
+  if (bytes <= 0) bytes = 16;
+  cudaError_t e = cudaMalloc(p, (size_t)bytes);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc (model)");
+  m->allocs.push_back(*p);
+  return LOGOS_OK;
+}
+
+logos_status_t alloc_mat(Model* m, Q8Mat* w, int64_t n, int64_t k) {
+  w->n = n;
+  w->k = k;
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&w->q), n * k));
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&w->s), n * (k / 32) * (int64_t)sizeof(float)));
+  return LOGOS_OK;
+}
+
+void destroy(Model* m) {
+  cudaSetDevice(m->device);
+  if (m->stream) cudaStreamSynchronize(m->stream);
+  tp_destroy(&m->tp);
+  for (void* p : m->allocs) cudaFree(p);
+  for (cudaEvent_t e : m->prof_events) cudaEventDestroy(e);
+  if (m->ev0) cudaEventDestroy(m->ev0);
+  if (m->ev1) cudaEventDestroy(m->ev1);
+  if (m->stream) cudaStreamDestroy(m->stream);
+  delete m;
+}
+
+logos_status_t gen(Model* m, Q8Mat* w, int64_t n, int64_t row0, int64_t col0, int64_t k_total, int64_t mul, int64_t add,
+                   uint64_t stream_id) {
+  return launch_q8_quantize(true, nullptr, w->q, w->s, n, w->k, row0, col0, k_total, mul, add, m->cfg.seed, stream_id,
+                            m->cfg.init_std, m->device, m->stream);
+}
+
+logos_status_t build(Model* m, const void* nccl_id) {
+  const logos_llm_config_t& c = m->cfg;
+  const int g = c.tp_degree, r = c.tp_rank;
+  const int64_t H = c.hidden, D = c.head_dim, B = c.batch;
+  m->hq_local = c.h_q / g;
+  m->hkv_local = c.h_kv / g;
+  m->nq = m->hq_local * D;
+  m->nkv = m->hkv_local * D;
+  m->nqkv = m->nq + 2 * m->nkv;
+  m->f_local = c.ffn / g;
+  const int64_t nq_total = c.h_q * D;
+
+  LOGOS_CUDA_TRY(cudaSetDevice(m->device));
+  LOGOS_CUDA_TRY(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
+  LOGOS_CUDA_TRY(cudaEventCreate(&m->ev0));
+  LOGOS_CUDA_TRY(cudaEventCreate(&m->ev1));
+  LOGOS_TRY(tp_init(&m->tp, g, r, nccl_id));
+
+  m->layers.resize((size_t)c.layers);
+  const int64_t kv_elems = B * m->hkv_local * c.l_max * D;
+  for (int64_t l = 0; l < c.layers; ++l) {
+    Layer& L = m->layers[(size_t)l];
+    const uint64_t st = (uint64_t)l * 16;
+    LOGOS_TRY(alloc_mat(m, &L.wqkv, m->nqkv, H));
+    LOGOS_TRY(alloc_mat(m, &L.wo, H, m->nq));
+    LOGOS_TRY(alloc_mat(m, &L.wgu, 2 * m->f_local, H));
+    LOGOS_TRY(alloc_mat(m, &L.wd, H, m->f_local));
+    LOGOS_TRY(gen(m, &L.wqkv, m->nq, r * m->nq, 0, H, 1, 0, st + 0));
+    LOGOS_TRY(gen(m, &L.wqkv, m->nkv, r * m->nkv, 0, H, 1, m->nq, st + 1));
+    LOGOS_TRY(gen(m, &L.wqkv, m->nkv, r * m->nkv, 0, H, 1, m->nq + m->nkv, st + 2));
+    LOGOS_TRY(gen(m, &L.wo, H, 0, r * m->nq, nq_total, 1, 0, st + 3));
+    LOGOS_TRY(gen(m, &L.wgu, m->f_local, r * m->f_local, 0, H, 2, 0, st + 4));
+    LOGOS_TRY(gen(m, &L.wgu, m->f_local, r * m->f_local, 0, H, 2, 1, st + 5));
+    LOGOS_TRY(gen(m, &L.wd, H, 0, r * m->f_local, c.ffn, 1, 0, st + 6));
+    LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&L.kc), kv_elems * 2));
+    LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&L.vc), kv_elems * 2));
+    LOGOS_CUDA_TRY(cudaMemsetAsync(L.kc, 0, (size_t)kv_elems * 2, m->stream));
+    LOGOS_CUDA_TRY(cudaMemsetAsync(L.vc, 0, (size_t)kv_elems * 2, m->stream));
+  }
+  LOGOS_TRY(alloc_mat(m, &m->embed, c.vocab, H));
+  LOGOS_TRY(gen(m, &m->embed, c.vocab, 0, 0, H, 1, 0, (uint64_t)1 << 20));
+  if (c.tied_embeddings) {
+    m->head = m->embed;
+  } else {
+    LOGOS_TRY(alloc_mat(m, &m->head, c.vocab, H));
+    LOGOS_TRY(gen(m, &m->head, c.vocab, 0, 0, H, 1, 0, ((uint64_t)1 << 20) + 1));
+  }
+
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->ones), H * 4));
+  LOGOS_TRY(launch_synth_fill(m->ones, LOGOS_F32, 1, 0, 0, 0, H, 1.0f, 1.0f, m->device, m->stream));
+  {
+    std::vector<float> tab((size_t)(c.l_max * D));
+    rope_table_host(tab.data(), c.l_max, D, (double)c.rope_theta);
+    LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->rope), c.l_max * D * 4));
+    LOGOS_CUDA_TRY(cudaMemcpyAsync(m->rope, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice, m->stream));
+    LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
+  }
+  m->max_splits = 1;
+  {
+    int s1 = gemm_pick_splits(B, H, m->nq, m->device);
+    int s2 = gemm_pick_splits(B, H, m->f_local, m->device);
+    m->max_splits = s1 > s2 ? s1 : s2;
+  }
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->h), B * H * 4));
+  LOGOS_TRY(dmalloc(m, &m->xn, B * H * 4));
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->qkv), B * m->nqkv * 4));
+  LOGOS_TRY(dmalloc(m, &m->att, B * m->nq * 4));
+  LOGOS_TRY(dmalloc(m, &m->ffn, B * m->f_local * 4));
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->partials), (int64_t)m->max_splits * B * H * 4));
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->logits), B * c.vocab * 4));
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->tokens), B * 4));
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->seq_len), B * 4));
+  LOGOS_CUDA_TRY(cudaMemsetAsync(m->tokens, 0, (size_t)B * 4, m->stream));
+  LOGOS_CUDA_TRY(cudaMemsetAsync(m->seq_len, 0, (size_t)B * 4, m->stream));
+  LOGOS_CUDA_TRY(cudaMemsetAsync(m->logits, 0, (size_t)(B * c.vocab) * 4, m->stream));
+  LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
+  return LOGOS_OK;
+}
+
+__global__ void sum_partials_kernel(float* __restrict__ p, int parts, int64_t stride, int64_t count) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  float v = p[i];
+  for (int s = 1; s < parts; ++s) v = __fadd_rn(v, p[(int64_t)s * stride + i]);
+  p[i] = v;
+}
+
+__global__ void bump_len_kernel(int32_t* seq_len, int b, int l_max) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < b && seq_len[i] < l_max) seq_len[i] += 1;
+}
+
+// GEMM producing f32 partials [splits][B][N] in m->partials; returns the split count.
+logos_status_t gemm_partials(Model* m, const void* a, const Q8Mat& w, int* splits_out) {
+  const int64_t B = m->cfg.batch;
+  GemmArgs g;
+  g.a = a; g.a_dtype = m->cfg.act_dtype; g.lda = w.k;
+  g.q = w.q; g.s = w.s;
+  g.m = B; g.n = w.n; g.k = w.k;
+  g.device = m->device;
+  int splits = gemm_pick_splits(B, w.n, w.k, m->device);
+  if (splits > m->max_splits) splits = m->max_splits;
+  if (splits > 1 && gemm_tc_applicable(g)) {
+    g.splits = splits;
+    g.partials = m->partials;
+  } else {
+    splits = 1;
+    g.c = m->partials; g.c_dtype = LOGOS_F32; g.ldc = w.n;
+  }
+  m->launch_counter += 1;
+  {
+    ProfScope ps(m, PROF_GEMM);
+    LOGOS_TRY(launch_q8_gemm(g, m->stream));
+  }
+  if (m->tp.degree > 1) {
+    ProfScope ps(m, PROF_COMM);
+    const int64_t count = B * w.n;
+    if (splits > 1) {
+      sum_partials_kernel<<<(unsigned)((count + 255) / 256), 256, 0, m->stream>>>(m->partials, splits, count, count);
+      LOGOS_TRY(check_launch("sum_partials_kernel"));
+      m->launch_counter += 1;
+      splits = 1;
+    }
+    LOGOS_TRY(tp_allreduce_sum_f32(&m->tp, m->partials, count, m->stream));
+  }
+  *splits_out = splits;
+  return LOGOS_OK;
+}
+
+// One lock-step decode step on the model's stream.  tokens_in: [B] device.
+logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, int32_t* history_slot) {
+  const logos_llm_config_t& c = m->cfg;
+  const int64_t B = c.batch, H = c.hidden, D = c.head_dim;
+  cudaStream_t st = m->stream;
+  m->launch_counter = 0;
+  {
+    ProfScope ps(m, PROF_ELEMWISE);
+    LOGOS_TRY(launch_embed(tokens_in, m->embed.q, m->embed.s, m->h, B, H, st));
+  }
+  m->launch_counter += 1;
+  int parts = 0;
+  for (int64_t l = 0; l < c.layers; ++l) {
+    Layer& L = m->layers[(size_t)l];
+    {
+      ProfScope ps(m, PROF_ELEMWISE);
+      LOGOS_TRY(launch_residual_rmsnorm(m->h, m->partials, parts, B * H, m->ones, m->xn, c.act_dtype, B, H, c.rms_eps, st));
+    }
+    m->launch_counter += 1;
+    {
+      ProfScope ps(m, PROF_GEMM);
+      GemmArgs g;
+      g.a = m->xn; g.a_dtype = c.act_dtype; g.lda = H;
+      g.q = L.wqkv.q; g.s = L.wqkv.s;
+      g.c = m->qkv; g.c_dtype = LOGOS_F32; g.ldc = m->nqkv;
+      g.m = B; g.n = m->nqkv; g.k = H;
+      g.device = m->device;
+      LOGOS_TRY(launch_q8_gemm(g, st));
+      m->launch_counter += 1;
+    }
+    {
+      ProfScope ps(m, PROF_ATTN);
+      AttnArgs a;
+      a.q_f32 = m->qkv; a.q_ld = m->nqkv; a.rotate_q = 1;
+      a.k_new_f32 = m->qkv + m->nq; a.v_new_f32 = m->qkv + m->nq + m->nkv; a.kv_ld = m->nqkv;
+      a.k_cache = L.kc; a.v_cache = L.vc; a.rope = m->rope; a.seq_len = m->seq_len;
+      a.bump_seq_len = 0;
+      a.o = m->att; a.o_dtype = c.act_dtype;
+      a.b = B; a.h_q = m->hq_local; a.h_kv = m->hkv_local; a.d = D; a.l_max = c.l_max;
+      a.scale = 1.0f / sqrtf((float)D);
+      a.device = m->device;
+      LOGOS_TRY(launch_gqa_decode_attn(a, st));
+      m->launch_counter += 2;
+    }
+    LOGOS_TRY(gemm_partials(m, m->att, L.wo, &parts));
+    {
+      ProfScope ps(m, PROF_ELEMWISE);
+      LOGOS_TRY(launch_residual_rmsnorm(m->h, m->partials, parts, B * H, m->ones, m->xn, c.act_dtype, B, H, c.rms_eps, st));
+    }
+    m->launch_counter += 1;
+    {
+      ProfScope ps(m, PROF_GEMM);
+      GemmArgs g;
+      g.a = m->xn; g.a_dtype = c.act_dtype; g.lda = H;
+      g.q = L.wgu.q; g.s = L.wgu.s;
+      g.c = m->ffn; g.c_dtype = c.act_dtype; g.ldc = m->f_local;
+      g.m = B; g.n = 2 * m->f_local; g.k = H;
+      g.epilogue = EPI_SWIGLU;
+      g.device = m->device;
+      LOGOS_TRY(launch_q8_gemm(g, st));
+      m->launch_counter += 1;
+    }
+    LOGOS_TRY(gemm_partials(m, m->ffn, L.wd, &parts));
+  }
+  if (sample) {
+    {
+      ProfScope ps(m, PROF_ELEMWISE);
+      LOGOS_TRY(launch_residual_rmsnorm(m->h, m->partials, parts, B * H, m->ones, m->xn, c.act_dtype, B, H, c.rms_eps, st));
+    }
+    GemmArgs g;
+    g.a = m->xn; g.a_dtype = c.act_dtype; g.lda = H;
+    g.q = m->head.q; g.s = m->head.s;
+    g.c = m->logits; g.c_dtype = LOGOS_F32; g.ldc = c.vocab;
+    g.m = B; g.n = c.vocab; g.k = H;
+    g.device = m->device;
+    {
+      ProfScope ps(m, PROF_GEMM);
+      LOGOS_TRY(launch_q8_gemm(g, st));
+    }
+    ProfScope ps(m, PROF_ELEMWISE);
+    LOGOS_TRY(launch_argmax(m->logits, m->tokens, history_slot, B, c.vocab, st));
+    m->launch_counter += 3;
+  }
+  ProfScope ps_tail(m, PROF_ELEMWISE);
+  bump_len_kernel<<<(unsigned)((B + 127) / 128), 128, 0, st>>>(m->seq_len, (int)B, (int)c.l_max);
+  LOGOS_TRY(check_launch("bump_len_kernel"));
+  m->launch_counter += 1;
+  m->launches_per_step = m->launch_counter;
+  return LOGOS_OK;
+}
+
+logos_status_t check_cfg(const logos_llm_config_t& c) {
+  if (c.layers <= 0 || c.hidden <= 0 || c.h_q <= 0 || c.h_kv <= 0 || c.head_dim <= 0 || c.ffn <= 0 || c.vocab <= 0 ||
+      c.l_max <= 0 || c.batch <= 0)
+    return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_create: every extent must be positive");
+  if (c.tp_degree < 1 || c.tp_rank < 0 || c.tp_rank >= c.tp_degree)
+    return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_create: tp_rank %d of tp_degree %d", c.tp_rank, c.tp_degree);
+  if (c.h_q % c.h_kv) return fail(LOGOS_ERROR, "logos_llm_create: h_q must be a multiple of h_kv");
+  if (c.h_kv % c.tp_degree || c.ffn % c.tp_degree)
+    return fail(LOGOS_ERROR, "logos_llm_create: h_kv and ffn must divide by tp_degree");
+  if (c.head_dim != 64 && c.head_dim != 128) return fail(LOGOS_ERROR, "logos_llm_create: head_dim must be 64 or 128");
+  if (c.hidden % 32 || (c.ffn / c.tp_degree) % 32 || ((c.h_q / c.tp_degree) * c.head_dim) % 32)
+    return fail(LOGOS_ERROR, "logos_llm_create: hidden, ffn/tp and q width/tp must be multiples of the Q8 block 32");
+  if (c.act_dtype != LOGOS_F32 && c.act_dtype != LOGOS_F16 && c.act_dtype != LOGOS_BF16)
+    return fail(LOGOS_ERROR, "logos_llm_create: act_dtype must be LOGOS_F32, LOGOS_F16 or LOGOS_BF16");
+  return LOGOS_OK;
+}
+
+Model* get_model(logos_handle_t h) { return static_cast<Model*>(registry_get(h, ObjKind::Model)); }
+
+#define MODEL_OR_FAIL(m, h, who)                                                           \
+  if (!(h)) return fail(LOGOS_NULL_POINTER, who ": null model handle");                    \
+  Model* m = get_model(h);                                                                 \
+  if (!m) return fail(LOGOS_INVALID_HANDLE, who ": invalid or freed model handle");        \
+  LOGOS_CUDA_TRY(cudaSetDevice(m->device));
+
+}  // namespace
+}  // namespace logos
+
+using namespace logos;
+
+extern "C" {
+
+logos_status_t logos_llm_create(const logos_llm_config_t* cfg, const void* nccl_unique_id_or_null, logos_handle_t* out) {
+  return guarded([&]() -> logos_status_t {
+    if (!out) return fail(LOGOS_NULL_POINTER, "logos_llm_create: out is null");
+    *out = nullptr;
+    if (!cfg) return fail(LOGOS_NULL_POINTER, "logos_llm_create: cfg is null");
+    LOGOS_TRY(check_cfg(*cfg));
+    int ndev = logos_device_count();
+    if (ndev == 0) return fail(LOGOS_ERROR, "logos_llm_create: no CUDA device (this library has no CPU path)");
+    if (cfg->device < 0 || cfg->device >= ndev)
+      return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_create: device %d of %d", cfg->device, ndev);
+    Model* m = new Model();
+    m->cfg = *cfg;
+    m->device = cfg->device;
+    logos_status_t s = build(m, nccl_unique_id_or_null);
+    if (s != LOGOS_OK) {
+      std::string keep = logos_last_error() ? logos_last_error() : "";
+      destroy(m);
+      set_last_error(keep);
+      return s;
+    }
+    *out = registry_put(ObjKind::Model, m);
+    return LOGOS_OK;
+  });
+}
+
+logos_status_t logos_llm_prefill(logos_handle_t model, const int32_t* tokens_host, int64_t t) {
+  return guarded([&]() -> logos_status_t {
+    MODEL_OR_FAIL(m, model, "logos_llm_prefill");
+    if (!tokens_host) return fail(LOGOS_NULL_POINTER, "logos_llm_prefill: tokens_host is null");
+    const int64_t B = m->cfg.batch;
+    if (t <= 0 || t > m->cfg.l_max) return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_prefill: t=%lld outside [1,%lld]", (long long)t, (long long)m->cfg.l_max);
+    for (int64_t i = 0; i < B * t; ++i)
+      if (tokens_host[i] < 0 || tokens_host[i] >= m->cfg.vocab)
+        return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_prefill: token id %d outside the vocabulary", tokens_host[i]);
+    if (m->prompt_cap < B * t) {
+      LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->prompt), B * t * 4));
+      m->prompt_cap = B * t;
+    }
+    std::vector<int32_t> tr((size_t)(B * t));
+    for (int64_t b = 0; b < B; ++b)
+      for (int64_t p = 0; p < t; ++p) tr[(size_t)(p * B + b)] = tokens_host[b * t + p];
+    LOGOS_CUDA_TRY(cudaMemcpyAsync(m->prompt, tr.data(), tr.size() * 4, cudaMemcpyHostToDevice, m->stream));
+    LOGOS_CUDA_TRY(cudaMemsetAsync(m->seq_len, 0, (size_t)B * 4, m->stream));
+    for (int64_t p = 0; p < t; ++p) LOGOS_TRY(step(m, m->prompt + p * B, p == t - 1, nullptr));
+    LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    return LOGOS_OK;
+  });
+}
+
+logos_status_t logos_llm_synth_kv(logos_handle_t model, int64_t t, uint64_t seed) {
+  return guarded([&]() -> logos_status_t {
+    MODEL_OR_FAIL(m, model, "logos_llm_synth_kv");
+    const logos_llm_config_t& c = m->cfg;
+    if (t < 0 || t > c.l_max) return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_synth_kv: t outside [0,l_max]");
+    const int64_t D = c.head_dim, B = c.batch;
+    for (int64_t l = 0; l < c.layers; ++l)
+      for (int64_t b = 0; b < B; ++b)
+        for (int64_t h = 0; h < m->hkv_local; ++h) {
+          // index space of the unsharded cache, so every rank fills its own heads with the same values
+          int64_t gh = (int64_t)c.tp_rank * m->hkv_local + h;
+          int64_t first = ((b * c.h_kv + gh) * c.l_max) * D;
+          int64_t off = ((b * m->hkv_local + h) * c.l_max) * D;
+          LOGOS_TRY(launch_synth_fill(m->layers[(size_t)l].kc + off, LOGOS_F16, 2, seed, (uint64_t)(2 * l), first, t * D,
+                                      0.f, 1.f, m->device, m->stream));
+          LOGOS_TRY(launch_synth_fill(m->layers[(size_t)l].vc + off, LOGOS_F16, 2, seed, (uint64_t)(2 * l + 1), first,
+                                      t * D, 0.f, 1.f, m->device, m->stream));
+        }
+    std::vector<int32_t> len((size_t)B, (int32_t)t);
+    LOGOS_CUDA_TRY(cudaMemcpyAsync(m->seq_len, len.data(), (size_t)B * 4, cudaMemcpyHostToDevice, m->stream));
+    LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    return LOGOS_OK;
+  });
+}
+
+logos_status_t logos_llm_set_tokens(logos_handle_t model, const int32_t* tokens_host) {
+  return guarded([&]() -> logos_status_t {
+    MODEL_OR_FAIL(m, model, "logos_llm_set_tokens");
+    if (!tokens_host) return fail(LOGOS_NULL_POINTER, "logos_llm_set_tokens: tokens_host is null");
+    for (int64_t i = 0; i < m->cfg.batch; ++i)
+      if (tokens_host[i] < 0 || tokens_host[i] >= m->cfg.vocab)
+        return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_set_tokens: token id %d outside the vocabulary", tokens_host[i]);
+    LOGOS_CUDA_TRY(cudaMemcpyAsync(m->tokens, tokens_host, (size_t)m->cfg.batch * 4, cudaMemcpyHostToDevice, m->stream));
+    LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    return LOGOS_OK;
+  });
+}
+
+logos_status_t logos_llm_decode_steps(logos_handle_t model, int64_t steps, int32_t* tokens_host_or_null) {
+  return guarded([&]() -> logos_status_t {
+    MODEL_OR_FAIL(m, model, "logos_llm_decode_steps");
+    const int64_t B = m->cfg.batch;
+    if (steps < 0) return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_decode_steps: negative step count");
+    if (steps == 0) return LOGOS_OK;
+    if (m->history_cap < steps) {
+      LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->history), steps * B * 4));
+      m->history_cap = steps;
+    }
+    LOGOS_CUDA_TRY(cudaEventRecord(m->ev0, m->stream));
+    for (int64_t i = 0; i < steps; ++i) LOGOS_TRY(step(m, m->tokens, true, m->history + i * B));
+    LOGOS_CUDA_TRY(cudaEventRecord(m->ev1, m->stream));
+    if (tokens_host_or_null)
+      LOGOS_CUDA_TRY(cudaMemcpyAsync(tokens_host_or_null, m->history, (size_t)(steps * B) * 4, cudaMemcpyDeviceToHost, m->stream));
+    LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    float ms = 0.f;
+    LOGOS_CUDA_TRY(cudaEventElapsedTime(&ms, m->ev0, m->ev1));
+    m->last_ms = ms;
+    int* status = kernel_status_ptr(m->device);
+    if (status && status[0] != 0) return fail(LOGOS_ERROR, "a device-side wait gave up (kernel status %d)", status[0]);
+    return LOGOS_OK;
+  });
+}
+
+logos_status_t logos_llm_profile_step(logos_handle_t model, double* ms_by_class_out) {
+  return guarded([&]() -> logos_status_t {
+    MODEL_OR_FAIL(m, model, "logos_llm_profile_step");
+    if (!ms_by_class_out) return fail(LOGOS_NULL_POINTER, "logos_llm_profile_step: null output");
+    m->profiling = true;
+    m->prof_used = 0;
+    m->prof_class.clear();
+    logos_status_t s = step(m, m->tokens, true, nullptr);
+    m->profiling = false;
+    LOGOS_TRY(s);
+    LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    for (int i = 0; i < PROF_CLASSES; ++i) ms_by_class_out[i] = 0.0;
+    for (size_t i = 0; i < m->prof_class.size(); ++i) {
+      float ms = 0.f;
+      LOGOS_CUDA_TRY(cudaEventElapsedTime(&ms, m->prof_events[2 * i], m->prof_events[2 * i + 1]));
+      ms_by_class_out[m->prof_class[i]] += ms;
+    }
+    return LOGOS_OK;
+  });
+}
+
+logos_status_t logos_llm_decode_step(logos_handle_t model, int32_t* next_tokens_host) {
+  return logos_llm_decode_steps(model, 1, next_tokens_host);
+}
+
+logos_status_t logos_llm_read_kv(logos_handle_t model, int64_t layer, void* k_host, void* v_host) {
+  return guarded([&]() -> logos_status_t {
+    MODEL_OR_FAIL(m, model, "logos_llm_read_kv");
+    if (!k_host || !v_host) return fail(LOGOS_NULL_POINTER, "logos_llm_read_kv: null output");
+    if (layer < 0 || layer >= m->cfg.layers) return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_read_kv: layer %lld", (long long)layer);
+    size_t bytes = (size_t)(m->cfg.batch * m->hkv_local * m->cfg.l_max * m->cfg.head_dim) * 2;
+    LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    LOGOS_CUDA_TRY(cudaMemcpy(k_host, m->layers[(size_t)layer].kc, bytes, cudaMemcpyDeviceToHost));
+    LOGOS_CUDA_TRY(cudaMemcpy(v_host, m->layers[(size_t)layer].vc, bytes, cudaMemcpyDeviceToHost));
+    return LOGOS_OK;
+  });
+}
+
+logos_status_t logos_llm_read_logits(logos_handle_t model, float* logits_host) {
+  return guarded([&]() -> logos_status_t {
+    MODEL_OR_FAIL(m, model, "logos_llm_read_logits");
+    if (!logits_host) return fail(LOGOS_NULL_POINTER, "logos_llm_read_logits: null output");
+    LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    LOGOS_CUDA_TRY(cudaMemcpy(logits_host, m->logits, (size_t)(m->cfg.batch * m->cfg.vocab) * 4, cudaMemcpyDeviceToHost));
+    return LOGOS_OK;
+  });
+}
+
+logos_status_t logos_llm_read_seq_len(logos_handle_t model, int32_t* seq_len_host) {
+  return guarded([&]() -> logos_status_t {
+    MODEL_OR_FAIL(m, model, "logos_llm_read_seq_len");
+    if (!seq_len_host) return fail(LOGOS_NULL_POINTER, "logos_llm_read_seq_len: null output");
+    LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    LOGOS_CUDA_TRY(cudaMemcpy(seq_len_host, m->seq_len, (size_t)m->cfg.batch * 4, cudaMemcpyDeviceToHost));
+    return LOGOS_OK;
+  });
+}
+
+logos_status_t logos_llm_set_seq_len(logos_handle_t model, int64_t t) {
+  return guarded([&]() -> logos_status_t {
+    MODEL_OR_FAIL(m, model, "logos_llm_set_seq_len");
+    if (t < 0 || t > m->cfg.l_max) return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_set_seq_len: t outside [0,l_max]");
+    std::vector<int32_t> len((size_t)m->cfg.batch, (int32_t)t);
+    LOGOS_CUDA_TRY(cudaMemcpyAsync(m->seq_len, len.data(), len.size() * 4, cudaMemcpyHostToDevice, m->stream));
+    LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    return LOGOS_OK;
+  });
+}
+
+logos_status_t logos_llm_last_timing(logos_handle_t model, double* ms_out, int64_t* launches_per_step_out) {
+  return guarded([&]() -> logos_status_t {
+    MODEL_OR_FAIL(m, model, "logos_llm_last_timing");
+    if (ms_out) *ms_out = m->last_ms;
+    if (launches_per_step_out) *launches_per_step_out = m->launches_per_step;
+    return LOGOS_OK;
+  });
+}
+
+logos_status_t logos_llm_free(logos_handle_t model) {
+  return guarded([&]() -> logos_status_t {
+    if (!model) return fail(LOGOS_NULL_POINTER, "logos_llm_free: null handle");
+    Model* m = static_cast<Model*>(registry_take(model, ObjKind::Model));
+    if (!m) return fail(LOGOS_INVALID_HANDLE, "logos_llm_free: invalid or already freed handle");
+    destroy(m);
+    return LOGOS_OK;
+  });
+}
+
+}  // extern "C"

@@ -1,0 +1,103 @@
+// Internal launchers: raw device pointers in, kernels enqueued on a stream.
+// The extern "C" wrappers and the decode step both go through these.
+#pragma once
+#include "common.cuh"
+
+namespace logos {
+
+// ---- synthetic inputs / weight prep (synth.cu)
+logos_status_t launch_synth_fill(void* dst, int dtype, int kind, uint64_t seed, uint64_t stream, int64_t first,
+                                 int64_t count, float a, float b, int device, cudaStream_t st);
+// Rows [row0,row0+n) x columns [col0,col0+k) of a logical [.][k_total] N(0,std)
+// matrix (or of `w`, ld k_total, when generate is false).  Output row r goes to
+// physical row r*out_row_mul + out_row_add of q/s, whose row length is k.
+logos_status_t launch_q8_quantize(bool generate, const float* w, int8_t* q, float* s, int64_t n, int64_t k,
+                                  int64_t row0, int64_t col0, int64_t k_total, int64_t out_row_mul,
+                                  int64_t out_row_add, uint64_t seed, uint64_t stream, float std, int device,
+                                  cudaStream_t st);
+
+// ---- GEMV (q8_gemv.cu)
+logos_status_t launch_q8_gemv(const int8_t* q, const float* s, const float* x, float* y, int64_t n, int64_t k,
+                              int device, cudaStream_t st);
+
+// ---- GEMM (q8_gemm.cu)
+enum GemmEpilogue : int {
+  EPI_NONE = 0,      // C = acc
+  EPI_RESIDUAL = 1,  // C = acc + aux
+  EPI_SWIGLU = 2,    // rows (2j,2j+1) = (gate_j, up_j); C[m][j] = silu(gate)*up
+};
+
+struct GemmArgs {
+  const void*   a = nullptr;   // activations [M][K], 16-bit, row stride lda elements
+  int           a_dtype = LOGOS_BF16;  // LOGOS_BF16 or LOGOS_F16
+  int64_t       lda = 0;
+  const int8_t* q = nullptr;   // [N][K]
+  const float*  s = nullptr;   // [N][K/32]
+  void*         c = nullptr;   // [M][N] (or [M][N/2] for EPI_SWIGLU), row stride ldc elements
+  int           c_dtype = LOGOS_BF16;  // LOGOS_BF16, LOGOS_F16 or LOGOS_F32
+  int64_t       ldc = 0;
+  const void*   aux = nullptr; // EPI_RESIDUAL: same type and stride as c
+  int64_t       m = 0, n = 0, k = 0;
+  int           epilogue = EPI_NONE;
+  // split-K: when > 1 the kernel writes f32 partials [splits][M][N] to
+  // `partials` and the caller reduces them; epilogue must be EPI_NONE.
+  int           splits = 1;
+  float*        partials = nullptr;
+  int           device = 0;
+  int           force_simt = 0;  // use the SIMT kernel even where the tensor-core one applies
+};
+logos_status_t launch_q8_gemm(const GemmArgs& g, cudaStream_t st);
+// How many K-splits launch_q8_gemm would like for this shape (1 = none).
+int gemm_pick_splits(int64_t m, int64_t n, int64_t k, int device);
+// Whether the tcgen05 kernel accepts this call (else the SIMT kernel runs).
+bool gemm_tc_applicable(const GemmArgs& g);
+
+// ---- attention (attention.cu)
+struct AttnArgs {
+  // query: either f16 [B][Hq][D] (q_f16) or f32 rows inside a wider matrix
+  // (q_f32, row stride q_ld floats per sequence, head h at column h*D).
+  const __half* q_f16 = nullptr;
+  const float*  q_f32 = nullptr;
+  int64_t       q_ld = 0;
+  int           rotate_q = 0;        // apply rotary embedding at position seq_len[b]
+  // new row to append before attending (fused form); null = none
+  const __half* k_new_f16 = nullptr;
+  const __half* v_new_f16 = nullptr;
+  const float*  k_new_f32 = nullptr; // f32 rows, stride kv_ld per sequence
+  const float*  v_new_f32 = nullptr;
+  int64_t       kv_ld = 0;
+  __half*       k_cache = nullptr;   // [B][Hkv][Lmax][D]
+  __half*       v_cache = nullptr;
+  const float*  rope = nullptr;      // [Lmax][D/2][2]
+  int32_t*      seq_len = nullptr;   // [B]
+  int           bump_seq_len = 0;    // seq_len[b] += 1 after the call
+  void*         o = nullptr;         // [B][Hq][D]
+  int           o_dtype = LOGOS_F16; // LOGOS_F16 / LOGOS_BF16 / LOGOS_F32
+  int64_t       b = 0, h_q = 0, h_kv = 0, d = 0, l_max = 0;
+  float         scale = 1.f;
+  int           device = 0;
+};
+logos_status_t launch_gqa_decode_attn(const AttnArgs& a, cudaStream_t st);
+logos_status_t launch_kv_append_rope(__half* k_cache, __half* v_cache, const __half* k_new, const __half* v_new,
+                                     const float* rope, int32_t* seq_len, int64_t b, int64_t h_kv, int64_t d,
+                                     int64_t l_max, int device, cudaStream_t st);
+void rope_table_host(float* out, int64_t l_max, int64_t d, double theta);
+
+// ---- norms and element-wise (elementwise.cu)
+logos_status_t launch_rmsnorm_f32(const float* x, const float* g, float* y, int64_t rows, int64_t h, float eps,
+                                  cudaStream_t st);
+logos_status_t launch_swiglu_f32(const float* gate, const float* up, float* y, int64_t count, cudaStream_t st);
+// h[row] = dequantised embedding row tokens[row]
+logos_status_t launch_embed(const int32_t* tokens, const int8_t* q, const float* s, float* h, int64_t rows,
+                            int64_t hidden, cudaStream_t st);
+// h += sum over `parts` partial deltas (each [rows][hidden] f32, spaced
+// part_stride floats, added in ascending order; parts may be 0), then
+// xn = act16( h * rsqrt(mean(h^2)+eps) * g ).
+logos_status_t launch_residual_rmsnorm(float* h, const float* delta, int parts, int64_t part_stride,
+                                       const float* g, void* xn, int xn_dtype, int64_t rows, int64_t hidden,
+                                       float eps, cudaStream_t st);
+// tokens[row] = argmax(logits[row]) with the lowest index winning ties
+logos_status_t launch_argmax(const float* logits, int32_t* tokens, int32_t* history_or_null, int64_t rows,
+                             int64_t vocab, cudaStream_t st);
+
+}  // namespace logos

@@ -1,0 +1,164 @@
+// Q8 GEMV: y[n] = sum_kb s[n,kb] * sum_{k in kb} q[n,k] * x[k].
+//
+// HBM-bound: 1.125 bytes of weights per multiply-add, so the kernel is a
+// coalesced stream.  One warp owns one row at a time; every lane issues 128-bit
+// read-only loads of 16 consecutive int8 (a half block), so a warp covers 512
+// columns per step and keeps several such loads in flight.  int8 -> f32 uses
+// the 2^23 mantissa trick (one byte-permute and one subtract), the half-block
+// dot product is scaled by its block's f32 scale in registers, and the row sum
+// is a warp-shuffle reduction.  x lives in shared memory, laid out so the
+// four 128-bit reads a lane needs are bank-conflict free.
+#include "ops.cuh"
+
+namespace logos {
+
+namespace {
+
+constexpr int GEMV_WARPS = 8;
+
+__device__ __forceinline__ uint4 ldg_nc_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// byte `sel` of the bias-flipped word -> exact float value of the int8
+__device__ __forceinline__ float byte_to_f32(uint32_t w_xor80, uint32_t selector) {
+  // 0x4B0000bb = 2^23 + bb ; bb = q + 128
+  uint32_t bits = __byte_perm(w_xor80, 0x4B000000u, selector);
+  return __uint_as_float(bits) - 8388736.0f;
+}
+
+__device__ __forceinline__ float dot4(uint32_t w, float4 x, float acc) {
+  uint32_t u = w ^ 0x80808080u;
+  acc = fmaf(byte_to_f32(u, 0x7650), x.x, acc);
+  acc = fmaf(byte_to_f32(u, 0x7651), x.y, acc);
+  acc = fmaf(byte_to_f32(u, 0x7652), x.z, acc);
+  acc = fmaf(byte_to_f32(u, 0x7653), x.w, acc);
+  return acc;
+}
+
+// xs4 layout: chunk c (16 floats) is split into 4 float4; float4 j of chunk c
+// sits at index (c/32)*128 + j*32 + (c%32), so the 32 lanes of a warp reading
+// the same j of consecutive chunks touch consecutive 16-byte slots.
+__device__ __forceinline__ int xs4_index(int chunk, int j) { return (chunk >> 5) * 128 + j * 32 + (chunk & 31); }
+
+template <bool X_IN_SMEM>
+__global__ void __launch_bounds__(GEMV_WARPS * 32)
+q8_gemv_kernel(const int8_t* __restrict__ q, const float* __restrict__ s, const float* __restrict__ x,
+               float* __restrict__ y, int64_t n, int64_t k) {
+  extern __shared__ float4 xs4[];
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int chunks = (int)(k >> 4);  // 16-element chunks per row
+  if (X_IN_SMEM) {
+    const float4* xg = reinterpret_cast<const float4*>(x);
+    for (int i = tid; i < chunks * 4; i += GEMV_WARPS * 32) {
+      int c = i >> 2, j = i & 3;
+      xs4[xs4_index(c, j)] = xg[i];
+    }
+    __syncthreads();
+  }
+  const int64_t kb_per_row = k >> 5;
+  for (int64_t row = (int64_t)blockIdx.x * GEMV_WARPS + warp; row < n; row += (int64_t)gridDim.x * GEMV_WARPS) {
+    const uint4* qr = reinterpret_cast<const uint4*>(q + row * k);
+    const float* sr = s + row * kb_per_row;
+    float acc = 0.f;
+    int c = lane;
+    // four loads in flight per lane
+    for (; c + 96 < chunks; c += 128) {
+      uint4 w0 = ldg_nc_v4(qr + c), w1 = ldg_nc_v4(qr + c + 32), w2 = ldg_nc_v4(qr + c + 64),
+            w3 = ldg_nc_v4(qr + c + 96);
+      float s0 = __ldg(sr + (c >> 1)), s1 = __ldg(sr + ((c + 32) >> 1)), s2 = __ldg(sr + ((c + 64) >> 1)),
+            s3 = __ldg(sr + ((c + 96) >> 1));
+      uint4 ws[4] = {w0, w1, w2, w3};
+      float ss[4] = {s0, s1, s2, s3};
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        int cc = c + 32 * u;
+        float4 x0, x1, x2, x3;
+        if (X_IN_SMEM) {
+          x0 = xs4[xs4_index(cc, 0)]; x1 = xs4[xs4_index(cc, 1)];
+          x2 = xs4[xs4_index(cc, 2)]; x3 = xs4[xs4_index(cc, 3)];
+        } else {
+          const float4* xg = reinterpret_cast<const float4*>(x) + cc * 4;
+          x0 = __ldg(xg); x1 = __ldg(xg + 1); x2 = __ldg(xg + 2); x3 = __ldg(xg + 3);
+        }
+        float p = 0.f;
+        p = dot4(ws[u].x, x0, p);
+        p = dot4(ws[u].y, x1, p);
+        p = dot4(ws[u].z, x2, p);
+        p = dot4(ws[u].w, x3, p);
+        acc = fmaf(ss[u], p, acc);
+      }
+    }
+    for (; c < chunks; c += 32) {
+      uint4 w = ldg_nc_v4(qr + c);
+      float sc = __ldg(sr + (c >> 1));
+      float4 x0, x1, x2, x3;
+      if (X_IN_SMEM) {
+        x0 = xs4[xs4_index(c, 0)]; x1 = xs4[xs4_index(c, 1)];
+        x2 = xs4[xs4_index(c, 2)]; x3 = xs4[xs4_index(c, 3)];
+      } else {
+        const float4* xg = reinterpret_cast<const float4*>(x) + c * 4;
+        x0 = __ldg(xg); x1 = __ldg(xg + 1); x2 = __ldg(xg + 2); x3 = __ldg(xg + 3);
+      }
+      float p = 0.f;
+      p = dot4(w.x, x0, p);
+      p = dot4(w.y, x1, p);
+      p = dot4(w.z, x2, p);
+      p = dot4(w.w, x3, p);
+      acc = fmaf(sc, p, acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) y[row] = acc;
+  }
+}
+
+}  // namespace
+
+logos_status_t launch_q8_gemv(const int8_t* q, const float* s, const float* x, float* y, int64_t n, int64_t k,
+                              int device, cudaStream_t st) {
+  if (n == 0) return LOGOS_OK;
+  if (k == 0) {
+    LOGOS_CUDA_TRY(cudaMemsetAsync(y, 0, sizeof(float) * n, st));
+    return LOGOS_OK;
+  }
+  int64_t ctas = (n + GEMV_WARPS - 1) / GEMV_WARPS;
+  int64_t cap = (int64_t)sm_count(device) * 8;
+  int grid = (int)(ctas < cap ? ctas : cap);
+  // x padded to whole groups of 32 chunks (512 floats)
+  size_t smem = (size_t)((k / 16 + 31) / 32) * 128 * sizeof(float4);
+  if (smem <= 96 * 1024) {
+    if (smem > 48 * 1024)
+      LOGOS_CUDA_TRY(cudaFuncSetAttribute(q8_gemv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    q8_gemv_kernel<true><<<grid, GEMV_WARPS * 32, smem, st>>>(q, s, x, y, n, k);
+  } else {
+    q8_gemv_kernel<false><<<grid, GEMV_WARPS * 32, 0, st>>>(q, s, x, y, n, k);
+  }
+  return check_launch("q8_gemv_kernel");
+}
+
+}  // namespace logos
+
+using namespace logos;
+
+extern "C" logos_status_t logos_q8_gemv(logos_handle_t q, logos_handle_t s, logos_handle_t x, logos_handle_t y,
+                                        int64_t n, int64_t k, void* stream_or_null) {
+  return guarded([&]() -> logos_status_t {
+    if (n < 0 || k < 0) return fail(LOGOS_OUT_OF_BOUNDS, "logos_q8_gemv: negative extent");
+    if (k % 32) return fail(LOGOS_OUT_OF_BOUNDS, "logos_q8_gemv: K=%lld is not a multiple of the block size 32", (long long)k);
+    int8_t* qp; float* sp; float* xp; float* yp;
+    int32_t dev = 0;
+    LOGOS_TRY(buf_ptr<int8_t>(q, n * k, "q", &qp, &dev));
+    LOGOS_TRY(buf_ptr<float>(s, n * (k / 32), "s", &sp));
+    LOGOS_TRY(buf_ptr<float>(x, k, "x", &xp));
+    LOGOS_TRY(buf_ptr<float>(y, n, "y", &yp));
+    LOGOS_CUDA_TRY(cudaSetDevice(dev));
+    return launch_q8_gemv(qp, sp, xp, yp, n, k, dev, as_stream(stream_or_null));
+  });
+}

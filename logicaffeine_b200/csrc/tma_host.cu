@@ -1,0 +1,79 @@
+// Host helpers for TMA tensor maps and the device-visible kernel status word.
+#include "ptx.cuh"
+
+#include <mutex>
+#include <unordered_map>
+
+namespace logos {
+
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+}  // namespace
+
+logos_status_t make_tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, uint32_t elem_bytes,
+                                  uint64_t inner, uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner,
+                                  uint32_t box_outer, CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(LOGOS_ERROR, "cuTensorMapEncodeTiled is not available from this driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) || (row_pitch_bytes & 15u))
+    return fail(LOGOS_ERROR, "tensor map: base address and row pitch must be multiples of 16 bytes");
+  if (((uint64_t)box_inner * elem_bytes) & 15u)
+    return fail(LOGOS_ERROR, "tensor map: inner box extent must be a multiple of 16 bytes");
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_pitch_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, dtype, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(LOGOS_ERROR, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return LOGOS_OK;
+}
+
+int* kernel_status_ptr(int device) {
+  static std::mutex mu;
+  static std::unordered_map<int, int*> words;
+  std::lock_guard<std::mutex> lk(mu);
+  auto it = words.find(device);
+  if (it != words.end()) return it->second;
+  int* p = nullptr;
+  if (cudaHostAlloc(reinterpret_cast<void**>(&p), sizeof(int) * 4, cudaHostAllocMapped | cudaHostAllocPortable) !=
+      cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  p[0] = p[1] = p[2] = p[3] = 0;
+  words[device] = p;
+  return p;
+}
+
+}  // namespace logos
+
+using namespace logos;
+
+// Reads and clears the status word kernels set when a bounded wait gives up
+// (0 = no kernel reported a problem since the last read).
+extern "C" logos_status_t logos_kernel_status(int32_t device, int32_t* out_code) {
+  return guarded([&]() -> logos_status_t {
+    if (!out_code) return fail(LOGOS_NULL_POINTER, "logos_kernel_status: out_code is null");
+    int* p = kernel_status_ptr(device);
+    if (!p) return fail(LOGOS_ERROR, "logos_kernel_status: no status word (no CUDA device?)");
+    *out_code = p[0];
+    p[0] = 0;
+    return LOGOS_OK;
+  });
+}

@@ -1,0 +1,222 @@
+"""Parity of every single operator, called through the C ABI, against the CPU
+oracle on the same seeded inputs.  Integer, index and KV-cache results are
+compared bit for bit; f32-accumulated results within a relative L2 error of
+1e-3 (the stated tolerance; observed values are around 1e-6)."""
+import numpy as np
+import pytest
+
+from conftest import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-3      # stated tolerance for Q8 GEMV / GEMM outputs
+TIGHT = 2e-5    # what f32 accumulation in another order should reach
+
+
+def _dev(llm, arr):
+    return llm.DeviceBuffer.from_host(arr)
+
+
+def test_generator_matches_oracle_bit_for_bit(llm, oracle):
+    O = oracle
+    n = 100_003
+    for dtype, kind, npdt, a, b in ((llm.I8, 0, np.int8, 0.0, 0.0), (llm.F32, 1, np.float32, 1e-3, 1e-2),
+                                    (llm.F32, 2, np.float32, 0.0, 1.0), (llm.F16, 2, np.uint16, 0.0, 1.0),
+                                    (llm.BF16, 2, np.uint16, 0.5, 0.02), (llm.I32, 3, np.int32, 0.0, 151936.0)):
+        buf = llm.DeviceBuffer(n * np.dtype(npdt).itemsize)
+        llm.synthFill(buf, dtype, kind, 42, 5, 7, n, a, b)
+        got = buf.download(npdt, (n,))
+        want = O.synth_fill(dtype, kind, 42, 5, 7, n, a, b)
+        assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (dtype, kind)
+        buf.free()
+
+
+def test_quantize_and_synth_weights_bit_exact(llm, oracle):
+    O = oracle
+    n, k = 37, 224
+    w = O.synth_fill(O.F32, 2, 1, 2, 0, n * k, 0.0, 0.02).reshape(n, k)
+    w[3, 64:96] = 0.0
+    dw, dq, ds = _dev(llm, w), llm.DeviceBuffer(n * k), llm.DeviceBuffer(n * (k // 32) * 4)
+    llm.q8Quantize(dw, dq, ds, n, k)
+    q0, s0 = O.q8_quantize(w)
+    assert np.array_equal(dq.download(np.int8, (n, k)), q0)
+    assert np.array_equal(ds.download(np.uint32, (n, k // 32)), s0.view(np.uint32))
+    llm.q8SynthWeights(dq, ds, n, k, 5, 9, 77, 0.02)
+    q1, s1 = O.q8_synth_weights(n, k, 9, 77, 0.02, row0=5)
+    assert np.array_equal(dq.download(np.int8, (n, k)), q1)
+    assert np.array_equal(ds.download(np.uint32, (n, k // 32)), s1.view(np.uint32))
+
+
+@pytest.mark.parametrize("n,k", [(4096, 4096), (1, 32), (7, 96), (130, 1024), (33, 9728)])
+def test_q8_gemv(llm, oracle, n, k):
+    O = oracle
+    q = O.synth_fill(O.I8, 0, 0, 1, 0, n * k).reshape(n, k)
+    s = O.synth_fill(O.F32, 1, 0, 2, 0, n * (k // 32), 1e-3, 1e-2).reshape(n, k // 32)
+    x = O.synth_fill(O.F32, 2, 0, 3, 0, k, 0.0, 1.0)
+    y = llm.q8GemvHost(q, s, x)
+    ref = O.q8_gemv(q, s, x)
+    err = rel_l2(y, ref)
+    assert err < TOL and err < TIGHT, err
+
+
+def test_q8_gemv_golden(llm, golden):
+    y = llm.q8GemvHost(golden["gemv_q"], golden["gemv_s"], golden["gemv_x"])
+    assert rel_l2(y, golden["gemv_y"]) < TIGHT
+
+
+def test_q8_gemv_empty(llm):
+    llm.q8Gemv(llm.DeviceBuffer(0), llm.DeviceBuffer(0), llm.DeviceBuffer(128), llm.DeviceBuffer(0), 0, 32)
+
+
+def _gemm_inputs(O, m, n, k, seed=0):
+    a = O.f32_to_bf16(O.synth_fill(O.F32, 2, seed, 10, 0, m * k, 0.0, 1.0).reshape(m, k))
+    q = O.synth_fill(O.I8, 0, seed, 11, 0, n * k).reshape(n, k)
+    s = O.synth_fill(O.F32, 1, seed, 12, 0, n * (k // 32), 1e-3, 1e-2).reshape(n, k // 32)
+    return a, q, s
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 256, 3584), (16, 1152, 896), (1, 128, 128), (5, 70, 96), (64, 512, 1024),
+                                   (33, 384, 512)])
+@pytest.mark.parametrize("simt", [False, True])
+def test_q8_gemm_plain(llm, oracle, m, n, k, simt):
+    O = oracle
+    a, q, s = _gemm_inputs(O, m, n, k)
+    c = O.bf16_to_f32(llm.q8GemmHost(a, q, s, simt=simt))
+    ref32 = O.q8_gemm_f32(a, O.BF16, q, s)
+    ref = O.bf16_to_f32(O.q8_gemm(a, q, s))
+    assert rel_l2(c, ref) < TOL
+    # compared before the bf16 rounding hides it: at most a few last-place flips
+    assert np.mean(c != ref) < 5e-3
+    assert rel_l2(c, ref32) < 3e-3  # bf16 output rounding alone is ~1.7e-3
+
+
+@pytest.mark.parametrize("simt", [False, True])
+def test_q8_gemm_epilogues(llm, oracle, golden, simt):
+    O = oracle
+    a, q, s, aux = golden["gemm_a"], golden["gemm_q"], golden["gemm_s"], golden["gemm_aux"]
+    c1 = llm.q8GemmHost(a, q, s, epilogue=1, aux=aux, simt=simt)
+    assert np.mean(c1 != O.q8_gemm(a, q, s, 1, aux)) < 0.01
+    assert rel_l2(O.bf16_to_f32(c1), golden["gemm_res"]) < 3e-3
+    c2 = llm.q8GemmHost(a, q, s, epilogue=2, simt=simt)
+    assert c2.shape == (a.shape[0], q.shape[0] // 2)
+    assert rel_l2(O.bf16_to_f32(c2), golden["gemm_swiglu"]) < 5e-3
+    m, n, k = 64, 512, 1024
+    a, q, s = _gemm_inputs(O, m, n, k, seed=4)
+    c2 = llm.q8GemmHost(a, q, s, epilogue=2, simt=simt)
+    assert np.mean(c2 != O.q8_gemm(a, q, s, 2)) < 0.01
+
+
+def test_q8_gemm_config1_slice(llm, oracle):
+    """Config 1 shapes (M=64, K=3584) on a 2048-row slice of N, both kernels."""
+    O = oracle
+    a, q, s = _gemm_inputs(O, 64, 2048, 3584, seed=1)
+    ref = O.bf16_to_f32(O.q8_gemm(a, q, s))
+    for simt in (False, True):
+        c = O.bf16_to_f32(llm.q8GemmHost(a, q, s, simt=simt))
+        assert rel_l2(c, ref) < TOL
+
+
+def _attn_inputs(O, b, hq, hkv, d, lmax, lens, seed=0):
+    kc = O.synth_fill(O.F16, 2, seed, 20, 0, b * hkv * lmax * d, 0.0, 1.0).reshape(b, hkv, lmax, d)
+    vc = O.synth_fill(O.F16, 2, seed, 21, 0, b * hkv * lmax * d, 0.0, 1.0).reshape(b, hkv, lmax, d)
+    q = O.synth_fill(O.F16, 2, seed, 22, 0, b * hq * d, 0.0, 1.0).reshape(b, hq, d)
+    kn = O.synth_fill(O.F16, 2, seed, 23, 0, b * hkv * d, 0.0, 1.0).reshape(b, hkv, d)
+    vn = O.synth_fill(O.F16, 2, seed, 24, 0, b * hkv * d, 0.0, 1.0).reshape(b, hkv, d)
+    return q, kn, vn, kc, vc, np.asarray(lens, np.int32)
+
+
+def test_kv_append_rope_bit_exact(llm, oracle):
+    O = oracle
+    b, hq, hkv, d, lmax = 5, 8, 2, 128, 96
+    q, kn, vn, kc, vc, seq = _attn_inputs(O, b, hq, hkv, d, lmax, [0, 1, 50, 95, 96])
+    tab = O.rope_table(lmax, d, 1e6)
+    dkc, dvc, dkn, dvn, dtab, dseq = (_dev(llm, x) for x in (kc, vc, kn, vn, tab, seq))
+    llm.kvAppendRope(dkc, dvc, dkn, dvn, dtab, dseq, b, hkv, d, lmax)
+    O.kv_append_rope(kc, vc, kn, vn, tab, seq)
+    assert np.array_equal(dkc.download(np.uint16, kc.shape), kc)
+    assert np.array_equal(dvc.download(np.uint16, vc.shape), vc)
+    assert np.array_equal(dseq.download(np.int32, (b,)), seq)  # the full sequence stays at l_max
+
+
+@pytest.mark.parametrize("b,hq,hkv,d,lmax,lens", [
+    (3, 6, 2, 64, 40, [0, 17, 39]),
+    (4, 28, 4, 128, 700, [1, 64, 65, 699]),
+    (2, 14, 2, 64, 384, [128, 383]),
+    (2, 16, 1, 128, 300, [299, 130]),
+    (1, 8, 8, 128, 129, [128]),
+])
+def test_gqa_decode_attn(llm, oracle, b, hq, hkv, d, lmax, lens):
+    O = oracle
+    q, kn, vn, kc, vc, seq = _attn_inputs(O, b, hq, hkv, d, lmax, lens)
+    scale = 1.0 / np.sqrt(d)
+    dq, dkc, dvc, dseq = (_dev(llm, x) for x in (q, kc, vc, seq))
+    do = llm.DeviceBuffer(b * hq * d * 2)
+    llm.gqaDecodeAttn(dq, dkc, dvc, dseq, do, b, hq, hkv, d, lmax, scale)
+    o = O.f16_to_f32(do.download(np.uint16, (b, hq, d)))
+    ref = O.f16_to_f32(O.gqa_decode_attn(q, kc, vc, seq, scale))
+    assert llm.kernelStatus() == 0
+    assert rel_l2(o, ref) < 1e-3
+    assert np.mean(o != ref) < 0.02  # fp16 outputs: only last-place differences
+
+
+@pytest.mark.parametrize("b,hq,hkv,d,lmax,lens", [
+    (3, 6, 2, 64, 40, [0, 17, 39]),
+    (4, 28, 4, 128, 700, [0, 63, 64, 698]),
+    (3, 14, 2, 64, 200, [127, 128, 199]),
+    (2, 28, 4, 128, 130, [129, 130]),   # second sequence is already full
+])
+def test_gqa_decode_attn_fused_kv_bit_exact(llm, oracle, b, hq, hkv, d, lmax, lens):
+    O = oracle
+    q, kn, vn, kc, vc, seq = _attn_inputs(O, b, hq, hkv, d, lmax, lens, seed=2)
+    tab = O.rope_table(lmax, d, 1e6)
+    scale = 1.0 / np.sqrt(d)
+    dq, dkn, dvn, dkc, dvc, dtab, dseq = (_dev(llm, x) for x in (q, kn, vn, kc, vc, tab, seq))
+    do = llm.DeviceBuffer(b * hq * d * 2)
+    llm.gqaDecodeAttnFused(dq, dkn, dvn, dkc, dvc, dtab, dseq, do, b, hq, hkv, d, lmax, scale)
+    o = O.f16_to_f32(do.download(np.uint16, (b, hq, d)))
+    ref = O.f16_to_f32(O.gqa_decode_attn_fused(q, kn, vn, kc, vc, tab, seq, scale))
+    assert llm.kernelStatus() == 0
+    assert np.array_equal(dkc.download(np.uint16, kc.shape), kc)   # KV cache contents and indexing: bit exact
+    assert np.array_equal(dvc.download(np.uint16, vc.shape), vc)
+    assert np.array_equal(dseq.download(np.int32, (b,)), seq)
+    assert rel_l2(o, ref) < 1e-3
+
+
+def test_gqa_golden(llm, oracle, golden):
+    O = oracle
+    g = golden
+    b, hq, d = g["att_q"].shape
+    hkv, lmax = g["att_kc"].shape[1], g["att_kc"].shape[2]
+    scale = float(g["att_scale"][0])
+    dq, dkn, dvn, dkc, dvc, dtab, dseq = (_dev(llm, g[k]) for k in
+                                          ("att_q", "att_kn", "att_vn", "att_kc", "att_vc", "rope_tab", "att_seq"))
+    do = llm.DeviceBuffer(b * hq * d * 2)
+    llm.gqaDecodeAttn(dq, dkc, dvc, dseq, do, b, hq, hkv, d, lmax, scale)
+    assert rel_l2(O.f16_to_f32(do.download(np.uint16, (b, hq, d))), g["att_o_plain"]) < 1e-3
+    llm.gqaDecodeAttnFused(dq, dkn, dvn, dkc, dvc, dtab, dseq, do, b, hq, hkv, d, lmax, scale)
+    assert np.array_equal(dkc.download(np.uint16, g["att_kc"].shape), g["att_kc_after"])
+    assert np.array_equal(dvc.download(np.uint16, g["att_vc"].shape), g["att_vc_after"])
+    assert rel_l2(O.f16_to_f32(do.download(np.uint16, (b, hq, d))), g["att_o_fused"]) < 1e-3
+
+
+def test_rmsnorm_and_swiglu(llm, oracle, golden):
+    O = oracle
+    x, g = golden["norm_x"], golden["norm_g"]
+    dx, dg, dy = _dev(llm, x), _dev(llm, g), llm.DeviceBuffer(x.nbytes)
+    llm.rmsNorm(dx, dg, dy, x.shape[0], x.shape[1], 1e-6)
+    assert rel_l2(dy.download(np.float32, x.shape), O.rmsnorm(x, g, 1e-6)) < 1e-6
+    a, b = golden["swi_g"], golden["swi_u"]
+    da, db, dc = _dev(llm, a), _dev(llm, b), llm.DeviceBuffer(a.nbytes)
+    llm.swiGlu(da, db, dc, a.size)
+    assert rel_l2(dc.download(np.float32, a.shape), O.swiglu(a, b)) < 1e-6
+
+
+def test_out_of_bounds_buffers_are_refused(llm):
+    small = llm.DeviceBuffer(64)
+    with pytest.raises(llm.LogosError) as e:
+        llm.q8Gemv(small, small, small, small, 64, 64)
+    assert e.value.status == 4
+    small.free()
+    with pytest.raises(llm.LogosError) as e:
+        llm.q8Gemv(small, small, small, small, 1, 32)
+    assert e.value.status in (3, 6)
