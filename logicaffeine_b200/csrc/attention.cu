@@ -391,8 +391,8 @@ gqa_decode_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 // One CTA per (sequence, query head): fold the units in ascending order.
 template <int D>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                  const int32_t* __restrict__ seq_len, void* __restrict__ o, int o_dtype, int h_q,
-                                  int l_max, int unit_len, int max_splits, int fused) {
+                                  const int32_t* __restrict__ seq_len, void* __restrict__ o, int o_dtype, ActOut o_act,
+                                  int h_q, int l_max, int unit_len, int max_splits, int fused) {
   const int hq = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   int len_eff = seq_len[b] + (fused ? 1 : 0);
   if (len_eff > l_max) len_eff = l_max;
@@ -409,7 +409,8 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
   }
   float v = (ns > 0) ? __fdiv_rn(acc, L) : 0.f;
   int64_t oi = ((int64_t)b * h_q + hq) * D + d;
-  if (o_dtype == LOGOS_F16) reinterpret_cast<__half*>(o)[oi] = __float2half_rn(v);
+  if (o_dtype == LOGOS_ACT_PLANES) act_store(o_act, oi, v);
+  else if (o_dtype == LOGOS_F16) reinterpret_cast<__half*>(o)[oi] = __float2half_rn(v);
   else if (o_dtype == LOGOS_BF16) reinterpret_cast<__nv_bfloat16*>(o)[oi] = __float2bfloat16_rn(v);
   else reinterpret_cast<float*>(o)[oi] = v;
 }
@@ -488,8 +489,8 @@ logos_status_t launch_attn_t(const AttnArgs& a, cudaStream_t st) {
   gqa_decode_attn_kernel<D><<<grid, ATT_THREADS, smem, st>>>(mk, mv, p);
   LOGOS_TRY(check_launch("gqa_decode_attn_kernel"));
   dim3 mgrid((unsigned)a.h_q, (unsigned)a.b);
-  attn_merge_kernel<D><<<mgrid, D, 0, st>>>(p.part_o, p.part_ml, a.seq_len, a.o, a.o_dtype, (int)a.h_q, (int)a.l_max,
-                                            (int)ul, max_splits, p.fused);
+  attn_merge_kernel<D><<<mgrid, D, 0, st>>>(p.part_o, p.part_ml, a.seq_len, a.o, a.o_dtype, a.o_act, (int)a.h_q,
+                                            (int)a.l_max, (int)ul, max_splits, p.fused);
   LOGOS_TRY(check_launch("attn_merge_kernel"));
   if (a.bump_seq_len) {
     bump_seq_len_kernel<<<(unsigned)((a.b + 127) / 128), 128, 0, st>>>(a.seq_len, (int)a.b, (int)a.l_max);

@@ -31,12 +31,6 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return t;
 }
 
-__device__ __forceinline__ void store_act(void* dst, int dtype, int64_t i, float v) {
-  if (dtype == LOGOS_F16) reinterpret_cast<__half*>(dst)[i] = __float2half_rn(v);
-  else if (dtype == LOGOS_BF16) reinterpret_cast<__nv_bfloat16*>(dst)[i] = __float2bfloat16_rn(v);
-  else reinterpret_cast<float*>(dst)[i] = v;
-}
-
 __global__ void rmsnorm_f32_kernel(const float* __restrict__ x, const float* __restrict__ g, float* __restrict__ y,
                                    int64_t h, float eps) {
   __shared__ float red[32];
@@ -71,8 +65,8 @@ __global__ void embed_kernel(const int32_t* __restrict__ tokens, const int8_t* _
 }
 
 __global__ void residual_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int parts,
-                                        int64_t part_stride, const float* __restrict__ g, void* __restrict__ xn,
-                                        int xn_dtype, int64_t hidden, float eps) {
+                                        int64_t part_stride, const float* __restrict__ g, ActOut xn,
+                                        int64_t hidden, float eps) {
   __shared__ float red[32];
   extern __shared__ float row_cache[];  // hidden floats
   const int64_t row = blockIdx.x;
@@ -88,7 +82,12 @@ __global__ void residual_rmsnorm_kernel(float* __restrict__ h, const float* __re
   ss = block_sum(ss, red);
   float inv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hidden), eps)));
   for (int64_t i = threadIdx.x; i < hidden; i += blockDim.x)
-    store_act(xn, xn_dtype, row * hidden + i, __fmul_rn(__fmul_rn(row_cache[i], inv), g[i]));
+    act_store(xn, row * hidden + i, __fmul_rn(__fmul_rn(row_cache[i], inv), g[i]));
+}
+
+__global__ void bf16_to_f16_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ y, int64_t count) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) y[i] = __float2half_rn(act_clamp(__bfloat162float(x[i])));
 }
 
 __global__ void argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ tokens,
@@ -157,14 +156,20 @@ logos_status_t launch_embed(const int32_t* tokens, const int8_t* q, const float*
   return check_launch("embed_kernel");
 }
 
+logos_status_t launch_bf16_to_f16(const __nv_bfloat16* x, __half* y, int64_t count, cudaStream_t st) {
+  if (count == 0) return LOGOS_OK;
+  bf16_to_f16_kernel<<<(unsigned)((count + 255) / 256), 256, 0, st>>>(x, y, count);
+  return check_launch("bf16_to_f16_kernel");
+}
+
 logos_status_t launch_residual_rmsnorm(float* h, const float* delta, int parts, int64_t part_stride,
-                                       const float* g, void* xn, int xn_dtype, int64_t rows, int64_t hidden,
-                                       float eps, cudaStream_t st) {
+                                       const float* g, ActOut xn, int64_t rows, int64_t hidden, float eps,
+                                       cudaStream_t st) {
   if (rows == 0) return LOGOS_OK;
   size_t smem = sizeof(float) * (size_t)hidden;
   if (smem > 48 * 1024)
     LOGOS_CUDA_TRY(cudaFuncSetAttribute(residual_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  residual_rmsnorm_kernel<<<(unsigned)rows, 256, smem, st>>>(h, delta, parts, part_stride, g, xn, xn_dtype, hidden, eps);
+  residual_rmsnorm_kernel<<<(unsigned)rows, 256, smem, st>>>(h, delta, parts, part_stride, g, xn, hidden, eps);
   return check_launch("residual_rmsnorm_kernel");
 }
 

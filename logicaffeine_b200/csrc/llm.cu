@@ -11,8 +11,9 @@
 // then final norm, lm_head GEMM (f32 logits), argmax.
 //
 // Memory: weights are int8 [N][K] + f32 [N][K/32]; the residual stream is f32;
-// GEMM inputs keep f32 precision by default (cfg.act_dtype = LOGOS_F32) or are
-// rounded to fp16 / bf16 when the configuration asks; the KV cache is fp16
+// GEMM inputs are fp16 planes: a high and a residual plane that together keep
+// f32-class precision (cfg.act_dtype = LOGOS_F32, the default), or one plane of
+// values rounded to fp16 / bf16 when the configuration asks; the KV cache is fp16
 // [B][Hkv][Lmax][D] per layer.  Tensor parallelism shards q/k/v/gate/up by
 // output rows (heads, FFN columns) and o_proj/down_proj by input columns, so
 // the only exchanges are the two sum all-reduces per layer.
@@ -47,10 +48,10 @@ struct Model {
   float* ones = nullptr;
   float* rope = nullptr;
   float* h = nullptr;        // [B][H] residual stream
-  void*  xn = nullptr;       // [B][H] 16-bit
+  ActOut xn;                 // [B][H] fp16 plane(s)
   float* qkv = nullptr;      // [B][nqkv]
-  void*  att = nullptr;      // [B][nq] 16-bit
-  void*  ffn = nullptr;      // [B][f_local] 16-bit
+  ActOut att;                // [B][nq]
+  ActOut ffn;                // [B][f_local]
   float* partials = nullptr; // [max_splits][B][H]
   int    max_splits = 1;
   float* logits = nullptr;   // [B][V]
@@ -196,10 +197,16 @@ logos_status_t build(Model* m, const void* nccl_id) {
     m->max_splits = s1 > s2 ? s1 : s2;
   }
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->h), B * H * 4));
-  LOGOS_TRY(dmalloc(m, &m->xn, B * H * 4));
+  auto planes = [&](ActOut* a, int64_t elems) -> logos_status_t {
+    a->mode = c.act_dtype;
+    LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&a->hi), elems * 2));
+    if (c.act_dtype == LOGOS_F32) LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&a->lo), elems * 2));
+    return LOGOS_OK;
+  };
+  LOGOS_TRY(planes(&m->xn, B * H));
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->qkv), B * m->nqkv * 4));
-  LOGOS_TRY(dmalloc(m, &m->att, B * m->nq * 4));
-  LOGOS_TRY(dmalloc(m, &m->ffn, B * m->f_local * 4));
+  LOGOS_TRY(planes(&m->att, B * m->nq));
+  LOGOS_TRY(planes(&m->ffn, B * m->f_local));
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->partials), (int64_t)m->max_splits * B * H * 4));
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->logits), B * c.vocab * 4));
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->tokens), B * 4));
@@ -225,10 +232,10 @@ __global__ void bump_len_kernel(int32_t* seq_len, int b, int l_max) {
 }
 
 // GEMM producing f32 partials [splits][B][N] in m->partials; returns the split count.
-logos_status_t gemm_partials(Model* m, const void* a, const Q8Mat& w, int* splits_out) {
+logos_status_t gemm_partials(Model* m, const ActOut& a, const Q8Mat& w, int* splits_out) {
   const int64_t B = m->cfg.batch;
   GemmArgs g;
-  g.a = a; g.a_dtype = m->cfg.act_dtype; g.lda = w.k;
+  g.a = a.hi; g.a_lo = a.lo; g.a_dtype = LOGOS_F16; g.lda = w.k;
   g.q = w.q; g.s = w.s;
   g.m = B; g.n = w.n; g.k = w.k;
   g.device = m->device;
@@ -277,13 +284,13 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, int32_t* hi
     Layer& L = m->layers[(size_t)l];
     {
       ProfScope ps(m, PROF_ELEMWISE);
-      LOGOS_TRY(launch_residual_rmsnorm(m->h, m->partials, parts, B * H, m->ones, m->xn, c.act_dtype, B, H, c.rms_eps, st));
+      LOGOS_TRY(launch_residual_rmsnorm(m->h, m->partials, parts, B * H, m->ones, m->xn, B, H, c.rms_eps, st));
     }
     m->launch_counter += 1;
     {
       ProfScope ps(m, PROF_GEMM);
       GemmArgs g;
-      g.a = m->xn; g.a_dtype = c.act_dtype; g.lda = H;
+      g.a = m->xn.hi; g.a_lo = m->xn.lo; g.a_dtype = LOGOS_F16; g.lda = H;
       g.q = L.wqkv.q; g.s = L.wqkv.s;
       g.c = m->qkv; g.c_dtype = LOGOS_F32; g.ldc = m->nqkv;
       g.m = B; g.n = m->nqkv; g.k = H;
@@ -298,7 +305,7 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, int32_t* hi
       a.k_new_f32 = m->qkv + m->nq; a.v_new_f32 = m->qkv + m->nq + m->nkv; a.kv_ld = m->nqkv;
       a.k_cache = L.kc; a.v_cache = L.vc; a.rope = m->rope; a.seq_len = m->seq_len;
       a.bump_seq_len = 0;
-      a.o = m->att; a.o_dtype = c.act_dtype;
+      a.o_dtype = LOGOS_ACT_PLANES; a.o_act = m->att;
       a.b = B; a.h_q = m->hq_local; a.h_kv = m->hkv_local; a.d = D; a.l_max = c.l_max;
       a.scale = 1.0f / sqrtf((float)D);
       a.device = m->device;
@@ -308,15 +315,15 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, int32_t* hi
     LOGOS_TRY(gemm_partials(m, m->att, L.wo, &parts));
     {
       ProfScope ps(m, PROF_ELEMWISE);
-      LOGOS_TRY(launch_residual_rmsnorm(m->h, m->partials, parts, B * H, m->ones, m->xn, c.act_dtype, B, H, c.rms_eps, st));
+      LOGOS_TRY(launch_residual_rmsnorm(m->h, m->partials, parts, B * H, m->ones, m->xn, B, H, c.rms_eps, st));
     }
     m->launch_counter += 1;
     {
       ProfScope ps(m, PROF_GEMM);
       GemmArgs g;
-      g.a = m->xn; g.a_dtype = c.act_dtype; g.lda = H;
+      g.a = m->xn.hi; g.a_lo = m->xn.lo; g.a_dtype = LOGOS_F16; g.lda = H;
       g.q = L.wgu.q; g.s = L.wgu.s;
-      g.c = m->ffn; g.c_dtype = c.act_dtype; g.ldc = m->f_local;
+      g.c_dtype = LOGOS_ACT_PLANES; g.c_act = m->ffn; g.ldc = m->f_local;
       g.m = B; g.n = 2 * m->f_local; g.k = H;
       g.epilogue = EPI_SWIGLU;
       g.device = m->device;
@@ -328,10 +335,10 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, int32_t* hi
   if (sample) {
     {
       ProfScope ps(m, PROF_ELEMWISE);
-      LOGOS_TRY(launch_residual_rmsnorm(m->h, m->partials, parts, B * H, m->ones, m->xn, c.act_dtype, B, H, c.rms_eps, st));
+      LOGOS_TRY(launch_residual_rmsnorm(m->h, m->partials, parts, B * H, m->ones, m->xn, B, H, c.rms_eps, st));
     }
     GemmArgs g;
-    g.a = m->xn; g.a_dtype = c.act_dtype; g.lda = H;
+    g.a = m->xn.hi; g.a_lo = m->xn.lo; g.a_dtype = LOGOS_F16; g.lda = H;
     g.q = m->head.q; g.s = m->head.s;
     g.c = m->logits; g.c_dtype = LOGOS_F32; g.ldc = c.vocab;
     g.m = B; g.n = c.vocab; g.k = H;

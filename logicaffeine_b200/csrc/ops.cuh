@@ -1,6 +1,7 @@
 // Internal launchers: raw device pointers in, kernels enqueued on a stream.
 // The extern "C" wrappers and the decode step both go through these.
 #pragma once
+#include "act.cuh"
 #include "common.cuh"
 
 namespace logos {
@@ -28,13 +29,15 @@ enum GemmEpilogue : int {
 };
 
 struct GemmArgs {
-  const void*   a = nullptr;   // activations [M][K], 16-bit, row stride lda elements
-  int           a_dtype = LOGOS_BF16;  // LOGOS_BF16 or LOGOS_F16
+  const void*   a = nullptr;   // activations [M][K], row stride lda elements
+  const __half* a_lo = nullptr;  // second fp16 plane (see act.cuh); only with a_dtype LOGOS_F16
+  int           a_dtype = LOGOS_BF16;  // LOGOS_F16 plane(s), LOGOS_BF16 or LOGOS_F32
   int64_t       lda = 0;
   const int8_t* q = nullptr;   // [N][K]
   const float*  s = nullptr;   // [N][K/32]
   void*         c = nullptr;   // [M][N] (or [M][N/2] for EPI_SWIGLU), row stride ldc elements
-  int           c_dtype = LOGOS_BF16;  // LOGOS_BF16, LOGOS_F16 or LOGOS_F32
+  int           c_dtype = LOGOS_BF16;  // LOGOS_BF16, LOGOS_F16, LOGOS_F32 or LOGOS_ACT_PLANES
+  ActOut        c_act;         // destination planes when c_dtype == LOGOS_ACT_PLANES
   int64_t       ldc = 0;
   const void*   aux = nullptr; // EPI_RESIDUAL: same type and stride as c
   int64_t       m = 0, n = 0, k = 0;
@@ -72,7 +75,8 @@ struct AttnArgs {
   int32_t*      seq_len = nullptr;   // [B]
   int           bump_seq_len = 0;    // seq_len[b] += 1 after the call
   void*         o = nullptr;         // [B][Hq][D]
-  int           o_dtype = LOGOS_F16; // LOGOS_F16 / LOGOS_BF16 / LOGOS_F32
+  int           o_dtype = LOGOS_F16; // LOGOS_F16 / LOGOS_BF16 / LOGOS_F32 / LOGOS_ACT_PLANES
+  ActOut        o_act;               // destination planes when o_dtype == LOGOS_ACT_PLANES
   int64_t       b = 0, h_q = 0, h_kv = 0, d = 0, l_max = 0;
   float         scale = 1.f;
   int           device = 0;
@@ -94,8 +98,10 @@ logos_status_t launch_embed(const int32_t* tokens, const int8_t* q, const float*
 // part_stride floats, added in ascending order; parts may be 0), then
 // xn = act16( h * rsqrt(mean(h^2)+eps) * g ).
 logos_status_t launch_residual_rmsnorm(float* h, const float* delta, int parts, int64_t part_stride,
-                                       const float* g, void* xn, int xn_dtype, int64_t rows, int64_t hidden,
-                                       float eps, cudaStream_t st);
+                                       const float* g, ActOut xn, int64_t rows, int64_t hidden, float eps,
+                                       cudaStream_t st);
+// bf16 [count] -> fp16 plane (exact inside fp16's normal range, saturating outside)
+logos_status_t launch_bf16_to_f16(const __nv_bfloat16* x, __half* y, int64_t count, cudaStream_t st);
 // tokens[row] = argmax(logits[row]) with the lowest index winning ties
 logos_status_t launch_argmax(const float* logits, int32_t* tokens, int32_t* history_or_null, int64_t rows,
                              int64_t vocab, cudaStream_t st);

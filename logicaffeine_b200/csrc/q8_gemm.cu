@@ -13,13 +13,14 @@ namespace logos {
 
 namespace {
 
-__device__ __forceinline__ float load_act(const void* a, int dtype, int64_t i) {
-  if (dtype == LOGOS_F16) return __half2float(reinterpret_cast<const __half*>(a)[i]);
+__device__ __forceinline__ float load_act(const void* a, int dtype, int64_t i, const __half* lo = nullptr) {
+  if (dtype == LOGOS_F16) return act_load(reinterpret_cast<const __half*>(a), lo, i);
   if (dtype == LOGOS_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a)[i]);
   return reinterpret_cast<const float*>(a)[i];
 }
-__device__ __forceinline__ void store_out(void* c, int dtype, int64_t i, float v) {
-  if (dtype == LOGOS_F16) reinterpret_cast<__half*>(c)[i] = __float2half_rn(v);
+__device__ __forceinline__ void store_out(void* c, int dtype, int64_t i, float v, const ActOut& planes) {
+  if (dtype == LOGOS_ACT_PLANES) act_store(planes, i, v);
+  else if (dtype == LOGOS_F16) reinterpret_cast<__half*>(c)[i] = __float2half_rn(v);
   else if (dtype == LOGOS_BF16) reinterpret_cast<__nv_bfloat16*>(c)[i] = __float2bfloat16_rn(v);
   else reinterpret_cast<float*>(c)[i] = v;
 }
@@ -30,8 +31,9 @@ constexpr int SIMT_TM = 32;  // tokens per CTA
 
 // 256 threads: lane = weight row inside the tile, warp w owns tokens 4w..4w+3.
 __global__ void __launch_bounds__(256)
-q8_gemm_simt_kernel(const void* __restrict__ a, int a_dtype, int64_t lda, const int8_t* __restrict__ q,
-                    const float* __restrict__ s, void* __restrict__ c, int c_dtype, int64_t ldc,
+q8_gemm_simt_kernel(const void* __restrict__ a, const __half* __restrict__ a_lo, int a_dtype, int64_t lda,
+                    const int8_t* __restrict__ q, const float* __restrict__ s, void* __restrict__ c, int c_dtype,
+                    ActOut c_act, int64_t ldc,
                     const void* __restrict__ aux, float* __restrict__ partials, int64_t m, int64_t n, int64_t k,
                     int epilogue, int splits) {
   __shared__ float as[SIMT_TM][33];
@@ -48,7 +50,7 @@ q8_gemm_simt_kernel(const void* __restrict__ a, int a_dtype, int64_t lda, const 
   for (int64_t kb = kb_begin; kb < kb_end; ++kb) {
     for (int i = threadIdx.x; i < SIMT_TM * 32; i += 256) {
       int r = i >> 5, cidx = i & 31;
-      as[r][cidx] = (m0 + r < m) ? load_act(a, a_dtype, (m0 + r) * lda + kb * 32 + cidx) : 0.f;
+      as[r][cidx] = (m0 + r < m) ? load_act(a, a_dtype, (m0 + r) * lda + kb * 32 + cidx, a_lo) : 0.f;
       qs[r][cidx] = (n0 + r < n) ? (float)q[(n0 + r) * k + kb * 32 + cidx] : 0.f;
     }
     __syncthreads();
@@ -74,17 +76,18 @@ q8_gemm_simt_kernel(const void* __restrict__ a, int a_dtype, int64_t lda, const 
     }
     if (epilogue == EPI_SWIGLU) {
       float other = __shfl_xor_sync(0xffffffffu, v, 1);
-      if (!(lane & 1) && mm < m && row + 1 < n) store_out(c, c_dtype, mm * ldc + (row >> 1), __fmul_rn(silu_f(v), other));
+      if (!(lane & 1) && mm < m && row + 1 < n) store_out(c, c_dtype, mm * ldc + (row >> 1), __fmul_rn(silu_f(v), other), c_act);
     } else if (mm < m && row < n) {
       if (epilogue == EPI_RESIDUAL) v = __fadd_rn(v, load_act(aux, c_dtype, mm * ldc + row));
-      store_out(c, c_dtype, mm * ldc + row, v);
+      store_out(c, c_dtype, mm * ldc + row, v, c_act);
     }
   }
 }
 
 // Sum split-K partials in ascending split order, then apply the epilogue.
 __global__ void splitk_reduce_kernel(const float* __restrict__ partials, int splits, void* __restrict__ c, int c_dtype,
-                                     int64_t ldc, const void* __restrict__ aux, int64_t m, int64_t n, int epilogue) {
+                                     ActOut c_act, int64_t ldc, const void* __restrict__ aux, int64_t m, int64_t n,
+                                     int epilogue) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (epilogue == EPI_SWIGLU) {
     int64_t half_n = n / 2;
@@ -95,7 +98,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partials, int spl
       g = __fadd_rn(g, partials[((int64_t)sp * m + mm) * n + 2 * j]);
       u = __fadd_rn(u, partials[((int64_t)sp * m + mm) * n + 2 * j + 1]);
     }
-    store_out(c, c_dtype, mm * ldc + j, __fmul_rn(silu_f(g), u));
+    store_out(c, c_dtype, mm * ldc + j, __fmul_rn(silu_f(g), u), c_act);
     return;
   }
   if (i >= m * n) return;
@@ -103,7 +106,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partials, int spl
   float v = 0.f;
   for (int sp = 0; sp < splits; ++sp) v = __fadd_rn(v, partials[((int64_t)sp * m + mm) * n + nn]);
   if (epilogue == EPI_RESIDUAL) v = __fadd_rn(v, load_act(aux, c_dtype, mm * ldc + nn));
-  store_out(c, c_dtype, mm * ldc + nn, v);
+  store_out(c, c_dtype, mm * ldc + nn, v, c_act);
 }
 
 }  // namespace
@@ -123,12 +126,13 @@ int gemm_pick_splits(int64_t m, int64_t n, int64_t k, int device) {
   return want < 1 ? 1 : (int)want;
 }
 
-logos_status_t launch_splitk_reduce(const float* partials, int splits, void* c, int c_dtype, int64_t ldc,
-                                    const void* aux, int64_t m, int64_t n, int epilogue, cudaStream_t st) {
+logos_status_t launch_splitk_reduce(const float* partials, int splits, void* c, int c_dtype, ActOut c_act,
+                                    int64_t ldc, const void* aux, int64_t m, int64_t n, int epilogue,
+                                    cudaStream_t st) {
   int64_t total = (epilogue == EPI_SWIGLU) ? m * (n / 2) : m * n;
   if (total == 0) return LOGOS_OK;
-  splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(partials, splits, c, c_dtype, ldc, aux, m, n,
-                                                                        epilogue);
+  splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(partials, splits, c, c_dtype, c_act, ldc, aux,
+                                                                        m, n, epilogue);
   return check_launch("splitk_reduce_kernel");
 }
 
@@ -141,8 +145,9 @@ logos_status_t launch_q8_gemm(const GemmArgs& g, cudaStream_t st) {
   if (!g.force_simt && gemm_tc_applicable(g)) return launch_q8_gemm_tc(g, st);
   dim3 grid((unsigned)((g.n + SIMT_TN - 1) / SIMT_TN), (unsigned)((g.m + SIMT_TM - 1) / SIMT_TM),
             (unsigned)(g.splits > 1 ? g.splits : 1));
-  q8_gemm_simt_kernel<<<grid, 256, 0, st>>>(g.a, g.a_dtype, g.lda, g.q, g.s, g.c, g.c_dtype, g.ldc, g.aux, g.partials,
-                                            g.m, g.n, g.k, g.epilogue, g.splits > 1 ? g.splits : 1);
+  q8_gemm_simt_kernel<<<grid, 256, 0, st>>>(g.a, g.a_lo, g.a_dtype, g.lda, g.q, g.s, g.c, g.c_dtype, g.c_act, g.ldc,
+                                            g.aux, g.partials, g.m, g.n, g.k, g.epilogue,
+                                            g.splits > 1 ? g.splits : 1);
   return check_launch("q8_gemm_simt_kernel");
 }
 
@@ -181,19 +186,31 @@ static logos_status_t gemm_abi(logos_handle_t a, logos_handle_t q, logos_handle_
   g.device = dev;
   g.force_simt = force_simt;
   cudaStream_t st = as_stream(stream);
-  int splits = force_simt ? 1 : gemm_pick_splits(m, n, k, dev);
-  if (splits > 1 && gemm_tc_applicable(g)) {
-    void* scratch = nullptr;
-    LOGOS_TRY(scratch_get(dev, 0, (int64_t)splits * m * n * (int64_t)sizeof(float), &scratch));
-    GemmArgs gp = g;
+  if (force_simt) return launch_q8_gemm(g, st);
+  // Tensor-core path: the kernel multiplies fp16 planes.  A bf16 value is exactly
+  // representable in fp16 inside fp16's normal range, so one plane is enough.
+  GemmArgs t = g;
+  t.a_dtype = LOGOS_F16;
+  t.a = reinterpret_cast<const void*>(uintptr_t(16));  // placeholder so applicability can be asked first
+  if (!gemm_tc_applicable(t)) return launch_q8_gemm(g, st);
+  int splits = gemm_pick_splits(m, n, k, dev);
+  void* scratch = nullptr;
+  int64_t plane_bytes = ((m * k * 2 + 255) / 256) * 256;
+  int64_t part_bytes = splits > 1 ? (int64_t)splits * m * n * (int64_t)sizeof(float) : 0;
+  LOGOS_TRY(scratch_get(dev, 0, plane_bytes + part_bytes, &scratch));
+  __half* plane = reinterpret_cast<__half*>(scratch);
+  LOGOS_TRY(launch_bf16_to_f16(ap, plane, m * k, st));
+  t.a = plane;
+  if (splits > 1) {
+    GemmArgs gp = t;
     gp.splits = splits;
-    gp.partials = reinterpret_cast<float*>(scratch);
+    gp.partials = reinterpret_cast<float*>(static_cast<char*>(scratch) + plane_bytes);
     gp.epilogue = EPI_NONE;
     gp.c = nullptr;
     LOGOS_TRY(launch_q8_gemm(gp, st));
-    return launch_splitk_reduce(gp.partials, splits, cp, LOGOS_BF16, n_out, xp, m, n, epilogue, st);
+    return launch_splitk_reduce(gp.partials, splits, cp, LOGOS_BF16, ActOut(), n_out, xp, m, n, epilogue, st);
   }
-  return launch_q8_gemm(g, st);
+  return launch_q8_gemm(t, st);
 }
 
 extern "C" {

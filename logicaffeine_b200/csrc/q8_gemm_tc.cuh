@@ -4,6 +4,7 @@
 
 namespace logos {
 logos_status_t launch_q8_gemm_tc(const GemmArgs& g, cudaStream_t st);
-logos_status_t launch_splitk_reduce(const float* partials, int splits, void* c, int c_dtype, int64_t ldc,
-                                    const void* aux, int64_t m, int64_t n, int epilogue, cudaStream_t st);
+logos_status_t launch_splitk_reduce(const float* partials, int splits, void* c, int c_dtype, ActOut c_act,
+                                    int64_t ldc, const void* aux, int64_t m, int64_t n, int epilogue,
+                                    cudaStream_t st);
 }  // namespace logos
