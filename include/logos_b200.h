@@ -138,6 +138,13 @@ LOGOS_API logos_status_t logos_q8_gemm(logos_handle_t a /*bf16 [M][K]*/, logos_h
                              logos_handle_t c /*bf16*/, int64_t m, int64_t n, int64_t k,
                              int32_t epilogue, logos_handle_t aux_or_null, void* stream_or_null);
 
+/* C[m,n] = sum_kb s[n,kb] * sum_k A[m,k] * q[n,k] with f32 A [M][K] and f32 C [M][N]:
+ * the form the decode step uses between its kernels.  The activations are split into
+ * two fp16 planes so the tensor-core product keeps f32-class accuracy. */
+LOGOS_API logos_status_t logos_q8_gemm_f32(logos_handle_t a /*f32 [M][K]*/, logos_handle_t q, logos_handle_t s,
+                                 logos_handle_t c /*f32 [M][N]*/, int64_t m, int64_t n, int64_t k,
+                                 void* stream_or_null);
+
 /* Same contract as logos_q8_gemm, always on the plain SIMT kernel (no tensor
  * cores, no split-K): the on-device cross-check the tests hold the tcgen05
  * kernel against, and the path for shapes the tcgen05 kernel does not take. */

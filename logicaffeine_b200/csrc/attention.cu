@@ -91,6 +91,12 @@ gqa_decode_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   if (len_eff > p.l_max) len_eff = p.l_max;
   const int unit_start = split * p.unit_len;
   if (unit_start >= len_eff) return;
+  // a kernel that gave up earlier left a code behind: do not start new work on top of it
+  // (one thread reads, everyone takes the same decision)
+  __shared__ int prior_status;
+  if (tid == 0) prior_status = *reinterpret_cast<volatile int*>(p.status);
+  __syncthreads();
+  if (prior_status != 0) return;
   const int unit_end = min(unit_start + p.unit_len, len_eff);
   const int ntiles = (unit_end - unit_start + ATT_TILE - 1) / ATT_TILE;
   const int64_t row_base = ((int64_t)b * p.h_kv + kvh) * p.l_max;

@@ -90,6 +90,11 @@ __global__ void bf16_to_f16_kernel(const __nv_bfloat16* __restrict__ x, __half* 
   if (i < count) y[i] = __float2half_rn(act_clamp(__bfloat162float(x[i])));
 }
 
+__global__ void act_split_kernel(const float* __restrict__ x, ActOut o, int64_t count) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) act_store(o, i, x[i]);
+}
+
 __global__ void argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ tokens,
                               int32_t* __restrict__ history, int64_t vocab) {
   __shared__ float bv[32];
@@ -160,6 +165,12 @@ logos_status_t launch_bf16_to_f16(const __nv_bfloat16* x, __half* y, int64_t cou
   if (count == 0) return LOGOS_OK;
   bf16_to_f16_kernel<<<(unsigned)((count + 255) / 256), 256, 0, st>>>(x, y, count);
   return check_launch("bf16_to_f16_kernel");
+}
+
+logos_status_t launch_act_split(const float* x, ActOut o, int64_t count, cudaStream_t st) {
+  if (count == 0) return LOGOS_OK;
+  act_split_kernel<<<(unsigned)((count + 255) / 256), 256, 0, st>>>(x, o, count);
+  return check_launch("act_split_kernel");
 }
 
 logos_status_t launch_residual_rmsnorm(float* h, const float* delta, int parts, int64_t part_stride,

@@ -47,12 +47,14 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
 }
-// Bounded wait: each try_wait already sleeps up to a hardware time limit, so
-// the cap below is seconds, not microseconds.  Returns false when it gave up.
-constexpr uint32_t kWaitLimit = 1u << 22;
+// Bounded wait: polls try_wait until the phase completes or about two seconds
+// of SM clock have passed.  Returns false when it gave up; the caller records a
+// status code and leaves.
+constexpr long long kWaitCycles = 4000000000ll;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t a = smem_u32(bar);
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+  const uint32_t a = smem_u32(bar);
+  const long long start = clock64();
+  for (;;) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -62,8 +64,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         : "r"(a), "r"(parity)
         : "memory");
     if (ok) return true;
+    if (clock64() - start > kWaitCycles) return false;
   }
-  return false;
 }
 
 // ------------------------------------------------------------ TMA (tile mode, no multicast)

@@ -215,6 +215,56 @@ static logos_status_t gemm_abi(logos_handle_t a, logos_handle_t q, logos_handle_
 
 extern "C" {
 
+// f32 activations, f32 output: the form the decode step uses internally (the
+// activations are split into two fp16 planes so the tensor-core product keeps
+// f32-class accuracy).
+logos_status_t logos_q8_gemm_f32(logos_handle_t a, logos_handle_t q, logos_handle_t s, logos_handle_t c, int64_t m,
+                                 int64_t n, int64_t k, void* stream_or_null) {
+  return guarded([&]() -> logos_status_t {
+    if (m < 0 || n < 0 || k < 0) return fail(LOGOS_OUT_OF_BOUNDS, "logos_q8_gemm_f32: negative extent");
+    if (k % 32) return fail(LOGOS_OUT_OF_BOUNDS, "logos_q8_gemm_f32: K=%lld is not a multiple of the block size 32", (long long)k);
+    float *ap, *sp, *cp;
+    int8_t* qp;
+    int32_t dev = 0;
+    LOGOS_TRY(buf_ptr<float>(a, m * k, "a", &ap, &dev));
+    LOGOS_TRY(buf_ptr<int8_t>(q, n * k, "q", &qp));
+    LOGOS_TRY(buf_ptr<float>(s, n * (k / 32), "s", &sp));
+    LOGOS_TRY(buf_ptr<float>(c, m * n, "c", &cp));
+    LOGOS_CUDA_TRY(cudaSetDevice(dev));
+    cudaStream_t st = as_stream(stream_or_null);
+    GemmArgs g;
+    g.a = ap; g.a_dtype = LOGOS_F32; g.lda = k;
+    g.q = qp; g.s = sp;
+    g.c = cp; g.c_dtype = LOGOS_F32; g.ldc = n;
+    g.m = m; g.n = n; g.k = k;
+    g.device = dev;
+    GemmArgs t = g;
+    t.a_dtype = LOGOS_F16;
+    t.a = reinterpret_cast<const void*>(uintptr_t(16));
+    if (m == 0 || n == 0 || !gemm_tc_applicable(t)) return launch_q8_gemm(g, st);
+    int splits = gemm_pick_splits(m, n, k, dev);
+    int64_t plane_bytes = ((m * k * 2 + 255) / 256) * 256;
+    int64_t part_bytes = splits > 1 ? (int64_t)splits * m * n * (int64_t)sizeof(float) : 0;
+    void* scratch = nullptr;
+    LOGOS_TRY(scratch_get(dev, 0, 2 * plane_bytes + part_bytes, &scratch));
+    ActOut planes;
+    planes.hi = reinterpret_cast<__half*>(scratch);
+    planes.lo = reinterpret_cast<__half*>(static_cast<char*>(scratch) + plane_bytes);
+    planes.mode = LOGOS_F32;
+    LOGOS_TRY(launch_act_split(ap, planes, m * k, st));
+    t.a = planes.hi;
+    t.a_lo = planes.lo;
+    if (splits > 1) {
+      t.splits = splits;
+      t.partials = reinterpret_cast<float*>(static_cast<char*>(scratch) + 2 * plane_bytes);
+      t.c = nullptr;
+      LOGOS_TRY(launch_q8_gemm(t, st));
+      return launch_splitk_reduce(t.partials, splits, cp, LOGOS_F32, ActOut(), n, nullptr, m, n, EPI_NONE, st);
+    }
+    return launch_q8_gemm(t, st);
+  });
+}
+
 logos_status_t logos_q8_gemm(logos_handle_t a, logos_handle_t q, logos_handle_t s, logos_handle_t c, int64_t m,
                              int64_t n, int64_t k, int32_t epilogue, logos_handle_t aux_or_null,
                              void* stream_or_null) {

@@ -1,6 +1,436 @@
-// placeholder until the tcgen05 kernel lands
+// Q8 GEMM on the 5th-generation tensor cores (tcgen05) for small token counts.
+//
+//   acc[n, m] = sum_kb s[n,kb] * ( sum_{k in kb} q[n,k] * a[m,k] )
+//
+// The problem is laid out "weights on the M side": one CTA owns 128 weight
+// rows (MMA M = 128, one TMEM lane per row) and MT tokens (MMA N), so the f32
+// scale of a (row, K-block) pair is one scalar per thread when the block's
+// partial sum is drained from tensor memory.
+//
+// Data flow per 128-column K stage (4 Q8 blocks):
+//   TMA  int8 weights [128 rows][128 B], 128-byte swizzle  -> smem ring   (warp 0)
+//   TMA  fp16 activation planes [MT][64] x 2 halves x limbs -> smem ring   (warp 1)
+//   4 converter warps: smem int8 -> fp16 (exact: 0x6400|b trick) -> tcgen05.st
+//        into a TMEM operand ring; the weights never go back to shared memory
+//   1 MMA thread: per Q8 block two tcgen05.mma kind::f16 (K=16 each), A from
+//        TMEM, B = activations from smem, D = a fresh TMEM accumulator slot
+//   4 drain warps: tcgen05.ld the block's partial sums, acc += s * partial in
+//        f32 registers (the high and residual activation planes sit side by
+//        side on the MMA N axis and are recombined here), then the epilogue.
+// All hand-offs are mbarriers; every wait is bounded and reports through the
+// device status word instead of spinning for ever.
+//
+// HBM roofline: 1.125 bytes per weight (int8 + f32/32); activations and
+// outputs are small next to that at decode batch sizes.
 #include "q8_gemm_tc.cuh"
+
+#include "ptx.cuh"
+
+#include <mutex>
+#include <unordered_map>
+
 namespace logos {
-bool gemm_tc_applicable(const GemmArgs&) { return false; }
-logos_status_t launch_q8_gemm_tc(const GemmArgs&, cudaStream_t) { return fail(LOGOS_ERROR, "tc gemm not built"); }
+
+namespace {
+
+using namespace ptx;
+
+constexpr int TC_ROWS = 128;     // weight rows per CTA (MMA M)
+constexpr int TC_KSTAGE = 128;   // K per stage
+constexpr int RAW_STAGES = 4;
+constexpr int ACT_STAGES = 3;
+constexpr int TA_STAGES = 2;
+constexpr int TA_COLS = 64;      // TMEM columns per converted stage: 128 fp16 per row
+constexpr int ACC_COL0 = TA_STAGES * TA_COLS;
+constexpr int TC_THREADS = 384;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr int RAW_BYTES = TC_ROWS * TC_KSTAGE;  // 16 KB
+
+template <int MT, int LIMBS>
+struct TcCfg {
+  static constexpr int NB = MT * LIMBS;                 // MMA N
+  static constexpr int ACC_SLOTS = (NB >= 128) ? 3 : 4; // TMEM accumulator ring
+  static constexpr int ACT_ATOM_BYTES = NB * 128;       // one 64-column half: NB rows x 128 B
+  static constexpr int ACT_BYTES = 2 * ACT_ATOM_BYTES;
+  static constexpr size_t SMEM_NEED = 1024 + (size_t)RAW_STAGES * RAW_BYTES + (size_t)ACT_STAGES * ACT_BYTES + 512;
+  // the CTA allocates all of tensor memory, so ask for enough shared memory that only one CTA fits an SM
+  static constexpr size_t SMEM = SMEM_NEED > 120 * 1024 ? SMEM_NEED : 120 * 1024;
+  static_assert(ACC_COL0 + ACC_SLOTS * NB <= (int)TMEM_COLS, "TMEM budget");
+  static_assert(NB % 16 == 0 && NB <= 256, "MMA N");
+};
+
+struct TcParams {
+  const float* s;
+  int64_t n, k, m;
+  void* c;
+  int c_dtype;
+  ActOut c_act;
+  int64_t ldc;
+  const void* aux;
+  int epilogue;
+  float* partials;
+  int splits;
+  int stages_total;
+  int* status;
+};
+
+__device__ __forceinline__ float silu_f(float g) { return __fdiv_rn(g, 1.0f + expf(-g)); }
+
+__device__ __forceinline__ void store_c(const TcParams& p, int64_t i, float v) {
+  if (p.c_dtype == LOGOS_ACT_PLANES) act_store(p.c_act, i, v);
+  else if (p.c_dtype == LOGOS_F16) reinterpret_cast<__half*>(p.c)[i] = __float2half_rn(v);
+  else if (p.c_dtype == LOGOS_BF16) reinterpret_cast<__nv_bfloat16*>(p.c)[i] = __float2bfloat16_rn(v);
+  else reinterpret_cast<float*>(p.c)[i] = v;
 }
+__device__ __forceinline__ float load_aux(const TcParams& p, int64_t i) {
+  if (p.c_dtype == LOGOS_F16) return __half2float(reinterpret_cast<const __half*>(p.aux)[i]);
+  if (p.c_dtype == LOGOS_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.aux)[i]);
+  return reinterpret_cast<const float*>(p.aux)[i];
+}
+
+// two int8 (bytes sel_lo / sel_hi of w ^ 0x80808080) -> packed fp16 pair, exact
+__device__ __forceinline__ uint32_t cvt_pair(uint32_t w_xor80, uint32_t selector) {
+  uint32_t bits = __byte_perm(w_xor80, 0x64646464u, selector);   // 0x64bb = 1024 + (q + 128)
+  __half2 h = *reinterpret_cast<__half2*>(&bits);
+  const uint32_t bias_bits = 0x64806480u;                        // 1152 = 1024 + 128
+  __half2 r = __hsub2(h, *reinterpret_cast<const __half2*>(&bias_bits));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+template <int MT, int LIMBS>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_ahi,
+                  const __grid_constant__ CUtensorMap map_alo, const TcParams p) {
+  using Cfg = TcCfg<MT, LIMBS>;
+  constexpr int NB = Cfg::NB;
+  constexpr int ACC_SLOTS = Cfg::ACC_SLOTS;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* raw = smem;
+  uint8_t* act = raw + RAW_STAGES * RAW_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(act + ACT_STAGES * Cfg::ACT_BYTES);
+  uint64_t* raw_full = bars;                    // [RAW_STAGES]
+  uint64_t* raw_empty = raw_full + RAW_STAGES;  // [RAW_STAGES]
+  uint64_t* act_full = raw_empty + RAW_STAGES;  // [ACT_STAGES]
+  uint64_t* act_empty = act_full + ACT_STAGES;  // [ACT_STAGES]
+  uint64_t* ta_full = act_empty + ACT_STAGES;   // [TA_STAGES]
+  uint64_t* ta_empty = ta_full + TA_STAGES;     // [TA_STAGES]
+  uint64_t* acc_full = ta_empty + TA_STAGES;    // [ACC_SLOTS]
+  uint64_t* acc_empty = acc_full + ACC_SLOTS;   // [ACC_SLOTS]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_SLOTS);
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int64_t n0 = (int64_t)blockIdx.x * TC_ROWS;
+  const int split = blockIdx.y;
+  const int64_t m0 = (int64_t)blockIdx.z * MT;
+  const int st_begin = (int)(((int64_t)split * p.stages_total) / p.splits);
+  const int st_end = (int)(((int64_t)(split + 1) * p.stages_total) / p.splits);
+  const int nst = st_end - st_begin;
+
+  // a kernel that gave up earlier left a code behind: do not start new work on top of it
+  // (one thread reads, everyone takes the same decision)
+  __shared__ int prior_status;
+  if (tid == 0) prior_status = *reinterpret_cast<volatile int*>(p.status);
+  __syncthreads();
+  if (prior_status != 0) return;
+
+  if (tid == 0) {
+    for (int i = 0; i < RAW_STAGES; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 4); }
+    for (int i = 0; i < ACT_STAGES; ++i) { mbar_init(&act_full[i], 1); mbar_init(&act_empty[i], 1); }
+    for (int i = 0; i < TA_STAGES; ++i) { mbar_init(&ta_full[i], 4); mbar_init(&ta_empty[i], 1); }
+    for (int i = 0; i < ACC_SLOTS; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+    fence_barrier_init();
+    prefetch_tensormap(&map_q);
+    prefetch_tensormap(&map_ahi);
+    if (LIMBS == 2) prefetch_tensormap(&map_alo);
+  }
+  if (warp == 3) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  bool ok = true;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ weight producer
+    if (lane == 0) {
+      const uint64_t pol = policy_evict_first();
+      for (int i = 0; i < nst; ++i) {
+        int st = i % RAW_STAGES;
+        uint32_t ph = (uint32_t)(i / RAW_STAGES) & 1u;
+        if (!mbar_wait(&raw_empty[st], ph ^ 1u)) { ok = false; break; }
+        mbar_arrive_expect_tx(&raw_full[st], RAW_BYTES);
+        tma_load_2d_hint(raw + st * RAW_BYTES, &map_q, &raw_full[st], (st_begin + i) * TC_KSTAGE, (int)n0, pol);
+      }
+      if (!ok) atomicExch(p.status, 201);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ activation producer
+    if (lane == 0) {
+      const uint64_t pol = policy_evict_last();
+      for (int i = 0; i < nst; ++i) {
+        int st = i % ACT_STAGES;
+        uint32_t ph = (uint32_t)(i / ACT_STAGES) & 1u;
+        if (!mbar_wait(&act_empty[st], ph ^ 1u)) { ok = false; break; }
+        mbar_arrive_expect_tx(&act_full[st], Cfg::ACT_BYTES);
+        uint8_t* sb = act + st * Cfg::ACT_BYTES;
+        int x = (st_begin + i) * TC_KSTAGE;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          tma_load_2d_hint(sb + h * Cfg::ACT_ATOM_BYTES, &map_ahi, &act_full[st], x + h * 64, (int)m0, pol);
+          if (LIMBS == 2)
+            tma_load_2d_hint(sb + h * Cfg::ACT_ATOM_BYTES + MT * 128, &map_alo, &act_full[st], x + h * 64, (int)m0, pol);
+        }
+      }
+      if (!ok) atomicExch(p.status, 202);
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(0, 0, TC_ROWS, NB);
+      int blk_count = 0;
+      for (int i = 0; i < nst && ok; ++i) {
+        int ts = i % TA_STAGES, as = i % ACT_STAGES;
+        uint32_t tph = (uint32_t)(i / TA_STAGES) & 1u, aph = (uint32_t)(i / ACT_STAGES) & 1u;
+        if (!mbar_wait(&ta_full[ts], tph) || !mbar_wait(&act_full[as], aph)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t act_base = smem_u32(act + as * Cfg::ACT_BYTES);
+#pragma unroll
+        for (int blk = 0; blk < 4; ++blk) {
+          int slot = blk_count % ACC_SLOTS;
+          uint32_t sph = (uint32_t)(blk_count / ACC_SLOTS) & 1u;
+          if (!mbar_wait(&acc_empty[slot], sph ^ 1u)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d = tmem_base + ACC_COL0 + slot * NB;
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int kk = blk * 2 + j;  // K=16 step inside the stage
+            const uint32_t a = tmem_base + ts * TA_COLS + kk * 8;
+            const uint64_t bdesc = make_desc_sw128(act_base + (kk >> 2) * Cfg::ACT_ATOM_BYTES + (kk & 3) * 32);
+            tc_mma_f16_ts(d, a, bdesc, idesc, (uint32_t)j);
+          }
+          tc_commit(&acc_full[slot]);
+          ++blk_count;
+        }
+        tc_commit(&ta_empty[ts]);
+        tc_commit(&act_empty[as]);
+      }
+      if (!ok) atomicExch(p.status, 203);
+    }
+  } else if (warp >= 4 && warp < 8) {
+    // ------------------------------------------------------------ converters: int8 smem -> fp16 TMEM
+    const int qd = warp & 3;
+    const uint32_t row = qd * 32 + lane;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16);
+    for (int i = 0; i < nst; ++i) {
+      int rs = i % RAW_STAGES, ts = i % TA_STAGES;
+      uint32_t rph = (uint32_t)(i / RAW_STAGES) & 1u, tph = (uint32_t)(i / TA_STAGES) & 1u;
+      if (!mbar_wait(&raw_full[rs], rph) || !mbar_wait(&ta_empty[ts], tph ^ 1u)) { ok = false; break; }
+      tc_fence_after();
+      const uint8_t* rb = raw + rs * RAW_BYTES;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 w = *reinterpret_cast<const uint4*>(rb + swz128(row, c));
+        uint32_t r[8];
+        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+          uint32_t u = ws[wi] ^ 0x80808080u;
+          r[2 * wi] = cvt_pair(u, 0x4140);
+          r[2 * wi + 1] = cvt_pair(u, 0x4342);
+        }
+        tc_st_32x32b_x8(t_lane + ts * TA_COLS + c * 8, r);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&raw_empty[rs]);
+        mbar_arrive(&ta_full[ts]);
+      }
+    }
+    if (!ok && lane == 0) atomicExch(p.status, 204);
+  } else if (warp >= 8) {
+    // ------------------------------------------------------------ drain + epilogue
+    const int qd = warp & 3;
+    const int64_t n = n0 + qd * 32 + lane;
+    const bool n_ok = n < p.n;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16) + ACC_COL0;
+    const int64_t kb_per_row = p.k >> 5;
+    const float* srow = p.s + (n_ok ? n : 0) * kb_per_row;
+    constexpr int CH = MT < 32 ? MT : 32;
+    float acc[MT];
+#pragma unroll
+    for (int j = 0; j < MT; ++j) acc[j] = 0.f;
+    int blk_count = 0;
+    for (int i = 0; i < nst && ok; ++i) {
+      float4 sc4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (n_ok) sc4 = __ldg(reinterpret_cast<const float4*>(srow + (int64_t)(st_begin + i) * 4));
+      const float scs[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
+#pragma unroll
+      for (int blk = 0; blk < 4; ++blk) {
+        int slot = blk_count % ACC_SLOTS;
+        uint32_t sph = (uint32_t)(blk_count / ACC_SLOTS) & 1u;
+        if (!mbar_wait(&acc_full[slot], sph)) { ok = false; break; }
+        tc_fence_after();
+        const float sc = scs[blk];
+        const uint32_t ta = t_lane + slot * NB;
+#pragma unroll
+        for (int ch = 0; ch < MT / CH; ++ch) {
+          uint32_t hi[CH], lo[CH];
+          if constexpr (CH == 32) {
+            tc_ld_32x32b_x32(ta + ch * CH, hi);
+            if (LIMBS == 2) tc_ld_32x32b_x32(ta + MT + ch * CH, lo);
+          } else {
+            tc_ld_32x32b_x16(ta + ch * CH, hi);
+            if (LIMBS == 2) tc_ld_32x32b_x16(ta + MT + ch * CH, lo);
+          }
+          tc_wait_ld();
+          if (ch == MT / CH - 1) {
+            // every column of the slot is in registers: hand it back before the math
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[slot]);
+          }
+#pragma unroll
+          for (int j = 0; j < CH; ++j) {
+            float t = __uint_as_float(hi[j]);
+            if (LIMBS == 2) t = fmaf(__uint_as_float(lo[j]), 4.8828125e-4f, t);
+            acc[ch * CH + j] = fmaf(sc, t, acc[ch * CH + j]);
+          }
+        }
+        ++blk_count;
+      }
+    }
+    if (!ok && lane == 0) atomicExch(p.status, 205);
+
+    if (ok) {
+      if (p.splits > 1) {
+        if (n_ok) {
+#pragma unroll
+          for (int j = 0; j < MT; ++j)
+            if (m0 + j < p.m) p.partials[((int64_t)split * p.m + m0 + j) * p.n + n] = acc[j];
+        }
+      } else if (p.epilogue == EPI_SWIGLU) {
+#pragma unroll
+        for (int j = 0; j < MT; ++j) {
+          float other = __shfl_xor_sync(0xffffffffu, acc[j], 1);
+          if (!(lane & 1) && n + 1 < p.n && m0 + j < p.m)
+            store_c(p, (m0 + j) * p.ldc + (n >> 1), __fmul_rn(silu_f(acc[j]), other));
+        }
+      } else if (n_ok) {
+#pragma unroll
+        for (int j = 0; j < MT; ++j)
+          if (m0 + j < p.m) {
+            float v = acc[j];
+            int64_t ci = (m0 + j) * p.ldc + n;
+            if (p.epilogue == EPI_RESIDUAL) v = __fadd_rn(v, load_aux(p, ci));
+            store_c(p, ci, v);
+          }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 3) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+struct MapKey {
+  const void* base;
+  uint64_t inner, outer, pitch;
+  uint32_t box_inner, box_outer, elem;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && inner == o.inner && outer == o.outer && pitch == o.pitch && box_inner == o.box_inner &&
+           box_outer == o.box_outer && elem == o.elem;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = reinterpret_cast<uint64_t>(k.base);
+    h = h * 0x9E3779B97F4A7C15ull + k.inner;
+    h = h * 0x9E3779B97F4A7C15ull + k.outer;
+    h = h * 0x9E3779B97F4A7C15ull + k.pitch;
+    h = h * 0x9E3779B97F4A7C15ull + ((uint64_t)k.box_inner << 32 | k.box_outer) + k.elem;
+    return (size_t)h;
+  }
+};
+
+// Tensor maps are pure functions of (address, shape, box): encode once, reuse.
+logos_status_t cached_map(CUtensorMap* out, const void* base, CUtensorMapDataType dt, uint32_t elem, uint64_t inner,
+                          uint64_t outer, uint64_t pitch, uint32_t box_inner, uint32_t box_outer) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  MapKey key{base, inner, outer, pitch, box_inner, box_outer, elem};
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return LOGOS_OK;
+    }
+  }
+  LOGOS_TRY(make_tensor_map_2d(out, base, dt, elem, inner, outer, pitch, box_inner, box_outer, CU_TENSOR_MAP_SWIZZLE_128B));
+  std::lock_guard<std::mutex> lk(mu);
+  if (cache.size() > 8192) cache.clear();
+  cache[key] = *out;
+  return LOGOS_OK;
+}
+
+template <int MT, int LIMBS>
+logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
+  using Cfg = TcCfg<MT, LIMBS>;
+  CUtensorMap mq, mhi, mlo;
+  LOGOS_TRY(cached_map(&mq, g.q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)g.k, (uint64_t)g.n, (uint64_t)g.k, TC_KSTAGE, TC_ROWS));
+  LOGOS_TRY(cached_map(&mhi, g.a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)g.k, (uint64_t)g.m, (uint64_t)g.lda * 2, 64, MT));
+  if (LIMBS == 2)
+    LOGOS_TRY(cached_map(&mlo, g.a_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)g.k, (uint64_t)g.m, (uint64_t)g.lda * 2, 64, MT));
+  else
+    mlo = mhi;
+  TcParams p{};
+  p.s = g.s; p.n = g.n; p.k = g.k; p.m = g.m;
+  p.c = g.c; p.c_dtype = g.c_dtype; p.c_act = g.c_act; p.ldc = g.ldc; p.aux = g.aux; p.epilogue = g.epilogue;
+  p.partials = g.partials;
+  p.splits = g.splits > 1 ? g.splits : 1;
+  p.stages_total = (int)(g.k / TC_KSTAGE);
+  p.status = kernel_status_ptr(g.device);
+  if (!p.status) return fail(LOGOS_ERROR, "q8_gemm: no kernel status word");
+  if (p.splits > p.stages_total) return fail(LOGOS_ERROR, "q8_gemm: more K splits than 128-column stages");
+  LOGOS_CUDA_TRY(cudaFuncSetAttribute(q8_gemm_tc_kernel<MT, LIMBS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
+  dim3 grid((unsigned)((g.n + TC_ROWS - 1) / TC_ROWS), (unsigned)p.splits, (unsigned)((g.m + MT - 1) / MT));
+  q8_gemm_tc_kernel<MT, LIMBS><<<grid, TC_THREADS, Cfg::SMEM, st>>>(mq, mhi, mlo, p);
+  return check_launch("q8_gemm_tc_kernel");
+}
+
+}  // namespace
+
+bool gemm_tc_applicable(const GemmArgs& g) {
+  if (g.a_dtype != LOGOS_F16) return false;
+  if (g.k < TC_KSTAGE || g.k % TC_KSTAGE) return false;
+  if (g.m < 1 || g.n < 1) return false;
+  if (g.lda % 8) return false;
+  if ((reinterpret_cast<uintptr_t>(g.a) & 15u) || (reinterpret_cast<uintptr_t>(g.a_lo) & 15u) ||
+      (reinterpret_cast<uintptr_t>(g.q) & 15u) || (reinterpret_cast<uintptr_t>(g.s) & 15u))
+    return false;
+  return true;
+}
+
+logos_status_t launch_q8_gemm_tc(const GemmArgs& g, cudaStream_t st) {
+  const bool two = g.a_lo != nullptr;
+  if (g.m <= 16) return two ? launch_t<16, 2>(g, st) : launch_t<16, 1>(g, st);
+  if (g.m <= 32) return two ? launch_t<32, 2>(g, st) : launch_t<32, 1>(g, st);
+  return two ? launch_t<64, 2>(g, st) : launch_t<64, 1>(g, st);
+}
+
+}  // namespace logos

@@ -124,6 +124,10 @@ def q8Gemm(a, q, s, c, m, n, k, epilogue=EPI_NONE, aux=None, stream=None):
          _s(stream))
 
 
+def q8GemmF32(a, q, s, c, m, n, k, stream=None):
+    call("logos_q8_gemm_f32", a.handle, q.handle, s.handle, c.handle, int(m), int(n), int(k), _s(stream))
+
+
 def q8GemmSimt(a, q, s, c, m, n, k, epilogue=EPI_NONE, aux=None, stream=None):
     call("logos_q8_gemm_simt", a.handle, q.handle, s.handle, c.handle, int(m), int(n), int(k), int(epilogue),
          _h(aux), _s(stream))
@@ -186,6 +190,18 @@ def q8GemmHost(a_bf16, q, s, epilogue=EPI_NONE, aux=None, device=0, simt=False):
     for b in (da, dq, ds, dc, dx):
         if b is not None:
             b.free()
+    return c
+
+
+def q8GemmF32Host(a_f32, q, s, device=0):
+    m, k = a_f32.shape
+    n = q.shape[0]
+    da, dq, ds = (DeviceBuffer.from_host(t, device) for t in (np.asarray(a_f32, np.float32), q, s))
+    dc = DeviceBuffer(m * n * 4, device)
+    q8GemmF32(da, dq, ds, dc, m, n, k)
+    c = dc.download(np.float32, (m, n))
+    for b in (da, dq, ds, dc):
+        b.free()
     return c
 
 

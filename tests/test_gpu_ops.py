@@ -90,6 +90,21 @@ def test_q8_gemm_plain(llm, oracle, m, n, k, simt):
     assert rel_l2(c, ref32) < 3e-3  # bf16 output rounding alone is ~1.7e-3
 
 
+@pytest.mark.parametrize("m,n,k", [(64, 256, 3584), (16, 1152, 896), (3, 200, 256), (64, 5120, 1024), (40, 128, 27648),
+                                   (7, 96, 64)])
+def test_q8_gemm_f32_activations(llm, oracle, m, n, k):
+    """f32 activations through the two-plane tensor-core path: f32-class accuracy."""
+    O = oracle
+    a = O.synth_fill(O.F32, 2, 3, 10, 0, m * k, 0.0, 1.0).reshape(m, k)
+    a[0, :8] = [0.0, 1e-7, -3e-5, 1000.0, -65000.0, 1.0, 0.333, -2.5]   # tiny, subnormal-in-fp16 and large entries
+    q = O.synth_fill(O.I8, 0, 3, 11, 0, n * k).reshape(n, k)
+    s = O.synth_fill(O.F32, 1, 3, 12, 0, n * (k // 32), 1e-3, 1e-2).reshape(n, k // 32)
+    c = llm.q8GemmF32Host(a, q, s)
+    ref = O.q8_gemm_f32(a, O.F32, q, s)
+    assert llm.kernelStatus() == 0
+    assert rel_l2(c, ref) < 2e-6, rel_l2(c, ref)
+
+
 @pytest.mark.parametrize("simt", [False, True])
 def test_q8_gemm_epilogues(llm, oracle, golden, simt):
     O = oracle
