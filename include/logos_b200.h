@@ -97,6 +97,11 @@ LOGOS_API logos_status_t logos_dev_free(logos_handle_t h);
  * reads and clears it (0 = nothing reported).  Call after a synchronisation. */
 LOGOS_API logos_status_t logos_kernel_status(int32_t device, int32_t* out_code);
 
+/* Kernel launches this process has made through the library, by kind:
+ * out8 = {q8_gemv, q8_gemm tcgen05, q8_gemm SIMT, attention, attention merge,
+ * norm/element-wise, synth/quantize, 0}.  Evidence that the CUDA path ran. */
+LOGOS_API logos_status_t logos_launch_counts(int64_t* out8);
+
 /* ---- seeded synthetic inputs, generated on the device ----
  * One counter-based generator (SplitMix64 finaliser over seed/stream/index, the
  * mixer the reference seeds with: crates/logicaffeine_runtime/src/seed.rs:15-28)

@@ -65,6 +65,7 @@ _SIGNATURES = {
     "logos_dev_sync": (None, [I32c]),
     "logos_dev_free": (None, [H]),
     "logos_kernel_status": (None, [I32c, C.POINTER(I32c)]),
+    "logos_launch_counts": (None, [C.POINTER(I64)]),
     "logos_synth_fill": (None, [H, I64, I32c, I32c, U64, U64, I64, I64, FLT, FLT, PTR]),
     "logos_q8_quantize": (None, [H, H, H, I64, I64, PTR]),
     "logos_q8_synth_weights": (None, [H, H, I64, I64, I64, U64, U64, FLT, PTR]),

@@ -493,10 +493,12 @@ logos_status_t launch_attn_t(const AttnArgs& a, cudaStream_t st) {
   LOGOS_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_attn_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(max_splits, (unsigned)a.h_kv, (unsigned)a.b);
   gqa_decode_attn_kernel<D><<<grid, ATT_THREADS, smem, st>>>(mk, mv, p);
+  count_launch(LK_ATTN);
   LOGOS_TRY(check_launch("gqa_decode_attn_kernel"));
   dim3 mgrid((unsigned)a.h_q, (unsigned)a.b);
   attn_merge_kernel<D><<<mgrid, D, 0, st>>>(p.part_o, p.part_ml, a.seq_len, a.o, a.o_dtype, a.o_act, (int)a.h_q,
                                             (int)a.l_max, (int)ul, max_splits, p.fused);
+  count_launch(LK_ATTN_MERGE);
   LOGOS_TRY(check_launch("attn_merge_kernel"));
   if (a.bump_seq_len) {
     bump_seq_len_kernel<<<(unsigned)((a.b + 127) / 128), 128, 0, st>>>(a.seq_len, (int)a.b, (int)a.l_max);

@@ -88,6 +88,13 @@ int* kernel_status_ptr(int device);
 // ---------------------------------------------------------------- launch helpers
 logos_status_t check_launch(const char* kernel);
 
+// Process-wide count of kernel launches by kind (read through logos_launch_counts).
+enum LaunchKind : int {
+  LK_GEMV = 0, LK_GEMM_TC = 1, LK_GEMM_SIMT = 2, LK_ATTN = 3, LK_ATTN_MERGE = 4, LK_ELEMWISE = 5, LK_SYNTH = 6,
+  LK_KINDS = 8
+};
+void count_launch(int kind, int64_t n = 1);
+
 static inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
 }  // namespace logos

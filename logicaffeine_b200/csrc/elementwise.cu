@@ -143,6 +143,7 @@ logos_status_t launch_rmsnorm_f32(const float* x, const float* g, float* y, int6
                                   cudaStream_t st) {
   if (rows == 0 || h == 0) return LOGOS_OK;
   rmsnorm_f32_kernel<<<(unsigned)rows, 256, 0, st>>>(x, g, y, h, eps);
+  count_launch(LK_ELEMWISE);
   return check_launch("rmsnorm_f32_kernel");
 }
 
@@ -151,6 +152,7 @@ logos_status_t launch_swiglu_f32(const float* gate, const float* up, float* y, i
   int64_t want = (count + 255) / 256;
   int grid = (int)(want < 148 * 8 ? want : 148 * 8);
   swiglu_f32_kernel<<<grid, 256, 0, st>>>(gate, up, y, count);
+  count_launch(LK_ELEMWISE);
   return check_launch("swiglu_f32_kernel");
 }
 
@@ -158,18 +160,21 @@ logos_status_t launch_embed(const int32_t* tokens, const int8_t* q, const float*
                             int64_t hidden, cudaStream_t st) {
   if (rows == 0) return LOGOS_OK;
   embed_kernel<<<(unsigned)rows, 256, 0, st>>>(tokens, q, s, h, hidden);
+  count_launch(LK_ELEMWISE);
   return check_launch("embed_kernel");
 }
 
 logos_status_t launch_bf16_to_f16(const __nv_bfloat16* x, __half* y, int64_t count, cudaStream_t st) {
   if (count == 0) return LOGOS_OK;
   bf16_to_f16_kernel<<<(unsigned)((count + 255) / 256), 256, 0, st>>>(x, y, count);
+  count_launch(LK_ELEMWISE);
   return check_launch("bf16_to_f16_kernel");
 }
 
 logos_status_t launch_act_split(const float* x, ActOut o, int64_t count, cudaStream_t st) {
   if (count == 0) return LOGOS_OK;
   act_split_kernel<<<(unsigned)((count + 255) / 256), 256, 0, st>>>(x, o, count);
+  count_launch(LK_ELEMWISE);
   return check_launch("act_split_kernel");
 }
 
@@ -181,6 +186,7 @@ logos_status_t launch_residual_rmsnorm(float* h, const float* delta, int parts, 
   if (smem > 48 * 1024)
     LOGOS_CUDA_TRY(cudaFuncSetAttribute(residual_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   residual_rmsnorm_kernel<<<(unsigned)rows, 256, smem, st>>>(h, delta, parts, part_stride, g, xn, hidden, eps);
+  count_launch(LK_ELEMWISE);
   return check_launch("residual_rmsnorm_kernel");
 }
 
@@ -188,6 +194,7 @@ logos_status_t launch_argmax(const float* logits, int32_t* tokens, int32_t* hist
                              int64_t vocab, cudaStream_t st) {
   if (rows == 0) return LOGOS_OK;
   argmax_kernel<<<(unsigned)rows, 1024, 0, st>>>(logits, tokens, history_or_null, vocab);
+  count_launch(LK_ELEMWISE);
   return check_launch("argmax_kernel");
 }
 

@@ -133,6 +133,7 @@ logos_status_t launch_splitk_reduce(const float* partials, int splits, void* c, 
   if (total == 0) return LOGOS_OK;
   splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(partials, splits, c, c_dtype, c_act, ldc, aux,
                                                                         m, n, epilogue);
+  count_launch(LK_ELEMWISE);
   return check_launch("splitk_reduce_kernel");
 }
 
@@ -148,6 +149,7 @@ logos_status_t launch_q8_gemm(const GemmArgs& g, cudaStream_t st) {
   q8_gemm_simt_kernel<<<grid, 256, 0, st>>>(g.a, g.a_lo, g.a_dtype, g.lda, g.q, g.s, g.c, g.c_dtype, g.c_act, g.ldc,
                                             g.aux, g.partials, g.m, g.n, g.k, g.epilogue,
                                             g.splits > 1 ? g.splits : 1);
+  count_launch(LK_GEMM_SIMT);
   return check_launch("q8_gemm_simt_kernel");
 }
 

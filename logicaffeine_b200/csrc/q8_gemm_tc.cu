@@ -410,6 +410,7 @@ logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
   LOGOS_CUDA_TRY(cudaFuncSetAttribute(q8_gemm_tc_kernel<MT, LIMBS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
   dim3 grid((unsigned)((g.n + TC_ROWS - 1) / TC_ROWS), (unsigned)p.splits, (unsigned)((g.m + MT - 1) / MT));
   q8_gemm_tc_kernel<MT, LIMBS><<<grid, TC_THREADS, Cfg::SMEM, st>>>(mq, mhi, mlo, p);
+  count_launch(LK_GEMM_TC);
   return check_launch("q8_gemm_tc_kernel");
 }
 

@@ -140,6 +140,7 @@ logos_status_t launch_q8_gemv(const int8_t* q, const float* s, const float* x, f
   } else {
     q8_gemv_kernel<false><<<grid, GEMV_WARPS * 32, 0, st>>>(q, s, x, y, n, k);
   }
+  count_launch(LK_GEMV);
   return check_launch("q8_gemv_kernel");
 }
 

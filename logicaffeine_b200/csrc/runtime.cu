@@ -4,6 +4,7 @@
 // text, ids instead of addresses, invalid ids reported instead of dereferenced.
 #include "common.cuh"
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -52,6 +53,9 @@ logos_status_t cuda_fail(cudaError_t e, const char* what) {
   logos_status_t code = (e == cudaErrorMemoryAllocation) ? LOGOS_MEMORY_EXHAUSTED : LOGOS_ERROR;
   return fail(code, "CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
 }
+
+static std::atomic<int64_t> g_launches[LK_KINDS];
+void count_launch(int kind, int64_t n) { g_launches[kind].fetch_add(n, std::memory_order_relaxed); }
 
 logos_status_t check_launch(const char* kernel) {
   cudaError_t e = cudaGetLastError();
@@ -150,6 +154,12 @@ int32_t logos_device_count(void) {
     return 0;
   }
   return n;
+}
+
+logos_status_t logos_launch_counts(int64_t* out8) {
+  if (!out8) return fail(LOGOS_NULL_POINTER, "logos_launch_counts: out is null");
+  for (int i = 0; i < LK_KINDS; ++i) out8[i] = g_launches[i].load(std::memory_order_relaxed);
+  return LOGOS_OK;
 }
 
 logos_status_t logos_dev_alloc(int64_t bytes, int32_t device, logos_handle_t* out) {

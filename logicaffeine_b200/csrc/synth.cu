@@ -75,6 +75,7 @@ logos_status_t launch_synth_fill(void* dst, int dtype, int kind, uint64_t seed, 
   int64_t cap = (int64_t)sm_count(device) * 16;
   int grid = (int)(want < cap ? want : cap);
   synth_fill_kernel<<<grid, threads, 0, st>>>(dst, dtype, kind, seed, stream, first, count, a, b);
+  count_launch(LK_SYNTH);
   return check_launch("synth_fill_kernel");
 }
 
@@ -94,6 +95,7 @@ logos_status_t launch_q8_quantize(bool generate, const float* w, int8_t* q, floa
   else
     q8_quantize_kernel<false><<<grid, threads, 0, st>>>(w, q, s, n, k, row0, col0, k_total, out_row_mul,
                                                         out_row_add, 0, 0, 0.f);
+  count_launch(LK_SYNTH);
   return check_launch("q8_quantize_kernel");
 }
 

@@ -91,6 +91,14 @@ def kernelStatus(device=0):
     return code.value
 
 
+def launchCounts():
+    """Kernel launches made through the library so far, by kind."""
+    out = (C.c_int64 * 8)()
+    call("logos_launch_counts", out)
+    names = ("q8_gemv", "q8_gemm_tc", "q8_gemm_simt", "attention", "attention_merge", "elementwise", "synth")
+    return dict(zip(names, (int(v) for v in out)))
+
+
 def _h(buf):
     return buf.handle if buf is not None else None
 

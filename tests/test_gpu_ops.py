@@ -99,7 +99,11 @@ def test_q8_gemm_f32_activations(llm, oracle, m, n, k):
     a[0, :8] = [0.0, 1e-7, -3e-5, 1000.0, -65000.0, 1.0, 0.333, -2.5]   # tiny, subnormal-in-fp16 and large entries
     q = O.synth_fill(O.I8, 0, 3, 11, 0, n * k).reshape(n, k)
     s = O.synth_fill(O.F32, 1, 3, 12, 0, n * (k // 32), 1e-3, 1e-2).reshape(n, k // 32)
+    before = llm.launchCounts()
     c = llm.q8GemmF32Host(a, q, s)
+    after = llm.launchCounts()
+    kind = "q8_gemm_tc" if k % 128 == 0 else "q8_gemm_simt"
+    assert after[kind] == before[kind] + 1   # the tcgen05 kernel takes every shape with K % 128 == 0
     ref = O.q8_gemm_f32(a, O.F32, q, s)
     assert llm.kernelStatus() == 0
     assert rel_l2(c, ref) < 2e-6, rel_l2(c, ref)
