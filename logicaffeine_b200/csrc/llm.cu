@@ -446,18 +446,13 @@ logos_status_t logos_llm_synth_kv(logos_handle_t model, int64_t t, uint64_t seed
     const logos_llm_config_t& c = m->cfg;
     if (t < 0 || t > c.l_max) return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_synth_kv: t outside [0,l_max]");
     const int64_t D = c.head_dim, B = c.batch;
-    for (int64_t l = 0; l < c.layers; ++l)
-      for (int64_t b = 0; b < B; ++b)
-        for (int64_t h = 0; h < m->hkv_local; ++h) {
-          // index space of the unsharded cache, so every rank fills its own heads with the same values
-          int64_t gh = (int64_t)c.tp_rank * m->hkv_local + h;
-          int64_t first = ((b * c.h_kv + gh) * c.l_max) * D;
-          int64_t off = ((b * m->hkv_local + h) * c.l_max) * D;
-          LOGOS_TRY(launch_synth_fill(m->layers[(size_t)l].kc + off, LOGOS_F16, 2, seed, (uint64_t)(2 * l), first, t * D,
-                                      0.f, 1.f, m->device, m->stream));
-          LOGOS_TRY(launch_synth_fill(m->layers[(size_t)l].vc + off, LOGOS_F16, 2, seed, (uint64_t)(2 * l + 1), first,
-                                      t * D, 0.f, 1.f, m->device, m->stream));
-        }
+    for (int64_t l = 0; l < c.layers; ++l) {
+      const int64_t h0 = (int64_t)c.tp_rank * m->hkv_local;
+      LOGOS_TRY(launch_synth_kv(m->layers[(size_t)l].kc, seed, (uint64_t)(2 * l), B, m->hkv_local, h0, c.h_kv, c.l_max, D,
+                                t, m->device, m->stream));
+      LOGOS_TRY(launch_synth_kv(m->layers[(size_t)l].vc, seed, (uint64_t)(2 * l + 1), B, m->hkv_local, h0, c.h_kv, c.l_max,
+                                D, t, m->device, m->stream));
+    }
     std::vector<int32_t> len((size_t)B, (int32_t)t);
     LOGOS_CUDA_TRY(cudaMemcpyAsync(m->seq_len, len.data(), (size_t)B * 4, cudaMemcpyHostToDevice, m->stream));
     LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));

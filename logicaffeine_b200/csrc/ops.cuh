@@ -17,6 +17,9 @@ logos_status_t launch_q8_quantize(bool generate, const float* w, int8_t* q, floa
                                   int64_t out_row_add, uint64_t seed, uint64_t stream, float std, int device,
                                   cudaStream_t st);
 
+logos_status_t launch_synth_kv(__half* cache, uint64_t seed, uint64_t stream, int64_t b, int64_t hkv_local, int64_t h0,
+                               int64_t hkv_total, int64_t l_max, int64_t d, int64_t t, int device, cudaStream_t st);
+
 // ---- GEMV (q8_gemv.cu)
 logos_status_t launch_q8_gemv(const int8_t* q, const float* s, const float* x, float* y, int64_t n, int64_t k,
                               int device, cudaStream_t st);

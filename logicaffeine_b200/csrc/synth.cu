@@ -30,6 +30,35 @@ __global__ void synth_fill_kernel(void* dst, int dtype, int kind, uint64_t seed,
   }
 }
 
+// Positions [0,t) of a [B][Hkv_local][Lmax][D] fp16 cache, valued by their index in the
+// unsharded [B][Hkv_total][Lmax][D] cache, so every rank fills its heads with the same bits.
+__global__ void synth_kv_kernel(__half* __restrict__ cache, uint64_t seed, uint64_t stream, int64_t b, int64_t hkv_local,
+                                int64_t h0, int64_t hkv_total, int64_t l_max, int64_t d, int64_t t) {
+  const int64_t per_head = t * d;
+  const int64_t total = b * hkv_local * per_head;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < total; i += step) {
+    int64_t bh = i / per_head, r = i - bh * per_head;
+    int64_t bb = bh / hkv_local, h = bh - bb * hkv_local;
+    int64_t logical = ((bb * hkv_total + h0 + h) * l_max) * d + r;
+    int64_t local = ((bb * hkv_local + h) * l_max) * d + r;
+    cache[local] = __float2half_rn(synth::normal_scaled(seed, stream, (uint64_t)logical, 0.f, 1.f));
+  }
+}
+
+logos_status_t launch_synth_kv(__half* cache, uint64_t seed, uint64_t stream, int64_t b, int64_t hkv_local, int64_t h0,
+                               int64_t hkv_total, int64_t l_max, int64_t d, int64_t t, int device, cudaStream_t st) {
+  int64_t total = b * hkv_local * t * d;
+  if (total == 0) return LOGOS_OK;
+  int64_t want = (total + 255) / 256;
+  int64_t cap = (int64_t)sm_count(device) * 16;
+  synth_kv_kernel<<<(int)(want < cap ? want : cap), 256, 0, st>>>(cache, seed, stream, b, hkv_local, h0, hkv_total, l_max,
+                                                                  d, t);
+  count_launch(LK_SYNTH);
+  return check_launch("synth_kv_kernel");
+}
+
 // One warp per 32-element block: lane l owns element l.
 template <bool GENERATE>
 __global__ void q8_quantize_kernel(const float* __restrict__ w, int8_t* __restrict__ q, float* __restrict__ s,

@@ -85,3 +85,25 @@ def test_qwen05b_shape_64_step_token_parity(llm, oracle):
     assert not mism, "first mismatching (step, sequence): %s" % mism[:4]
     gpu.free()
     ref.close()
+
+
+def test_synth_kv_matches_oracle_and_decodes(llm, oracle):
+    """Seeded KV fill (the benchmark's way to reach a context length): same bits as the oracle's, then decode."""
+    O = oracle
+    cfg = dict(SMALL, l_max=80)
+    ref = O.Llm(tp_degree=1, tp_rank=0, device=0, act_dtype=O.F32, **cfg)
+    gpu = llm.Llm(**cfg)
+    ref.synth_kv(40, 7)
+    gpu.synthKv(40, 7)
+    for layer in range(cfg["layers"]):
+        k, v = gpu.readKv(layer)
+        kr, vr = ref.read_kv(layer)
+        assert np.array_equal(k, kr) and np.array_equal(v, vr)
+    toks = np.arange(cfg["batch"], dtype=np.int32) + 3
+    ref.set_tokens(toks)
+    gpu.setTokens(toks)
+    want = np.array([ref.decode_step().copy() for _ in range(12)])
+    got = gpu.decodeSteps(12)
+    assert np.array_equal(got, want)
+    gpu.free()
+    ref.close()
