@@ -81,9 +81,10 @@ logos_status_t scratch_get(int32_t device, int slot, int64_t bytes, void** out);
 
 int sm_count(int device);
 
-// Device-visible status word (mapped host memory): kernels store a non-zero
-// code when a bounded wait gives up.  0 = fine.
+// Per-device status word in device memory: kernels store a non-zero code when
+// a bounded wait gives up.  0 = fine.
 int* kernel_status_ptr(int device);
+logos_status_t kernel_status_read(int device, int* out, bool clear);
 
 // ---------------------------------------------------------------- launch helpers
 logos_status_t check_launch(const char* kernel);

@@ -492,8 +492,9 @@ logos_status_t logos_llm_decode_steps(logos_handle_t model, int64_t steps, int32
     float ms = 0.f;
     LOGOS_CUDA_TRY(cudaEventElapsedTime(&ms, m->ev0, m->ev1));
     m->last_ms = ms;
-    int* status = kernel_status_ptr(m->device);
-    if (status && status[0] != 0) return fail(LOGOS_ERROR, "a device-side wait gave up (kernel status %d)", status[0]);
+    int code = 0;
+    LOGOS_TRY(kernel_status_read(m->device, &code, false));
+    if (code != 0) return fail(LOGOS_ERROR, "a device-side wait gave up (kernel status %d)", code);
     return LOGOS_OK;
   });
 }

@@ -50,15 +50,29 @@ int* kernel_status_ptr(int device) {
   std::lock_guard<std::mutex> lk(mu);
   auto it = words.find(device);
   if (it != words.end()) return it->second;
+  // Device memory, not mapped host memory: every CTA reads this word once, and a read that
+  // crosses PCIe costs about a microsecond and serialises.
+  int prev = 0;
+  cudaGetDevice(&prev);
   int* p = nullptr;
-  if (cudaHostAlloc(reinterpret_cast<void**>(&p), sizeof(int) * 4, cudaHostAllocMapped | cudaHostAllocPortable) !=
-      cudaSuccess) {
+  if (cudaSetDevice(device) != cudaSuccess || cudaMalloc(reinterpret_cast<void**>(&p), 256) != cudaSuccess ||
+      cudaMemset(p, 0, 256) != cudaSuccess) {
     cudaGetLastError();
+    cudaSetDevice(prev);
     return nullptr;
   }
-  p[0] = p[1] = p[2] = p[3] = 0;
+  cudaSetDevice(prev);
   words[device] = p;
   return p;
+}
+
+logos_status_t kernel_status_read(int device, int* out, bool clear) {
+  int* p = kernel_status_ptr(device);
+  if (!p) return fail(LOGOS_ERROR, "no kernel status word (no CUDA device?)");
+  LOGOS_CUDA_TRY(cudaSetDevice(device));
+  LOGOS_CUDA_TRY(cudaMemcpy(out, p, sizeof(int), cudaMemcpyDeviceToHost));
+  if (clear && *out != 0) LOGOS_CUDA_TRY(cudaMemset(p, 0, sizeof(int)));
+  return LOGOS_OK;
 }
 
 }  // namespace logos
@@ -70,10 +84,11 @@ using namespace logos;
 extern "C" logos_status_t logos_kernel_status(int32_t device, int32_t* out_code) {
   return guarded([&]() -> logos_status_t {
     if (!out_code) return fail(LOGOS_NULL_POINTER, "logos_kernel_status: out_code is null");
-    int* p = kernel_status_ptr(device);
-    if (!p) return fail(LOGOS_ERROR, "logos_kernel_status: no status word (no CUDA device?)");
-    *out_code = p[0];
-    p[0] = 0;
+    int n = logos_device_count();
+    if (device < 0 || device >= n) return fail(LOGOS_OUT_OF_BOUNDS, "logos_kernel_status: device %d of %d", device, n);
+    int code = 0;
+    LOGOS_TRY(kernel_status_read(device, &code, true));
+    *out_code = code;
     return LOGOS_OK;
   });
 }
