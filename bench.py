@@ -206,6 +206,84 @@ def gemv_probe(llm, torch, device):
             "timing": "CUDA graph of %d launches over %d rotating weight copies (> L2)" % (launches, copies)}
 
 
+def op_probe(args):
+    """Single-operator timing (used for ncu captures and kernel work): one JSON line."""
+    import torch
+    from logicaffeine_b200 import llm
+    dev = 0
+    torch.cuda.set_device(dev)
+    peak, peak_kind = peaks()
+    stream = torch.cuda.Stream()
+    sp = stream.cuda_stream
+    m, n, k, reps, copies = args.m, args.n, args.k, args.reps, args.copies
+    if args.op == "q8_gemm":
+        a = llm.DeviceBuffer(m * k * 4, dev)
+        c = llm.DeviceBuffer(m * n * 4, dev)
+        llm.synthFill(a, llm.F32, 2, 0, 1, 0, m * k, 0.0, 1.0)
+        qs, ss = [], []
+        for i in range(copies):
+            q = llm.DeviceBuffer(n * k, dev)
+            s_ = llm.DeviceBuffer(n * (k // 32) * 4, dev)
+            llm.synthFill(q, llm.I8, 0, 0, 10 + i, 0, n * k)
+            llm.synthFill(s_, llm.F32, 1, 0, 50 + i, 0, n * (k // 32), 1e-3, 1e-2)
+            qs.append(q)
+            ss.append(s_)
+        run = lambda i: llm.q8GemmF32(a, qs[i % copies], ss[i % copies], c, m, n, k, stream=sp)
+        nbytes = n * k * 1.125
+    elif args.op == "q8_gemv":
+        x = llm.DeviceBuffer(k * 4, dev)
+        y = llm.DeviceBuffer(n * 4, dev)
+        llm.synthFill(x, llm.F32, 2, 0, 1, 0, k, 0.0, 1.0)
+        qs, ss = [], []
+        for i in range(copies):
+            q = llm.DeviceBuffer(n * k, dev)
+            s_ = llm.DeviceBuffer(n * (k // 32) * 4, dev)
+            llm.synthFill(q, llm.I8, 0, 0, 10 + i, 0, n * k)
+            llm.synthFill(s_, llm.F32, 1, 0, 50 + i, 0, n * (k // 32), 1e-3, 1e-2)
+            qs.append(q)
+            ss.append(s_)
+        run = lambda i: llm.q8Gemv(qs[i % copies], ss[i % copies], x, y, n, k, stream=sp)
+        nbytes = n * k * 1.125 + k * 4 + n * 4
+    else:  # attention: b = m sequences, n = context, config-2 heads unless overridden
+        b, ctx, hq, hkv, d = m, n, args.hq, args.hkv, args.d
+        lmax = ctx + 1
+        kc = llm.DeviceBuffer(b * hkv * lmax * d * 2, dev)
+        vc = llm.DeviceBuffer(b * hkv * lmax * d * 2, dev)
+        llm.synthFill(kc, llm.F16, 2, 0, 1, 0, b * hkv * lmax * d, 0.0, 1.0)
+        llm.synthFill(vc, llm.F16, 2, 0, 2, 0, b * hkv * lmax * d, 0.0, 1.0)
+        qb, kn, vn = (llm.DeviceBuffer(b * h * d * 2, dev) for h in (hq, hkv, hkv))
+        for j, (buf, h) in enumerate(((qb, hq), (kn, hkv), (vn, hkv))):
+            llm.synthFill(buf, llm.F16, 2, 0, 3 + j, 0, b * h * d, 0.0, 1.0)
+        tab = llm.DeviceBuffer.from_host(llm.ropeTable(lmax, d, 1e6), dev)
+        ob = llm.DeviceBuffer(b * hq * d * 2, dev)
+        lens = np.full(b, ctx, np.int32)
+        seq = llm.DeviceBuffer.from_host(lens, dev)
+
+        def run(i):
+            seq.upload(lens)  # the fused call bumps the lengths; rewind so every launch sees the same work
+            llm.gqaDecodeAttnFused(qb, kn, vn, kc, vc, tab, seq, ob, b, hq, hkv, d, lmax, 1.0 / np.sqrt(d), stream=sp)
+        nbytes = 2 * b * hkv * (ctx + 1) * d * 2 + 2 * b * hq * d * 2
+    llm.devSync(dev)
+    with torch.cuda.stream(stream):
+        for i in range(3):
+            run(i)
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        times = []
+        for i in range(reps):
+            e0.record(stream)
+            run(i)
+            e1.record(stream)
+            stream.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e3)
+    us = float(np.median(times))
+    print(json.dumps({"op": args.op, "m": m, "n": n, "k": k, "us_median": us, "us_min": float(min(times)),
+                      "algorithmic_bytes": nbytes, "gbs": nbytes / us / 1e3, "frac": nbytes / us / 1e3 / peak,
+                      "peak_kind": "of " + peak_kind, "status": llm.kernelStatus(dev),
+                      "timing": "CUDA events around single launches (includes launch latency), %d rotating weight "
+                                "copies" % copies}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -216,7 +294,20 @@ def main():
     ap.add_argument("--prefill", default="synthetic-kv", choices=["synthetic-kv", "prompt"])
     ap.add_argument("--act", default="f32", choices=["f32", "f16", "bf16"])
     ap.add_argument("--no-extras", action="store_true", help="skip the CPU baseline and the GEMV probe")
+    ap.add_argument("--op", default="decode", choices=["decode", "q8_gemm", "q8_gemv", "attention"],
+                    help="time one operator instead of the decode loop (attention: --m sequences, --n context)")
+    ap.add_argument("--m", type=int, default=64)
+    ap.add_argument("--n", type=int, default=18944)
+    ap.add_argument("--k", type=int, default=3584)
+    ap.add_argument("--hq", type=int, default=28)
+    ap.add_argument("--hkv", type=int, default=4)
+    ap.add_argument("--d", type=int, default=128)
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--copies", type=int, default=3)
     args = ap.parse_args()
+    if args.op != "decode":
+        op_probe(args)
+        return
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -64,20 +64,39 @@ __global__ void embed_kernel(const int32_t* __restrict__ tokens, const int8_t* _
     h[row * hidden + e] = __fmul_rn(sr[e >> 5], (float)qr[e]);
 }
 
-__global__ void residual_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int parts,
-                                        int64_t part_stride, const float* __restrict__ g, ActOut xn,
-                                        int64_t hidden, float eps) {
+// One CTA per row, 128-bit accesses: fold the split-K partials into the residual
+// stream in ascending order, keep the updated row in shared memory, reduce the
+// sum of squares, then write the normalised row as activation planes.
+__global__ void __launch_bounds__(512)
+residual_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int parts, int64_t part_stride,
+                        const float* __restrict__ g, ActOut xn, int64_t hidden, float eps) {
   __shared__ float red[32];
-  extern __shared__ float row_cache[];  // hidden floats
+  extern __shared__ float4 row_cache4[];  // hidden floats
+  float* row_cache = reinterpret_cast<float*>(row_cache4);
   const int64_t row = blockIdx.x;
   float* hr = h + row * hidden;
   float ss = 0.f;
-  for (int64_t i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float v = hr[i];
-    for (int p = 0; p < parts; ++p) v = __fadd_rn(v, delta[(int64_t)p * part_stride + row * hidden + i]);
-    if (parts > 0) hr[i] = v;
-    row_cache[i] = v;
-    ss = fmaf(v, v, ss);
+  if ((hidden & 3) == 0) {
+    const int64_t n4 = hidden >> 2;
+    float4* hr4 = reinterpret_cast<float4*>(hr);
+    for (int64_t i = threadIdx.x; i < n4; i += blockDim.x) {
+      float4 v = hr4[i];
+      for (int p = 0; p < parts; ++p) {
+        const float4 d = __ldg(reinterpret_cast<const float4*>(delta + (int64_t)p * part_stride + row * hidden) + i);
+        v.x = __fadd_rn(v.x, d.x); v.y = __fadd_rn(v.y, d.y); v.z = __fadd_rn(v.z, d.z); v.w = __fadd_rn(v.w, d.w);
+      }
+      if (parts > 0) hr4[i] = v;
+      row_cache4[i] = v;
+      ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+  } else {
+    for (int64_t i = threadIdx.x; i < hidden; i += blockDim.x) {
+      float v = hr[i];
+      for (int p = 0; p < parts; ++p) v = __fadd_rn(v, delta[(int64_t)p * part_stride + row * hidden + i]);
+      if (parts > 0) hr[i] = v;
+      row_cache[i] = v;
+      ss = fmaf(v, v, ss);
+    }
   }
   ss = block_sum(ss, red);
   float inv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hidden), eps)));
@@ -185,7 +204,7 @@ logos_status_t launch_residual_rmsnorm(float* h, const float* delta, int parts, 
   size_t smem = sizeof(float) * (size_t)hidden;
   if (smem > 48 * 1024)
     LOGOS_CUDA_TRY(cudaFuncSetAttribute(residual_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  residual_rmsnorm_kernel<<<(unsigned)rows, 256, smem, st>>>(h, delta, parts, part_stride, g, xn, hidden, eps);
+  residual_rmsnorm_kernel<<<(unsigned)rows, 512, smem, st>>>(h, delta, parts, part_stride, g, xn, hidden, eps);
   count_launch(LK_ELEMWISE);
   return check_launch("residual_rmsnorm_kernel");
 }

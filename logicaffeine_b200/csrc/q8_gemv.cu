@@ -3,7 +3,7 @@
 // HBM-bound: 1.125 bytes of weights per multiply-add, so the kernel is a
 // coalesced stream.  One warp owns one row at a time; every lane issues 128-bit
 // read-only loads of 16 consecutive int8 (a half block), so a warp covers 512
-// columns per step and keeps several such loads in flight.  int8 -> f32 uses
+// columns per load and keeps eight such loads in flight.  int8 -> f32 uses
 // the 2^23 mantissa trick (one byte-permute and one subtract), the half-block
 // dot product is scaled by its block's f32 scale in registers, and the row sum
 // is a warp-shuffle reduction.  x lives in shared memory, laid out so the
@@ -45,6 +45,9 @@ __device__ __forceinline__ float dot4(uint32_t w, float4 x, float acc) {
 // the same j of consecutive chunks touch consecutive 16-byte slots.
 __device__ __forceinline__ int xs4_index(int chunk, int j) { return (chunk >> 5) * 128 + j * 32 + (chunk & 31); }
 
+// A warp owns one row.  For each super-chunk of 4096 columns a lane first issues
+// all of its eight 128-bit weight loads (and the eight scales), and only then
+// waits for x to be staged, so the HBM stream starts at the first instruction.
 template <bool X_IN_SMEM>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
 q8_gemv_kernel(const int8_t* __restrict__ q, const float* __restrict__ s, const float* __restrict__ x,
@@ -54,68 +57,61 @@ q8_gemv_kernel(const int8_t* __restrict__ q, const float* __restrict__ s, const 
   const int lane = tid & 31;
   const int warp = tid >> 5;
   const int chunks = (int)(k >> 4);  // 16-element chunks per row
-  if (X_IN_SMEM) {
-    const float4* xg = reinterpret_cast<const float4*>(x);
-    for (int i = tid; i < chunks * 4; i += GEMV_WARPS * 32) {
-      int c = i >> 2, j = i & 3;
-      xs4[xs4_index(c, j)] = xg[i];
-    }
-    __syncthreads();
-  }
   const int64_t kb_per_row = k >> 5;
-  for (int64_t row = (int64_t)blockIdx.x * GEMV_WARPS + warp; row < n; row += (int64_t)gridDim.x * GEMV_WARPS) {
-    const uint4* qr = reinterpret_cast<const uint4*>(q + row * k);
-    const float* sr = s + row * kb_per_row;
+  bool x_ready = !X_IN_SMEM;
+  for (int64_t row0 = (int64_t)blockIdx.x * GEMV_WARPS; row0 < n; row0 += (int64_t)gridDim.x * GEMV_WARPS) {
+    const int64_t row = row0 + warp;
+    const bool row_ok = row < n;
+    const uint4* qr = reinterpret_cast<const uint4*>(q + (row_ok ? row : 0) * k);
+    const float* sr = s + (row_ok ? row : 0) * kb_per_row;
     float acc = 0.f;
-    int c = lane;
-    // four loads in flight per lane
-    for (; c + 96 < chunks; c += 128) {
-      uint4 w0 = ldg_nc_v4(qr + c), w1 = ldg_nc_v4(qr + c + 32), w2 = ldg_nc_v4(qr + c + 64),
-            w3 = ldg_nc_v4(qr + c + 96);
-      float s0 = __ldg(sr + (c >> 1)), s1 = __ldg(sr + ((c + 32) >> 1)), s2 = __ldg(sr + ((c + 64) >> 1)),
-            s3 = __ldg(sr + ((c + 96) >> 1));
-      uint4 ws[4] = {w0, w1, w2, w3};
-      float ss[4] = {s0, s1, s2, s3};
+    for (int c0 = 0; c0 < chunks; c0 += 256) {
+      uint4 w[8];
+      float sc[8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        int cc = c + 32 * u;
-        float4 x0, x1, x2, x3;
-        if (X_IN_SMEM) {
-          x0 = xs4[xs4_index(cc, 0)]; x1 = xs4[xs4_index(cc, 1)];
-          x2 = xs4[xs4_index(cc, 2)]; x3 = xs4[xs4_index(cc, 3)];
+      for (int u = 0; u < 8; ++u) {
+        int c = c0 + lane + 32 * u;
+        if (row_ok && c < chunks) {
+          w[u] = ldg_nc_v4(qr + c);
+          sc[u] = __ldg(sr + (c >> 1));
         } else {
-          const float4* xg = reinterpret_cast<const float4*>(x) + cc * 4;
-          x0 = __ldg(xg); x1 = __ldg(xg + 1); x2 = __ldg(xg + 2); x3 = __ldg(xg + 3);
+          w[u] = make_uint4(0x0, 0x0, 0x0, 0x0);
+          sc[u] = 0.f;
         }
-        float p = 0.f;
-        p = dot4(ws[u].x, x0, p);
-        p = dot4(ws[u].y, x1, p);
-        p = dot4(ws[u].z, x2, p);
-        p = dot4(ws[u].w, x3, p);
-        acc = fmaf(ss[u], p, acc);
       }
-    }
-    for (; c < chunks; c += 32) {
-      uint4 w = ldg_nc_v4(qr + c);
-      float sc = __ldg(sr + (c >> 1));
-      float4 x0, x1, x2, x3;
-      if (X_IN_SMEM) {
-        x0 = xs4[xs4_index(c, 0)]; x1 = xs4[xs4_index(c, 1)];
-        x2 = xs4[xs4_index(c, 2)]; x3 = xs4[xs4_index(c, 3)];
-      } else {
-        const float4* xg = reinterpret_cast<const float4*>(x) + c * 4;
-        x0 = __ldg(xg); x1 = __ldg(xg + 1); x2 = __ldg(xg + 2); x3 = __ldg(xg + 3);
+      if (!x_ready) {
+        const float4* xg = reinterpret_cast<const float4*>(x);
+        for (int i = tid; i < chunks * 4; i += GEMV_WARPS * 32) {
+          int c = i >> 2, j = i & 3;
+          xs4[xs4_index(c, j)] = xg[i];
+        }
+        __syncthreads();
+        x_ready = true;
       }
-      float p = 0.f;
-      p = dot4(w.x, x0, p);
-      p = dot4(w.y, x1, p);
-      p = dot4(w.z, x2, p);
-      p = dot4(w.w, x3, p);
-      acc = fmaf(sc, p, acc);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        int c = c0 + lane + 32 * u;
+        if (c < chunks) {
+          float4 x0, x1, x2, x3;
+          if (X_IN_SMEM) {
+            x0 = xs4[xs4_index(c, 0)]; x1 = xs4[xs4_index(c, 1)];
+            x2 = xs4[xs4_index(c, 2)]; x3 = xs4[xs4_index(c, 3)];
+          } else {
+            const float4* xg = reinterpret_cast<const float4*>(x) + c * 4;
+            x0 = __ldg(xg); x1 = __ldg(xg + 1); x2 = __ldg(xg + 2); x3 = __ldg(xg + 3);
+          }
+          float p = 0.f;
+          p = dot4(w[u].x, x0, p);
+          p = dot4(w[u].y, x1, p);
+          p = dot4(w[u].z, x2, p);
+          p = dot4(w[u].w, x3, p);
+          acc = fmaf(sc[u], p, acc);
+        }
+      }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) y[row] = acc;
+    if (lane == 0 && row_ok) y[row] = acc;
   }
 }
 
