@@ -12,11 +12,12 @@
 //   TMA  fp16 activation planes [MT][64] x 2 halves x limbs -> smem ring   (warp 1)
 //   4 converter warps: smem int8 -> fp16 (exact: 0x6400|b trick) -> tcgen05.st
 //        into a TMEM operand ring; the weights never go back to shared memory
-//   1 MMA thread: per Q8 block two tcgen05.mma kind::f16 (K=16 each), A from
-//        TMEM, B = activations from smem, D = a fresh TMEM accumulator slot
-//   4 drain warps: tcgen05.ld the block's partial sums, acc += s * partial in
-//        f32 registers (the high and residual activation planes sit side by
-//        side on the MMA N axis and are recombined here), then the epilogue.
+//        (plus a copy scaled by 2^-11 that pairs with the residual activation plane)
+//   1 MMA thread: per Q8 block two tcgen05.mma kind::f16 (K=16 each) per plane,
+//        A from TMEM, B = activations from smem, all into one fresh TMEM
+//        accumulator slot: hi*q + lo*(q*2^-11) is summed by the tensor core
+//   8 drain warps: tcgen05.ld the block's partial sums (two blocks per wait),
+//        acc += s * partial in f32 registers, then the epilogue.
 // All hand-offs are mbarriers; every wait is bounded and reports through the
 // device status word instead of spinning for ever.
 //
@@ -40,23 +41,24 @@ constexpr int TC_KSTAGE = 128;   // K per stage
 constexpr int RAW_STAGES = 4;
 constexpr int ACT_STAGES = 3;
 constexpr int TA_STAGES = 2;
-constexpr int TA_COLS = 64;      // TMEM columns per converted stage: 128 fp16 per row
-constexpr int ACC_COL0 = TA_STAGES * TA_COLS;
-constexpr int TC_THREADS = 384;
+constexpr int TA_LIMB_COLS = 64; // TMEM columns per converted stage and copy: 128 fp16 per row
+constexpr int TC_THREADS = 512;  // 4 single-role warps, 4 converter warps, 8 drain warps
+constexpr int ACC_SLOTS = 4;     // TMEM accumulator ring (one Q8 block each)
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int RAW_BYTES = TC_ROWS * TC_KSTAGE;  // 16 KB
 
 template <int MT, int LIMBS>
 struct TcCfg {
-  static constexpr int NB = MT * LIMBS;                 // MMA N
-  static constexpr int ACC_SLOTS = (NB >= 128) ? 3 : 4; // TMEM accumulator ring
+  static constexpr int NB = MT * LIMBS;                 // activation rows staged per stage (planes stacked)
+  static constexpr int TA_COLS = TA_LIMB_COLS * LIMBS;  // weights, plus a copy scaled by 2^-11 for the residual plane
+  static constexpr int ACC_COL0 = TA_STAGES * TA_COLS;
   static constexpr int ACT_ATOM_BYTES = NB * 128;       // one 64-column half: NB rows x 128 B
   static constexpr int ACT_BYTES = 2 * ACT_ATOM_BYTES;
   static constexpr size_t SMEM_NEED = 1024 + (size_t)RAW_STAGES * RAW_BYTES + (size_t)ACT_STAGES * ACT_BYTES + 512;
   // the CTA allocates all of tensor memory, so ask for enough shared memory that only one CTA fits an SM
   static constexpr size_t SMEM = SMEM_NEED > 120 * 1024 ? SMEM_NEED : 120 * 1024;
-  static_assert(ACC_COL0 + ACC_SLOTS * NB <= (int)TMEM_COLS, "TMEM budget");
-  static_assert(NB % 16 == 0 && NB <= 256, "MMA N");
+  static_assert(ACC_COL0 + ACC_SLOTS * MT <= (int)TMEM_COLS, "TMEM budget");
+  static_assert(MT % 16 == 0 && MT <= 64, "MMA N");
 };
 
 struct TcParams {
@@ -97,13 +99,20 @@ __device__ __forceinline__ uint32_t cvt_pair(uint32_t w_xor80, uint32_t selector
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
+template <int N>
+__device__ __forceinline__ void tc_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
+  if constexpr (N == 32) tc_ld_32x32b_x32(taddr, r);
+  else if constexpr (N == 16) tc_ld_32x32b_x16(taddr, r);
+  else tc_ld_32x32b_x8(taddr, r);
+}
+
 template <int MT, int LIMBS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_ahi,
                   const __grid_constant__ CUtensorMap map_alo, const TcParams p) {
   using Cfg = TcCfg<MT, LIMBS>;
-  constexpr int NB = Cfg::NB;
-  constexpr int ACC_SLOTS = Cfg::ACC_SLOTS;
+  constexpr int TA_COLS = Cfg::TA_COLS;
+  constexpr int ACC_COL0 = Cfg::ACC_COL0;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -141,7 +150,7 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     for (int i = 0; i < RAW_STAGES; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 4); }
     for (int i = 0; i < ACT_STAGES; ++i) { mbar_init(&act_full[i], 1); mbar_init(&act_empty[i], 1); }
     for (int i = 0; i < TA_STAGES; ++i) { mbar_init(&ta_full[i], 4); mbar_init(&ta_empty[i], 1); }
-    for (int i = 0; i < ACC_SLOTS; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+    for (int i = 0; i < ACC_SLOTS; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 8); }
     fence_barrier_init();
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_ahi);
@@ -194,7 +203,7 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   } else if (warp == 2) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_f16(0, 0, TC_ROWS, NB);
+      constexpr uint32_t idesc = make_idesc_f16(0, 0, TC_ROWS, MT);
       int blk_count = 0;
       for (int i = 0; i < nst && ok; ++i) {
         int ts = i % TA_STAGES, as = i % ACT_STAGES;
@@ -208,13 +217,19 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           uint32_t sph = (uint32_t)(blk_count / ACC_SLOTS) & 1u;
           if (!mbar_wait(&acc_empty[slot], sph ^ 1u)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t d = tmem_base + ACC_COL0 + slot * NB;
+          const uint32_t d = tmem_base + ACC_COL0 + slot * MT;
+          // high plane against the weights, residual plane against the weights * 2^-11:
+          // both land in the same MT accumulator columns
 #pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            const int kk = blk * 2 + j;  // K=16 step inside the stage
-            const uint32_t a = tmem_base + ts * TA_COLS + kk * 8;
-            const uint64_t bdesc = make_desc_sw128(act_base + (kk >> 2) * Cfg::ACT_ATOM_BYTES + (kk & 3) * 32);
-            tc_mma_f16_ts(d, a, bdesc, idesc, (uint32_t)j);
+          for (int l = 0; l < LIMBS; ++l) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int kk = blk * 2 + j;  // K=16 step inside the stage
+              const uint32_t a = tmem_base + ts * TA_COLS + l * TA_LIMB_COLS + kk * 8;
+              const uint64_t bdesc = make_desc_sw128(act_base + (kk >> 2) * Cfg::ACT_ATOM_BYTES + l * MT * 128 +
+                                                     (kk & 3) * 32);
+              tc_mma_f16_ts(d, a, bdesc, idesc, (uint32_t)((l | j) != 0));
+            }
           }
           tc_commit(&acc_full[slot]);
           ++blk_count;
@@ -247,6 +262,16 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           r[2 * wi + 1] = cvt_pair(u, 0x4342);
         }
         tc_st_32x32b_x8(t_lane + ts * TA_COLS + c * 8, r);
+        if (LIMBS == 2) {
+          uint32_t r2[8];
+          const uint32_t scale_bits = 0x10001000u;  // 2^-11 in both halves: exact, stays normal (|q| >= 1 -> 2^-11)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            __half2 v = __hmul2(*reinterpret_cast<const __half2*>(&r[e]), *reinterpret_cast<const __half2*>(&scale_bits));
+            r2[e] = *reinterpret_cast<uint32_t*>(&v);
+          }
+          tc_st_32x32b_x8(t_lane + ts * TA_COLS + TA_LIMB_COLS + c * 8, r2);
+        }
       }
       tc_wait_st();
       tc_fence_before();
@@ -259,78 +284,73 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     if (!ok && lane == 0) atomicExch(p.status, 204);
   } else if (warp >= 8) {
     // ------------------------------------------------------------ drain + epilogue
+    // Two warps per lane quarter, each owning half of the token columns.  Blocks are taken two
+    // at a time so one tcgen05.wait::ld covers both loads: the TMEM read latency, not the
+    // arithmetic, is what bounds this role.
     const int qd = warp & 3;
+    const int half = (warp - 8) >> 2;
+    constexpr int HC = MT / 2;  // token columns per drain warp
     const int64_t n = n0 + qd * 32 + lane;
     const bool n_ok = n < p.n;
-    const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16) + ACC_COL0;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16) + ACC_COL0 + half * HC;
     const int64_t kb_per_row = p.k >> 5;
     const float* srow = p.s + (n_ok ? n : 0) * kb_per_row;
-    constexpr int CH = MT < 32 ? MT : 32;
-    float acc[MT];
+    float acc[HC];
 #pragma unroll
-    for (int j = 0; j < MT; ++j) acc[j] = 0.f;
+    for (int j = 0; j < HC; ++j) acc[j] = 0.f;
     int blk_count = 0;
     for (int i = 0; i < nst && ok; ++i) {
       float4 sc4 = make_float4(0.f, 0.f, 0.f, 0.f);
       if (n_ok) sc4 = __ldg(reinterpret_cast<const float4*>(srow + (int64_t)(st_begin + i) * 4));
       const float scs[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
 #pragma unroll
-      for (int blk = 0; blk < 4; ++blk) {
-        int slot = blk_count % ACC_SLOTS;
-        uint32_t sph = (uint32_t)(blk_count / ACC_SLOTS) & 1u;
-        if (!mbar_wait(&acc_full[slot], sph)) { ok = false; break; }
+      for (int pr = 0; pr < 2; ++pr) {
+        const int s0 = blk_count % ACC_SLOTS, s1 = (blk_count + 1) % ACC_SLOTS;
+        const uint32_t ph0 = (uint32_t)(blk_count / ACC_SLOTS) & 1u, ph1 = (uint32_t)((blk_count + 1) / ACC_SLOTS) & 1u;
+        if (!mbar_wait(&acc_full[s0], ph0) || !mbar_wait(&acc_full[s1], ph1)) { ok = false; break; }
         tc_fence_after();
-        const float sc = scs[blk];
-        const uint32_t ta = t_lane + slot * NB;
-#pragma unroll
-        for (int ch = 0; ch < MT / CH; ++ch) {
-          uint32_t hi[CH], lo[CH];
-          if constexpr (CH == 32) {
-            tc_ld_32x32b_x32(ta + ch * CH, hi);
-            if (LIMBS == 2) tc_ld_32x32b_x32(ta + MT + ch * CH, lo);
-          } else {
-            tc_ld_32x32b_x16(ta + ch * CH, hi);
-            if (LIMBS == 2) tc_ld_32x32b_x16(ta + MT + ch * CH, lo);
-          }
-          tc_wait_ld();
-          if (ch == MT / CH - 1) {
-            // every column of the slot is in registers: hand it back before the math
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[slot]);
-          }
-#pragma unroll
-          for (int j = 0; j < CH; ++j) {
-            float t = __uint_as_float(hi[j]);
-            if (LIMBS == 2) t = fmaf(__uint_as_float(lo[j]), 4.8828125e-4f, t);
-            acc[ch * CH + j] = fmaf(sc, t, acc[ch * CH + j]);
-          }
+        uint32_t b0[HC], b1[HC];
+        tc_ld_cols<HC>(t_lane + s0 * MT, b0);
+        tc_ld_cols<HC>(t_lane + s1 * MT, b1);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&acc_empty[s0]);
+          mbar_arrive(&acc_empty[s1]);
         }
-        ++blk_count;
+        const float sc0 = scs[2 * pr], sc1 = scs[2 * pr + 1];
+#pragma unroll
+        for (int j = 0; j < HC; ++j) {
+          acc[j] = fmaf(sc0, __uint_as_float(b0[j]), acc[j]);
+          acc[j] = fmaf(sc1, __uint_as_float(b1[j]), acc[j]);
+        }
+        blk_count += 2;
       }
     }
     if (!ok && lane == 0) atomicExch(p.status, 205);
 
     if (ok) {
+      const int64_t mb = m0 + half * HC;  // first token of this warp's columns
       if (p.splits > 1) {
         if (n_ok) {
 #pragma unroll
-          for (int j = 0; j < MT; ++j)
-            if (m0 + j < p.m) p.partials[((int64_t)split * p.m + m0 + j) * p.n + n] = acc[j];
+          for (int j = 0; j < HC; ++j)
+            if (mb + j < p.m) p.partials[((int64_t)split * p.m + mb + j) * p.n + n] = acc[j];
         }
       } else if (p.epilogue == EPI_SWIGLU) {
 #pragma unroll
-        for (int j = 0; j < MT; ++j) {
+        for (int j = 0; j < HC; ++j) {
           float other = __shfl_xor_sync(0xffffffffu, acc[j], 1);
-          if (!(lane & 1) && n + 1 < p.n && m0 + j < p.m)
-            store_c(p, (m0 + j) * p.ldc + (n >> 1), __fmul_rn(silu_f(acc[j]), other));
+          if (!(lane & 1) && n + 1 < p.n && mb + j < p.m)
+            store_c(p, (mb + j) * p.ldc + (n >> 1), __fmul_rn(silu_f(acc[j]), other));
         }
       } else if (n_ok) {
 #pragma unroll
-        for (int j = 0; j < MT; ++j)
-          if (m0 + j < p.m) {
+        for (int j = 0; j < HC; ++j)
+          if (mb + j < p.m) {
             float v = acc[j];
-            int64_t ci = (m0 + j) * p.ldc + n;
+            int64_t ci = (mb + j) * p.ldc + n;
             if (p.epilogue == EPI_RESIDUAL) v = __fadd_rn(v, load_aux(p, ci));
             store_c(p, ci, v);
           }
