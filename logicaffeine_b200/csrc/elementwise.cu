@@ -114,8 +114,11 @@ __global__ void act_split_kernel(const float* __restrict__ x, ActOut o, int64_t 
   if (i < count) act_store(o, i, x[i]);
 }
 
+// history (optional): row `*step_counter` of a [history_rows][rows] log also receives the ids,
+// so a captured step needs no per-step pointer.
 __global__ void argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ tokens,
-                              int32_t* __restrict__ history, int64_t vocab) {
+                              int32_t* __restrict__ history, const int32_t* __restrict__ step_counter,
+                              int64_t history_rows, int64_t vocab) {
   __shared__ float bv[32];
   __shared__ int bi[32];
   const int64_t row = blockIdx.x;
@@ -152,7 +155,10 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int32_t* __restr
       }
     if (idx == 0x7fffffff) idx = 0;  // all NaN / empty row
     tokens[row] = idx;
-    if (history) history[row] = idx;
+    if (history) {
+      int64_t slot = step_counter ? *step_counter : 0;
+      if (slot < history_rows) history[slot * gridDim.x + row] = idx;
+    }
   }
 }
 
@@ -209,10 +215,12 @@ logos_status_t launch_residual_rmsnorm(float* h, const float* delta, int parts, 
   return check_launch("residual_rmsnorm_kernel");
 }
 
-logos_status_t launch_argmax(const float* logits, int32_t* tokens, int32_t* history_or_null, int64_t rows,
-                             int64_t vocab, cudaStream_t st) {
+logos_status_t launch_argmax(const float* logits, int32_t* tokens, int32_t* history_or_null,
+                             const int32_t* step_counter_or_null, int64_t history_rows, int64_t rows, int64_t vocab,
+                             cudaStream_t st) {
   if (rows == 0) return LOGOS_OK;
-  argmax_kernel<<<(unsigned)rows, 1024, 0, st>>>(logits, tokens, history_or_null, vocab);
+  argmax_kernel<<<(unsigned)rows, 1024, 0, st>>>(logits, tokens, history_or_null, step_counter_or_null, history_rows,
+                                                 vocab);
   count_launch(LK_ELEMWISE);
   return check_launch("argmax_kernel");
 }

@@ -20,6 +20,8 @@
 #include "ops.cuh"
 #include "tp.cuh"
 
+#include <stdlib.h>
+
 #include <vector>
 
 namespace logos {
@@ -57,8 +59,13 @@ struct Model {
   float* logits = nullptr;   // [B][V]
   int32_t* tokens = nullptr; // [B] current input / last output
   int32_t* seq_len = nullptr;
-  int32_t* history = nullptr; // [history_cap][B]
+  int32_t* history = nullptr; // [history_cap][B] token log of the current decode_steps call
   int64_t  history_cap = 0;
+  int32_t* step_counter = nullptr;  // device: steps taken since the current decode_steps call began
+  // one decode step captured as a CUDA graph (launch-bound at small per-step times)
+  cudaGraphExec_t step_graph = nullptr;
+  bool graph_failed = false;
+  int64_t eager_sample_steps = 0;
   int32_t* prompt = nullptr;  // [T][B]
   int64_t  prompt_cap = 0;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -120,6 +127,7 @@ void destroy(Model* m) {
   if (m->stream) cudaStreamSynchronize(m->stream);
   tp_destroy(&m->tp);
   for (void* p : m->allocs) cudaFree(p);
+  if (m->step_graph) cudaGraphExecDestroy(m->step_graph);
   for (cudaEvent_t e : m->prof_events) cudaEventDestroy(e);
   if (m->ev0) cudaEventDestroy(m->ev0);
   if (m->ev1) cudaEventDestroy(m->ev1);
@@ -209,6 +217,10 @@ logos_status_t build(Model* m, const void* nccl_id) {
   LOGOS_TRY(planes(&m->ffn, B * m->f_local));
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->partials), (int64_t)m->max_splits * B * H * 4));
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->logits), B * c.vocab * 4));
+  m->history_cap = c.l_max;
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->history), m->history_cap * B * 4));
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->step_counter), 256));
+  LOGOS_CUDA_TRY(cudaMemsetAsync(m->step_counter, 0, 256, m->stream));
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->tokens), B * 4));
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->seq_len), B * 4));
   LOGOS_CUDA_TRY(cudaMemsetAsync(m->tokens, 0, (size_t)B * 4, m->stream));
@@ -226,9 +238,10 @@ __global__ void sum_partials_kernel(float* __restrict__ p, int parts, int64_t st
   p[i] = v;
 }
 
-__global__ void bump_len_kernel(int32_t* seq_len, int b, int l_max) {
+__global__ void bump_len_kernel(int32_t* seq_len, int32_t* step_counter, int b, int l_max) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < b && seq_len[i] < l_max) seq_len[i] += 1;
+  if (i == 0) *step_counter += 1;
 }
 
 // GEMM producing f32 partials [splits][B][N] in m->partials; returns the split count.
@@ -269,7 +282,7 @@ logos_status_t gemm_partials(Model* m, const ActOut& a, const Q8Mat& w, int* spl
 }
 
 // One lock-step decode step on the model's stream.  tokens_in: [B] device.
-logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, int32_t* history_slot) {
+logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_tokens) {
   const logos_llm_config_t& c = m->cfg;
   const int64_t B = c.batch, H = c.hidden, D = c.head_dim;
   cudaStream_t st = m->stream;
@@ -348,15 +361,21 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, int32_t* hi
       LOGOS_TRY(launch_q8_gemm(g, st));
     }
     ProfScope ps(m, PROF_ELEMWISE);
-    LOGOS_TRY(launch_argmax(m->logits, m->tokens, history_slot, B, c.vocab, st));
+    LOGOS_TRY(launch_argmax(m->logits, m->tokens, log_tokens ? m->history : nullptr, m->step_counter, m->history_cap, B,
+                            c.vocab, st));
     m->launch_counter += 3;
   }
   ProfScope ps_tail(m, PROF_ELEMWISE);
-  bump_len_kernel<<<(unsigned)((B + 127) / 128), 128, 0, st>>>(m->seq_len, (int)B, (int)c.l_max);
+  bump_len_kernel<<<(unsigned)((B + 127) / 128), 128, 0, st>>>(m->seq_len, m->step_counter, (int)B, (int)c.l_max);
   LOGOS_TRY(check_launch("bump_len_kernel"));
   m->launch_counter += 1;
   m->launches_per_step = m->launch_counter;
   return LOGOS_OK;
+}
+
+bool graphs_enabled() {
+  const char* e = getenv("LOGOS_B200_GRAPH");
+  return !(e && e[0] == '0');
 }
 
 logos_status_t check_cfg(const logos_llm_config_t& c) {
@@ -434,7 +453,7 @@ logos_status_t logos_llm_prefill(logos_handle_t model, const int32_t* tokens_hos
       for (int64_t p = 0; p < t; ++p) tr[(size_t)(p * B + b)] = tokens_host[b * t + p];
     LOGOS_CUDA_TRY(cudaMemcpyAsync(m->prompt, tr.data(), tr.size() * 4, cudaMemcpyHostToDevice, m->stream));
     LOGOS_CUDA_TRY(cudaMemsetAsync(m->seq_len, 0, (size_t)B * 4, m->stream));
-    for (int64_t p = 0; p < t; ++p) LOGOS_TRY(step(m, m->prompt + p * B, p == t - 1, nullptr));
+    for (int64_t p = 0; p < t; ++p) LOGOS_TRY(step(m, m->prompt + p * B, p == t - 1, false));
     LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
     return LOGOS_OK;
   });
@@ -479,12 +498,35 @@ logos_status_t logos_llm_decode_steps(logos_handle_t model, int64_t steps, int32
     const int64_t B = m->cfg.batch;
     if (steps < 0) return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_decode_steps: negative step count");
     if (steps == 0) return LOGOS_OK;
-    if (m->history_cap < steps) {
-      LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->history), steps * B * 4));
-      m->history_cap = steps;
-    }
+    if (steps > m->history_cap)
+      return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_decode_steps: %lld steps exceed l_max = %lld", (long long)steps,
+                  (long long)m->history_cap);
+    LOGOS_CUDA_TRY(cudaMemsetAsync(m->step_counter, 0, sizeof(int32_t), m->stream));
     LOGOS_CUDA_TRY(cudaEventRecord(m->ev0, m->stream));
-    for (int64_t i = 0; i < steps; ++i) LOGOS_TRY(step(m, m->tokens, true, m->history + i * B));
+    for (int64_t i = 0; i < steps; ++i) {
+      // The first step of a model runs eagerly (it sizes the library's scratch buffers); after
+      // that one step is captured once and replayed: all of its arguments are device-resident.
+      if (!m->step_graph && !m->graph_failed && m->eager_sample_steps >= 1 && graphs_enabled()) {
+        cudaGraph_t graph = nullptr;
+        bool good = cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+        logos_status_t cs = good ? step(m, m->tokens, true, true) : LOGOS_ERROR;
+        cudaError_t ee = good ? cudaStreamEndCapture(m->stream, &graph) : cudaErrorUnknown;
+        good = good && cs == LOGOS_OK && ee == cudaSuccess && graph &&
+               cudaGraphInstantiate(&m->step_graph, graph, 0) == cudaSuccess;
+        if (graph) cudaGraphDestroy(graph);
+        if (!good) {
+          cudaGetLastError();
+          m->step_graph = nullptr;
+          m->graph_failed = true;  // stay on the eager path
+        }
+      }
+      if (m->step_graph) {
+        LOGOS_CUDA_TRY(cudaGraphLaunch(m->step_graph, m->stream));
+      } else {
+        LOGOS_TRY(step(m, m->tokens, true, true));
+        m->eager_sample_steps += 1;
+      }
+    }
     LOGOS_CUDA_TRY(cudaEventRecord(m->ev1, m->stream));
     if (tokens_host_or_null)
       LOGOS_CUDA_TRY(cudaMemcpyAsync(tokens_host_or_null, m->history, (size_t)(steps * B) * 4, cudaMemcpyDeviceToHost, m->stream));
@@ -506,7 +548,7 @@ logos_status_t logos_llm_profile_step(logos_handle_t model, double* ms_by_class_
     m->profiling = true;
     m->prof_used = 0;
     m->prof_class.clear();
-    logos_status_t s = step(m, m->tokens, true, nullptr);
+    logos_status_t s = step(m, m->tokens, true, false);
     m->profiling = false;
     LOGOS_TRY(s);
     LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));

@@ -108,7 +108,8 @@ logos_status_t launch_bf16_to_f16(const __nv_bfloat16* x, __half* y, int64_t cou
 // f32 [count] -> activation planes
 logos_status_t launch_act_split(const float* x, ActOut o, int64_t count, cudaStream_t st);
 // tokens[row] = argmax(logits[row]) with the lowest index winning ties
-logos_status_t launch_argmax(const float* logits, int32_t* tokens, int32_t* history_or_null, int64_t rows,
-                             int64_t vocab, cudaStream_t st);
+logos_status_t launch_argmax(const float* logits, int32_t* tokens, int32_t* history_or_null,
+                             const int32_t* step_counter_or_null, int64_t history_rows, int64_t rows, int64_t vocab,
+                             cudaStream_t st);
 
 }  // namespace logos
