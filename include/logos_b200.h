@@ -150,6 +150,11 @@ LOGOS_API logos_status_t logos_q8_gemm_f32(logos_handle_t a /*f32 [M][K]*/, logo
                                  logos_handle_t c /*f32 [M][N]*/, int64_t m, int64_t n, int64_t k,
                                  void* stream_or_null);
 
+/* Tracing aid: with a device buffer of at least 64*16 int64 set, CTA (0,0,0) of every
+ * tcgen05 GEMM launch stores SM-clock timestamps of its pipeline roles per 128-column
+ * K stage ([stage][16]); NULL turns tracing off. */
+LOGOS_API logos_status_t logos_gemm_trace_buffer(logos_handle_t buf_or_null);
+
 /* Same contract as logos_q8_gemm, always on the plain SIMT kernel (no tensor
  * cores, no split-K): the on-device cross-check the tests hold the tcgen05
  * kernel against, and the path for shapes the tcgen05 kernel does not take. */

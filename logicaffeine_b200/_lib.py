@@ -72,6 +72,7 @@ _SIGNATURES = {
     "logos_q8_gemv": (None, [H, H, H, H, I64, I64, PTR]),
     "logos_q8_gemm": (None, [H, H, H, H, I64, I64, I64, I32c, H, PTR]),
     "logos_q8_gemm_f32": (None, [H, H, H, H, I64, I64, I64, PTR]),
+    "logos_gemm_trace_buffer": (None, [H]),
     "logos_q8_gemm_simt": (None, [H, H, H, H, I64, I64, I64, I32c, H, PTR]),
     "logos_rope_table": (None, [PTR, I64, I64, C.c_double]),
     "logos_kv_append_rope": (None, [H, H, H, H, H, H, I64, I64, I64, I64, PTR]),

@@ -51,19 +51,23 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 // of SM clock have passed.  Returns false when it gave up; the caller records a
 // status code and leaves.
 constexpr long long kWaitCycles = 4000000000ll;
+__device__ __forceinline__ bool mbar_try(uint32_t bar_addr, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar_addr), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   const uint32_t a = smem_u32(bar);
+  if (mbar_try(a, parity)) return true;  // fast path: no clock read
   const long long start = clock64();
   for (;;) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(a), "r"(parity)
-        : "memory");
-    if (ok) return true;
+    if (mbar_try(a, parity)) return true;
     if (clock64() - start > kWaitCycles) return false;
   }
 }
@@ -158,6 +162,17 @@ __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, 
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] = A[tmem] * B[smem desc] + D * 2^-SHIFT   (scale-input-d form, f16/tf32 kinds only)
+template <int SHIFT>
+__device__ __forceinline__ void tc_mma_f16_ts_scaled_d(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                                       uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, 1, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%4, %4, %4, %4}, p, %5;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(0), "n"(SHIFT)
       : "memory");
 }
 // D[tmem] (+)= A[smem desc] * B[smem desc]

@@ -217,6 +217,22 @@ static logos_status_t gemm_abi(logos_handle_t a, logos_handle_t q, logos_handle_
 
 extern "C" {
 
+// Tracing: when a buffer of at least 64*16 int64 is set, CTA (0,0,0) of every tcgen05 GEMM
+// launch stores SM-clock timestamps of its pipeline roles per K stage ([stage][16]); null turns
+// it off.  A development aid for reading where a stage's time goes.
+logos_status_t logos_gemm_trace_buffer(logos_handle_t buf_or_null) {
+  return guarded([&]() -> logos_status_t {
+    if (!buf_or_null) {
+      gemm_set_trace(nullptr);
+      return LOGOS_OK;
+    }
+    long long* p = nullptr;
+    LOGOS_TRY(buf_ptr<long long>(buf_or_null, 64 * 16, "trace", &p));
+    gemm_set_trace(p);
+    return LOGOS_OK;
+  });
+}
+
 // f32 activations, f32 output: the form the decode step uses internally (the
 // activations are split into two fp16 planes so the tensor-core product keeps
 // f32-class accuracy).

@@ -12,10 +12,10 @@
 //   TMA  fp16 activation planes [MT][64] x 2 halves x limbs -> smem ring   (warp 1)
 //   4 converter warps: smem int8 -> fp16 (exact: 0x6400|b trick) -> tcgen05.st
 //        into a TMEM operand ring; the weights never go back to shared memory
-//        (plus a copy scaled by 2^-11 that pairs with the residual activation plane)
-//   1 MMA thread: per Q8 block two tcgen05.mma kind::f16 (K=16 each) per plane,
-//        A from TMEM, B = activations from smem, all into one fresh TMEM
-//        accumulator slot: hi*q + lo*(q*2^-11) is summed by the tensor core
+//   2 MMA warps (alternate stages): per Q8 block two tcgen05.mma kind::f16 (K=16
+//        each) per plane, A from TMEM, B = activations from smem, into a fresh TMEM
+//        accumulator: first q*lo', then q*hi + D*2^-11 through the MMA's own
+//        accumulator scaling, so hi + lo*2^-11 is recombined on the tensor core
 //   8 drain warps: tcgen05.ld the block's partial sums (two blocks per wait),
 //        acc += s * partial in f32 registers, then the epilogue.
 // All hand-offs are mbarriers; every wait is bounded and reports through the
@@ -39,25 +39,25 @@ using namespace ptx;
 constexpr int TC_ROWS = 128;     // weight rows per CTA (MMA M)
 constexpr int TC_KSTAGE = 128;   // K per stage
 constexpr int RAW_STAGES = 4;
-constexpr int ACT_STAGES = 3;
-constexpr int TA_STAGES = 2;
+constexpr int ACT_STAGES = 4;
+constexpr int TA_STAGES = 4;
 constexpr int TA_LIMB_COLS = 64; // TMEM columns per converted stage and copy: 128 fp16 per row
 constexpr int TC_THREADS = 512;  // 4 single-role warps, 4 converter warps, 8 drain warps
-constexpr int ACC_SLOTS = 4;     // TMEM accumulator ring (one Q8 block each)
+constexpr int ACC_PAIRS = 2;     // TMEM accumulator ring: each entry holds two Q8 blocks
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int RAW_BYTES = TC_ROWS * TC_KSTAGE;  // 16 KB
 
 template <int MT, int LIMBS>
 struct TcCfg {
   static constexpr int NB = MT * LIMBS;                 // activation rows staged per stage (planes stacked)
-  static constexpr int TA_COLS = TA_LIMB_COLS * LIMBS;  // weights, plus a copy scaled by 2^-11 for the residual plane
+  static constexpr int TA_COLS = TA_LIMB_COLS;
   static constexpr int ACC_COL0 = TA_STAGES * TA_COLS;
   static constexpr int ACT_ATOM_BYTES = NB * 128;       // one 64-column half: NB rows x 128 B
   static constexpr int ACT_BYTES = 2 * ACT_ATOM_BYTES;
   static constexpr size_t SMEM_NEED = 1024 + (size_t)RAW_STAGES * RAW_BYTES + (size_t)ACT_STAGES * ACT_BYTES + 512;
   // the CTA allocates all of tensor memory, so ask for enough shared memory that only one CTA fits an SM
   static constexpr size_t SMEM = SMEM_NEED > 120 * 1024 ? SMEM_NEED : 120 * 1024;
-  static_assert(ACC_COL0 + ACC_SLOTS * MT <= (int)TMEM_COLS, "TMEM budget");
+  static_assert(ACC_COL0 + ACC_PAIRS * 2 * MT <= (int)TMEM_COLS, "TMEM budget");
   static_assert(MT % 16 == 0 && MT <= 64, "MMA N");
 };
 
@@ -74,7 +74,15 @@ struct TcParams {
   int splits;
   int stages_total;
   int* status;
+  long long* trace;  // optional: SM-clock timestamps of CTA (0,0,0), [stage][16]
 };
+
+// Timestamp slot `ev` of stage `i` (tracing only; CTA 0, one lane per role).
+#define TC_TRACE(i, ev)                                                                          \
+  do {                                                                                           \
+    if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (i) < 64)            \
+      p.trace[(i) * 16 + (ev)] = clock64();                                                      \
+  } while (0)
 
 __device__ __forceinline__ float silu_f(float g) { return __fdiv_rn(g, 1.0f + expf(-g)); }
 
@@ -125,9 +133,9 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   uint64_t* act_empty = act_full + ACT_STAGES;  // [ACT_STAGES]
   uint64_t* ta_full = act_empty + ACT_STAGES;   // [TA_STAGES]
   uint64_t* ta_empty = ta_full + TA_STAGES;     // [TA_STAGES]
-  uint64_t* acc_full = ta_empty + TA_STAGES;    // [ACC_SLOTS]
-  uint64_t* acc_empty = acc_full + ACC_SLOTS;   // [ACC_SLOTS]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_SLOTS);
+  uint64_t* acc_full = ta_empty + TA_STAGES;    // [ACC_PAIRS]
+  uint64_t* acc_empty = acc_full + ACC_PAIRS;   // [ACC_PAIRS]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_PAIRS);
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -150,7 +158,7 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     for (int i = 0; i < RAW_STAGES; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 4); }
     for (int i = 0; i < ACT_STAGES; ++i) { mbar_init(&act_full[i], 1); mbar_init(&act_empty[i], 1); }
     for (int i = 0; i < TA_STAGES; ++i) { mbar_init(&ta_full[i], 4); mbar_init(&ta_empty[i], 1); }
-    for (int i = 0; i < ACC_SLOTS; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 8); }
+    for (int i = 0; i < ACC_PAIRS; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 8); }
     fence_barrier_init();
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_ahi);
@@ -175,6 +183,7 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         int st = i % RAW_STAGES;
         uint32_t ph = (uint32_t)(i / RAW_STAGES) & 1u;
         if (!mbar_wait(&raw_empty[st], ph ^ 1u)) { ok = false; break; }
+        TC_TRACE(i, 0);
         mbar_arrive_expect_tx(&raw_full[st], RAW_BYTES);
         tma_load_2d_hint(raw + st * RAW_BYTES, &map_q, &raw_full[st], (st_begin + i) * TC_KSTAGE, (int)n0, pol);
       }
@@ -188,6 +197,7 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         int st = i % ACT_STAGES;
         uint32_t ph = (uint32_t)(i / ACT_STAGES) & 1u;
         if (!mbar_wait(&act_empty[st], ph ^ 1u)) { ok = false; break; }
+        TC_TRACE(i, 1);
         mbar_arrive_expect_tx(&act_full[st], Cfg::ACT_BYTES);
         uint8_t* sb = act + st * Cfg::ACT_BYTES;
         int x = (st_begin + i) * TC_KSTAGE;
@@ -200,45 +210,75 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
       if (!ok) atomicExch(p.status, 202);
     }
-  } else if (warp == 2) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_f16(0, 0, TC_ROWS, MT);
-      int blk_count = 0;
-      for (int i = 0; i < nst && ok; ++i) {
-        int ts = i % TA_STAGES, as = i % ACT_STAGES;
-        uint32_t tph = (uint32_t)(i / TA_STAGES) & 1u, aph = (uint32_t)(i / ACT_STAGES) & 1u;
-        if (!mbar_wait(&ta_full[ts], tph) || !mbar_wait(&act_full[as], aph)) { ok = false; break; }
+  } else if (warp == 2 || warp == 3) {
+    // ------------------------------------------------------------ MMA issuers
+    // Two warps take alternate stages: what bounds this role is the serial latency of
+    // wait -> issue -> commit, not tensor throughput, so two chains run side by side.  Each
+    // warp runs its loop with all lanes (addresses and descriptors stay warp-uniform) and one
+    // elected lane issues the tcgen05 instructions.  A stage is two pairs of Q8 blocks; a pair
+    // owns one accumulator ring entry of 2*MT columns.
+    constexpr uint32_t idesc = make_idesc_f16(0, 0, TC_ROWS, MT);
+    static_assert(ACC_PAIRS == 2 && TA_STAGES % 2 == 0 && ACT_STAGES % 2 == 0,
+                  "ring sizes are tied to the two-warp schedule below");
+    for (int i = 0; i < nst && ok; ++i) {
+      if ((i & 1) != warp - 2) {
+        // Not this warp's stage.  An mbarrier wait only tells odd phases from even ones, so
+        // this warp still steps through the accumulator ring's phases one at a time: the wait
+        // below is for the release of its own previous stage.
+        const uint32_t sph = (uint32_t)i & 1u;
+        if (!mbar_wait(&acc_empty[0], sph ^ 1u) || !mbar_wait(&acc_empty[1], sph ^ 1u)) ok = false;
+        continue;
+      }
+      const int ts = i % TA_STAGES, as = i % ACT_STAGES;
+      const uint32_t tph = (uint32_t)(i / TA_STAGES) & 1u, aph = (uint32_t)(i / ACT_STAGES) & 1u;
+      if (!mbar_wait(&ta_full[ts], tph)) { ok = false; break; }
+      if (lane == 0) TC_TRACE(i, 2);
+      if (!mbar_wait(&act_full[as], aph)) { ok = false; break; }
+      if (lane == 0) TC_TRACE(i, 3);
+      tc_fence_after();
+      const uint32_t act_base = smem_u32(act + as * Cfg::ACT_BYTES);
+#pragma unroll
+      for (int pr = 0; pr < 2; ++pr) {
+        const int pair = 2 * i + pr;
+        const int slot = pair % ACC_PAIRS;
+        const uint32_t sph = (uint32_t)(pair / ACC_PAIRS) & 1u;
+        if (pr == 1 && lane == 0) TC_TRACE(i, 11);
+        if (!mbar_wait(&acc_empty[slot], sph ^ 1u)) { ok = false; break; }
+        if (pr == 1 && lane == 0) TC_TRACE(i, 12);
         tc_fence_after();
-        const uint32_t act_base = smem_u32(act + as * Cfg::ACT_BYTES);
+        if (elect_one()) {
 #pragma unroll
-        for (int blk = 0; blk < 4; ++blk) {
-          int slot = blk_count % ACC_SLOTS;
-          uint32_t sph = (uint32_t)(blk_count / ACC_SLOTS) & 1u;
-          if (!mbar_wait(&acc_empty[slot], sph ^ 1u)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t d = tmem_base + ACC_COL0 + slot * MT;
-          // high plane against the weights, residual plane against the weights * 2^-11:
-          // both land in the same MT accumulator columns
+          for (int bb = 0; bb < 2; ++bb) {
+            const int blk = 2 * pr + bb;
+            const uint32_t d = tmem_base + ACC_COL0 + (slot * 2 + bb) * MT;
+            // d = q * lo' first, then d = q * hi + d * 2^-11: the residual plane is folded in by
+            // the accumulator scaling of the MMA itself, from one copy of the weights
 #pragma unroll
-          for (int l = 0; l < LIMBS; ++l) {
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
+            for (int u = 0; u < 2 * LIMBS; ++u) {
+              const int l = (LIMBS == 2) ? 1 - (u >> 1) : 0, j = u & 1;
               const int kk = blk * 2 + j;  // K=16 step inside the stage
-              const uint32_t a = tmem_base + ts * TA_COLS + l * TA_LIMB_COLS + kk * 8;
+              const uint32_t a = tmem_base + ts * TA_COLS + kk * 8;
               const uint64_t bdesc = make_desc_sw128(act_base + (kk >> 2) * Cfg::ACT_ATOM_BYTES + l * MT * 128 +
                                                      (kk & 3) * 32);
-              tc_mma_f16_ts(d, a, bdesc, idesc, (uint32_t)((l | j) != 0));
+              if (LIMBS == 2 && u == 2) tc_mma_f16_ts_scaled_d<11>(d, a, bdesc, idesc);
+              else tc_mma_f16_ts(d, a, bdesc, idesc, (uint32_t)(u != 0));
             }
           }
+          if (pr == 1) TC_TRACE(i, 13);
           tc_commit(&acc_full[slot]);
-          ++blk_count;
+          if (pr == 1) TC_TRACE(i, 14);
         }
+        __syncwarp();
+        if (pr == 1 && lane == 0) TC_TRACE(i, 15);
+      }
+      if (elect_one()) {
         tc_commit(&ta_empty[ts]);
         tc_commit(&act_empty[as]);
       }
-      if (!ok) atomicExch(p.status, 203);
+      __syncwarp();
+      if (lane == 0) TC_TRACE(i, 4);
     }
+    if (!ok && lane == 0) atomicExch(p.status, 203);
   } else if (warp >= 4 && warp < 8) {
     // ------------------------------------------------------------ converters: int8 smem -> fp16 TMEM
     const int qd = warp & 3;
@@ -247,7 +287,10 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     for (int i = 0; i < nst; ++i) {
       int rs = i % RAW_STAGES, ts = i % TA_STAGES;
       uint32_t rph = (uint32_t)(i / RAW_STAGES) & 1u, tph = (uint32_t)(i / TA_STAGES) & 1u;
-      if (!mbar_wait(&raw_full[rs], rph) || !mbar_wait(&ta_empty[ts], tph ^ 1u)) { ok = false; break; }
+      if (!mbar_wait(&raw_full[rs], rph)) { ok = false; break; }
+      if (warp == 4 && lane == 0) TC_TRACE(i, 5);
+      if (!mbar_wait(&ta_empty[ts], tph ^ 1u)) { ok = false; break; }
+      if (warp == 4 && lane == 0) TC_TRACE(i, 6);
       tc_fence_after();
       const uint8_t* rb = raw + rs * RAW_BYTES;
 #pragma unroll
@@ -262,18 +305,9 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           r[2 * wi + 1] = cvt_pair(u, 0x4342);
         }
         tc_st_32x32b_x8(t_lane + ts * TA_COLS + c * 8, r);
-        if (LIMBS == 2) {
-          uint32_t r2[8];
-          const uint32_t scale_bits = 0x10001000u;  // 2^-11 in both halves: exact, stays normal (|q| >= 1 -> 2^-11)
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            __half2 v = __hmul2(*reinterpret_cast<const __half2*>(&r[e]), *reinterpret_cast<const __half2*>(&scale_bits));
-            r2[e] = *reinterpret_cast<uint32_t*>(&v);
-          }
-          tc_st_32x32b_x8(t_lane + ts * TA_COLS + TA_LIMB_COLS + c * 8, r2);
-        }
       }
       tc_wait_st();
+      if (warp == 4 && lane == 0) TC_TRACE(i, 7);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
@@ -305,26 +339,27 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       const float scs[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
 #pragma unroll
       for (int pr = 0; pr < 2; ++pr) {
-        const int s0 = blk_count % ACC_SLOTS, s1 = (blk_count + 1) % ACC_SLOTS;
-        const uint32_t ph0 = (uint32_t)(blk_count / ACC_SLOTS) & 1u, ph1 = (uint32_t)((blk_count + 1) / ACC_SLOTS) & 1u;
-        if (!mbar_wait(&acc_full[s0], ph0) || !mbar_wait(&acc_full[s1], ph1)) { ok = false; break; }
+        const int pair = blk_count >> 1;
+        const int slot = pair % ACC_PAIRS;
+        const uint32_t fph = (uint32_t)(pair / ACC_PAIRS) & 1u;
+        if (!mbar_wait(&acc_full[slot], fph)) { ok = false; break; }
+        if (warp == 8 && lane == 0 && pr == 0) TC_TRACE(i, 8);
         tc_fence_after();
         uint32_t b0[HC], b1[HC];
-        tc_ld_cols<HC>(t_lane + s0 * MT, b0);
-        tc_ld_cols<HC>(t_lane + s1 * MT, b1);
+        tc_ld_cols<HC>(t_lane + (slot * 2) * MT, b0);
+        tc_ld_cols<HC>(t_lane + (slot * 2 + 1) * MT, b1);
         tc_wait_ld();
+        if (warp == 8 && lane == 0 && pr == 0) TC_TRACE(i, 9);
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(&acc_empty[s0]);
-          mbar_arrive(&acc_empty[s1]);
-        }
+        if (lane == 0) mbar_arrive(&acc_empty[slot]);
         const float sc0 = scs[2 * pr], sc1 = scs[2 * pr + 1];
 #pragma unroll
         for (int j = 0; j < HC; ++j) {
           acc[j] = fmaf(sc0, __uint_as_float(b0[j]), acc[j]);
           acc[j] = fmaf(sc1, __uint_as_float(b1[j]), acc[j]);
         }
+        if (warp == 8 && lane == 0 && pr == 0) TC_TRACE(i, 10);
         blk_count += 2;
       }
     }
@@ -361,12 +396,15 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   tc_fence_before();
   __syncthreads();
   if (warp == 3) {
+    __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
 // ---------------------------------------------------------------- host side
+long long* g_trace = nullptr;  // set through logos_gemm_trace_buffer; null = tracing off
+
 struct MapKey {
   const void* base;
   uint64_t inner, outer, pitch;
@@ -425,6 +463,7 @@ logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
   p.splits = g.splits > 1 ? g.splits : 1;
   p.stages_total = (int)(g.k / TC_KSTAGE);
   p.status = kernel_status_ptr(g.device);
+  p.trace = g_trace;
   if (!p.status) return fail(LOGOS_ERROR, "q8_gemm: no kernel status word");
   if (p.splits > p.stages_total) return fail(LOGOS_ERROR, "q8_gemm: more K splits than 128-column stages");
   LOGOS_CUDA_TRY(cudaFuncSetAttribute(q8_gemm_tc_kernel<MT, LIMBS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
@@ -435,6 +474,8 @@ logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
 }
 
 }  // namespace
+
+void gemm_set_trace(long long* buf) { g_trace = buf; }
 
 bool gemm_tc_applicable(const GemmArgs& g) {
   if (g.a_dtype != LOGOS_F16) return false;
