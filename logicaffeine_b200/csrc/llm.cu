@@ -281,6 +281,19 @@ logos_status_t gemm_partials(Model* m, const ActOut& a, const Q8Mat& w, int* spl
   return LOGOS_OK;
 }
 
+bool debug_sync();
+logos_status_t debug_check(Model* m, const char* what, int64_t layer) {
+  if (!debug_sync()) return LOGOS_OK;
+  LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
+  int code = 0;
+  LOGOS_TRY(kernel_status_read(m->device, &code, false));
+  if (code != 0) {
+    std::string detail = logos_last_error() ? logos_last_error() : "";
+    return fail(LOGOS_ERROR, "kernel status %d first seen after %s of layer %lld [%s]", code, what, (long long)layer, detail.c_str());
+  }
+  return LOGOS_OK;
+}
+
 // One lock-step decode step on the model's stream.  tokens_in: [B] device.
 logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_tokens) {
   const logos_llm_config_t& c = m->cfg;
@@ -311,6 +324,7 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
       LOGOS_TRY(launch_q8_gemm(g, st));
       m->launch_counter += 1;
     }
+    LOGOS_TRY(debug_check(m, "qkv gemm", l));
     {
       ProfScope ps(m, PROF_ATTN);
       AttnArgs a;
@@ -325,7 +339,9 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
       LOGOS_TRY(launch_gqa_decode_attn(a, st));
       m->launch_counter += 2;
     }
+    LOGOS_TRY(debug_check(m, "attention", l));
     LOGOS_TRY(gemm_partials(m, m->att, L.wo, &parts));
+    LOGOS_TRY(debug_check(m, "o_proj gemm", l));
     {
       ProfScope ps(m, PROF_ELEMWISE);
       LOGOS_TRY(launch_residual_rmsnorm(m->h, m->partials, parts, B * H, m->ones, m->xn, B, H, c.rms_eps, st));
@@ -343,7 +359,9 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
       LOGOS_TRY(launch_q8_gemm(g, st));
       m->launch_counter += 1;
     }
+    LOGOS_TRY(debug_check(m, "gate/up gemm", l));
     LOGOS_TRY(gemm_partials(m, m->ffn, L.wd, &parts));
+    LOGOS_TRY(debug_check(m, "down_proj gemm", l));
   }
   if (sample) {
     {
@@ -371,6 +389,17 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
   m->launch_counter += 1;
   m->launches_per_step = m->launch_counter;
   return LOGOS_OK;
+}
+
+// LOGOS_B200_DEBUG_SYNC=1: synchronise after every launch group of a step and name the first
+// one after which the device status word is set.
+bool debug_sync() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("LOGOS_B200_DEBUG_SYNC");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
 }
 
 bool graphs_enabled() {

@@ -10,7 +10,7 @@
 // Data flow per 128-column K stage (4 Q8 blocks):
 //   TMA  int8 weights [128 rows][128 B], 128-byte swizzle  -> smem ring   (warp 0)
 //   TMA  fp16 activation planes [MT][64] x 2 halves x limbs -> smem ring   (warp 1)
-//   4 converter warps: smem int8 -> fp16 (exact: 0x6400|b trick) -> tcgen05.st
+//   8 converter warps: smem int8 -> fp16 (exact: 0x6400|b trick) -> tcgen05.st
 //        into a TMEM operand ring; the weights never go back to shared memory
 //   2 MMA warps (alternate stages): per Q8 block two tcgen05.mma kind::f16 (K=16
 //        each) per plane, A from TMEM, B = activations from smem, into a fresh TMEM
@@ -42,7 +42,12 @@ constexpr int RAW_STAGES = 4;
 constexpr int ACT_STAGES = 4;
 constexpr int TA_STAGES = 4;
 constexpr int TA_LIMB_COLS = 64; // TMEM columns per converted stage and copy: 128 fp16 per row
-constexpr int TC_THREADS = 512;  // 4 single-role warps, 4 converter warps, 8 drain warps
+// 4 or 8.  Eight converter warps halve the conversion time of a stage but measured no faster
+// overall (the MMA -> drain -> MMA hand-off is what bounds a stage), so four is the default;
+// with eight the kernel rebalances registers between its warpgroups (20 warps x 96 at launch).
+constexpr int CONV_WARPS = 4;
+constexpr int CONV_WARP0 = 4, DRAIN_WARP0 = CONV_WARP0 + CONV_WARPS;
+constexpr int TC_THREADS = (DRAIN_WARP0 + 8) * 32;  // 4 single-role warps, converter warps, 8 drain warps
 constexpr int ACC_PAIRS = 2;     // TMEM accumulator ring: each entry holds two Q8 blocks
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int RAW_BYTES = TC_ROWS * TC_KSTAGE;  // 16 KB
@@ -77,6 +82,13 @@ struct TcParams {
   long long* trace;  // optional: SM-clock timestamps of CTA (0,0,0), [stage][16]
 };
 
+// First failure wins: code in word 0, where it happened in words 1..5.
+__device__ __forceinline__ void tc_report(int* status, int code, int stage, int nst) {
+  if (atomicCAS(status, 0, code) == 0) {
+    status[1] = blockIdx.x; status[2] = blockIdx.y; status[3] = stage; status[4] = nst; status[5] = threadIdx.x >> 5;
+  }
+}
+
 // Timestamp slot `ev` of stage `i` (tracing only; CTA 0, one lane per role).
 #define TC_TRACE(i, ev)                                                                          \
   do {                                                                                           \
@@ -105,6 +117,19 @@ __device__ __forceinline__ uint32_t cvt_pair(uint32_t w_xor80, uint32_t selector
   const uint32_t bias_bits = 0x64806480u;                        // 1152 = 1024 + 128
   __half2 r = __hsub2(h, *reinterpret_cast<const __half2*>(&bias_bits));
   return *reinterpret_cast<uint32_t*>(&r);
+}
+
+__device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t pack2(float v) { return pack2(__float_as_uint(v), __float_as_uint(v)); }
+// two f32 FMAs in one instruction (sm_100): d = a * b + c on both halves, round to nearest
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
 }
 
 template <int N>
@@ -155,9 +180,9 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   if (prior_status != 0) return;
 
   if (tid == 0) {
-    for (int i = 0; i < RAW_STAGES; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 4); }
-    for (int i = 0; i < ACT_STAGES; ++i) { mbar_init(&act_full[i], 1); mbar_init(&act_empty[i], 1); }
-    for (int i = 0; i < TA_STAGES; ++i) { mbar_init(&ta_full[i], 4); mbar_init(&ta_empty[i], 1); }
+    for (int i = 0; i < RAW_STAGES; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], CONV_WARPS); }
+    for (int i = 0; i < ACT_STAGES; ++i) { mbar_init(&act_full[i], 1); mbar_init(&act_empty[i], 2); }
+    for (int i = 0; i < TA_STAGES; ++i) { mbar_init(&ta_full[i], CONV_WARPS); mbar_init(&ta_empty[i], 2); }
     for (int i = 0; i < ACC_PAIRS; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 8); }
     fence_barrier_init();
     prefetch_tensormap(&map_q);
@@ -175,28 +200,35 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
   bool ok = true;
 
+  // With 20 warps the launch grants 96 registers each; the single-role and converter
+  // warpgroups hand most of theirs back and the two drain warpgroups take them (the first
+  // statement of every role below).
+  constexpr bool kRebalance = (CONV_WARPS == 8);
+
   if (warp == 0) {
     // ------------------------------------------------------------ weight producer
+    if (kRebalance) setmaxnreg_dec<48>();
     if (lane == 0) {
       const uint64_t pol = policy_evict_first();
       for (int i = 0; i < nst; ++i) {
         int st = i % RAW_STAGES;
         uint32_t ph = (uint32_t)(i / RAW_STAGES) & 1u;
-        if (!mbar_wait(&raw_empty[st], ph ^ 1u)) { ok = false; break; }
+        if (!mbar_wait(&raw_empty[st], ph ^ 1u)) { ok = false; tc_report(p.status, 2010, i, nst); break; }
         TC_TRACE(i, 0);
         mbar_arrive_expect_tx(&raw_full[st], RAW_BYTES);
         tma_load_2d_hint(raw + st * RAW_BYTES, &map_q, &raw_full[st], (st_begin + i) * TC_KSTAGE, (int)n0, pol);
       }
-      if (!ok) atomicExch(p.status, 201);
+
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ activation producer
+    if (kRebalance) setmaxnreg_dec<48>();
     if (lane == 0) {
       const uint64_t pol = policy_evict_last();
       for (int i = 0; i < nst; ++i) {
         int st = i % ACT_STAGES;
         uint32_t ph = (uint32_t)(i / ACT_STAGES) & 1u;
-        if (!mbar_wait(&act_empty[st], ph ^ 1u)) { ok = false; break; }
+        if (!mbar_wait(&act_empty[st], ph ^ 1u)) { ok = false; tc_report(p.status, 2020, i, nst); break; }
         TC_TRACE(i, 1);
         mbar_arrive_expect_tx(&act_full[st], Cfg::ACT_BYTES);
         uint8_t* sb = act + st * Cfg::ACT_BYTES;
@@ -208,93 +240,83 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             tma_load_2d_hint(sb + h * Cfg::ACT_ATOM_BYTES + MT * 128, &map_alo, &act_full[st], x + h * 64, (int)m0, pol);
         }
       }
-      if (!ok) atomicExch(p.status, 202);
+
     }
   } else if (warp == 2 || warp == 3) {
     // ------------------------------------------------------------ MMA issuers
-    // Two warps take alternate stages: what bounds this role is the serial latency of
-    // wait -> issue -> commit, not tensor throughput, so two chains run side by side.  Each
-    // warp runs its loop with all lanes (addresses and descriptors stay warp-uniform) and one
-    // elected lane issues the tcgen05 instructions.  A stage is two pairs of Q8 blocks; a pair
-    // owns one accumulator ring entry of 2*MT columns.
+    if (kRebalance) setmaxnreg_dec<48>();
+    // Two warps, one per half of a stage: warp 2 issues the first pair of Q8 blocks of every
+    // stage, warp 3 the second.  What bounds this role is the serial latency of wait -> issue ->
+    // commit, not tensor throughput, so two chains run side by side; and every barrier is
+    // waited on, phase after phase, by the same warp, which the odd/even phase test needs.
+    // A warp runs its loop with all lanes (addresses and descriptors stay warp-uniform) and one
+    // elected lane issues the tcgen05 instructions.  A pair owns accumulator ring entry `pr`.
     constexpr uint32_t idesc = make_idesc_f16(0, 0, TC_ROWS, MT);
-    static_assert(ACC_PAIRS == 2 && TA_STAGES % 2 == 0 && ACT_STAGES % 2 == 0,
-                  "ring sizes are tied to the two-warp schedule below");
+    static_assert(ACC_PAIRS == 2, "one accumulator ring entry per MMA warp");
+    const int pr = warp - 2;
     for (int i = 0; i < nst && ok; ++i) {
-      if ((i & 1) != warp - 2) {
-        // Not this warp's stage.  An mbarrier wait only tells odd phases from even ones, so
-        // this warp still steps through the accumulator ring's phases one at a time: the wait
-        // below is for the release of its own previous stage.
-        const uint32_t sph = (uint32_t)i & 1u;
-        if (!mbar_wait(&acc_empty[0], sph ^ 1u) || !mbar_wait(&acc_empty[1], sph ^ 1u)) ok = false;
-        continue;
-      }
       const int ts = i % TA_STAGES, as = i % ACT_STAGES;
       const uint32_t tph = (uint32_t)(i / TA_STAGES) & 1u, aph = (uint32_t)(i / ACT_STAGES) & 1u;
-      if (!mbar_wait(&ta_full[ts], tph)) { ok = false; break; }
-      if (lane == 0) TC_TRACE(i, 2);
-      if (!mbar_wait(&act_full[as], aph)) { ok = false; break; }
-      if (lane == 0) TC_TRACE(i, 3);
-      tc_fence_after();
+      if (!mbar_wait(&ta_full[ts], tph)) { ok = false; if (lane == 0) tc_report(p.status, 2031, i, nst); break; }
+      if (lane == 0 && pr == 0) TC_TRACE(i, 2);
+      if (!mbar_wait(&act_full[as], aph)) { ok = false; if (lane == 0) tc_report(p.status, 2032, i, nst); break; }
+      if (lane == 0 && pr == 0) TC_TRACE(i, 3);
       const uint32_t act_base = smem_u32(act + as * Cfg::ACT_BYTES);
-#pragma unroll
-      for (int pr = 0; pr < 2; ++pr) {
-        const int pair = 2 * i + pr;
-        const int slot = pair % ACC_PAIRS;
-        const uint32_t sph = (uint32_t)(pair / ACC_PAIRS) & 1u;
-        if (pr == 1 && lane == 0) TC_TRACE(i, 11);
-        if (!mbar_wait(&acc_empty[slot], sph ^ 1u)) { ok = false; break; }
-        if (pr == 1 && lane == 0) TC_TRACE(i, 12);
-        tc_fence_after();
-        if (elect_one()) {
-#pragma unroll
-          for (int bb = 0; bb < 2; ++bb) {
-            const int blk = 2 * pr + bb;
-            const uint32_t d = tmem_base + ACC_COL0 + (slot * 2 + bb) * MT;
-            // d = q * lo' first, then d = q * hi + d * 2^-11: the residual plane is folded in by
-            // the accumulator scaling of the MMA itself, from one copy of the weights
-#pragma unroll
-            for (int u = 0; u < 2 * LIMBS; ++u) {
-              const int l = (LIMBS == 2) ? 1 - (u >> 1) : 0, j = u & 1;
-              const int kk = blk * 2 + j;  // K=16 step inside the stage
-              const uint32_t a = tmem_base + ts * TA_COLS + kk * 8;
-              const uint64_t bdesc = make_desc_sw128(act_base + (kk >> 2) * Cfg::ACT_ATOM_BYTES + l * MT * 128 +
-                                                     (kk & 3) * 32);
-              if (LIMBS == 2 && u == 2) tc_mma_f16_ts_scaled_d<11>(d, a, bdesc, idesc);
-              else tc_mma_f16_ts(d, a, bdesc, idesc, (uint32_t)(u != 0));
-            }
-          }
-          if (pr == 1) TC_TRACE(i, 13);
-          tc_commit(&acc_full[slot]);
-          if (pr == 1) TC_TRACE(i, 14);
-        }
-        __syncwarp();
-        if (pr == 1 && lane == 0) TC_TRACE(i, 15);
-      }
+      const uint32_t sph = (uint32_t)i & 1u;
+      if (pr == 1 && lane == 0) TC_TRACE(i, 11);
+      if (!mbar_wait(&acc_empty[pr], sph ^ 1u)) { ok = false; if (lane == 0) tc_report(p.status, 2033, i, nst); break; }
+      if (pr == 1 && lane == 0) TC_TRACE(i, 12);
+      tc_fence_after();
       if (elect_one()) {
+#pragma unroll
+        for (int bb = 0; bb < 2; ++bb) {
+          const int blk = 2 * pr + bb;
+          const uint32_t d = tmem_base + ACC_COL0 + blk * MT;
+          // d = q * lo' first, then d = q * hi + d * 2^-11: the residual plane is folded in by
+          // the accumulator scaling of the MMA itself, from one copy of the weights
+#pragma unroll
+          for (int u = 0; u < 2 * LIMBS; ++u) {
+            const int l = (LIMBS == 2) ? 1 - (u >> 1) : 0, j = u & 1;
+            const int kk = blk * 2 + j;  // K=16 step inside the stage
+            const uint32_t a = tmem_base + ts * TA_COLS + kk * 8;
+            const uint64_t bdesc = make_desc_sw128(act_base + (kk >> 2) * Cfg::ACT_ATOM_BYTES + l * MT * 128 +
+                                                   (kk & 3) * 32);
+            if (LIMBS == 2 && u == 2) tc_mma_f16_ts_scaled_d<11>(d, a, bdesc, idesc);
+            else tc_mma_f16_ts(d, a, bdesc, idesc, (uint32_t)(u != 0));
+          }
+        }
+        if (pr == 1) TC_TRACE(i, 13);
+        tc_commit(&acc_full[pr]);
+        // the stage's operands are free once both warps' MMAs have completed
         tc_commit(&ta_empty[ts]);
         tc_commit(&act_empty[as]);
+        if (pr == 1) TC_TRACE(i, 14);
       }
       __syncwarp();
-      if (lane == 0) TC_TRACE(i, 4);
+      if (lane == 0 && pr == 0) TC_TRACE(i, 4);
+      if (lane == 0 && pr == 1) TC_TRACE(i, 15);
     }
-    if (!ok && lane == 0) atomicExch(p.status, 203);
-  } else if (warp >= 4 && warp < 8) {
+
+  } else if (warp >= CONV_WARP0 && warp < DRAIN_WARP0) {
     // ------------------------------------------------------------ converters: int8 smem -> fp16 TMEM
+    // Two warps per lane quarter; each converts half of the stage's eight 16-byte chunks per row.
+    if (kRebalance) setmaxnreg_dec<64>();
     const int qd = warp & 3;
+    const int chalf = (warp - CONV_WARP0) >> 2;
     const uint32_t row = qd * 32 + lane;
     const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16);
     for (int i = 0; i < nst; ++i) {
       int rs = i % RAW_STAGES, ts = i % TA_STAGES;
       uint32_t rph = (uint32_t)(i / RAW_STAGES) & 1u, tph = (uint32_t)(i / TA_STAGES) & 1u;
-      if (!mbar_wait(&raw_full[rs], rph)) { ok = false; break; }
-      if (warp == 4 && lane == 0) TC_TRACE(i, 5);
-      if (!mbar_wait(&ta_empty[ts], tph ^ 1u)) { ok = false; break; }
-      if (warp == 4 && lane == 0) TC_TRACE(i, 6);
+      if (!mbar_wait(&raw_full[rs], rph)) { ok = false; if (lane == 0) tc_report(p.status, 2041, i, nst); break; }
+      if (warp == CONV_WARP0 && lane == 0) TC_TRACE(i, 5);
+      if (!mbar_wait(&ta_empty[ts], tph ^ 1u)) { ok = false; if (lane == 0) tc_report(p.status, 2042, i, nst); break; }
+      if (warp == CONV_WARP0 && lane == 0) TC_TRACE(i, 6);
       tc_fence_after();
       const uint8_t* rb = raw + rs * RAW_BYTES;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int cc = 0; cc < 32 / CONV_WARPS; ++cc) {
+        const int c = chalf * (32 / CONV_WARPS) + cc;
         const uint4 w = *reinterpret_cast<const uint4*>(rb + swz128(row, c));
         uint32_t r[8];
         const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
@@ -307,7 +329,7 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         tc_st_32x32b_x8(t_lane + ts * TA_COLS + c * 8, r);
       }
       tc_wait_st();
-      if (warp == 4 && lane == 0) TC_TRACE(i, 7);
+      if (warp == CONV_WARP0 && lane == 0) TC_TRACE(i, 7);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
@@ -315,23 +337,24 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         mbar_arrive(&ta_full[ts]);
       }
     }
-    if (!ok && lane == 0) atomicExch(p.status, 204);
-  } else if (warp >= 8) {
+
+  } else if (warp >= DRAIN_WARP0) {
     // ------------------------------------------------------------ drain + epilogue
     // Two warps per lane quarter, each owning half of the token columns.  Blocks are taken two
     // at a time so one tcgen05.wait::ld covers both loads: the TMEM read latency, not the
     // arithmetic, is what bounds this role.
+    if (kRebalance) setmaxnreg_inc<144>();
     const int qd = warp & 3;
-    const int half = (warp - 8) >> 2;
+    const int half = (warp - DRAIN_WARP0) >> 2;
     constexpr int HC = MT / 2;  // token columns per drain warp
     const int64_t n = n0 + qd * 32 + lane;
     const bool n_ok = n < p.n;
     const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16) + ACC_COL0 + half * HC;
     const int64_t kb_per_row = p.k >> 5;
     const float* srow = p.s + (n_ok ? n : 0) * kb_per_row;
-    float acc[HC];
+    uint64_t acc2[HC / 2];  // packed f32 pairs: the drain arithmetic uses two-wide f32 FMAs
 #pragma unroll
-    for (int j = 0; j < HC; ++j) acc[j] = 0.f;
+    for (int j = 0; j < HC / 2; ++j) acc2[j] = 0ull;
     int blk_count = 0;
     for (int i = 0; i < nst && ok; ++i) {
       float4 sc4 = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -342,29 +365,35 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const int pair = blk_count >> 1;
         const int slot = pair % ACC_PAIRS;
         const uint32_t fph = (uint32_t)(pair / ACC_PAIRS) & 1u;
-        if (!mbar_wait(&acc_full[slot], fph)) { ok = false; break; }
-        if (warp == 8 && lane == 0 && pr == 0) TC_TRACE(i, 8);
+        if (!mbar_wait(&acc_full[slot], fph)) { ok = false; if (lane == 0) tc_report(p.status, 2050, i, nst); break; }
+        if (warp == DRAIN_WARP0 && lane == 0 && pr == 0) TC_TRACE(i, 8);
         tc_fence_after();
         uint32_t b0[HC], b1[HC];
         tc_ld_cols<HC>(t_lane + (slot * 2) * MT, b0);
         tc_ld_cols<HC>(t_lane + (slot * 2 + 1) * MT, b1);
         tc_wait_ld();
-        if (warp == 8 && lane == 0 && pr == 0) TC_TRACE(i, 9);
+        if (warp == DRAIN_WARP0 && lane == 0 && pr == 0) TC_TRACE(i, 9);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[slot]);
-        const float sc0 = scs[2 * pr], sc1 = scs[2 * pr + 1];
+        const uint64_t sc0 = pack2(scs[2 * pr]), sc1 = pack2(scs[2 * pr + 1]);
 #pragma unroll
-        for (int j = 0; j < HC; ++j) {
-          acc[j] = fmaf(sc0, __uint_as_float(b0[j]), acc[j]);
-          acc[j] = fmaf(sc1, __uint_as_float(b1[j]), acc[j]);
+        for (int j = 0; j < HC / 2; ++j) {
+          acc2[j] = ffma2(sc0, pack2(b0[2 * j], b0[2 * j + 1]), acc2[j]);
+          acc2[j] = ffma2(sc1, pack2(b1[2 * j], b1[2 * j + 1]), acc2[j]);
         }
-        if (warp == 8 && lane == 0 && pr == 0) TC_TRACE(i, 10);
+        if (warp == DRAIN_WARP0 && lane == 0 && pr == 0) TC_TRACE(i, 10);
         blk_count += 2;
       }
     }
-    if (!ok && lane == 0) atomicExch(p.status, 205);
 
+
+    float acc[HC];
+#pragma unroll
+    for (int j = 0; j < HC / 2; ++j) {
+      acc[2 * j] = __uint_as_float((uint32_t)acc2[j]);
+      acc[2 * j + 1] = __uint_as_float((uint32_t)(acc2[j] >> 32));
+    }
     if (ok) {
       const int64_t mb = m0 + half * HC;  // first token of this warp's columns
       if (p.splits > 1) {

@@ -2,6 +2,7 @@
 #include "ptx.cuh"
 
 #include <mutex>
+#include <string>
 #include <unordered_map>
 
 namespace logos {
@@ -70,8 +71,16 @@ logos_status_t kernel_status_read(int device, int* out, bool clear) {
   int* p = kernel_status_ptr(device);
   if (!p) return fail(LOGOS_ERROR, "no kernel status word (no CUDA device?)");
   LOGOS_CUDA_TRY(cudaSetDevice(device));
-  LOGOS_CUDA_TRY(cudaMemcpy(out, p, sizeof(int), cudaMemcpyDeviceToHost));
-  if (clear && *out != 0) LOGOS_CUDA_TRY(cudaMemset(p, 0, sizeof(int)));
+  int words[8];
+  LOGOS_CUDA_TRY(cudaMemcpy(words, p, sizeof(words), cudaMemcpyDeviceToHost));
+  *out = words[0];
+  if (words[0] != 0) {
+    // where the first kernel to give up was: block (x, y), K stage, stages of that block, warp
+    set_last_error("device-side wait gave up: code " + std::to_string(words[0]) + " block (" + std::to_string(words[1]) +
+                   "," + std::to_string(words[2]) + ") stage " + std::to_string(words[3]) + " of " +
+                   std::to_string(words[4]) + " warp " + std::to_string(words[5]));
+    if (clear) LOGOS_CUDA_TRY(cudaMemset(p, 0, sizeof(words)));
+  }
   return LOGOS_OK;
 }
 
