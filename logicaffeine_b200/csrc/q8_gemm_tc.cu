@@ -27,6 +27,8 @@
 
 #include "ptx.cuh"
 
+#include <stdlib.h>
+
 #include <mutex>
 #include <unordered_map>
 
@@ -39,6 +41,7 @@ using namespace ptx;
 constexpr int TC_ROWS = 128;     // weight rows per CTA (MMA M)
 constexpr int TC_KSTAGE = 128;   // K per stage
 constexpr int RAW_STAGES = 4;
+constexpr int RAW_PREFETCH = 12;  // L2 prefetch distance of the weight stream, in stages
 constexpr int ACT_STAGES = 4;
 constexpr int TA_STAGES = 4;
 constexpr int TA_LIMB_COLS = 64; // TMEM columns per converted stage and copy: 128 fp16 per row
@@ -172,6 +175,7 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const int st_end = (int)(((int64_t)(split + 1) * p.stages_total) / p.splits);
   const int nst = st_end - st_begin;
 
+  if (tid == 0) TC_TRACE(63, 0);  // kernel entry
   // a kernel that gave up earlier left a code behind: do not start new work on top of it
   // (one thread reads, everyone takes the same decision)
   __shared__ int prior_status;
@@ -199,7 +203,7 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const uint32_t tmem_base = *tmem_slot;
 
   bool ok = true;
-
+  if (tid == 0) TC_TRACE(63, 1);  // set-up done
   // With 20 warps the launch grants 96 registers each; the single-role and converter
   // warpgroups hand most of theirs back and the two drain warpgroups take them (the first
   // statement of every role below).
@@ -210,7 +214,12 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     if (kRebalance) setmaxnreg_dec<48>();
     if (lane == 0) {
       const uint64_t pol = policy_evict_first();
+      // The smem ring alone (RAW_STAGES x 16 KB per SM) does not cover HBM latency under load:
+      // L2 prefetches run RAW_PREFETCH stages ahead of the TMA loads.
+      for (int i = 0; i < RAW_PREFETCH && i < nst; ++i)
+        tma_prefetch_l2_2d(&map_q, (st_begin + i) * TC_KSTAGE, (int)n0);
       for (int i = 0; i < nst; ++i) {
+        if (i + RAW_PREFETCH < nst) tma_prefetch_l2_2d(&map_q, (st_begin + i + RAW_PREFETCH) * TC_KSTAGE, (int)n0);
         int st = i % RAW_STAGES;
         uint32_t ph = (uint32_t)(i / RAW_STAGES) & 1u;
         if (!mbar_wait(&raw_empty[st], ph ^ 1u)) { ok = false; tc_report(p.status, 2010, i, nst); break; }
@@ -388,42 +397,59 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
 
 
-    float acc[HC];
+    if (warp == DRAIN_WARP0 && lane == 0) TC_TRACE(63, 2);  // main loop done
+    // ---- epilogue.  The accumulators go to shared memory first (the weight ring is idle by
+    // now) and a short rolled loop applies the epilogue and writes rows of consecutive n:
+    // unrolling 32 generic stores per thread made the code so large that its instruction
+    // fetches, cold in every CTA, cost more than the stores.
+    float* stage_c = reinterpret_cast<float*>(raw);  // [MT][EPI_PITCH]
+    constexpr int EPI_PITCH = TC_ROWS + 4;
 #pragma unroll
     for (int j = 0; j < HC / 2; ++j) {
-      acc[2 * j] = __uint_as_float((uint32_t)acc2[j]);
-      acc[2 * j + 1] = __uint_as_float((uint32_t)(acc2[j] >> 32));
+      stage_c[(half * HC + 2 * j) * EPI_PITCH + qd * 32 + lane] = __uint_as_float((uint32_t)acc2[j]);
+      stage_c[(half * HC + 2 * j + 1) * EPI_PITCH + qd * 32 + lane] = __uint_as_float((uint32_t)(acc2[j] >> 32));
     }
+    if (warp == DRAIN_WARP0 && lane == 0) TC_TRACE(63, 5);  // staged
+    asm volatile("bar.sync 2, 256;" ::: "memory");  // the eight drain warps
     if (ok) {
-      const int64_t mb = m0 + half * HC;  // first token of this warp's columns
-      if (p.splits > 1) {
-        if (n_ok) {
-#pragma unroll
-          for (int j = 0; j < HC; ++j)
-            if (mb + j < p.m) p.partials[((int64_t)split * p.m + mb + j) * p.n + n] = acc[j];
-        }
-      } else if (p.epilogue == EPI_SWIGLU) {
-#pragma unroll
-        for (int j = 0; j < HC; ++j) {
-          float other = __shfl_xor_sync(0xffffffffu, acc[j], 1);
-          if (!(lane & 1) && n + 1 < p.n && mb + j < p.m)
-            store_c(p, (mb + j) * p.ldc + (n >> 1), __fmul_rn(silu_f(acc[j]), other));
-        }
-      } else if (n_ok) {
-#pragma unroll
-        for (int j = 0; j < HC; ++j)
-          if (mb + j < p.m) {
-            float v = acc[j];
-            int64_t ci = (mb + j) * p.ldc + n;
-            if (p.epilogue == EPI_RESIDUAL) v = __fadd_rn(v, load_aux(p, ci));
-            store_c(p, ci, v);
+      const int et = tid - DRAIN_WARP0 * 32;  // 0..255
+      const int64_t rows_here = (p.m - m0 < MT) ? (p.m - m0) : MT;
+      if (p.splits <= 1 && p.epilogue == EPI_SWIGLU) {
+        // rows (2j, 2j+1) of the tile are (gate_j, up_j): 64 outputs per token
+        const int64_t out0 = n0 >> 1;
+        const int64_t outs = ((p.n - n0 < TC_ROWS ? p.n - n0 : TC_ROWS)) >> 1;
+#pragma unroll 1
+        for (int e = et; e < MT * (TC_ROWS / 2); e += 256) {
+          const int mm = e / (TC_ROWS / 2), jj = e % (TC_ROWS / 2);
+          if (mm < rows_here && jj < outs) {
+            const float g = stage_c[mm * EPI_PITCH + 2 * jj], u = stage_c[mm * EPI_PITCH + 2 * jj + 1];
+            store_c(p, (m0 + mm) * p.ldc + out0 + jj, __fmul_rn(silu_f(g), u));
           }
+        }
+      } else {
+        const int64_t cols_here = (p.n - n0 < TC_ROWS) ? (p.n - n0) : TC_ROWS;
+#pragma unroll 1
+        for (int e = et; e < MT * TC_ROWS; e += 256) {
+          const int mm = e / TC_ROWS, nn = e % TC_ROWS;
+          if (mm < rows_here && nn < cols_here) {
+            float v = stage_c[mm * EPI_PITCH + nn];
+            if (p.splits > 1) {
+              p.partials[((int64_t)split * p.m + m0 + mm) * p.n + n0 + nn] = v;
+            } else {
+              const int64_t ci = (m0 + mm) * p.ldc + n0 + nn;
+              if (p.epilogue == EPI_RESIDUAL) v = __fadd_rn(v, load_aux(p, ci));
+              store_c(p, ci, v);
+            }
+          }
+        }
       }
     }
   }
 
+  if (warp == DRAIN_WARP0 && lane == 0) TC_TRACE(63, 3);  // epilogue stores issued
   tc_fence_before();
   __syncthreads();
+  if (tid == 0) TC_TRACE(63, 4);
   if (warp == 3) {
     __syncwarp();
     tc_fence_after();
@@ -493,6 +519,11 @@ logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
   p.stages_total = (int)(g.k / TC_KSTAGE);
   p.status = kernel_status_ptr(g.device);
   p.trace = g_trace;
+  if (g_trace) {
+    // optional filter: trace only launches whose grid has this many row tiles
+    static const char* f = getenv("LOGOS_B200_TRACE_TILES");
+    if (f && atoi(f) != (int)((g.n + TC_ROWS - 1) / TC_ROWS)) p.trace = nullptr;
+  }
   if (!p.status) return fail(LOGOS_ERROR, "q8_gemm: no kernel status word");
   if (p.splits > p.stages_total) return fail(LOGOS_ERROR, "q8_gemm: more K splits than 128-column stages");
   LOGOS_CUDA_TRY(cudaFuncSetAttribute(q8_gemm_tc_kernel<MT, LIMBS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
