@@ -125,9 +125,12 @@ logos_status_t alloc_mat(Model* m, Q8Mat* w, int64_t n, int64_t k) {
 void destroy(Model* m) {
   cudaSetDevice(m->device);
   if (m->stream) cudaStreamSynchronize(m->stream);
+  // The captured step holds NCCL nodes: it has to go before the communicator does, or the
+  // communicator's destruction waits on it.
+  if (m->step_graph) cudaGraphExecDestroy(m->step_graph);
+  m->step_graph = nullptr;
   tp_destroy(&m->tp);
   for (void* p : m->allocs) cudaFree(p);
-  if (m->step_graph) cudaGraphExecDestroy(m->step_graph);
   for (cudaEvent_t e : m->prof_events) cudaEventDestroy(e);
   if (m->ev0) cudaEventDestroy(m->ev0);
   if (m->ev1) cudaEventDestroy(m->ev1);
