@@ -183,6 +183,26 @@ LOGOS_API logos_status_t logos_gqa_decode_attn(logos_handle_t q, logos_handle_t 
                                      int64_t b, int64_t h_q, int64_t h_kv, int64_t d, int64_t l_max,
                                      float softmax_scale, void* stream_or_null);
 
+/* No counterpart in the reference.  Same contract and same kernels as
+ * logos_gqa_decode_attn, for hosts that must not trigger a device allocation when they
+ * call an operator: a serving process that hands the whole GPU to its own KV-cache and
+ * weight arena at start-up (a later cudaMalloc from inside the library would fail or
+ * fragment that arena), or a decode loop with a latency budget that an allocation's
+ * device-wide synchronisation would break.  The split-KV partial results go to a fixed
+ * 16 MiB array inside the library image instead of library-allocated scratch, so every GPU
+ * that loads the library holds those 16 MiB until the process exits.  A shape whose
+ * partials need more (b * h_q * ceil(l_max / unit) * (d + 2) * 4 bytes) is refused with
+ * LOGOS_OUT_OF_BOUNDS and a message giving both sizes.  The call itself makes no
+ * cudaMalloc / cudaFree.  The first call on a device looks up the array's device address;
+ * make that first call outside any stream capture.  All calls share the one array and its
+ * status word (the word is cleared at the start of every call; the partials are always
+ * written before they are read), so two calls that overlap on the GPU race: keep calls on
+ * this entry point ordered, for instance on one stream. */
+LOGOS_API logos_status_t logos_gqa_decode_attn_fixed_scratch(logos_handle_t q, logos_handle_t k_cache,
+                                     logos_handle_t v_cache, logos_handle_t seq_len, logos_handle_t o,
+                                     int64_t b, int64_t h_q, int64_t h_kv, int64_t d, int64_t l_max,
+                                     float softmax_scale, void* stream_or_null);
+
 /* The fused form the decode step uses: rotate q and k_new at position seq_len[b],
  * append k,v, attend over [0, seq_len[b]] including the new row, then
  * seq_len[b] += 1.  q_raw / k_new / v_new are un-rotated f16. */

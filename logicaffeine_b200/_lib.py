@@ -77,6 +77,7 @@ _SIGNATURES = {
     "logos_rope_table": (None, [PTR, I64, I64, C.c_double]),
     "logos_kv_append_rope": (None, [H, H, H, H, H, H, I64, I64, I64, I64, PTR]),
     "logos_gqa_decode_attn": (None, [H, H, H, H, H, I64, I64, I64, I64, I64, FLT, PTR]),
+    "logos_gqa_decode_attn_fixed_scratch": (None, [H, H, H, H, H, I64, I64, I64, I64, I64, FLT, PTR]),
     "logos_gqa_decode_attn_fused": (None, [H, H, H, H, H, H, H, H, I64, I64, I64, I64, I64, FLT, PTR]),
     "logos_rmsnorm": (None, [H, H, H, I64, I64, FLT, PTR]),
     "logos_swiglu": (None, [H, H, H, I64, PTR]),

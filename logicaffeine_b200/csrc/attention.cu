@@ -22,6 +22,8 @@
 
 #include <math.h>
 
+#include <mutex>
+
 namespace logos {
 
 namespace {
@@ -473,7 +475,15 @@ logos_status_t launch_attn_t(const AttnArgs& a, cudaStream_t st) {
   void* scratch = nullptr;
   int64_t po_bytes = a.b * a.h_q * max_splits * D * (int64_t)sizeof(float);
   int64_t pml_bytes = a.b * a.h_q * max_splits * 2 * (int64_t)sizeof(float);
-  LOGOS_TRY(scratch_get(a.device, 1, po_bytes + pml_bytes, &scratch));
+  if (a.ext_scratch) {
+    if (po_bytes + pml_bytes > a.ext_scratch_bytes)
+      return fail(LOGOS_OUT_OF_BOUNDS,
+                  "attention: this shape needs %lld bytes of split-KV scratch, the fixed scratch holds %lld",
+                  (long long)(po_bytes + pml_bytes), (long long)a.ext_scratch_bytes);
+    scratch = a.ext_scratch;
+  } else {
+    LOGOS_TRY(scratch_get(a.device, 1, po_bytes + pml_bytes, &scratch));
+  }
 
   AttnParams p{};
   p.q_f16 = a.q_f16; p.q_f32 = a.q_f32; p.q_ld = a.q_ld; p.rotate_q = a.rotate_q;
@@ -486,7 +496,7 @@ logos_status_t launch_attn_t(const AttnArgs& a, cudaStream_t st) {
   p.b = (int)a.b; p.h_q = (int)a.h_q; p.h_kv = (int)a.h_kv; p.l_max = (int)a.l_max;
   p.unit_len = (int)ul; p.max_splits = max_splits;
   p.scale_log2 = a.scale * 1.4426950408889634f;
-  p.status = kernel_status_ptr(a.device);
+  p.status = a.ext_status ? a.ext_status : kernel_status_ptr(a.device);
   if (!p.status) return fail(LOGOS_ERROR, "attention: no kernel status word");
 
   constexpr size_t smem = attn_smem_bytes<D>();
@@ -542,11 +552,84 @@ logos_status_t launch_kv_append_rope(__half* k_cache, __half* v_cache, const __h
   return check_launch("bump_seq_len_kernel");
 }
 
+// ---------------------------------------------------------------- fixed-scratch variant
+// Scratch that lives in the library image instead of coming from cudaMalloc: every GPU
+// that loads the library holds these 16 MiB (+ one status word) until the process exits.
+constexpr int64_t kStaticScratchBytes = 16ll << 20;
+static __device__ __align__(256) unsigned char g_static_attn_scratch[kStaticScratchBytes];
+static __device__ __align__(256) int g_static_attn_status[8];
+
+namespace {
+constexpr int kMaxStaticDevices = 64;
+struct StaticAddr {
+  void* scratch = nullptr;
+  int*  status = nullptr;
+  bool  ready = false;
+};
+StaticAddr g_static_addr[kMaxStaticDevices];
+std::mutex g_static_mu;
+
+// In host code the array names above are host-side stand-ins, not device addresses: the
+// address a kernel may use comes from cudaGetSymbolAddress, asked once per device with
+// that device current.
+logos_status_t static_scratch_for(int device, StaticAddr* out) {
+  if (device < 0 || device >= kMaxStaticDevices)
+    return fail(LOGOS_OUT_OF_BOUNDS, "fixed-scratch attention: device %d is beyond the %d this build tracks", device,
+                kMaxStaticDevices);
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  StaticAddr& sa = g_static_addr[device];
+  if (!sa.ready) {
+    void* p = nullptr;
+    void* q = nullptr;
+    LOGOS_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_attn_scratch));
+    LOGOS_CUDA_TRY(cudaGetSymbolAddress(&q, g_static_attn_status));
+    sa.scratch = p;
+    sa.status = static_cast<int*>(q);
+    sa.ready = true;
+  }
+  *out = sa;
+  return LOGOS_OK;
+}
+}  // namespace
+
 }  // namespace logos
 
 using namespace logos;
 
 extern "C" {
+
+logos_status_t logos_gqa_decode_attn_fixed_scratch(logos_handle_t q, logos_handle_t k_cache, logos_handle_t v_cache,
+                                                   logos_handle_t seq_len, logos_handle_t o, int64_t b, int64_t h_q,
+                                                   int64_t h_kv, int64_t d, int64_t l_max, float softmax_scale,
+                                                   void* stream_or_null) {
+  return guarded([&]() -> logos_status_t {
+    if (b < 0 || h_q < 0 || h_kv <= 0 || d <= 0 || l_max <= 0)
+      return fail(LOGOS_OUT_OF_BOUNDS, "logos_gqa_decode_attn_fixed_scratch: bad extents");
+    AttnArgs a;
+    __half *qp, *kc, *vc, *op;
+    int32_t* sl;
+    int32_t dev = 0;
+    LOGOS_TRY(buf_ptr<__half>(q, b * h_q * d, "q", &qp, &dev));
+    LOGOS_TRY(buf_ptr<__half>(k_cache, b * h_kv * l_max * d, "k_cache", &kc));
+    LOGOS_TRY(buf_ptr<__half>(v_cache, b * h_kv * l_max * d, "v_cache", &vc));
+    LOGOS_TRY(buf_ptr<int32_t>(seq_len, b, "seq_len", &sl));
+    LOGOS_TRY(buf_ptr<__half>(o, b * h_q * d, "o", &op));
+    LOGOS_CUDA_TRY(cudaSetDevice(dev));
+    StaticAddr sa;
+    LOGOS_TRY(static_scratch_for(dev, &sa));
+    cudaStream_t st = as_stream(stream_or_null);
+    // The status word is shared by every call on this path and keeps the last call's value:
+    // it has to start at zero.  The partials need no clearing: every entry the merge reads is
+    // written by this call first.
+    LOGOS_CUDA_TRY(cudaMemsetAsync(sa.status, 0, sizeof(int) * 8, st));
+    a.q_f16 = qp; a.k_cache = kc; a.v_cache = vc; a.seq_len = sl; a.o = op; a.o_dtype = LOGOS_F16;
+    a.b = b; a.h_q = h_q; a.h_kv = h_kv; a.d = d; a.l_max = l_max; a.scale = softmax_scale; a.device = dev;
+    a.ext_scratch = sa.scratch;
+    a.ext_scratch_bytes = kStaticScratchBytes;
+    a.ext_status = sa.status;
+    return launch_gqa_decode_attn(a, st);
+  });
+}
 
 logos_status_t logos_rope_table(float* out_host, int64_t l_max, int64_t d, double theta) {
   return guarded([&]() -> logos_status_t {

@@ -83,6 +83,11 @@ struct AttnArgs {
   int64_t       b = 0, h_q = 0, h_kv = 0, d = 0, l_max = 0;
   float         scale = 1.f;
   int           device = 0;
+  // Caller-provided scratch for the split-KV partials and the status word (both device
+  // addresses).  Null = the library's own per-device scratch, allocated on first use.
+  void*         ext_scratch = nullptr;
+  int64_t       ext_scratch_bytes = 0;
+  int*          ext_status = nullptr;
 };
 logos_status_t launch_gqa_decode_attn(const AttnArgs& a, cudaStream_t st);
 logos_status_t launch_kv_append_rope(__half* k_cache, __half* v_cache, const __half* k_new, const __half* v_new,

@@ -157,6 +157,13 @@ def gqaDecodeAttn(q, k_cache, v_cache, seq_len, o, b, h_q, h_kv, d, l_max, softm
          int(h_q), int(h_kv), int(d), int(l_max), float(softmax_scale), _s(stream))
 
 
+def gqaDecodeAttnFixedScratch(q, k_cache, v_cache, seq_len, o, b, h_q, h_kv, d, l_max, softmax_scale, stream=None):
+    """gqaDecodeAttn for hosts that cannot let an operator allocate device memory: the split-KV partials use a
+    fixed 16 MiB array inside the library; larger shapes raise LogosError (OutOfBounds)."""
+    call("logos_gqa_decode_attn_fixed_scratch", q.handle, k_cache.handle, v_cache.handle, seq_len.handle, o.handle,
+         int(b), int(h_q), int(h_kv), int(d), int(l_max), float(softmax_scale), _s(stream))
+
+
 def gqaDecodeAttnFused(q_raw, k_new, v_new, k_cache, v_cache, rope_table, seq_len, o, b, h_q, h_kv, d, l_max,
                        softmax_scale, stream=None):
     call("logos_gqa_decode_attn_fused", q_raw.handle, k_new.handle, v_new.handle, k_cache.handle, v_cache.handle,

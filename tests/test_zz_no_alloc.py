@@ -1,0 +1,61 @@
+"""The attention entry point that allocates nothing.
+
+Some hosts cannot afford a device allocation inside an operator call: a server that gave
+the whole GPU to its own arena at start-up, or a decode loop whose latency budget has no
+room for the device-wide synchronisation an allocation implies.  For them
+logos_gqa_decode_attn_fixed_scratch keeps its split-KV partial results in a fixed 16 MiB
+array inside the library.  It runs the same kernels as logos_gqa_decode_attn, so on the
+same inputs the two must agree bit for bit, call after call (the array keeps the previous
+call's contents), and a shape that does not fit must be refused, not truncated.
+
+This file sorts last on purpose: if it fails under `pytest -x`, every other test has
+already run."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(O, b, hq, hkv, d, lmax, lens, seed):
+    kc = O.synth_fill(O.F16, 2, seed, 20, 0, b * hkv * lmax * d, 0.0, 1.0).reshape(b, hkv, lmax, d)
+    vc = O.synth_fill(O.F16, 2, seed, 21, 0, b * hkv * lmax * d, 0.0, 1.0).reshape(b, hkv, lmax, d)
+    q = O.synth_fill(O.F16, 2, seed, 22, 0, b * hq * d, 0.0, 1.0).reshape(b, hq, d)
+    return q, kc, vc, np.asarray(lens, np.int32)
+
+
+def test_fixed_scratch_attention_matches_the_allocating_entry_point_twice(llm, oracle):
+    O = oracle
+    # two different shapes back to back: the second call finds the first call's partials in the array
+    cases = [(4, 28, 4, 128, 700, [1, 64, 65, 699], 3), (3, 14, 2, 64, 300, [299, 130, 7], 4)]
+    for b, hq, hkv, d, lmax, lens, seed in cases:
+        q, kc, vc, seq = _inputs(O, b, hq, hkv, d, lmax, lens, seed)
+        scale = 1.0 / np.sqrt(d)
+        dq, dkc, dvc, dseq = (llm.DeviceBuffer.from_host(x) for x in (q, kc, vc, seq))
+        want_buf = llm.DeviceBuffer(b * hq * d * 2)
+        got_buf = llm.DeviceBuffer(b * hq * d * 2)
+        llm.gqaDecodeAttn(dq, dkc, dvc, dseq, want_buf, b, hq, hkv, d, lmax, scale)
+        want = want_buf.download(np.uint16, (b, hq, d))
+        for call in range(2):
+            got_buf.memset(0xFF)
+            llm.gqaDecodeAttnFixedScratch(dq, dkc, dvc, dseq, got_buf, b, hq, hkv, d, lmax, scale)
+            got = got_buf.download(np.uint16, (b, hq, d))
+            assert np.array_equal(got, want), "call %d differs from logos_gqa_decode_attn" % call
+        ref = O.gqa_decode_attn(q, kc, vc, seq, scale)
+        a, r = O.f16_to_f32(want), O.f16_to_f32(ref)
+        assert np.linalg.norm(a - r) / np.linalg.norm(r) < 1e-3   # and both agree with the oracle
+        assert llm.kernelStatus() == 0
+
+
+def test_fixed_scratch_refuses_what_does_not_fit(llm):
+    # 64 sequences x 128 query heads x 5 splits x 130 floats: about 21 MiB of partials, more than the 16 MiB array
+    b, hq, hkv, d, lmax = 64, 128, 8, 128, 2048
+    tiny = llm.DeviceBuffer(16)
+    big_q = llm.DeviceBuffer(b * hq * d * 2)
+    cache = llm.DeviceBuffer(b * hkv * lmax * d * 2)
+    seq = llm.DeviceBuffer(b * 4)
+    seq.memset(0)
+    with pytest.raises(llm.LogosError) as e:
+        llm.gqaDecodeAttnFixedScratch(big_q, cache, cache, seq, big_q, b, hq, hkv, d, lmax, 0.1)
+    assert e.value.status == 4 and "fixed scratch" in str(e.value)
+    for x in (tiny, big_q, cache, seq):
+        x.free()
