@@ -104,6 +104,10 @@ __device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const CUtensorM
       : "memory");
 }
 // Ask L2 to fetch a tile ahead of the TMA load that will want it.
+// brings the 128-byte line holding `p` into L2; no register result, no fault on a bad address
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
 __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* m, int x, int y) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
                ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y)

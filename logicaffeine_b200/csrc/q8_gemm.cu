@@ -113,17 +113,26 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partials, int spl
 
 int gemm_pick_splits(int64_t m, int64_t n, int64_t k, int device) {
   (void)m;
-  // Tiles of 128 weight rows; split K (in whole 128-column stages) until there
-  // are about two work units per SM.
-  int64_t tiles = (n + 127) / 128;
-  int64_t stages = k / 128;
-  int sms = sm_count(device);
+  // Work units are (tile of 128 weight rows) x (K split); a CTA's time is a fixed part (pipeline
+  // fill, epilogue: about twelve stage times, measured) plus its K stages, and CTAs run in
+  // rounds of one per SM.  Take the split count with the smallest rounds x (fixed + stages);
+  // ties go to fewer splits (fewer partials to write and fold).
+  const int64_t tiles = (n + 127) / 128;
+  const int64_t stages = k / 128;
+  const int sms = sm_count(device);
   if (tiles >= sms || stages < 8) return 1;
-  int64_t want = (2 * (int64_t)sms + tiles - 1) / tiles;
-  int64_t max_by_k = stages / 4;  // at least 4 stages (512 columns) per split
-  if (want > max_by_k) want = max_by_k;
-  if (want > 16) want = 16;
-  return want < 1 ? 1 : (int)want;
+  const int64_t fixed = 12;
+  int64_t max_splits = stages / 4;  // at least 4 stages (512 columns) per split
+  if (max_splits > 16) max_splits = 16;
+  int best = 1;
+  int64_t best_cost = INT64_MAX;
+  for (int64_t sp = 1; sp <= max_splits; ++sp) {
+    const int64_t rounds = (tiles * sp + sms - 1) / sms;
+    const int64_t per = (stages + sp - 1) / sp;
+    const int64_t cost = rounds * (fixed + per) * 8 + sp;
+    if (cost < best_cost) { best_cost = cost; best = (int)sp; }
+  }
+  return best;
 }
 
 logos_status_t launch_splitk_reduce(const float* partials, int splits, void* c, int c_dtype, ActOut c_act,

@@ -215,17 +215,21 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     if (lane == 0) {
       const uint64_t pol = policy_evict_first();
       // The smem ring alone (RAW_STAGES x 16 KB per SM) does not cover HBM latency under load:
-      // L2 prefetches run RAW_PREFETCH stages ahead of the TMA loads.
-      for (int i = 0; i < RAW_PREFETCH && i < nst; ++i)
-        tma_prefetch_l2_2d(&map_q, (st_begin + i) * TC_KSTAGE, (int)n0);
+      // L2 prefetches run RAW_PREFETCH stages ahead of the TMA loads.  They start only after
+      // the first loads are on their way, so that nothing queues in front of those.
       for (int i = 0; i < nst; ++i) {
-        if (i + RAW_PREFETCH < nst) tma_prefetch_l2_2d(&map_q, (st_begin + i + RAW_PREFETCH) * TC_KSTAGE, (int)n0);
         int st = i % RAW_STAGES;
         uint32_t ph = (uint32_t)(i / RAW_STAGES) & 1u;
         if (!mbar_wait(&raw_empty[st], ph ^ 1u)) { ok = false; tc_report(p.status, 2010, i, nst); break; }
         TC_TRACE(i, 0);
         mbar_arrive_expect_tx(&raw_full[st], RAW_BYTES);
         tma_load_2d_hint(raw + st * RAW_BYTES, &map_q, &raw_full[st], (st_begin + i) * TC_KSTAGE, (int)n0, pol);
+        if (i + 1 >= RAW_STAGES) {
+          // after the ring's first fill: stages RAW_STAGES .. RAW_PREFETCH in one go, then one per stage
+          const int first = (i + 1 == RAW_STAGES) ? RAW_STAGES : i + RAW_PREFETCH;
+          for (int j = first; j <= i + RAW_PREFETCH && j < nst; ++j)
+            tma_prefetch_l2_2d(&map_q, (st_begin + j) * TC_KSTAGE, (int)n0);
+        }
       }
 
     }
@@ -365,9 +369,20 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
     for (int j = 0; j < HC / 2; ++j) acc2[j] = 0ull;
     int blk_count = 0;
+    // The four scales of a stage are one 16-byte load per row.  Their latency (L2, or HBM
+    // once per 128-byte line, i.e. every eight stages) must not sit between the TMEM load and
+    // the arithmetic: registers hold the scales two stages ahead, and the line after next
+    // is prefetched into L2.
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4* sc_src = reinterpret_cast<const float4*>(srow) + st_begin;
+    float4 sc_a = (n_ok && 0 < nst) ? __ldg(sc_src) : zero4;
+    float4 sc_b = (n_ok && 1 < nst) ? __ldg(sc_src + 1) : zero4;
+    if (n_ok && 8 < nst) prefetch_l2(sc_src + 8);
     for (int i = 0; i < nst && ok; ++i) {
-      float4 sc4 = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (n_ok) sc4 = __ldg(reinterpret_cast<const float4*>(srow + (int64_t)(st_begin + i) * 4));
+      const float4 sc4 = sc_a;
+      sc_a = sc_b;
+      sc_b = (n_ok && i + 2 < nst) ? __ldg(sc_src + i + 2) : zero4;
+      if (n_ok && (i & 7) == 0 && i + 16 < nst) prefetch_l2(sc_src + i + 16);
       const float scs[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
 #pragma unroll
       for (int pr = 0; pr < 2; ++pr) {
@@ -418,7 +433,7 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         // rows (2j, 2j+1) of the tile are (gate_j, up_j): 64 outputs per token
         const int64_t out0 = n0 >> 1;
         const int64_t outs = ((p.n - n0 < TC_ROWS ? p.n - n0 : TC_ROWS)) >> 1;
-#pragma unroll 1
+#pragma unroll 4
         for (int e = et; e < MT * (TC_ROWS / 2); e += 256) {
           const int mm = e / (TC_ROWS / 2), jj = e % (TC_ROWS / 2);
           if (mm < rows_here && jj < outs) {
@@ -428,7 +443,7 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         }
       } else {
         const int64_t cols_here = (p.n - n0 < TC_ROWS) ? (p.n - n0) : TC_ROWS;
-#pragma unroll 1
+#pragma unroll 4
         for (int e = et; e < MT * TC_ROWS; e += 256) {
           const int mm = e / TC_ROWS, nn = e % TC_ROWS;
           if (mm < rows_here && nn < cols_here) {
