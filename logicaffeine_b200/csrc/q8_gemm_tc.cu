@@ -281,14 +281,16 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       if (pr == 1 && lane == 0) TC_TRACE(i, 12);
       tc_fence_after();
       if (elect_one()) {
+        // Per block: d = q * lo' first, then d = q * hi + d * 2^-11 (the residual plane is folded
+        // in by the accumulator scaling of the MMA itself, from one copy of the weights).  The
+        // two blocks' chains are interleaved: back-to-back MMAs on one accumulator run at
+        // their latency, alternating accumulators at their throughput.
 #pragma unroll
-        for (int bb = 0; bb < 2; ++bb) {
-          const int blk = 2 * pr + bb;
-          const uint32_t d = tmem_base + ACC_COL0 + blk * MT;
-          // d = q * lo' first, then d = q * hi + d * 2^-11: the residual plane is folded in by
-          // the accumulator scaling of the MMA itself, from one copy of the weights
+        for (int u = 0; u < 2 * LIMBS; ++u) {
 #pragma unroll
-          for (int u = 0; u < 2 * LIMBS; ++u) {
+          for (int bb = 0; bb < 2; ++bb) {
+            const int blk = 2 * pr + bb;
+            const uint32_t d = tmem_base + ACC_COL0 + blk * MT;
             const int l = (LIMBS == 2) ? 1 - (u >> 1) : 0, j = u & 1;
             const int kk = blk * 2 + j;  // K=16 step inside the stage
             const uint32_t a = tmem_base + ts * TA_COLS + kk * 8;
