@@ -104,6 +104,24 @@ __device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const CUtensorM
       : "memory");
 }
 // Ask L2 to fetch a tile ahead of the TMA load that will want it.
+// ---- TMA stores (shared -> global, bulk async-group completion).  Coordinates past the
+// tensor's extents are clipped by the hardware; x * element size must be a multiple of 16.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* smem_src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all of this thread's bulk groups have finished READING shared memory (it may be rewritten)
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all of this thread's bulk groups are complete (their global writes are done)
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // brings the 128-byte line holding `p` into L2; no register result, no fault on a bad address
 __device__ __forceinline__ void prefetch_l2(const void* p) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
@@ -282,5 +300,9 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(int a_fmt, int b_fmt, int 
 logos_status_t make_tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, uint32_t elem_bytes,
                                   uint64_t inner, uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner,
                                   uint32_t box_outer, CUtensorMapSwizzle swizzle);
+// Three dimensions, no swizzle: d0 innermost (contiguous), pitches of d1 and d2 in bytes.
+logos_status_t make_tensor_map_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, uint32_t elem_bytes,
+                                  uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1_bytes, uint64_t pitch2_bytes,
+                                  uint32_t box0, uint32_t box1, uint32_t box2);
 
 }  // namespace logos

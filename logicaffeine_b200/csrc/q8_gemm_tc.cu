@@ -18,6 +18,12 @@
 //        accumulator scaling, so hi + lo*2^-11 is recombined on the tensor core
 //   8 drain warps: tcgen05.ld the block's partial sums (two blocks per wait),
 //        acc += s * partial in f32 registers, then the epilogue.
+// A CTA is persistent: it takes work items (tile of 128 weight rows x K split) in turn,
+// and the rings keep running across items, so the next item's weights stream in, are
+// converted and multiplied while the drain warps finish the previous item's epilogue.
+// The epilogue forms the output tile in shared memory in its final type and hands it to
+// one TMA store (split-K partials, plain outputs, SwiGLU into activation planes); other
+// output forms go through a plain loop of global stores.
 // All hand-offs are mbarriers; every wait is bounded and reports through the
 // device status word instead of spinning for ever.
 //
@@ -51,6 +57,12 @@ constexpr int TA_LIMB_COLS = 64; // TMEM columns per converted stage and copy: 1
 constexpr int CONV_WARPS = 4;
 constexpr int CONV_WARP0 = 4, DRAIN_WARP0 = CONV_WARP0 + CONV_WARPS;
 constexpr int TC_THREADS = (DRAIN_WARP0 + 8) * 32;  // 4 single-role warps, converter warps, 8 drain warps
+// Token groups an MMA warp cuts each block into (MMA N = MT / NSPLIT).  Measured: an MMA costs
+// about 45 cycles whether N is 32 or 64 once four independent accumulation chains are in
+// flight, and about 85 with two, so more, smaller MMAs lose what the extra chains gain.
+#ifndef LOGOS_TC_NSPLIT
+#define LOGOS_TC_NSPLIT 1
+#endif
 constexpr int ACC_PAIRS = 2;     // TMEM accumulator ring: each entry holds two Q8 blocks
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int RAW_BYTES = TC_ROWS * TC_KSTAGE;  // 16 KB
@@ -62,11 +74,22 @@ struct TcCfg {
   static constexpr int ACC_COL0 = TA_STAGES * TA_COLS;
   static constexpr int ACT_ATOM_BYTES = NB * 128;       // one 64-column half: NB rows x 128 B
   static constexpr int ACT_BYTES = 2 * ACT_ATOM_BYTES;
-  static constexpr size_t SMEM_NEED = 1024 + (size_t)RAW_STAGES * RAW_BYTES + (size_t)ACT_STAGES * ACT_BYTES + 512;
+  static constexpr int EPI_BYTES = MT * TC_ROWS * 4;    // output tile staged for the store: [MT][128] f32 at most
+  static constexpr size_t SMEM_NEED =
+      1024 + (size_t)RAW_STAGES * RAW_BYTES + (size_t)ACT_STAGES * ACT_BYTES + EPI_BYTES + 512;
   // the CTA allocates all of tensor memory, so ask for enough shared memory that only one CTA fits an SM
   static constexpr size_t SMEM = SMEM_NEED > 120 * 1024 ? SMEM_NEED : 120 * 1024;
+  static_assert(SMEM <= 227 * 1024, "shared memory budget");
   static_assert(ACC_COL0 + ACC_PAIRS * 2 * MT <= (int)TMEM_COLS, "TMEM budget");
   static_assert(MT % 16 == 0 && MT <= 64, "MMA N");
+};
+
+// How a finished tile leaves the CTA.
+enum : int {
+  STORE_GENERIC = 0,      // loop of global stores (any epilogue and output type)
+  STORE_TMA_PARTIAL = 1,  // f32 split-K partials [splits][M][N], one 3-D TMA store
+  STORE_TMA_PLAIN = 2,    // f32 / f16 / bf16 [M][ldc], no epilogue, one TMA store
+  STORE_TMA_SWIGLU = 3,   // SwiGLU into fp16 activation planes [M][ldc], one TMA store per plane
 };
 
 struct TcParams {
@@ -81,9 +104,22 @@ struct TcParams {
   float* partials;
   int splits;
   int stages_total;
+  int items;        // work items: row tiles x splits
+  int store_mode;
   int* status;
-  long long* trace;  // optional: SM-clock timestamps of CTA (0,0,0), [stage][16]
+  long long* trace;  // optional: SM-clock timestamps of CTA (0,0,0), first item, [stage][16]
 };
+
+// Work item w = (row tile, K split): the splits of a tile are neighbours.
+struct TcItem { int tile, split, st_begin, nst; };
+__device__ __forceinline__ TcItem tc_item(const TcParams& p, int w) {
+  TcItem it;
+  it.tile = w / p.splits;
+  it.split = w - it.tile * p.splits;
+  it.st_begin = (int)(((int64_t)it.split * p.stages_total) / p.splits);
+  it.nst = (int)(((int64_t)(it.split + 1) * p.stages_total) / p.splits) - it.st_begin;
+  return it;
+}
 
 // First failure wins: code in word 0, where it happened in words 1..5.
 __device__ __forceinline__ void tc_report(int* status, int code, int stage, int nst) {
@@ -92,11 +128,10 @@ __device__ __forceinline__ void tc_report(int* status, int code, int stage, int 
   }
 }
 
-// Timestamp slot `ev` of stage `i` (tracing only; CTA 0, one lane per role).
+// Timestamp slot `ev` of stage `i` (tracing only; CTA 0, its first item, one lane per role).
 #define TC_TRACE(i, ev)                                                                          \
   do {                                                                                           \
-    if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (i) < 64)            \
-      p.trace[(i) * 16 + (ev)] = clock64();                                                      \
+    if (trace_on && (i) < 64) p.trace[(i) * 16 + (ev)] = clock64();                              \
   } while (0)
 
 __device__ __forceinline__ float silu_f(float g) { return __fdiv_rn(g, 1.0f + expf(-g)); }
@@ -142,10 +177,19 @@ __device__ __forceinline__ void tc_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
   else tc_ld_32x32b_x8(taddr, r);
 }
 
+// fp32 -> the value(s) an activation plane pair stores (same rounding as act_store)
+__device__ __forceinline__ void act_split_planes(int mode, float x, __half* h, __half* l) {
+  if (mode == LOGOS_BF16) x = __bfloat162float(__float2bfloat16_rn(x));
+  x = act_clamp(x);
+  *h = __float2half_rn(x);
+  *l = __float2half_rn((x - __half2float(*h)) * 2048.f);
+}
+
 template <int MT, int LIMBS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_ahi,
-                  const __grid_constant__ CUtensorMap map_alo, const TcParams p) {
+                  const __grid_constant__ CUtensorMap map_alo, const __grid_constant__ CUtensorMap map_o0,
+                  const __grid_constant__ CUtensorMap map_o1, const TcParams p) {
   using Cfg = TcCfg<MT, LIMBS>;
   constexpr int TA_COLS = Cfg::TA_COLS;
   constexpr int ACC_COL0 = Cfg::ACC_COL0;
@@ -154,7 +198,8 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* raw = smem;
   uint8_t* act = raw + RAW_STAGES * RAW_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(act + ACT_STAGES * Cfg::ACT_BYTES);
+  uint8_t* epi = act + ACT_STAGES * Cfg::ACT_BYTES;  // 1024-aligned: all sizes before it are multiples of 1024
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi + Cfg::EPI_BYTES);
   uint64_t* raw_full = bars;                    // [RAW_STAGES]
   uint64_t* raw_empty = raw_full + RAW_STAGES;  // [RAW_STAGES]
   uint64_t* act_full = raw_empty + RAW_STAGES;  // [ACT_STAGES]
@@ -168,12 +213,10 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const int64_t n0 = (int64_t)blockIdx.x * TC_ROWS;
-  const int split = blockIdx.y;
   const int64_t m0 = (int64_t)blockIdx.z * MT;
-  const int st_begin = (int)(((int64_t)split * p.stages_total) / p.splits);
-  const int st_end = (int)(((int64_t)(split + 1) * p.stages_total) / p.splits);
-  const int nst = st_end - st_begin;
+  const int items = p.items;
+  const bool cta0 = p.trace && blockIdx.x == 0 && blockIdx.z == 0;
+  bool trace_on = cta0;
 
   if (tid == 0) TC_TRACE(63, 0);  // kernel entry
   // a kernel that gave up earlier left a code behind: do not start new work on top of it
@@ -192,6 +235,8 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_ahi);
     if (LIMBS == 2) prefetch_tensormap(&map_alo);
+    if (p.store_mode != STORE_GENERIC) prefetch_tensormap(&map_o0);
+    if (p.store_mode == STORE_TMA_SWIGLU) prefetch_tensormap(&map_o1);
   }
   if (warp == 3) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -209,51 +254,63 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   // statement of every role below).
   constexpr bool kRebalance = (CONV_WARPS == 8);
 
+  // Every role walks the same sequence of (item, stage) pairs; `gs` counts stages across items
+  // and alone decides ring slots and barrier phases, so the rings never drain between items.
   if (warp == 0) {
     // ------------------------------------------------------------ weight producer
     if (kRebalance) setmaxnreg_dec<48>();
     if (lane == 0) {
       const uint64_t pol = policy_evict_first();
-      // The smem ring alone (RAW_STAGES x 16 KB per SM) does not cover HBM latency under load:
-      // L2 prefetches run RAW_PREFETCH stages ahead of the TMA loads.  They start only after
-      // the first loads are on their way, so that nothing queues in front of those.
-      for (int i = 0; i < nst; ++i) {
-        int st = i % RAW_STAGES;
-        uint32_t ph = (uint32_t)(i / RAW_STAGES) & 1u;
-        if (!mbar_wait(&raw_empty[st], ph ^ 1u)) { ok = false; tc_report(p.status, 2010, i, nst); break; }
-        TC_TRACE(i, 0);
-        mbar_arrive_expect_tx(&raw_full[st], RAW_BYTES);
-        tma_load_2d_hint(raw + st * RAW_BYTES, &map_q, &raw_full[st], (st_begin + i) * TC_KSTAGE, (int)n0, pol);
-        if (i + 1 >= RAW_STAGES) {
-          // after the ring's first fill: stages RAW_STAGES .. RAW_PREFETCH in one go, then one per stage
-          const int first = (i + 1 == RAW_STAGES) ? RAW_STAGES : i + RAW_PREFETCH;
-          for (int j = first; j <= i + RAW_PREFETCH && j < nst; ++j)
-            tma_prefetch_l2_2d(&map_q, (st_begin + j) * TC_KSTAGE, (int)n0);
+      int gs = 0;
+      for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
+        const TcItem it = tc_item(p, w);
+        const int n0 = it.tile * TC_ROWS, nst = it.nst, st_begin = it.st_begin;
+        trace_on = cta0 && w == 0;
+        // The smem ring alone (RAW_STAGES x 16 KB per SM) does not cover HBM latency under load:
+        // L2 prefetches run RAW_PREFETCH stages ahead of the TMA loads.  They start only after
+        // the item's first loads are on their way, so that nothing queues in front of those.
+        for (int i = 0; i < nst; ++i, ++gs) {
+          const int st = gs % RAW_STAGES;
+          const uint32_t ph = (uint32_t)(gs / RAW_STAGES) & 1u;
+          if (!mbar_wait(&raw_empty[st], ph ^ 1u)) { ok = false; tc_report(p.status, 2010, i, nst); break; }
+          TC_TRACE(i, 0);
+          mbar_arrive_expect_tx(&raw_full[st], RAW_BYTES);
+          tma_load_2d_hint(raw + st * RAW_BYTES, &map_q, &raw_full[st], (st_begin + i) * TC_KSTAGE, n0, pol);
+          if (i + 1 >= RAW_STAGES) {
+            // after the first fill: stages RAW_STAGES .. RAW_PREFETCH in one go, then one per stage
+            const int first = (i + 1 == RAW_STAGES) ? RAW_STAGES : i + RAW_PREFETCH;
+            for (int j = first; j <= i + RAW_PREFETCH && j < nst; ++j)
+              tma_prefetch_l2_2d(&map_q, (st_begin + j) * TC_KSTAGE, n0);
+          }
         }
       }
-
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ activation producer
     if (kRebalance) setmaxnreg_dec<48>();
     if (lane == 0) {
       const uint64_t pol = policy_evict_last();
-      for (int i = 0; i < nst; ++i) {
-        int st = i % ACT_STAGES;
-        uint32_t ph = (uint32_t)(i / ACT_STAGES) & 1u;
-        if (!mbar_wait(&act_empty[st], ph ^ 1u)) { ok = false; tc_report(p.status, 2020, i, nst); break; }
-        TC_TRACE(i, 1);
-        mbar_arrive_expect_tx(&act_full[st], Cfg::ACT_BYTES);
-        uint8_t* sb = act + st * Cfg::ACT_BYTES;
-        int x = (st_begin + i) * TC_KSTAGE;
+      int gs = 0;
+      for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
+        const TcItem it = tc_item(p, w);
+        const int nst = it.nst, st_begin = it.st_begin;
+        trace_on = cta0 && w == 0;
+        for (int i = 0; i < nst; ++i, ++gs) {
+          const int st = gs % ACT_STAGES;
+          const uint32_t ph = (uint32_t)(gs / ACT_STAGES) & 1u;
+          if (!mbar_wait(&act_empty[st], ph ^ 1u)) { ok = false; tc_report(p.status, 2020, i, nst); break; }
+          TC_TRACE(i, 1);
+          mbar_arrive_expect_tx(&act_full[st], Cfg::ACT_BYTES);
+          uint8_t* sb = act + st * Cfg::ACT_BYTES;
+          const int x = (st_begin + i) * TC_KSTAGE;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          tma_load_2d_hint(sb + h * Cfg::ACT_ATOM_BYTES, &map_ahi, &act_full[st], x + h * 64, (int)m0, pol);
-          if (LIMBS == 2)
-            tma_load_2d_hint(sb + h * Cfg::ACT_ATOM_BYTES + MT * 128, &map_alo, &act_full[st], x + h * 64, (int)m0, pol);
+          for (int h = 0; h < 2; ++h) {
+            tma_load_2d_hint(sb + h * Cfg::ACT_ATOM_BYTES, &map_ahi, &act_full[st], x + h * 64, (int)m0, pol);
+            if (LIMBS == 2)
+              tma_load_2d_hint(sb + h * Cfg::ACT_ATOM_BYTES + MT * 128, &map_alo, &act_full[st], x + h * 64, (int)m0, pol);
+          }
         }
       }
-
     }
   } else if (warp == 2 || warp == 3) {
     // ------------------------------------------------------------ MMA issuers
@@ -264,92 +321,106 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // waited on, phase after phase, by the same warp, which the odd/even phase test needs.
     // A warp runs its loop with all lanes (addresses and descriptors stay warp-uniform) and one
     // elected lane issues the tcgen05 instructions.  A pair owns accumulator ring entry `pr`.
-    constexpr uint32_t idesc = make_idesc_f16(0, 0, TC_ROWS, MT);
+    constexpr int NSPLIT = LOGOS_TC_NSPLIT <= MT / 16 ? LOGOS_TC_NSPLIT : MT / 16;  // token groups per block
+    constexpr int MN = MT / NSPLIT;                  // tokens per MMA (MMA N, a multiple of 16)
+    constexpr uint32_t idesc = make_idesc_f16(0, 0, TC_ROWS, MN);
     static_assert(ACC_PAIRS == 2, "one accumulator ring entry per MMA warp");
     const int pr = warp - 2;
-    for (int i = 0; i < nst && ok; ++i) {
-      const int ts = i % TA_STAGES, as = i % ACT_STAGES;
-      const uint32_t tph = (uint32_t)(i / TA_STAGES) & 1u, aph = (uint32_t)(i / ACT_STAGES) & 1u;
-      if (!mbar_wait(&ta_full[ts], tph)) { ok = false; if (lane == 0) tc_report(p.status, 2031, i, nst); break; }
-      if (lane == 0 && pr == 0) TC_TRACE(i, 2);
-      if (!mbar_wait(&act_full[as], aph)) { ok = false; if (lane == 0) tc_report(p.status, 2032, i, nst); break; }
-      if (lane == 0 && pr == 0) TC_TRACE(i, 3);
-      const uint32_t act_base = smem_u32(act + as * Cfg::ACT_BYTES);
-      const uint32_t sph = (uint32_t)i & 1u;
-      if (pr == 1 && lane == 0) TC_TRACE(i, 11);
-      if (!mbar_wait(&acc_empty[pr], sph ^ 1u)) { ok = false; if (lane == 0) tc_report(p.status, 2033, i, nst); break; }
-      if (pr == 1 && lane == 0) TC_TRACE(i, 12);
-      tc_fence_after();
-      if (elect_one()) {
-        // Per block: d = q * lo' first, then d = q * hi + d * 2^-11 (the residual plane is folded
-        // in by the accumulator scaling of the MMA itself, from one copy of the weights).  The
-        // two blocks' chains are interleaved: back-to-back MMAs on one accumulator run at
-        // their latency, alternating accumulators at their throughput.
+    int gs = 0;
+    for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
+      const int nst = tc_item(p, w).nst;
+      trace_on = cta0 && w == 0;
+      for (int i = 0; i < nst && ok; ++i, ++gs) {
+        const int ts = gs % TA_STAGES, as = gs % ACT_STAGES;
+        const uint32_t tph = (uint32_t)(gs / TA_STAGES) & 1u, aph = (uint32_t)(gs / ACT_STAGES) & 1u;
+        if (!mbar_wait(&ta_full[ts], tph)) { ok = false; if (lane == 0) tc_report(p.status, 2031, i, nst); break; }
+        if (lane == 0 && pr == 0) TC_TRACE(i, 2);
+        if (!mbar_wait(&act_full[as], aph)) { ok = false; if (lane == 0) tc_report(p.status, 2032, i, nst); break; }
+        const uint32_t act_base = smem_u32(act + as * Cfg::ACT_BYTES);
+        const uint32_t sph = (uint32_t)gs & 1u;
+        if (pr == 1 && lane == 0) TC_TRACE(i, 11);
+        if (!mbar_wait(&acc_empty[pr], sph ^ 1u)) { ok = false; if (lane == 0) tc_report(p.status, 2033, i, nst); break; }
+        if (pr == 1 && lane == 0) TC_TRACE(i, 12);
+        tc_fence_after();
+        if (elect_one()) {
+          // Per block: d = q * lo' first, then d = q * hi + d * 2^-11 (the residual plane is folded
+          // in by the accumulator scaling of the MMA itself, from one copy of the weights).
+          // Back-to-back MMAs on one accumulator run at their latency, not at their throughput,
+          // so the work is cut into as many independent chains as the tile allows - two blocks x
+          // NSPLIT token groups - and the chains are issued interleaved.
 #pragma unroll
-        for (int u = 0; u < 2 * LIMBS; ++u) {
+          for (int u = 0; u < 2 * LIMBS; ++u) {
 #pragma unroll
-          for (int bb = 0; bb < 2; ++bb) {
-            const int blk = 2 * pr + bb;
-            const uint32_t d = tmem_base + ACC_COL0 + blk * MT;
-            const int l = (LIMBS == 2) ? 1 - (u >> 1) : 0, j = u & 1;
-            const int kk = blk * 2 + j;  // K=16 step inside the stage
-            const uint32_t a = tmem_base + ts * TA_COLS + kk * 8;
-            const uint64_t bdesc = make_desc_sw128(act_base + (kk >> 2) * Cfg::ACT_ATOM_BYTES + l * MT * 128 +
-                                                   (kk & 3) * 32);
-            if (LIMBS == 2 && u == 2) tc_mma_f16_ts_scaled_d<11>(d, a, bdesc, idesc);
-            else tc_mma_f16_ts(d, a, bdesc, idesc, (uint32_t)(u != 0));
+            for (int bb = 0; bb < 2; ++bb) {
+#pragma unroll
+              for (int hh = 0; hh < NSPLIT; ++hh) {
+                const int blk = 2 * pr + bb;
+                const uint32_t d = tmem_base + ACC_COL0 + blk * MT + hh * MN;
+                const int l = (LIMBS == 2) ? 1 - (u >> 1) : 0, j = u & 1;
+                const int kk = blk * 2 + j;  // K=16 step inside the stage
+                const uint32_t a = tmem_base + ts * TA_COLS + kk * 8;
+                const uint64_t bdesc = make_desc_sw128(act_base + (kk >> 2) * Cfg::ACT_ATOM_BYTES + l * MT * 128 +
+                                                       hh * MN * 128 + (kk & 3) * 32);
+                if (LIMBS == 2 && u == 2) tc_mma_f16_ts_scaled_d<11>(d, a, bdesc, idesc);
+                else tc_mma_f16_ts(d, a, bdesc, idesc, (uint32_t)(u != 0));
+              }
+            }
           }
+          if (pr == 1) TC_TRACE(i, 13);
+          tc_commit(&acc_full[pr]);
+          // the stage's operands are free once both warps' MMAs have completed
+          tc_commit(&ta_empty[ts]);
+          tc_commit(&act_empty[as]);
         }
-        if (pr == 1) TC_TRACE(i, 13);
-        tc_commit(&acc_full[pr]);
-        // the stage's operands are free once both warps' MMAs have completed
-        tc_commit(&ta_empty[ts]);
-        tc_commit(&act_empty[as]);
-        if (pr == 1) TC_TRACE(i, 14);
+        __syncwarp();
+        if (lane == 0 && pr == 0) TC_TRACE(i, 4);
       }
-      __syncwarp();
-      if (lane == 0 && pr == 0) TC_TRACE(i, 4);
-      if (lane == 0 && pr == 1) TC_TRACE(i, 15);
     }
 
   } else if (warp >= CONV_WARP0 && warp < DRAIN_WARP0) {
     // ------------------------------------------------------------ converters: int8 smem -> fp16 TMEM
-    // Two warps per lane quarter; each converts half of the stage's eight 16-byte chunks per row.
+    // One or two warps per lane quarter; each converts its share of the stage's eight 16-byte
+    // chunks per row.
     if (kRebalance) setmaxnreg_dec<64>();
     const int qd = warp & 3;
     const int chalf = (warp - CONV_WARP0) >> 2;
     const uint32_t row = qd * 32 + lane;
     const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16);
-    for (int i = 0; i < nst; ++i) {
-      int rs = i % RAW_STAGES, ts = i % TA_STAGES;
-      uint32_t rph = (uint32_t)(i / RAW_STAGES) & 1u, tph = (uint32_t)(i / TA_STAGES) & 1u;
-      if (!mbar_wait(&raw_full[rs], rph)) { ok = false; if (lane == 0) tc_report(p.status, 2041, i, nst); break; }
-      if (warp == CONV_WARP0 && lane == 0) TC_TRACE(i, 5);
-      if (!mbar_wait(&ta_empty[ts], tph ^ 1u)) { ok = false; if (lane == 0) tc_report(p.status, 2042, i, nst); break; }
-      if (warp == CONV_WARP0 && lane == 0) TC_TRACE(i, 6);
-      tc_fence_after();
-      const uint8_t* rb = raw + rs * RAW_BYTES;
+    int gs = 0;
+    for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
+      const int nst = tc_item(p, w).nst;
+      trace_on = cta0 && w == 0;
+      for (int i = 0; i < nst; ++i, ++gs) {
+        const int rs = gs % RAW_STAGES, ts = gs % TA_STAGES;
+        const uint32_t rph = (uint32_t)(gs / RAW_STAGES) & 1u, tph = (uint32_t)(gs / TA_STAGES) & 1u;
+        if (!mbar_wait(&raw_full[rs], rph)) { ok = false; if (lane == 0) tc_report(p.status, 2041, i, nst); break; }
+        if (warp == CONV_WARP0 && lane == 0) TC_TRACE(i, 5);
+        if (!mbar_wait(&ta_empty[ts], tph ^ 1u)) { ok = false; if (lane == 0) tc_report(p.status, 2042, i, nst); break; }
+        if (warp == CONV_WARP0 && lane == 0) TC_TRACE(i, 6);
+        tc_fence_after();
+        const uint8_t* rb = raw + rs * RAW_BYTES;
 #pragma unroll
-      for (int cc = 0; cc < 32 / CONV_WARPS; ++cc) {
-        const int c = chalf * (32 / CONV_WARPS) + cc;
-        const uint4 w = *reinterpret_cast<const uint4*>(rb + swz128(row, c));
-        uint32_t r[8];
-        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+        for (int cc = 0; cc < 32 / CONV_WARPS; ++cc) {
+          const int c = chalf * (32 / CONV_WARPS) + cc;
+          const uint4 wv = *reinterpret_cast<const uint4*>(rb + swz128(row, c));
+          uint32_t r[8];
+          const uint32_t ws[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
-        for (int wi = 0; wi < 4; ++wi) {
-          uint32_t u = ws[wi] ^ 0x80808080u;
-          r[2 * wi] = cvt_pair(u, 0x4140);
-          r[2 * wi + 1] = cvt_pair(u, 0x4342);
+          for (int wi = 0; wi < 4; ++wi) {
+            uint32_t u = ws[wi] ^ 0x80808080u;
+            r[2 * wi] = cvt_pair(u, 0x4140);
+            r[2 * wi + 1] = cvt_pair(u, 0x4342);
+          }
+          tc_st_32x32b_x8(t_lane + ts * TA_COLS + c * 8, r);
         }
-        tc_st_32x32b_x8(t_lane + ts * TA_COLS + c * 8, r);
-      }
-      tc_wait_st();
-      if (warp == CONV_WARP0 && lane == 0) TC_TRACE(i, 7);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&raw_empty[rs]);
-        mbar_arrive(&ta_full[ts]);
+        tc_wait_st();
+        if (warp == CONV_WARP0 && lane == 0) TC_TRACE(i, 7);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&raw_empty[rs]);
+          mbar_arrive(&ta_full[ts]);
+        }
       }
     }
 
@@ -362,111 +433,170 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int qd = warp & 3;
     const int half = (warp - DRAIN_WARP0) >> 2;
     constexpr int HC = MT / 2;  // token columns per drain warp
-    const int64_t n = n0 + qd * 32 + lane;
-    const bool n_ok = n < p.n;
+    const int nl = qd * 32 + lane;  // row of the tile this thread drains
     const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16) + ACC_COL0 + half * HC;
     const int64_t kb_per_row = p.k >> 5;
-    const float* srow = p.s + (n_ok ? n : 0) * kb_per_row;
-    uint64_t acc2[HC / 2];  // packed f32 pairs: the drain arithmetic uses two-wide f32 FMAs
+    const int et = tid - DRAIN_WARP0 * 32;  // 0..255 among the drain warps
+    const int64_t rows_here = (p.m - m0 < MT) ? (p.m - m0) : MT;
+    bool stored = false;  // thread et == 0: a TMA store of this CTA may still be reading the staging tile
+    int gs = 0;
+    for (int w = blockIdx.x; w < items; w += gridDim.x) {
+      const TcItem it = tc_item(p, w);
+      const int nst = it.nst, st_begin = it.st_begin;
+      const int64_t n0 = (int64_t)it.tile * TC_ROWS;
+      trace_on = cta0 && w == 0;
+      const int64_t n = n0 + nl;
+      const bool n_ok = n < p.n;
+      const float* srow = p.s + (n_ok ? n : 0) * kb_per_row;
+      uint64_t acc2[HC / 2];  // packed f32 pairs: the drain arithmetic uses two-wide f32 FMAs
 #pragma unroll
-    for (int j = 0; j < HC / 2; ++j) acc2[j] = 0ull;
-    int blk_count = 0;
-    // The four scales of a stage are one 16-byte load per row.  Their latency (L2, or HBM
-    // once per 128-byte line, i.e. every eight stages) must not sit between the TMEM load and
-    // the arithmetic: registers hold the scales two stages ahead, and the line after next
-    // is prefetched into L2.
-    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4* sc_src = reinterpret_cast<const float4*>(srow) + st_begin;
-    float4 sc_a = (n_ok && 0 < nst) ? __ldg(sc_src) : zero4;
-    float4 sc_b = (n_ok && 1 < nst) ? __ldg(sc_src + 1) : zero4;
-    if (n_ok && 8 < nst) prefetch_l2(sc_src + 8);
-    for (int i = 0; i < nst && ok; ++i) {
-      const float4 sc4 = sc_a;
-      sc_a = sc_b;
-      sc_b = (n_ok && i + 2 < nst) ? __ldg(sc_src + i + 2) : zero4;
-      if (n_ok && (i & 7) == 0 && i + 16 < nst) prefetch_l2(sc_src + i + 16);
-      const float scs[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
+      for (int j = 0; j < HC / 2; ++j) acc2[j] = 0ull;
+      // The four scales of a stage are one 16-byte load per row.  Their latency (L2, or HBM
+      // once per 128-byte line, i.e. every eight stages) must not sit between the TMEM load and
+      // the arithmetic: registers hold the scales two stages ahead, and the line after next
+      // is prefetched into L2.
+      const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4* sc_src = reinterpret_cast<const float4*>(srow) + st_begin;
+      float4 sc_a = (n_ok && 0 < nst) ? __ldg(sc_src) : zero4;
+      float4 sc_b = (n_ok && 1 < nst) ? __ldg(sc_src + 1) : zero4;
+      if (n_ok && 8 < nst) prefetch_l2(sc_src + 8);
+      for (int i = 0; i < nst && ok; ++i, ++gs) {
+        const float4 sc4 = sc_a;
+        sc_a = sc_b;
+        sc_b = (n_ok && i + 2 < nst) ? __ldg(sc_src + i + 2) : zero4;
+        if (n_ok && (i & 7) == 0 && i + 16 < nst) prefetch_l2(sc_src + i + 16);
+        const float scs[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
+        const uint32_t fph = (uint32_t)gs & 1u;
 #pragma unroll
-      for (int pr = 0; pr < 2; ++pr) {
-        const int pair = blk_count >> 1;
-        const int slot = pair % ACC_PAIRS;
-        const uint32_t fph = (uint32_t)(pair / ACC_PAIRS) & 1u;
-        if (!mbar_wait(&acc_full[slot], fph)) { ok = false; if (lane == 0) tc_report(p.status, 2050, i, nst); break; }
-        if (warp == DRAIN_WARP0 && lane == 0 && pr == 0) TC_TRACE(i, 8);
-        tc_fence_after();
-        uint32_t b0[HC], b1[HC];
-        tc_ld_cols<HC>(t_lane + (slot * 2) * MT, b0);
-        tc_ld_cols<HC>(t_lane + (slot * 2 + 1) * MT, b1);
-        tc_wait_ld();
-        if (warp == DRAIN_WARP0 && lane == 0 && pr == 0) TC_TRACE(i, 9);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[slot]);
-        const uint64_t sc0 = pack2(scs[2 * pr]), sc1 = pack2(scs[2 * pr + 1]);
+        for (int pr = 0; pr < 2; ++pr) {
+          if (!mbar_wait(&acc_full[pr], fph)) { ok = false; if (lane == 0) tc_report(p.status, 2050, i, nst); break; }
+          if (warp == DRAIN_WARP0 && lane == 0 && pr == 0) TC_TRACE(i, 8);
+          tc_fence_after();
+          uint32_t b0[HC], b1[HC];
+          tc_ld_cols<HC>(t_lane + (pr * 2) * MT, b0);
+          tc_ld_cols<HC>(t_lane + (pr * 2 + 1) * MT, b1);
+          tc_wait_ld();
+          if (warp == DRAIN_WARP0 && lane == 0) TC_TRACE(i, pr == 0 ? 9 : 14);
+          if (trace_on && lane == 0 && i < 64)  // the last of the eight drain warps to get here
+            atomicMax(reinterpret_cast<unsigned long long*>(&p.trace[i * 16 + (pr == 0 ? 3 : 15)]), (unsigned long long)clock64());
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[pr]);
+          const uint64_t sc0 = pack2(scs[2 * pr]), sc1 = pack2(scs[2 * pr + 1]);
 #pragma unroll
-        for (int j = 0; j < HC / 2; ++j) {
-          acc2[j] = ffma2(sc0, pack2(b0[2 * j], b0[2 * j + 1]), acc2[j]);
-          acc2[j] = ffma2(sc1, pack2(b1[2 * j], b1[2 * j + 1]), acc2[j]);
-        }
-        if (warp == DRAIN_WARP0 && lane == 0 && pr == 0) TC_TRACE(i, 10);
-        blk_count += 2;
-      }
-    }
-
-
-    if (warp == DRAIN_WARP0 && lane == 0) TC_TRACE(63, 2);  // main loop done
-    // ---- epilogue.  The accumulators go to shared memory first (the weight ring is idle by
-    // now) and a short rolled loop applies the epilogue and writes rows of consecutive n:
-    // unrolling 32 generic stores per thread made the code so large that its instruction
-    // fetches, cold in every CTA, cost more than the stores.
-    float* stage_c = reinterpret_cast<float*>(raw);  // [MT][EPI_PITCH]
-    constexpr int EPI_PITCH = TC_ROWS + 4;
-#pragma unroll
-    for (int j = 0; j < HC / 2; ++j) {
-      stage_c[(half * HC + 2 * j) * EPI_PITCH + qd * 32 + lane] = __uint_as_float((uint32_t)acc2[j]);
-      stage_c[(half * HC + 2 * j + 1) * EPI_PITCH + qd * 32 + lane] = __uint_as_float((uint32_t)(acc2[j] >> 32));
-    }
-    if (warp == DRAIN_WARP0 && lane == 0) TC_TRACE(63, 5);  // staged
-    asm volatile("bar.sync 2, 256;" ::: "memory");  // the eight drain warps
-    if (ok) {
-      const int et = tid - DRAIN_WARP0 * 32;  // 0..255
-      const int64_t rows_here = (p.m - m0 < MT) ? (p.m - m0) : MT;
-      if (p.splits <= 1 && p.epilogue == EPI_SWIGLU) {
-        // rows (2j, 2j+1) of the tile are (gate_j, up_j): 64 outputs per token
-        const int64_t out0 = n0 >> 1;
-        const int64_t outs = ((p.n - n0 < TC_ROWS ? p.n - n0 : TC_ROWS)) >> 1;
-#pragma unroll 4
-        for (int e = et; e < MT * (TC_ROWS / 2); e += 256) {
-          const int mm = e / (TC_ROWS / 2), jj = e % (TC_ROWS / 2);
-          if (mm < rows_here && jj < outs) {
-            const float g = stage_c[mm * EPI_PITCH + 2 * jj], u = stage_c[mm * EPI_PITCH + 2 * jj + 1];
-            store_c(p, (m0 + mm) * p.ldc + out0 + jj, __fmul_rn(silu_f(g), u));
+          for (int j = 0; j < HC / 2; ++j) {
+            acc2[j] = ffma2(sc0, pack2(b0[2 * j], b0[2 * j + 1]), acc2[j]);
+            acc2[j] = ffma2(sc1, pack2(b1[2 * j], b1[2 * j + 1]), acc2[j]);
           }
+          if (warp == DRAIN_WARP0 && lane == 0 && pr == 0) TC_TRACE(i, 10);
+        }
+      }
+      if (warp == DRAIN_WARP0 && lane == 0) TC_TRACE(63, 2);  // main loop of the first item done
+
+      // ---- epilogue.  The tile goes to shared memory in the form it will have in global
+      // memory, and one thread hands it to the TMA; the next item's stages are already being
+      // loaded, converted and multiplied meanwhile.  The staging tile is free again once the
+      // previous store has read it.
+      if (et == 0 && stored) bulk_wait_read_all();
+      int all_ok;
+      asm volatile(
+          "{\n\t.reg .pred q, r;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred r, 2, 256, q;\n\tselp.u32 %0, 1, 0, r;\n\t}"
+          : "=r"(all_ok)
+          : "r"((uint32_t)ok)
+          : "memory");  // the eight drain warps agree on leaving
+      if (!all_ok) { ok = false; break; }
+      // element x (0..HC-1) of this thread's row: token half * HC + x
+#define TC_ACC(x) __uint_as_float((uint32_t)(((x) & 1) ? (acc2[(x) >> 1] >> 32) : acc2[(x) >> 1]))
+      const int mode = p.store_mode;
+      if (mode == STORE_TMA_SWIGLU) {
+        // rows (2j, 2j+1) of the tile are (gate_j, up_j): neighbouring lanes.  The even lane
+        // takes the first half of this warp's tokens, the odd lane the second half.
+        __half* eh = reinterpret_cast<__half*>(epi);   // [MT][64] hi plane
+        __half* el = eh + MT * (TC_ROWS / 2);           // [MT][64] lo plane
+        const int par = lane & 1, jj = nl >> 1;
+#pragma unroll
+        for (int t = 0; t < HC / 2; ++t) {
+          const float a = TC_ACC(t), b = TC_ACC(t + HC / 2);
+          const float recv = __shfl_xor_sync(0xffffffffu, par ? a : b, 1);
+          const float mine = par ? b : a;
+          const float g = par ? recv : mine, u = par ? mine : recv;
+          const int mm = half * HC + (par ? t + HC / 2 : t);
+          __half h, l;
+          act_split_planes(p.c_act.mode, __fmul_rn(silu_f(g), u), &h, &l);
+          eh[mm * (TC_ROWS / 2) + jj] = h;
+          el[mm * (TC_ROWS / 2) + jj] = l;
+        }
+      } else if (mode == STORE_TMA_PLAIN && p.c_dtype != LOGOS_F32) {
+        __half* e16 = reinterpret_cast<__half*>(epi);  // [MT][128] f16 or bf16
+#pragma unroll
+        for (int x = 0; x < HC; ++x) {
+          const float v = TC_ACC(x);
+          if (p.c_dtype == LOGOS_F16) e16[(half * HC + x) * TC_ROWS + nl] = __float2half_rn(v);
+          else reinterpret_cast<__nv_bfloat16*>(e16)[(half * HC + x) * TC_ROWS + nl] = __float2bfloat16_rn(v);
         }
       } else {
-        const int64_t cols_here = (p.n - n0 < TC_ROWS) ? (p.n - n0) : TC_ROWS;
+        float* e32 = reinterpret_cast<float*>(epi);    // [MT][128] f32
+#pragma unroll
+        for (int x = 0; x < HC; ++x) e32[(half * HC + x) * TC_ROWS + nl] = TC_ACC(x);
+      }
+#undef TC_ACC
+      if (mode != STORE_GENERIC) fence_proxy_async_smem();
+      if (warp == DRAIN_WARP0 && lane == 0) TC_TRACE(63, 5);  // staged
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      if (mode != STORE_GENERIC) {
+        if (et == 0) {
+          if (mode == STORE_TMA_PARTIAL) {
+            tma_store_3d(&map_o0, epi, (int)n0, (int)m0, it.split);
+          } else if (mode == STORE_TMA_PLAIN) {
+            tma_store_2d(&map_o0, epi, (int)n0, (int)m0);
+          } else {
+            tma_store_2d(&map_o0, epi, (int)(n0 >> 1), (int)m0);
+            if (p.c_act.mode == LOGOS_F32) tma_store_2d(&map_o1, epi + MT * TC_ROWS, (int)(n0 >> 1), (int)m0);
+          }
+          bulk_commit();
+          stored = true;
+        }
+      } else {
+        const float* stage_c = reinterpret_cast<const float*>(epi);
+        if (p.splits <= 1 && p.epilogue == EPI_SWIGLU) {
+          // rows (2j, 2j+1) of the tile are (gate_j, up_j): 64 outputs per token
+          const int64_t out0 = n0 >> 1;
+          const int64_t outs = ((p.n - n0 < TC_ROWS ? p.n - n0 : TC_ROWS)) >> 1;
 #pragma unroll 4
-        for (int e = et; e < MT * TC_ROWS; e += 256) {
-          const int mm = e / TC_ROWS, nn = e % TC_ROWS;
-          if (mm < rows_here && nn < cols_here) {
-            float v = stage_c[mm * EPI_PITCH + nn];
-            if (p.splits > 1) {
-              p.partials[((int64_t)split * p.m + m0 + mm) * p.n + n0 + nn] = v;
-            } else {
-              const int64_t ci = (m0 + mm) * p.ldc + n0 + nn;
-              if (p.epilogue == EPI_RESIDUAL) v = __fadd_rn(v, load_aux(p, ci));
-              store_c(p, ci, v);
+          for (int e = et; e < MT * (TC_ROWS / 2); e += 256) {
+            const int mm = e / (TC_ROWS / 2), jj = e % (TC_ROWS / 2);
+            if (mm < rows_here && jj < outs) {
+              const float g = stage_c[mm * TC_ROWS + 2 * jj], u = stage_c[mm * TC_ROWS + 2 * jj + 1];
+              store_c(p, (m0 + mm) * p.ldc + out0 + jj, __fmul_rn(silu_f(g), u));
+            }
+          }
+        } else {
+          const int64_t cols_here = (p.n - n0 < TC_ROWS) ? (p.n - n0) : TC_ROWS;
+#pragma unroll 4
+          for (int e = et; e < MT * TC_ROWS; e += 256) {
+            const int mm = e / TC_ROWS, nn = e % TC_ROWS;
+            if (mm < rows_here && nn < cols_here) {
+              float v = stage_c[mm * TC_ROWS + nn];
+              if (p.splits > 1) {
+                p.partials[((int64_t)it.split * p.m + m0 + mm) * p.n + n0 + nn] = v;
+              } else {
+                const int64_t ci = (m0 + mm) * p.ldc + n0 + nn;
+                if (p.epilogue == EPI_RESIDUAL) v = __fadd_rn(v, load_aux(p, ci));
+                store_c(p, ci, v);
+              }
             }
           }
         }
       }
+      if (warp == DRAIN_WARP0 && lane == 0) TC_TRACE(63, 3);  // first item's stores issued
     }
+    // global writes of the TMA stores are complete before the CTA ends
+    if (et == 0 && stored) bulk_wait_all();
   }
 
-  if (warp == DRAIN_WARP0 && lane == 0) TC_TRACE(63, 3);  // epilogue stores issued
   tc_fence_before();
   __syncthreads();
-  if (tid == 0) TC_TRACE(63, 4);
+  if (tid == 0) { trace_on = cta0; TC_TRACE(63, 4); }
   if (warp == 3) {
     __syncwarp();
     tc_fence_after();
@@ -479,30 +609,33 @@ long long* g_trace = nullptr;  // set through logos_gemm_trace_buffer; null = tr
 
 struct MapKey {
   const void* base;
-  uint64_t inner, outer, pitch;
-  uint32_t box_inner, box_outer, elem;
+  uint64_t d0, d1, d2, pitch1, pitch2;
+  uint32_t box0, box1, elem, swizzle;
   bool operator==(const MapKey& o) const {
-    return base == o.base && inner == o.inner && outer == o.outer && pitch == o.pitch && box_inner == o.box_inner &&
-           box_outer == o.box_outer && elem == o.elem;
+    return base == o.base && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && pitch1 == o.pitch1 && pitch2 == o.pitch2 &&
+           box0 == o.box0 && box1 == o.box1 && elem == o.elem && swizzle == o.swizzle;
   }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& k) const {
     uint64_t h = reinterpret_cast<uint64_t>(k.base);
-    h = h * 0x9E3779B97F4A7C15ull + k.inner;
-    h = h * 0x9E3779B97F4A7C15ull + k.outer;
-    h = h * 0x9E3779B97F4A7C15ull + k.pitch;
-    h = h * 0x9E3779B97F4A7C15ull + ((uint64_t)k.box_inner << 32 | k.box_outer) + k.elem;
+    for (uint64_t v : {k.d0, k.d1, k.d2, k.pitch1, k.pitch2, ((uint64_t)k.box0 << 32) | k.box1,
+                       ((uint64_t)k.elem << 32) | k.swizzle})
+      h = h * 0x9E3779B97F4A7C15ull + v;
     return (size_t)h;
   }
 };
 
-// Tensor maps are pure functions of (address, shape, box): encode once, reuse.
-logos_status_t cached_map(CUtensorMap* out, const void* base, CUtensorMapDataType dt, uint32_t elem, uint64_t inner,
-                          uint64_t outer, uint64_t pitch, uint32_t box_inner, uint32_t box_outer) {
+// Tensor maps are pure functions of (address, shape, box): encode once, reuse.  d2 == 0 asks
+// for a 2-D map [d1][d0] with the given swizzle; otherwise a 3-D map [d2][d1][d0], box depth 1,
+// no swizzle.
+logos_status_t cached_map(CUtensorMap* out, const void* base, CUtensorMapDataType dt, uint32_t elem, uint64_t d0,
+                          uint64_t d1, uint64_t pitch1, uint32_t box0, uint32_t box1,
+                          CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B, uint64_t d2 = 0,
+                          uint64_t pitch2 = 0) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  MapKey key{base, inner, outer, pitch, box_inner, box_outer, elem};
+  MapKey key{base, d0, d1, d2, pitch1, pitch2, box0, box1, elem, (uint32_t)swizzle};
   {
     std::lock_guard<std::mutex> lk(mu);
     auto it = cache.find(key);
@@ -511,17 +644,20 @@ logos_status_t cached_map(CUtensorMap* out, const void* base, CUtensorMapDataTyp
       return LOGOS_OK;
     }
   }
-  LOGOS_TRY(make_tensor_map_2d(out, base, dt, elem, inner, outer, pitch, box_inner, box_outer, CU_TENSOR_MAP_SWIZZLE_128B));
+  if (d2 == 0) LOGOS_TRY(make_tensor_map_2d(out, base, dt, elem, d0, d1, pitch1, box0, box1, swizzle));
+  else LOGOS_TRY(make_tensor_map_3d(out, base, dt, elem, d0, d1, d2, pitch1, pitch2, box0, box1, 1));
   std::lock_guard<std::mutex> lk(mu);
   if (cache.size() > 8192) cache.clear();
   cache[key] = *out;
   return LOGOS_OK;
 }
 
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
 template <int MT, int LIMBS>
 logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
   using Cfg = TcCfg<MT, LIMBS>;
-  CUtensorMap mq, mhi, mlo;
+  CUtensorMap mq, mhi, mlo, mo0, mo1;
   LOGOS_TRY(cached_map(&mq, g.q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)g.k, (uint64_t)g.n, (uint64_t)g.k, TC_KSTAGE, TC_ROWS));
   LOGOS_TRY(cached_map(&mhi, g.a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)g.k, (uint64_t)g.m, (uint64_t)g.lda * 2, 64, MT));
   if (LIMBS == 2)
@@ -534,18 +670,62 @@ logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
   p.partials = g.partials;
   p.splits = g.splits > 1 ? g.splits : 1;
   p.stages_total = (int)(g.k / TC_KSTAGE);
+  const int64_t tiles = (g.n + TC_ROWS - 1) / TC_ROWS;
+  if (tiles * p.splits > INT32_MAX) return fail(LOGOS_OUT_OF_BOUNDS, "q8_gemm: too many work items");
+  p.items = (int)(tiles * p.splits);
   p.status = kernel_status_ptr(g.device);
   p.trace = g_trace;
   if (g_trace) {
     // optional filter: trace only launches whose grid has this many row tiles
     static const char* f = getenv("LOGOS_B200_TRACE_TILES");
-    if (f && atoi(f) != (int)((g.n + TC_ROWS - 1) / TC_ROWS)) p.trace = nullptr;
+    if (f && atoi(f) != (int)tiles) p.trace = nullptr;
   }
   if (!p.status) return fail(LOGOS_ERROR, "q8_gemm: no kernel status word");
   if (p.splits > p.stages_total) return fail(LOGOS_ERROR, "q8_gemm: more K splits than 128-column stages");
+
+  // How the tile is stored: through the TMA where the destination allows a tensor map
+  // (16-byte aligned base and row pitch), else by a loop of plain stores.
+  static const bool no_tma_store = getenv("LOGOS_B200_GEMM_PLAIN_STORES") != nullptr;
+  p.store_mode = STORE_GENERIC;
+  mo0 = mq;
+  mo1 = mq;
+  if (no_tma_store) {
+  } else if (p.splits > 1) {
+    if (aligned16(g.partials) && g.n % 4 == 0) {
+      LOGOS_TRY(cached_map(&mo0, g.partials, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)g.n, (uint64_t)g.m,
+                           (uint64_t)g.n * 4, TC_ROWS, MT, CU_TENSOR_MAP_SWIZZLE_NONE, (uint64_t)p.splits,
+                           (uint64_t)g.m * g.n * 4));
+      p.store_mode = STORE_TMA_PARTIAL;
+    }
+  } else if (g.epilogue == EPI_NONE &&
+             (g.c_dtype == LOGOS_F32 || g.c_dtype == LOGOS_F16 || g.c_dtype == LOGOS_BF16)) {
+    const uint32_t eb = g.c_dtype == LOGOS_F32 ? 4 : 2;
+    const CUtensorMapDataType dt = g.c_dtype == LOGOS_F32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                   : g.c_dtype == LOGOS_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                            : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    if (aligned16(g.c) && (g.ldc * eb) % 16 == 0) {
+      LOGOS_TRY(cached_map(&mo0, g.c, dt, eb, (uint64_t)g.n, (uint64_t)g.m, (uint64_t)g.ldc * eb, TC_ROWS, MT,
+                           CU_TENSOR_MAP_SWIZZLE_NONE));
+      p.store_mode = STORE_TMA_PLAIN;
+    }
+  } else if (g.epilogue == EPI_SWIGLU && g.c_dtype == LOGOS_ACT_PLANES && g.n % 2 == 0) {
+    const bool two = g.c_act.mode == LOGOS_F32;
+    if (aligned16(g.c_act.hi) && (!two || aligned16(g.c_act.lo)) && (g.ldc * 2) % 16 == 0) {
+      LOGOS_TRY(cached_map(&mo0, g.c_act.hi, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)(g.n / 2), (uint64_t)g.m,
+                           (uint64_t)g.ldc * 2, TC_ROWS / 2, MT, CU_TENSOR_MAP_SWIZZLE_NONE));
+      if (two)
+        LOGOS_TRY(cached_map(&mo1, g.c_act.lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)(g.n / 2),
+                             (uint64_t)g.m, (uint64_t)g.ldc * 2, TC_ROWS / 2, MT, CU_TENSOR_MAP_SWIZZLE_NONE));
+      p.store_mode = STORE_TMA_SWIGLU;
+    }
+  }
+
   LOGOS_CUDA_TRY(cudaFuncSetAttribute(q8_gemm_tc_kernel<MT, LIMBS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
-  dim3 grid((unsigned)((g.n + TC_ROWS - 1) / TC_ROWS), (unsigned)p.splits, (unsigned)((g.m + MT - 1) / MT));
-  q8_gemm_tc_kernel<MT, LIMBS><<<grid, TC_THREADS, Cfg::SMEM, st>>>(mq, mhi, mlo, p);
+  // persistent CTAs: one per SM at most, each takes items blockIdx.x, blockIdx.x + gridDim.x, ...
+  static const bool one_item_ctas = getenv("LOGOS_B200_GEMM_ONE_ITEM_CTAS") != nullptr;
+  const int sms = one_item_ctas ? INT32_MAX : sm_count(g.device);
+  dim3 grid((unsigned)(p.items < sms ? p.items : sms), 1u, (unsigned)((g.m + MT - 1) / MT));
+  q8_gemm_tc_kernel<MT, LIMBS><<<grid, TC_THREADS, Cfg::SMEM, st>>>(mq, mhi, mlo, mo0, mo1, p);
   count_launch(LK_GEMM_TC);
   return check_launch("q8_gemm_tc_kernel");
 }

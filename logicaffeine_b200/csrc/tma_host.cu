@@ -45,6 +45,25 @@ logos_status_t make_tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMa
   return LOGOS_OK;
 }
 
+logos_status_t make_tensor_map_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, uint32_t elem_bytes,
+                                  uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1_bytes, uint64_t pitch2_bytes,
+                                  uint32_t box0, uint32_t box1, uint32_t box2) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(LOGOS_ERROR, "cuTensorMapEncodeTiled is not available from this driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) || (pitch1_bytes & 15u) || (pitch2_bytes & 15u))
+    return fail(LOGOS_ERROR, "tensor map: base address and pitches must be multiples of 16 bytes");
+  if (((uint64_t)box0 * elem_bytes) & 15u)
+    return fail(LOGOS_ERROR, "tensor map: inner box extent must be a multiple of 16 bytes");
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {pitch1_bytes, pitch2_bytes};
+  cuuint32_t box[3] = {box0, box1, box2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, dtype, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(LOGOS_ERROR, "cuTensorMapEncodeTiled (3d) failed with code %d", (int)r);
+  return LOGOS_OK;
+}
+
 int* kernel_status_ptr(int device) {
   static std::mutex mu;
   static std::unordered_map<int, int*> words;
