@@ -87,7 +87,11 @@ gqa_decode_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int G = p.h_q / p.h_kv;
 
-  const int len0 = p.seq_len[b];
+  // The lengths, the query and the new K/V rows come from kernels of the same step: wait for
+  // them (the launch may have let this kernel start early), and read them past L1.
+  pdl_wait();
+  pdl_trigger();
+  const int len0 = __ldcg(p.seq_len + b);
   const bool append = p.fused && len0 < p.l_max;
   int len_eff = p.fused ? len0 + 1 : len0;
   if (len_eff > p.l_max) len_eff = p.l_max;
@@ -128,12 +132,12 @@ gqa_decode_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         int hq = kvh * G + g;
         if (p.q_f16) {
           const __half* qp = p.q_f16 + ((int64_t)b * p.h_q + hq) * D;
-          x1 = __half2float(qp[e]);
-          x2 = __half2float(qp[e + half_d]);
+          x1 = __half2float(__ldcg(qp + e));
+          x2 = __half2float(__ldcg(qp + e + half_d));
         } else {
           const float* qp = p.q_f32 + (int64_t)b * p.q_ld + (int64_t)hq * D;
-          x1 = qp[e];
-          x2 = qp[e + half_d];
+          x1 = __ldcg(qp + e);
+          x2 = __ldcg(qp + e + half_d);
         }
         if (p.rotate_q) {
           float c = tab[2 * e], s = tab[2 * e + 1];
@@ -154,13 +158,13 @@ gqa_decode_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         if (p.k_new_f16) {
           const __half* kp = p.k_new_f16 + ((int64_t)b * p.h_kv + kvh) * D;
           const __half* vp = p.v_new_f16 + ((int64_t)b * p.h_kv + kvh) * D;
-          k1 = __half2float(kp[e]); k2 = __half2float(kp[e + half_d]);
-          v1 = __half2float(vp[e]); v2 = __half2float(vp[e + half_d]);
+          k1 = __half2float(__ldcg(kp + e)); k2 = __half2float(__ldcg(kp + e + half_d));
+          v1 = __half2float(__ldcg(vp + e)); v2 = __half2float(__ldcg(vp + e + half_d));
         } else {
           const float* kp = p.k_new_f32 + (int64_t)b * p.kv_ld + (int64_t)kvh * D;
           const float* vp = p.v_new_f32 + (int64_t)b * p.kv_ld + (int64_t)kvh * D;
-          k1 = kp[e]; k2 = kp[e + half_d];
-          v1 = vp[e]; v2 = vp[e + half_d];
+          k1 = __ldcg(kp + e); k2 = __ldcg(kp + e + half_d);
+          v1 = __ldcg(vp + e); v2 = __ldcg(vp + e + half_d);
         }
         float c = tabn[2 * e], s = tabn[2 * e + 1];
         __half r1 = __float2half_rn(__fsub_rn(__fmul_rn(k1, c), __fmul_rn(k2, s)));
@@ -401,19 +405,21 @@ template <int D>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   const int32_t* __restrict__ seq_len, void* __restrict__ o, int o_dtype, ActOut o_act,
                                   int h_q, int l_max, int unit_len, int max_splits, int fused) {
+  pdl_wait();
+  pdl_trigger();
   const int hq = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
-  int len_eff = seq_len[b] + (fused ? 1 : 0);
+  int len_eff = __ldcg(seq_len + b) + (fused ? 1 : 0);
   if (len_eff > l_max) len_eff = l_max;
   int ns = len_eff > 0 ? (len_eff + unit_len - 1) / unit_len : 0;
   int64_t base = ((int64_t)b * h_q + hq) * max_splits;
   float mstar = -INFINITY;
-  for (int s = 0; s < ns; ++s) mstar = fmaxf(mstar, part_ml[(base + s) * 2]);
+  for (int s = 0; s < ns; ++s) mstar = fmaxf(mstar, __ldcg(part_ml + (base + s) * 2));
   float muse = (mstar == -INFINITY) ? 0.f : mstar;
   float acc = 0.f, L = 0.f;
   for (int s = 0; s < ns; ++s) {
-    float wgt = exp2f(part_ml[(base + s) * 2] - muse);
-    acc = fmaf(part_o[(base + s) * D + d], wgt, acc);
-    L = fmaf(part_ml[(base + s) * 2 + 1], wgt, L);
+    float wgt = exp2f(__ldcg(part_ml + (base + s) * 2) - muse);
+    acc = fmaf(__ldcg(part_o + (base + s) * D + d), wgt, acc);
+    L = fmaf(__ldcg(part_ml + (base + s) * 2 + 1), wgt, L);
   }
   float v = (ns > 0) ? __fdiv_rn(acc, L) : 0.f;
   int64_t oi = ((int64_t)b * h_q + hq) * D + d;
@@ -424,6 +430,8 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
 }
 
 __global__ void bump_seq_len_kernel(int32_t* seq_len, int b, int l_max) {
+  pdl_wait();
+  pdl_trigger();
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < b && seq_len[i] < l_max) seq_len[i] += 1;
 }
@@ -502,16 +510,18 @@ logos_status_t launch_attn_t(const AttnArgs& a, cudaStream_t st) {
   constexpr size_t smem = attn_smem_bytes<D>();
   LOGOS_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_attn_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(max_splits, (unsigned)a.h_kv, (unsigned)a.b);
-  gqa_decode_attn_kernel<D><<<grid, ATT_THREADS, smem, st>>>(mk, mv, p);
+  LOGOS_CUDA_TRY(launch_kernel(gqa_decode_attn_kernel<D>, grid, dim3(ATT_THREADS), smem, st, mk, mv, p));
   count_launch(LK_ATTN);
   LOGOS_TRY(check_launch("gqa_decode_attn_kernel"));
   dim3 mgrid((unsigned)a.h_q, (unsigned)a.b);
-  attn_merge_kernel<D><<<mgrid, D, 0, st>>>(p.part_o, p.part_ml, a.seq_len, a.o, a.o_dtype, a.o_act, (int)a.h_q,
-                                            (int)a.l_max, (int)ul, max_splits, p.fused);
+  LOGOS_CUDA_TRY(launch_kernel(attn_merge_kernel<D>, mgrid, dim3(D), 0, st, (const float*)p.part_o,
+                               (const float*)p.part_ml, (const int32_t*)a.seq_len, a.o, a.o_dtype, a.o_act, (int)a.h_q,
+                               (int)a.l_max, (int)ul, (int)max_splits, (int)p.fused));
   count_launch(LK_ATTN_MERGE);
   LOGOS_TRY(check_launch("attn_merge_kernel"));
   if (a.bump_seq_len) {
-    bump_seq_len_kernel<<<(unsigned)((a.b + 127) / 128), 128, 0, st>>>(a.seq_len, (int)a.b, (int)a.l_max);
+    LOGOS_CUDA_TRY(launch_kernel(bump_seq_len_kernel, dim3((unsigned)((a.b + 127) / 128)), dim3(128), 0, st, a.seq_len,
+                                 (int)a.b, (int)a.l_max));
     LOGOS_TRY(check_launch("bump_seq_len_kernel"));
   }
   return LOGOS_OK;

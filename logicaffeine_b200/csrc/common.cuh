@@ -1,6 +1,7 @@
 // Shared internals of liblogos_b200: status/error plumbing, the handle
 // registry, and small device helpers.  Nothing here is part of the C ABI.
 #pragma once
+#include <utility>
 
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
@@ -97,5 +98,44 @@ enum LaunchKind : int {
 void count_launch(int kind, int64_t n = 1);
 
 static inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// Inside a PdlScope (the decode step opens one) kernels are launched so that the next kernel in
+// the stream may start while the previous one is still running: its CTAs are scheduled, do the
+// work that depends on nothing (barrier set-up, tensor-memory allocation, fetching WEIGHTS, which
+// nothing in a decode step writes) and then block in pdl_wait() until the previous kernel has
+// completed and its writes are visible.  The contract every kernel of the step keeps:
+//   * no read or write of anything another kernel of the step writes before pdl_wait();
+//   * at least the threads that do such accesses call pdl_wait(), and every path through the
+//     kernel has some thread calling it (so "this kernel completed" implies "its predecessor did");
+//   * pdl_trigger() after the point where a successor's CTAs may take up SM resources.
+// Outside a scope the launch is an ordinary one and both calls are no-ops.
+bool pdl_active();
+struct PdlScope {
+  bool prev;
+  explicit PdlScope(bool on);
+  ~PdlScope();
+};
+
+#if defined(__CUDACC__)
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_active() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+#endif
 
 }  // namespace logos

@@ -56,8 +56,10 @@ __global__ void swiglu_f32_kernel(const float* __restrict__ gate, const float* _
 
 __global__ void embed_kernel(const int32_t* __restrict__ tokens, const int8_t* __restrict__ q,
                              const float* __restrict__ s, float* __restrict__ h, int64_t hidden) {
+  pdl_wait();
+  pdl_trigger();
   int64_t row = blockIdx.x;
-  int64_t t = tokens[row];
+  int64_t t = __ldcg(tokens + row);
   const int8_t* qr = q + t * hidden;
   const float* sr = s + t * (hidden / 32);
   for (int64_t e = threadIdx.x; e < hidden; e += blockDim.x)
@@ -73,6 +75,9 @@ residual_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, 
   __shared__ float red[32];
   extern __shared__ float4 row_cache4[];  // hidden floats
   float* row_cache = reinterpret_cast<float*>(row_cache4);
+  // h and the partials come from kernels of the same step: wait for them, and read them past L1
+  pdl_wait();
+  pdl_trigger();
   const int64_t row = blockIdx.x;
   float* hr = h + row * hidden;
   float ss = 0.f;
@@ -80,9 +85,9 @@ residual_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, 
     const int64_t n4 = hidden >> 2;
     float4* hr4 = reinterpret_cast<float4*>(hr);
     for (int64_t i = threadIdx.x; i < n4; i += blockDim.x) {
-      float4 v = hr4[i];
+      float4 v = __ldcg(hr4 + i);
       for (int p = 0; p < parts; ++p) {
-        const float4 d = __ldg(reinterpret_cast<const float4*>(delta + (int64_t)p * part_stride + row * hidden) + i);
+        const float4 d = __ldcg(reinterpret_cast<const float4*>(delta + (int64_t)p * part_stride + row * hidden) + i);
         v.x = __fadd_rn(v.x, d.x); v.y = __fadd_rn(v.y, d.y); v.z = __fadd_rn(v.z, d.z); v.w = __fadd_rn(v.w, d.w);
       }
       if (parts > 0) hr4[i] = v;
@@ -91,8 +96,8 @@ residual_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, 
     }
   } else {
     for (int64_t i = threadIdx.x; i < hidden; i += blockDim.x) {
-      float v = hr[i];
-      for (int p = 0; p < parts; ++p) v = __fadd_rn(v, delta[(int64_t)p * part_stride + row * hidden + i]);
+      float v = __ldcg(hr + i);
+      for (int p = 0; p < parts; ++p) v = __fadd_rn(v, __ldcg(delta + (int64_t)p * part_stride + row * hidden + i));
       if (parts > 0) hr[i] = v;
       row_cache[i] = v;
       ss = fmaf(v, v, ss);
@@ -121,12 +126,14 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int32_t* __restr
                               int64_t history_rows, int64_t vocab) {
   __shared__ float bv[32];
   __shared__ int bi[32];
+  pdl_wait();
+  pdl_trigger();
   const int64_t row = blockIdx.x;
   const float* lr = logits + row * vocab;
   float best = -INFINITY;
   int idx = 0x7fffffff;
   for (int64_t i = threadIdx.x; i < vocab; i += blockDim.x) {
-    float v = lr[i];
+    float v = __ldcg(lr + i);
     if (v > best || (v == best && (int)i < idx)) {
       best = v;
       idx = (int)i;
@@ -156,7 +163,7 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int32_t* __restr
     if (idx == 0x7fffffff) idx = 0;  // all NaN / empty row
     tokens[row] = idx;
     if (history) {
-      int64_t slot = step_counter ? *step_counter : 0;
+      int64_t slot = step_counter ? __ldcg(step_counter) : 0;
       if (slot < history_rows) history[slot * gridDim.x + row] = idx;
     }
   }
@@ -184,7 +191,7 @@ logos_status_t launch_swiglu_f32(const float* gate, const float* up, float* y, i
 logos_status_t launch_embed(const int32_t* tokens, const int8_t* q, const float* s, float* h, int64_t rows,
                             int64_t hidden, cudaStream_t st) {
   if (rows == 0) return LOGOS_OK;
-  embed_kernel<<<(unsigned)rows, 256, 0, st>>>(tokens, q, s, h, hidden);
+  LOGOS_CUDA_TRY(launch_kernel(embed_kernel, dim3((unsigned)rows), dim3(256), 0, st, tokens, q, s, h, hidden));
   count_launch(LK_ELEMWISE);
   return check_launch("embed_kernel");
 }
@@ -210,7 +217,8 @@ logos_status_t launch_residual_rmsnorm(float* h, const float* delta, int parts, 
   size_t smem = sizeof(float) * (size_t)hidden;
   if (smem > 48 * 1024)
     LOGOS_CUDA_TRY(cudaFuncSetAttribute(residual_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  residual_rmsnorm_kernel<<<(unsigned)rows, 512, smem, st>>>(h, delta, parts, part_stride, g, xn, hidden, eps);
+  LOGOS_CUDA_TRY(launch_kernel(residual_rmsnorm_kernel, dim3((unsigned)rows), dim3(512), smem, st, h, delta, parts,
+                               part_stride, g, xn, hidden, eps));
   count_launch(LK_ELEMWISE);
   return check_launch("residual_rmsnorm_kernel");
 }
@@ -219,8 +227,8 @@ logos_status_t launch_argmax(const float* logits, int32_t* tokens, int32_t* hist
                              const int32_t* step_counter_or_null, int64_t history_rows, int64_t rows, int64_t vocab,
                              cudaStream_t st) {
   if (rows == 0) return LOGOS_OK;
-  argmax_kernel<<<(unsigned)rows, 1024, 0, st>>>(logits, tokens, history_or_null, step_counter_or_null, history_rows,
-                                                 vocab);
+  LOGOS_CUDA_TRY(launch_kernel(argmax_kernel, dim3((unsigned)rows), dim3(1024), 0, st, logits, tokens, history_or_null,
+                               step_counter_or_null, history_rows, vocab));
   count_launch(LK_ELEMWISE);
   return check_launch("argmax_kernel");
 }

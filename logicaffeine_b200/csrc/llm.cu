@@ -234,14 +234,18 @@ logos_status_t build(Model* m, const void* nccl_id) {
 }
 
 __global__ void sum_partials_kernel(float* __restrict__ p, int parts, int64_t stride, int64_t count) {
+  pdl_wait();
+  pdl_trigger();
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= count) return;
-  float v = p[i];
-  for (int s = 1; s < parts; ++s) v = __fadd_rn(v, p[(int64_t)s * stride + i]);
+  float v = __ldcg(p + i);
+  for (int s = 1; s < parts; ++s) v = __fadd_rn(v, __ldcg(p + (int64_t)s * stride + i));
   p[i] = v;
 }
 
 __global__ void bump_len_kernel(int32_t* seq_len, int32_t* step_counter, int b, int l_max) {
+  pdl_wait();
+  pdl_trigger();
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < b && seq_len[i] < l_max) seq_len[i] += 1;
   if (i == 0) *step_counter += 1;
@@ -273,7 +277,8 @@ logos_status_t gemm_partials(Model* m, const ActOut& a, const Q8Mat& w, int* spl
     ProfScope ps(m, PROF_COMM);
     const int64_t count = B * w.n;
     if (splits > 1) {
-      sum_partials_kernel<<<(unsigned)((count + 255) / 256), 256, 0, m->stream>>>(m->partials, splits, count, count);
+      LOGOS_CUDA_TRY(launch_kernel(sum_partials_kernel, dim3((unsigned)((count + 255) / 256)), dim3(256), 0, m->stream,
+                                   m->partials, splits, count, count));
       LOGOS_TRY(check_launch("sum_partials_kernel"));
       m->launch_counter += 1;
       splits = 1;
@@ -285,6 +290,7 @@ logos_status_t gemm_partials(Model* m, const ActOut& a, const Q8Mat& w, int* spl
 }
 
 bool debug_sync();
+bool pdl_enabled();
 logos_status_t debug_check(Model* m, const char* what, int64_t layer) {
   if (!debug_sync()) return LOGOS_OK;
   LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
@@ -303,6 +309,9 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
   const int64_t B = c.batch, H = c.hidden, D = c.head_dim;
   cudaStream_t st = m->stream;
   m->launch_counter = 0;
+  // Every kernel of a step keeps the dependent-launch contract (common.cuh): weights are the
+  // only thing a kernel touches before it has waited for its predecessor.
+  PdlScope pdl(pdl_enabled());
   {
     ProfScope ps(m, PROF_ELEMWISE);
     LOGOS_TRY(launch_embed(tokens_in, m->embed.q, m->embed.s, m->h, B, H, st));
@@ -387,7 +396,8 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
     m->launch_counter += 3;
   }
   ProfScope ps_tail(m, PROF_ELEMWISE);
-  bump_len_kernel<<<(unsigned)((B + 127) / 128), 128, 0, st>>>(m->seq_len, m->step_counter, (int)B, (int)c.l_max);
+  LOGOS_CUDA_TRY(launch_kernel(bump_len_kernel, dim3((unsigned)((B + 127) / 128)), dim3(128), 0, st, m->seq_len,
+                               m->step_counter, (int)B, (int)c.l_max));
   LOGOS_TRY(check_launch("bump_len_kernel"));
   m->launch_counter += 1;
   m->launches_per_step = m->launch_counter;
@@ -401,6 +411,15 @@ bool debug_sync() {
   if (v < 0) {
     const char* e = getenv("LOGOS_B200_DEBUG_SYNC");
     v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
+}
+
+bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("LOGOS_B200_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
   }
   return v == 1;
 }

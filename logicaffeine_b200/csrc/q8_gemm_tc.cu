@@ -224,7 +224,10 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   __shared__ int prior_status;
   if (tid == 0) prior_status = *reinterpret_cast<volatile int*>(p.status);
   __syncthreads();
-  if (prior_status != 0) return;
+  if (prior_status != 0) {
+    pdl_wait();  // "this kernel completed" must keep implying "its predecessor did"
+    return;
+  }
 
   if (tid == 0) {
     for (int i = 0; i < RAW_STAGES; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], CONV_WARPS); }
@@ -246,6 +249,11 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Dependent launch: this CTA holds its SM's shared and tensor memory by now, so a successor's
+  // CTAs may be scheduled wherever room is left.  Weights and scales are read without waiting
+  // for the previous kernel (nothing in a decode step writes them); the activation producer
+  // and the drain warps (the only ones that touch what other kernels write) wait first.
+  pdl_trigger();
 
   bool ok = true;
   if (tid == 0) TC_TRACE(63, 1);  // set-up done
@@ -289,6 +297,7 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // ------------------------------------------------------------ activation producer
     if (kRebalance) setmaxnreg_dec<48>();
     if (lane == 0) {
+      pdl_wait();  // the activations are the previous kernel's output
       const uint64_t pol = policy_evict_last();
       int gs = 0;
       for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
@@ -438,6 +447,7 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int64_t kb_per_row = p.k >> 5;
     const int et = tid - DRAIN_WARP0 * 32;  // 0..255 among the drain warps
     const int64_t rows_here = (p.m - m0 < MT) ? (p.m - m0) : MT;
+    pdl_wait();  // before any write to global memory (nothing to drain before the activations are in anyway)
     bool stored = false;  // thread et == 0: a TMA store of this CTA may still be reading the staging tile
     int gs = 0;
     for (int w = blockIdx.x; w < items; w += gridDim.x) {
@@ -725,7 +735,7 @@ logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
   static const bool one_item_ctas = getenv("LOGOS_B200_GEMM_ONE_ITEM_CTAS") != nullptr;
   const int sms = one_item_ctas ? INT32_MAX : sm_count(g.device);
   dim3 grid((unsigned)(p.items < sms ? p.items : sms), 1u, (unsigned)((g.m + MT - 1) / MT));
-  q8_gemm_tc_kernel<MT, LIMBS><<<grid, TC_THREADS, Cfg::SMEM, st>>>(mq, mhi, mlo, mo0, mo1, p);
+  LOGOS_CUDA_TRY(launch_kernel(q8_gemm_tc_kernel<MT, LIMBS>, grid, dim3(TC_THREADS), Cfg::SMEM, st, mq, mhi, mlo, mo0, mo1, p));
   count_launch(LK_GEMM_TC);
   return check_launch("q8_gemm_tc_kernel");
 }

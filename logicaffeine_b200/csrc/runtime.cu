@@ -57,6 +57,11 @@ logos_status_t cuda_fail(cudaError_t e, const char* what) {
 static std::atomic<int64_t> g_launches[LK_KINDS];
 void count_launch(int kind, int64_t n) { g_launches[kind].fetch_add(n, std::memory_order_relaxed); }
 
+static thread_local bool g_pdl = false;
+bool pdl_active() { return g_pdl; }
+PdlScope::PdlScope(bool on) : prev(g_pdl) { g_pdl = on; }
+PdlScope::~PdlScope() { g_pdl = prev; }
+
 logos_status_t check_launch(const char* kernel) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(LOGOS_ERROR, "launch of %s failed: %s", kernel, cudaGetErrorString(e));
