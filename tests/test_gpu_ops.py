@@ -47,7 +47,8 @@ def test_quantize_and_synth_weights_bit_exact(llm, oracle):
     assert np.array_equal(ds.download(np.uint32, (n, k // 32)), s1.view(np.uint32))
 
 
-@pytest.mark.parametrize("n,k", [(4096, 4096), (1, 32), (7, 96), (130, 1024), (33, 9728)])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (1, 32), (7, 96), (130, 1024), (33, 9728), (1000, 5120), (300, 512),
+                                 (257, 8192), (65, 16384)])
 def test_q8_gemv(llm, oracle, n, k):
     O = oracle
     q = O.synth_fill(O.I8, 0, 0, 1, 0, n * k).reshape(n, k)
