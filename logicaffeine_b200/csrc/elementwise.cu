@@ -9,9 +9,6 @@
 // tree, then warps in ascending order), so results do not depend on timing.
 #include "ops.cuh"
 
-#include <cooperative_groups.h>
-#include <stdlib.h>
-
 namespace logos {
 
 namespace {
@@ -110,50 +107,6 @@ residual_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, 
   float inv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hidden), eps)));
   for (int64_t i = threadIdx.x; i < hidden; i += blockDim.x)
     act_store(xn, row * hidden + i, __fmul_rn(__fmul_rn(row_cache[i], inv), g[i]));
-}
-
-// The same operator with a row spread over a cluster of RMS_CLUSTER CTAs: at decode batch sizes
-// there are fewer rows than SMs and one CTA per row is bound by the latency of its own load ->
-// reduce -> store chain.  Each CTA folds and squares its slice of the row, the slices' sums of
-// squares meet through distributed shared memory (summed in rank order by every CTA, so all
-// ranks normalise with the same bits), and each CTA writes its slice of the planes.
-constexpr int RMS_CLUSTER = 4;
-__global__ void __launch_bounds__(512)
-residual_rmsnorm_cluster_kernel(float* __restrict__ h, const float* __restrict__ delta, int parts, int64_t part_stride,
-                                const float* __restrict__ g, ActOut xn, int64_t hidden, float eps) {
-  namespace cg = cooperative_groups;
-  cg::cluster_group cluster = cg::this_cluster();
-  __shared__ float red[32];
-  __shared__ float slice_ss;
-  extern __shared__ float4 row_cache4[];  // this CTA's slice
-  pdl_wait();
-  pdl_trigger();
-  const unsigned rank = cluster.block_rank();
-  const int64_t row = blockIdx.x / RMS_CLUSTER;
-  const int64_t n4 = hidden >> 2, per = n4 / RMS_CLUSTER;  // float4 per CTA (hidden % (4 * RMS_CLUSTER) == 0)
-  float4* hr4 = reinterpret_cast<float4*>(h + row * hidden) + rank * per;
-  float ss = 0.f;
-  for (int64_t i = threadIdx.x; i < per; i += blockDim.x) {
-    float4 v = __ldcg(hr4 + i);
-    for (int p = 0; p < parts; ++p) {
-      const float4 d = __ldcg(reinterpret_cast<const float4*>(delta + (int64_t)p * part_stride + row * hidden) + rank * per + i);
-      v.x = __fadd_rn(v.x, d.x); v.y = __fadd_rn(v.y, d.y); v.z = __fadd_rn(v.z, d.z); v.w = __fadd_rn(v.w, d.w);
-    }
-    if (parts > 0) hr4[i] = v;
-    row_cache4[i] = v;
-    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
-  }
-  ss = block_sum(ss, red);
-  if (threadIdx.x == 0) slice_ss = ss;
-  cluster.sync();
-  float total = 0.f;
-  for (unsigned r = 0; r < RMS_CLUSTER; ++r) total += *cluster.map_shared_rank(&slice_ss, r);
-  const float inv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)hidden), eps)));
-  const float* row_cache = reinterpret_cast<const float*>(row_cache4);
-  const int64_t e0 = (int64_t)rank * per * 4;
-  for (int64_t i = threadIdx.x; i < per * 4; i += blockDim.x)
-    act_store(xn, row * hidden + e0 + i, __fmul_rn(__fmul_rn(row_cache[i], inv), g[e0 + i]));
-  cluster.sync();  // a peer may still be reading this CTA's slice_ss
 }
 
 __global__ void bf16_to_f16_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ y, int64_t count) {
@@ -261,29 +214,6 @@ logos_status_t launch_residual_rmsnorm(float* h, const float* delta, int parts, 
                                        const float* g, ActOut xn, int64_t rows, int64_t hidden, float eps,
                                        cudaStream_t st) {
   if (rows == 0) return LOGOS_OK;
-  static const bool no_cluster = getenv("LOGOS_B200_RMSNORM_CLUSTER") == nullptr;  // opt-in until measured on the GPU
-  if (!no_cluster && hidden % (4 * RMS_CLUSTER) == 0 && rows * RMS_CLUSTER <= 4096 && hidden >= 1024) {
-    const int64_t per = hidden / 4 / RMS_CLUSTER;
-    int threads = (int)(((per + 31) / 32) * 32);
-    if (threads > 512) threads = 512;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(rows * RMS_CLUSTER));
-    cfg.blockDim = dim3((unsigned)threads);
-    cfg.dynamicSmemBytes = sizeof(float4) * (size_t)per;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = RMS_CLUSTER;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl_active() ? 2 : 1;
-    LOGOS_CUDA_TRY(cudaLaunchKernelEx(&cfg, residual_rmsnorm_cluster_kernel, h, delta, parts, part_stride, g, xn, hidden, eps));
-    count_launch(LK_ELEMWISE);
-    return check_launch("residual_rmsnorm_cluster_kernel");
-  }
   size_t smem = sizeof(float) * (size_t)hidden;
   if (smem > 48 * 1024)
     LOGOS_CUDA_TRY(cudaFuncSetAttribute(residual_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -10,8 +10,6 @@
 // four 128-bit reads a lane needs are bank-conflict free.
 #include "ops.cuh"
 
-#include <stdlib.h>
-
 namespace logos {
 
 namespace {
@@ -118,96 +116,6 @@ q8_gemv_kernel(const int8_t* __restrict__ q, const float* __restrict__ s, const 
 }
 
 
-// ---- slab kernel: K a multiple of 512, x fits shared memory.
-// One persistent CTA per SM owns a contiguous range of rows, i.e. one contiguous piece of the
-// weight array, and streams it in slabs of SLAB_ROWS rows: thread t takes the 16-byte chunks
-// t, t + 512, ... of the slab, so every load instruction of the CTA covers 8 KB of consecutive
-// memory.  The chunks of a row lie on whole warps (K / 16 chunks per row is a multiple of 32),
-// so a row's dot product is a warp-shuffle reduction followed by a fixed-order sum of its
-// warps' partials in shared memory: deterministic, no atomics.  The loads of the next slab are
-// issued before the current one is consumed.
-constexpr int SLAB_THREADS = 512;
-constexpr int SLAB_LOADS = 4;  // 16-byte loads per thread and slab: a slab is 32 KB
-
-__global__ void __launch_bounds__(SLAB_THREADS)
-q8_gemv_slab_kernel(const int8_t* __restrict__ q, const float* __restrict__ s, const float* __restrict__ x,
-                    float* __restrict__ y, int64_t n, int64_t k) {
-  extern __shared__ float4 xs4[];
-  __shared__ float part[2][SLAB_LOADS * (SLAB_THREADS / 32)];  // per slab parity: one partial per (load, warp)
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int cpr = (int)(k >> 4);             // 16-byte chunks per row, a multiple of 32
-  const int wpr = cpr >> 5;                  // warps per row
-  const int slab_rows = (SLAB_LOADS * SLAB_THREADS) / cpr;  // whole rows per slab (>= 1: k <= 32768)
-  const int64_t kb_per_row = k >> 5;
-  const int64_t row_begin = (n * blockIdx.x) / gridDim.x, row_end = (n * (blockIdx.x + 1)) / gridDim.x;
-  const int nslabs = (int)((row_end - row_begin + slab_rows - 1) / slab_rows);
-  const int live = slab_rows * cpr;          // chunks of a full slab (<= SLAB_LOADS * SLAB_THREADS)
-
-  // two register buffers with compile-time names (a run-time buffer index would put them in
-  // local memory): slabs are taken in pairs
-  uint4 w0[SLAB_LOADS], w1[SLAB_LOADS];
-  float sc0[SLAB_LOADS], sc1[SLAB_LOADS];
-#define GEMV_ISSUE(W, SC, sl)                                                                 \
-  do {                                                                                        \
-    const int64_t r0_ = row_begin + (int64_t)(sl) * slab_rows;                                \
-    _Pragma("unroll") for (int u = 0; u < SLAB_LOADS; ++u) {                                  \
-      const int L = tid + u * SLAB_THREADS;                                                   \
-      const int rr = L / cpr, cc = L - rr * cpr;                                              \
-      const int64_t row = r0_ + rr;                                                           \
-      if (L < live && row < row_end) {                                                        \
-        W[u] = ldg_nc_v4(reinterpret_cast<const uint4*>(q + row * k) + cc);                   \
-        SC[u] = __ldg(s + row * kb_per_row + (cc >> 1));                                      \
-      } else {                                                                                \
-        W[u] = make_uint4(0, 0, 0, 0);                                                        \
-        SC[u] = 0.f;                                                                          \
-      }                                                                                       \
-    }                                                                                         \
-  } while (0)
-#define GEMV_CONSUME(W, SC, sl, buf)                                                          \
-  do {                                                                                        \
-    _Pragma("unroll") for (int u = 0; u < SLAB_LOADS; ++u) {                                  \
-      const int cc = (tid + u * SLAB_THREADS) % cpr;                                          \
-      const float4 x0 = xs4[xs4_index(cc, 0)], x1 = xs4[xs4_index(cc, 1)];                    \
-      const float4 x2 = xs4[xs4_index(cc, 2)], x3 = xs4[xs4_index(cc, 3)];                    \
-      float pacc = 0.f;                                                                       \
-      pacc = dot4(W[u].x, x0, pacc);                                                          \
-      pacc = dot4(W[u].y, x1, pacc);                                                          \
-      pacc = dot4(W[u].z, x2, pacc);                                                          \
-      pacc = dot4(W[u].w, x3, pacc);                                                          \
-      float v = __fmul_rn(SC[u], pacc);                                                       \
-      _Pragma("unroll") for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o); \
-      if (lane == 0) part[buf][u * (SLAB_THREADS / 32) + warp] = v;                           \
-    }                                                                                         \
-    __syncthreads(); /* partials of this slab are in; part[buf] is rewritten two slabs later */ \
-    if (tid < slab_rows) {                                                                    \
-      const int64_t row = row_begin + (int64_t)(sl) * slab_rows + tid;                        \
-      if (row < row_end) {                                                                    \
-        /* the row's warp-sized groups in chunk order: group g = (load u) * 16 + warp */      \
-        float acc = 0.f;                                                                      \
-        for (int j = 0; j < wpr; ++j) acc += part[buf][tid * wpr + j];                        \
-        y[row] = acc;                                                                         \
-      }                                                                                       \
-    }                                                                                         \
-  } while (0)
-
-  if (nslabs > 0) GEMV_ISSUE(w0, sc0, 0);
-  {  // stage x while the first slab is in flight
-    const float4* xg = reinterpret_cast<const float4*>(x);
-    for (int i = tid; i < cpr * 4; i += SLAB_THREADS) xs4[xs4_index(i >> 2, i & 3)] = xg[i];
-  }
-  __syncthreads();
-  for (int sl = 0; sl < nslabs; sl += 2) {
-    if (sl + 1 < nslabs) GEMV_ISSUE(w1, sc1, sl + 1);
-    GEMV_CONSUME(w0, sc0, sl, 0);
-    if (sl + 1 < nslabs) {
-      if (sl + 2 < nslabs) GEMV_ISSUE(w0, sc0, sl + 2);
-      GEMV_CONSUME(w1, sc1, sl + 1, 1);
-    }
-  }
-#undef GEMV_ISSUE
-#undef GEMV_CONSUME
-}
-
 }  // namespace
 
 logos_status_t launch_q8_gemv(const int8_t* q, const float* s, const float* x, float* y, int64_t n, int64_t k,
@@ -216,22 +124,6 @@ logos_status_t launch_q8_gemv(const int8_t* q, const float* s, const float* x, f
   if (k == 0) {
     LOGOS_CUDA_TRY(cudaMemsetAsync(y, 0, sizeof(float) * n, st));
     return LOGOS_OK;
-  }
-  // x padded to whole groups of 32 chunks (512 floats)
-  const size_t x_smem = (size_t)((k / 16 + 31) / 32) * 128 * sizeof(float4);
-  static const bool no_slab = getenv("LOGOS_B200_GEMV_SLAB") == nullptr;  // opt-in until measured on the GPU
-  if (!no_slab && k % 512 == 0 && k <= 16384 && x_smem <= 96 * 1024 && n >= 64 &&
-      (reinterpret_cast<uintptr_t>(q) & 15u) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
-    if (x_smem > 40 * 1024)
-      LOGOS_CUDA_TRY(cudaFuncSetAttribute(q8_gemv_slab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-    const int sms = sm_count(device);
-    const int64_t min_rows = (SLAB_LOADS * SLAB_THREADS) / (k >> 4);  // at least one slab per CTA
-    int64_t g = n / (min_rows > 0 ? min_rows : 1);
-    if (g > sms) g = sms;
-    if (g < 1) g = 1;
-    q8_gemv_slab_kernel<<<(unsigned)g, SLAB_THREADS, x_smem, st>>>(q, s, x, y, n, k);
-    count_launch(LK_GEMV);
-    return check_launch("q8_gemv_slab_kernel");
   }
   int64_t ctas = (n + GEMV_WARPS - 1) / GEMV_WARPS;
   int64_t cap = (int64_t)sm_count(device) * 8;
