@@ -263,6 +263,10 @@ LOGOS_API logos_status_t logos_llm_set_seq_len(logos_handle_t model, int64_t t);
 /* Device-side time of the last logos_llm_decode_steps call, milliseconds
  * (CUDA events on the model's stream), and kernels launched per step. */
 LOGOS_API logos_status_t logos_llm_last_timing(logos_handle_t model, double* ms_out, int64_t* launches_per_step_out);
+/* How the ranks of the model's tensor-parallel group exchange the partial products of the
+ * row-parallel GEMMs: 0 = no group (tp_degree 1), 1 = NCCL all-reduce, 2 = folded into the
+ * residual + RMSNorm kernel over peer-mapped memory (one process per GPU, one node). */
+LOGOS_API logos_status_t logos_llm_tp_exchange(logos_handle_t model, int32_t* mode_out);
 /* One greedy step with CUDA events around every launch group; ms_by_class_out
  * receives 4 doubles: Q8 GEMMs, attention (+merge), norms/element-wise, and
  * tensor-parallel exchange.  Advances the model like logos_llm_decode_step. */

@@ -109,6 +109,111 @@ residual_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, 
     act_store(xn, row * hidden + i, __fmul_rn(__fmul_rn(row_cache[i], inv), g[i]));
 }
 
+// ---- residual + RMSNorm with the tensor-parallel all-reduce folded in (see ops.cuh)
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded: false when the flag did not reach `target` within about two seconds of SM clock.
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target) {
+  if ((int32_t)(ld_acquire_sys(p) - target) >= 0) return true;
+  const long long start = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int k = 0; k < 64; ++k)
+      if ((int32_t)(ld_acquire_sys(p) - target) >= 0) return true;
+    if (clock64() - start > 4000000000ll) return false;
+  }
+}
+
+constexpr int TP_MAX_SRC = 64;  // degree x parts
+
+__global__ void __launch_bounds__(512)
+tp_residual_rmsnorm_kernel(float* __restrict__ h, const TpFusedArgs t, int parts, int64_t part_stride,
+                           const float* __restrict__ g, int64_t rows_own, int64_t hidden, float eps, int* status) {
+  __shared__ float red[32];
+  __shared__ uint32_t epoch_s;
+  __shared__ int last_s;
+  __shared__ const float* src[TP_MAX_SRC];
+  extern __shared__ float4 row_cache4[];  // hidden floats
+  const int tid = threadIdx.x;
+  pdl_wait();  // this rank's own GEMM has completed: its partials are in this GPU's memory
+  pdl_trigger();
+  uint32_t* my = t.flags[t.rank];
+  if (tid == 0) epoch_s = ld_acquire_sys(my + 16) + 1u;
+  const int nsrc = t.degree * parts;
+  if (tid < nsrc) src[tid] = t.partials[tid / parts] + (int64_t)(tid % parts) * part_stride;  // rank-major, then split
+  __syncthreads();
+  const uint32_t e = epoch_s;
+  // ---- barrier 1: every rank's partials are complete.  One CTA announces this rank to all
+  // (itself included); every CTA polls its own rank's words, which are local memory.
+  if (blockIdx.x == 0 && tid < t.degree) st_release_sys(t.flags[tid] + t.rank, e);
+  if (tid < t.degree && !wait_flag_ge(my + tid, e)) atomicExch(status, 3010);
+  __syncthreads();
+
+  const int64_t row = (int64_t)t.rank * rows_own + blockIdx.x;
+  const int64_t n4 = hidden >> 2;
+  float4* hr4 = reinterpret_cast<float4*>(h + row * hidden);
+  float ss = 0.f;
+  for (int64_t i = tid; i < n4; i += blockDim.x) {
+    float4 v = __ldcg(hr4 + i);
+    // peers' buffers are read past L1 (ld.global.cg): the lines are rewritten every call
+#pragma unroll 4
+    for (int q = 0; q < nsrc; ++q) {
+      const float4 d = __ldcg(reinterpret_cast<const float4*>(src[q] + row * hidden) + i);
+      v.x = __fadd_rn(v.x, d.x); v.y = __fadd_rn(v.y, d.y); v.z = __fadd_rn(v.z, d.z); v.w = __fadd_rn(v.w, d.w);
+    }
+    hr4[i] = v;
+    row_cache4[i] = v;
+    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+  }
+  ss = block_sum(ss, red);
+  const float inv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hidden), eps)));
+  const float4* g4 = reinterpret_cast<const float4*>(g);
+  for (int64_t i = tid; i < n4; i += blockDim.x) {
+    const float4 v = row_cache4[i], gg = g4[i];
+    const float o[4] = {__fmul_rn(__fmul_rn(v.x, inv), gg.x), __fmul_rn(__fmul_rn(v.y, inv), gg.y),
+                        __fmul_rn(__fmul_rn(v.z, inv), gg.z), __fmul_rn(__fmul_rn(v.w, inv), gg.w)};
+    __half hh[4], ll[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float x = o[k];
+      if (t.act_mode == LOGOS_BF16) x = __bfloat162float(__float2bfloat16_rn(x));
+      x = act_clamp(x);
+      hh[k] = __float2half_rn(x);
+      ll[k] = __float2half_rn((x - __half2float(hh[k])) * 2048.f);
+    }
+    const uint2 hp = *reinterpret_cast<const uint2*>(hh), lp = *reinterpret_cast<const uint2*>(ll);
+    for (int r = 0; r < t.degree; ++r) {
+      reinterpret_cast<uint2*>(t.xn_hi[r] + row * hidden)[i] = hp;
+      if (t.xn_lo[r]) reinterpret_cast<uint2*>(t.xn_lo[r] + row * hidden)[i] = lp;
+    }
+  }
+  // ---- barrier 2: the last CTA of this rank to finish tells every rank that this rank's rows
+  // have been delivered, and holds the kernel until every peer's rows are here.
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence_system();
+    const uint32_t ticket = atomicAdd(my + 17, 1u);
+    last_s = (ticket == gridDim.x - 1) ? 1 : 0;
+    if (last_s) {
+      __threadfence_system();
+      my[17] = 0u;
+    }
+  }
+  __syncthreads();
+  if (last_s) {
+    if (tid < t.degree) st_release_sys(t.flags[tid] + 8 + t.rank, e);
+    if (tid < t.degree && !wait_flag_ge(my + 8 + tid, e)) atomicExch(status, 3020);
+    __syncthreads();
+    if (tid == 0) st_release_sys(my + 16, e);
+  }
+}
+
 __global__ void bf16_to_f16_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ y, int64_t count) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < count) y[i] = __float2half_rn(act_clamp(__bfloat162float(x[i])));
@@ -221,6 +326,24 @@ logos_status_t launch_residual_rmsnorm(float* h, const float* delta, int parts, 
                                part_stride, g, xn, hidden, eps));
   count_launch(LK_ELEMWISE);
   return check_launch("residual_rmsnorm_kernel");
+}
+
+logos_status_t launch_tp_residual_rmsnorm(float* h, const TpFusedArgs& t, int parts, int64_t part_stride, const float* g,
+                                          int64_t rows, int64_t hidden, float eps, int device, cudaStream_t st) {
+  if (rows == 0) return LOGOS_OK;
+  if (t.degree < 2 || t.degree > 8 || rows % t.degree || (hidden & 3) || parts < 1 || t.degree * parts > TP_MAX_SRC)
+    return fail(LOGOS_ERROR, "tp_residual_rmsnorm: unsupported shape (rows %lld, hidden %lld, degree %d, parts %d)",
+                (long long)rows, (long long)hidden, t.degree, parts);
+  int* status = kernel_status_ptr(device);
+  if (!status) return fail(LOGOS_ERROR, "tp_residual_rmsnorm: no kernel status word");
+  const size_t smem = sizeof(float) * (size_t)hidden;
+  if (smem > 48 * 1024)
+    LOGOS_CUDA_TRY(cudaFuncSetAttribute(tp_residual_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int64_t rows_own = rows / t.degree;
+  LOGOS_CUDA_TRY(launch_kernel(tp_residual_rmsnorm_kernel, dim3((unsigned)rows_own), dim3(512), smem, st, h, t, parts,
+                               part_stride, g, rows_own, hidden, eps, status));
+  count_launch(LK_ELEMWISE);
+  return check_launch("tp_residual_rmsnorm_kernel");
 }
 
 logos_status_t launch_argmax(const float* logits, int32_t* tokens, int32_t* history_or_null,

@@ -55,6 +55,11 @@ struct Model {
   ActOut att;                // [B][nq]
   ActOut ffn;                // [B][f_local]
   float* partials = nullptr; // [max_splits][B][H]
+  // tensor parallelism with peer-addressable memory: partials, xn planes and flag words live in
+  // one block per rank that every rank maps; the all-reduce is folded into residual + RMSNorm
+  TpSymm symm;
+  bool tp_fused = false;
+  TpFusedArgs tpf;
   int    max_splits = 1;
   float* logits = nullptr;   // [B][V]
   int32_t* tokens = nullptr; // [B] current input / last output
@@ -129,6 +134,7 @@ void destroy(Model* m) {
   // communicator's destruction waits on it.
   if (m->step_graph) cudaGraphExecDestroy(m->step_graph);
   m->step_graph = nullptr;
+  tp_symm_free(&m->symm);
   tp_destroy(&m->tp);
   for (void* p : m->allocs) cudaFree(p);
   for (cudaEvent_t e : m->prof_events) cudaEventDestroy(e);
@@ -214,11 +220,41 @@ logos_status_t build(Model* m, const void* nccl_id) {
     if (c.act_dtype == LOGOS_F32) LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&a->lo), elems * 2));
     return LOGOS_OK;
   };
-  LOGOS_TRY(planes(&m->xn, B * H));
+  // The block the ranks of a TP group share: [partials][xn hi][xn lo][flag words], 256-byte aligned.
+  {
+    auto up = [](int64_t v) { return (v + 255) / 256 * 256; };
+    const int64_t part_bytes = up((int64_t)m->max_splits * B * H * 4), plane_bytes = up(B * H * 2);
+    const bool two = c.act_dtype == LOGOS_F32;
+    const int64_t off_hi = part_bytes, off_lo = off_hi + plane_bytes, off_flags = off_lo + (two ? plane_bytes : 0);
+    const int64_t total = off_flags + up(TP_FLAG_WORDS * 4);
+    const char* e = getenv("LOGOS_B200_TP_FUSED");
+    // opt-in until it has been measured on 2 to 8 GPUs
+    const bool want = g > 1 && g <= 8 && B % g == 0 && H % 4 == 0 && g * m->max_splits <= 64 && (e && e[0] == '1');
+    if (want) LOGOS_TRY(tp_symm_alloc(&m->tp, (size_t)total, &m->symm, m->stream));
+    m->tp_fused = want && m->symm.ok;
+    if (m->tp_fused) {
+      m->tpf.degree = g;
+      m->tpf.rank = r;
+      m->tpf.act_mode = c.act_dtype;
+      for (int k = 0; k < g; ++k) {
+        char* base = static_cast<char*>(m->symm.base[k]);
+        m->tpf.partials[k] = reinterpret_cast<const float*>(base);
+        m->tpf.xn_hi[k] = reinterpret_cast<__half*>(base + off_hi);
+        m->tpf.xn_lo[k] = two ? reinterpret_cast<__half*>(base + off_lo) : nullptr;
+        m->tpf.flags[k] = reinterpret_cast<uint32_t*>(base + off_flags);
+      }
+      char* mine = static_cast<char*>(m->symm.base[r]);
+      m->partials = reinterpret_cast<float*>(mine);
+      m->xn.mode = c.act_dtype;
+      m->xn.hi = reinterpret_cast<__half*>(mine + off_hi);
+      m->xn.lo = two ? reinterpret_cast<__half*>(mine + off_lo) : nullptr;
+    }
+  }
+  if (!m->tp_fused) LOGOS_TRY(planes(&m->xn, B * H));
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->qkv), B * m->nqkv * 4));
   LOGOS_TRY(planes(&m->att, B * m->nq));
   LOGOS_TRY(planes(&m->ffn, B * m->f_local));
-  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->partials), (int64_t)m->max_splits * B * H * 4));
+  if (!m->tp_fused) LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->partials), (int64_t)m->max_splits * B * H * 4));
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->logits), B * c.vocab * 4));
   m->history_cap = c.l_max;
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->history), m->history_cap * B * 4));
@@ -273,7 +309,7 @@ logos_status_t gemm_partials(Model* m, const ActOut& a, const Q8Mat& w, int* spl
     ProfScope ps(m, PROF_GEMM);
     LOGOS_TRY(launch_q8_gemm(g, m->stream));
   }
-  if (m->tp.degree > 1) {
+  if (m->tp.degree > 1 && !m->tp_fused) {
     ProfScope ps(m, PROF_COMM);
     const int64_t count = B * w.n;
     if (splits > 1) {
@@ -303,6 +339,20 @@ logos_status_t debug_check(Model* m, const char* what, int64_t layer) {
   return LOGOS_OK;
 }
 
+// Fold the pending partial sums into the residual stream and normalise: h += sum(partials),
+// xn = planes(rmsnorm(h)).  With a peer-mapped TP group the sum runs over every rank's partials
+// (the all-reduce is part of the kernel) and each rank updates only the rows it owns.
+logos_status_t norm_step(Model* m, int parts) {
+  const logos_llm_config_t& c = m->cfg;
+  const int64_t B = c.batch, H = c.hidden;
+  if (m->tp_fused && parts > 0) {
+    ProfScope ps(m, PROF_COMM);
+    return launch_tp_residual_rmsnorm(m->h, m->tpf, parts, B * H, m->ones, B, H, c.rms_eps, m->device, m->stream);
+  }
+  ProfScope ps(m, PROF_ELEMWISE);
+  return launch_residual_rmsnorm(m->h, m->partials, parts, B * H, m->ones, m->xn, B, H, c.rms_eps, m->stream);
+}
+
 // One lock-step decode step on the model's stream.  tokens_in: [B] device.
 logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_tokens) {
   const logos_llm_config_t& c = m->cfg;
@@ -320,10 +370,7 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
   int parts = 0;
   for (int64_t l = 0; l < c.layers; ++l) {
     Layer& L = m->layers[(size_t)l];
-    {
-      ProfScope ps(m, PROF_ELEMWISE);
-      LOGOS_TRY(launch_residual_rmsnorm(m->h, m->partials, parts, B * H, m->ones, m->xn, B, H, c.rms_eps, st));
-    }
+    LOGOS_TRY(norm_step(m, parts));
     m->launch_counter += 1;
     {
       ProfScope ps(m, PROF_GEMM);
@@ -354,10 +401,7 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
     LOGOS_TRY(debug_check(m, "attention", l));
     LOGOS_TRY(gemm_partials(m, m->att, L.wo, &parts));
     LOGOS_TRY(debug_check(m, "o_proj gemm", l));
-    {
-      ProfScope ps(m, PROF_ELEMWISE);
-      LOGOS_TRY(launch_residual_rmsnorm(m->h, m->partials, parts, B * H, m->ones, m->xn, B, H, c.rms_eps, st));
-    }
+    LOGOS_TRY(norm_step(m, parts));
     m->launch_counter += 1;
     {
       ProfScope ps(m, PROF_GEMM);
@@ -376,10 +420,7 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
     LOGOS_TRY(debug_check(m, "down_proj gemm", l));
   }
   if (sample) {
-    {
-      ProfScope ps(m, PROF_ELEMWISE);
-      LOGOS_TRY(launch_residual_rmsnorm(m->h, m->partials, parts, B * H, m->ones, m->xn, B, H, c.rms_eps, st));
-    }
+    LOGOS_TRY(norm_step(m, parts));
     GemmArgs g;
     g.a = m->xn.hi; g.a_lo = m->xn.lo; g.a_dtype = LOGOS_F16; g.lda = H;
     g.q = m->head.q; g.s = m->head.s;
@@ -666,6 +707,15 @@ logos_status_t logos_llm_last_timing(logos_handle_t model, double* ms_out, int64
     MODEL_OR_FAIL(m, model, "logos_llm_last_timing");
     if (ms_out) *ms_out = m->last_ms;
     if (launches_per_step_out) *launches_per_step_out = m->launches_per_step;
+    return LOGOS_OK;
+  });
+}
+
+logos_status_t logos_llm_tp_exchange(logos_handle_t model, int32_t* mode_out) {
+  return guarded([&]() -> logos_status_t {
+    MODEL_OR_FAIL(m, model, "logos_llm_tp_exchange");
+    if (!mode_out) return fail(LOGOS_NULL_POINTER, "logos_llm_tp_exchange: mode_out is null");
+    *mode_out = m->tp.degree <= 1 ? 0 : (m->tp_fused ? 2 : 1);
     return LOGOS_OK;
   });
 }

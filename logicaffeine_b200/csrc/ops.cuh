@@ -108,6 +108,24 @@ logos_status_t launch_embed(const int32_t* tokens, const int8_t* q, const float*
 logos_status_t launch_residual_rmsnorm(float* h, const float* delta, int parts, int64_t part_stride,
                                        const float* g, ActOut xn, int64_t rows, int64_t hidden, float eps,
                                        cudaStream_t st);
+// The same operator for a tensor-parallel group whose ranks can address each other's memory:
+// the all-reduce of the row-parallel GEMM's partial sums is folded in.  Rank r owns rows
+// [r * rows / degree, (r + 1) * rows / degree): it adds every rank's partials for its rows to
+// its slice of the residual stream (reading the peers' buffers over NVLink), normalises them,
+// and writes the resulting activation rows into every rank's plane buffers; two flag
+// barriers (peers' partials complete; everybody's rows delivered) frame the kernel.  Only the
+// owner keeps a row of h up to date.
+constexpr int TP_FLAG_WORDS = 64;  // u32 per rank: [0..7] stage 1, [8..15] stage 2, [16] epoch, [17] CTA ticket
+struct TpFusedArgs {
+  int degree = 1, rank = 0;
+  const float* partials[8] = {};  // each rank's [parts][rows][hidden] f32
+  __half* xn_hi[8] = {};          // each rank's planes [rows][hidden]
+  __half* xn_lo[8] = {};          // null in the one-plane modes
+  uint32_t* flags[8] = {};        // each rank's TP_FLAG_WORDS words, zero at creation
+  int act_mode = LOGOS_F32;
+};
+logos_status_t launch_tp_residual_rmsnorm(float* h, const TpFusedArgs& t, int parts, int64_t part_stride, const float* g,
+                                          int64_t rows, int64_t hidden, float eps, int device, cudaStream_t st);
 // bf16 [count] -> fp16 plane (exact inside fp16's normal range, saturating outside)
 logos_status_t launch_bf16_to_f16(const __nv_bfloat16* x, __half* y, int64_t count, cudaStream_t st);
 // f32 [count] -> activation planes

@@ -99,6 +99,80 @@ logos_status_t tp_allgather_bytes(TpGroup* g, const void* send, void* recv, int6
   return LOGOS_OK;
 }
 
+logos_status_t tp_symm_alloc(TpGroup* g, size_t bytes, TpSymm* out, cudaStream_t st) {
+  *out = TpSymm();
+  out->degree = g->degree;
+  out->rank = g->rank;
+  out->bytes = bytes;
+  if (g->degree <= 1 || g->degree > 8) return LOGOS_OK;
+  void* local = nullptr;
+  LOGOS_CUDA_TRY(cudaMalloc(&local, bytes));
+  LOGOS_CUDA_TRY(cudaMemset(local, 0, bytes));
+  cudaIpcMemHandle_t mine;
+  bool good = cudaIpcGetMemHandle(&mine, local) == cudaSuccess;
+  if (!good) cudaGetLastError();
+  // exchange the handles (and each rank's verdict so far) through the group's own all-gather
+  struct Slot { cudaIpcMemHandle_t h; int32_t good; int32_t pad[15]; };
+  static_assert(sizeof(Slot) == 128, "exchange slot");
+  Slot send_h;
+  memset(&send_h, 0, sizeof(send_h));
+  send_h.h = mine;
+  send_h.good = good ? 1 : 0;
+  Slot* dev = nullptr;
+  LOGOS_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&dev), sizeof(Slot) * (size_t)(g->degree + 1)));
+  LOGOS_CUDA_TRY(cudaMemcpyAsync(dev + g->degree, &send_h, sizeof(Slot), cudaMemcpyHostToDevice, st));
+  logos_status_t rc = tp_allgather_bytes(g, dev + g->degree, dev, (int64_t)sizeof(Slot), st);
+  Slot all[8];
+  if (rc == LOGOS_OK) {
+    LOGOS_CUDA_TRY(cudaMemcpyAsync(all, dev, sizeof(Slot) * (size_t)g->degree, cudaMemcpyDeviceToHost, st));
+    LOGOS_CUDA_TRY(cudaStreamSynchronize(st));
+  }
+  if (rc != LOGOS_OK) {
+    cudaFree(dev);
+    cudaFree(local);
+    return rc;
+  }
+  for (int r = 0; r < g->degree; ++r) good = good && all[r].good == 1;
+  out->base[g->rank] = local;
+  if (good) {
+    for (int r = 0; r < g->degree && good; ++r) {
+      if (r == g->rank) continue;
+      void* p = nullptr;
+      if (cudaIpcOpenMemHandle(&p, all[r].h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        cudaGetLastError();
+        good = false;
+      } else {
+        out->base[r] = p;
+      }
+    }
+  }
+  // second round: did every rank map every peer?
+  send_h.good = good ? 1 : 0;
+  LOGOS_CUDA_TRY(cudaMemcpyAsync(dev + g->degree, &send_h, sizeof(Slot), cudaMemcpyHostToDevice, st));
+  rc = tp_allgather_bytes(g, dev + g->degree, dev, (int64_t)sizeof(Slot), st);
+  if (rc == LOGOS_OK) {
+    LOGOS_CUDA_TRY(cudaMemcpyAsync(all, dev, sizeof(Slot) * (size_t)g->degree, cudaMemcpyDeviceToHost, st));
+    LOGOS_CUDA_TRY(cudaStreamSynchronize(st));
+    for (int r = 0; r < g->degree; ++r) good = good && all[r].good == 1;
+  } else {
+    good = false;
+  }
+  cudaFree(dev);
+  out->ok = good;
+  if (!good) tp_symm_free(out);
+  return rc;
+}
+
+void tp_symm_free(TpSymm* s) {
+  for (int r = 0; r < 8; ++r) {
+    if (!s->base[r]) continue;
+    if (r == s->rank) cudaFree(s->base[r]);
+    else cudaIpcCloseMemHandle(s->base[r]);
+    s->base[r] = nullptr;
+  }
+  s->ok = false;
+}
+
 }  // namespace logos
 
 extern "C" logos_status_t logos_tp_unique_id(void* out_128_bytes) {

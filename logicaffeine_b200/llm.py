@@ -292,6 +292,12 @@ class Llm:
         call("logos_llm_last_timing", self.handle, C.byref(ms), C.byref(launches))
         return ms.value, launches.value
 
+    def tpExchange(self):
+        """0 = no TP group, 1 = NCCL all-reduce, 2 = exchange folded into residual + RMSNorm over peer memory."""
+        mode = C.c_int32()
+        call("logos_llm_tp_exchange", self.handle, C.byref(mode))
+        return mode.value
+
     def profileStep(self):
         """One step with per-class device timing: ms for (gemm, attention, elementwise, exchange)."""
         ms = (C.c_double * 4)()

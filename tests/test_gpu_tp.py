@@ -1,7 +1,8 @@
 """Tensor parallelism on two GPUs of one node: every rank (its own process, as under
-torchrun) builds its shard of the seeded weights, the only exchange is the NCCL sum
-all-reduce after o_proj and down_proj, and the greedy tokens must equal the oracle's
-(unsharded) ones.  Skipped when fewer than two GPUs are visible."""
+torchrun) builds its shard of the seeded weights, the only exchange is the sum of the partial
+products after o_proj and down_proj - folded into the residual + RMSNorm kernel over
+peer-mapped memory, or as an NCCL all-reduce (LOGOS_B200_TP_FUSED=0) - and the greedy tokens
+must equal the oracle's (unsharded) ones.  Skipped when fewer than two GPUs are visible."""
 import os
 import subprocess
 import sys
@@ -15,7 +16,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 @pytest.mark.timeout(300)
-def test_tp2_tokens_match_the_oracle(llm, oracle, tmp_path):
+@pytest.mark.parametrize("fused", ["1", "0"])
+def test_tp2_tokens_match_the_oracle(llm, oracle, tmp_path, fused):
     if llm.deviceCount() < 2:
         pytest.skip("needs two GPUs")
     sys.path.insert(0, HERE)
@@ -23,7 +25,8 @@ def test_tp2_tokens_match_the_oracle(llm, oracle, tmp_path):
     O = oracle
     steps, t = 16, 7
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), str(r), "2", str(tmp_path),
-                               str(steps), str(t)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+                               str(steps), str(t)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                              env=dict(os.environ, LOGOS_B200_TP_FUSED=fused))
              for r in range(2)]
     outs = []
     try:
@@ -40,6 +43,7 @@ def test_tp2_tokens_match_the_oracle(llm, oracle, tmp_path):
     ref.prefill(toks)
     want = np.array([ref.decode_step().copy() for _ in range(steps)])
     r0, r1 = (np.load(tmp_path / ("r%d.npz" % i)) for i in range(2))
+    assert int(r0["exchange"]) == int(r1["exchange"]) == (2 if fused == "1" else 1)   # no silent fall-back
     assert np.array_equal(r0["tokens"], want) and np.array_equal(r1["tokens"], want)
     assert np.array_equal(r0["logits"], r1["logits"])           # replicated lm_head on identical inputs
     # each rank holds its own KV heads: rank r's head 0 is the oracle's head r

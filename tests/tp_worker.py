@@ -41,7 +41,7 @@ def main():
     m.prefill(toks)
     got = m.decodeSteps(steps)
     k, v = m.readKv(0)
-    np.savez(os.path.join(out_dir, "r%d.npz" % rank), tokens=got, k=k, v=v, logits=m.readLogits())
+    np.savez(os.path.join(out_dir, "r%d.npz" % rank), tokens=got, k=k, v=v, logits=m.readLogits(), exchange=m.tpExchange())
     print("rank", rank, "done", flush=True)
 
 
