@@ -118,7 +118,8 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-// Bounded: false when the flag did not reach `target` within about two seconds of SM clock.
+// Bounded: false when the flag did not reach `target` within about ten seconds of SM clock (a
+// peer is another process on another GPU: it may lag by a graph instantiation or a page-in).
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target) {
   if ((int32_t)(ld_acquire_sys(p) - target) >= 0) return true;
   const long long start = clock64();
@@ -126,7 +127,7 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target)
 #pragma unroll 1
     for (int k = 0; k < 64; ++k)
       if ((int32_t)(ld_acquire_sys(p) - target) >= 0) return true;
-    if (clock64() - start > 4000000000ll) return false;
+    if (clock64() - start > 20000000000ll) return false;
   }
 }
 
