@@ -263,6 +263,15 @@ LOGOS_API logos_status_t logos_llm_set_seq_len(logos_handle_t model, int64_t t);
 /* Device-side time of the last logos_llm_decode_steps call, milliseconds
  * (CUDA events on the model's stream), and kernels launched per step. */
 LOGOS_API logos_status_t logos_llm_last_timing(logos_handle_t model, double* ms_out, int64_t* launches_per_step_out);
+/* Measurement aid (no counterpart in the reference): SM cycles one thread needs to issue
+ * `count` back-to-back tcgen05.mma kind::f16 instructions (M = 128, K = 16, N = n in
+ * {32, 64, 128, 256}; A operand in tensor memory when a_in_tmem != 0, else in shared memory)
+ * that alternate between `accumulators` accumulators, and cycles until their completion is
+ * seen through an mbarrier.  One CTA; operand contents are irrelevant.  This is where the
+ * "about 85 cycles per MMA whatever N" figure behind the Q8 GEMM's design comes from. */
+LOGOS_API logos_status_t logos_tc_mma_probe(int32_t device, int32_t n, int32_t a_in_tmem, int32_t count,
+                                            int32_t accumulators, int64_t* issue_cycles_out,
+                                            int64_t* complete_cycles_out);
 /* How the ranks of the model's tensor-parallel group exchange the partial products of the
  * row-parallel GEMMs: 0 = no group (tp_degree 1), 1 = NCCL all-reduce, 2 = folded into the
  * residual + RMSNorm kernel over peer-mapped memory (one process per GPU, one node). */

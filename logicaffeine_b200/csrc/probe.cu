@@ -1,0 +1,121 @@
+// Measurement aid: how long one tcgen05.mma (kind::f16, M = 128, K = 16) occupies the tensor
+// pipe, as a function of N, of where the A operand lives and of how many accumulators the
+// instructions alternate between.  One CTA issues `count` MMAs back to back from one thread,
+// commits them to an mbarrier and reports SM cycles from the first issue to the moment the
+// completion is seen.  Operand contents do not matter (shared memory is zeroed, tensor memory
+// is whatever it holds); nothing is written outside the CTA except the two counters.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace logos {
+namespace {
+
+using namespace ptx;
+
+template <int N, bool A_IN_TMEM>
+__global__ void mma_probe_kernel(long long* out, int count, int accumulators) {
+  extern __shared__ uint8_t probe_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(probe_smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t bar;
+  __shared__ uint32_t slot;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  for (int i = tid; i < 64 * 1024 / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(smem)[i] = 0u;
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&slot, 512);
+    tmem_relinquish();
+  }
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tb = slot;
+  constexpr uint32_t idesc = make_idesc_f16(0, 0, 128, N);
+  if (warp == 1) {
+    long long t0 = 0, t1 = 0;
+    if (elect_one()) {
+      t0 = clock64();
+      for (int i = 0; i < count; ++i) {
+        const uint32_t d = tb + 128 + (uint32_t)(i % accumulators) * N;  // accumulators after 128 columns of A
+        const uint64_t bd = make_desc_sw128(smem_u32(smem) + (i & 3) * 32);
+        if (A_IN_TMEM) {
+          tc_mma_f16_ts(d, tb + (uint32_t)(i & 7) * 8, bd, idesc, 1u);
+        } else {
+          const uint64_t ad = make_desc_sw128(smem_u32(smem) + 32768 + (i & 3) * 32);
+          tc_mma_f16_ss(d, ad, bd, idesc, 1u);
+        }
+      }
+      t1 = clock64();
+      tc_commit(&bar);
+    }
+    __syncwarp();
+    const bool seen = mbar_wait(&bar, 0);
+    const long long t2 = clock64();
+    if (elect_one()) {
+      out[0] = t1 - t0;
+      out[1] = seen ? t2 - t0 : -1;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tb, 512);
+  }
+}
+
+template <int N>
+logos_status_t run_probe(bool a_in_tmem, long long* dev_out, int count, int accumulators, cudaStream_t st) {
+  const size_t smem = 66 * 1024;
+  if (a_in_tmem) {
+    LOGOS_CUDA_TRY(cudaFuncSetAttribute(mma_probe_kernel<N, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    mma_probe_kernel<N, true><<<1, 128, smem, st>>>(dev_out, count, accumulators);
+  } else {
+    LOGOS_CUDA_TRY(cudaFuncSetAttribute(mma_probe_kernel<N, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    mma_probe_kernel<N, false><<<1, 128, smem, st>>>(dev_out, count, accumulators);
+  }
+  return check_launch("mma_probe_kernel");
+}
+
+}  // namespace
+}  // namespace logos
+
+using namespace logos;
+
+extern "C" logos_status_t logos_tc_mma_probe(int32_t device, int32_t n, int32_t a_in_tmem, int32_t count,
+                                             int32_t accumulators, int64_t* issue_cycles_out,
+                                             int64_t* complete_cycles_out) {
+  return guarded([&]() -> logos_status_t {
+    if (!issue_cycles_out || !complete_cycles_out) return fail(LOGOS_NULL_POINTER, "logos_tc_mma_probe: null out");
+    if (count < 1 || count > 4096) return fail(LOGOS_OUT_OF_BOUNDS, "logos_tc_mma_probe: count must be 1..4096");
+    if (accumulators < 1 || (int64_t)accumulators * n > 384)
+      return fail(LOGOS_OUT_OF_BOUNDS, "logos_tc_mma_probe: accumulators x N must fit 384 tensor-memory columns");
+    LOGOS_CUDA_TRY(cudaSetDevice(device));
+    long long* dev = nullptr;
+    LOGOS_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&dev), 16));
+    logos_status_t rc = LOGOS_OK;
+    // the second launch is the one reported: the first warms the instruction cache
+    for (int rep = 0; rep < 2 && rc == LOGOS_OK; ++rep) {
+      if (n == 32) rc = run_probe<32>(a_in_tmem != 0, dev, count, accumulators, nullptr);
+      else if (n == 64) rc = run_probe<64>(a_in_tmem != 0, dev, count, accumulators, nullptr);
+      else if (n == 128) rc = run_probe<128>(a_in_tmem != 0, dev, count, accumulators, nullptr);
+      else if (n == 256) rc = run_probe<256>(a_in_tmem != 0, dev, count, accumulators, nullptr);
+      else rc = fail(LOGOS_OUT_OF_BOUNDS, "logos_tc_mma_probe: N must be 32, 64, 128 or 256");
+    }
+    long long host[2] = {0, 0};
+    if (rc == LOGOS_OK) {
+      cudaError_t e = cudaDeviceSynchronize();
+      if (e == cudaSuccess) e = cudaMemcpy(host, dev, 16, cudaMemcpyDeviceToHost);
+      if (e != cudaSuccess) rc = cuda_fail(e, "mma probe");
+    }
+    cudaFree(dev);
+    if (rc != LOGOS_OK) return rc;
+    if (host[1] < 0) return fail(LOGOS_ERROR, "logos_tc_mma_probe: the completion barrier was not seen in time");
+    *issue_cycles_out = host[0];
+    *complete_cycles_out = host[1];
+    return LOGOS_OK;
+  });
+}
