@@ -267,8 +267,8 @@ LOGOS_API logos_status_t logos_llm_last_timing(logos_handle_t model, double* ms_
  * `count` back-to-back tcgen05.mma kind::f16 instructions (M = 128, K = 16, N = n in
  * {32, 64, 128, 256}; A operand in tensor memory when a_in_tmem != 0, else in shared memory)
  * that alternate between `accumulators` accumulators, and cycles until their completion is
- * seen through an mbarrier.  One CTA; operand contents are irrelevant.  This is where the
- * "about 85 cycles per MMA whatever N" figure behind the Q8 GEMM's design comes from. */
+ * seen through an mbarrier.  One CTA; operand contents are irrelevant.  The Q8 GEMM's design
+ * notes quote its figures (38 cycles at N = 64 with A in tensor memory on a B200). */
 LOGOS_API logos_status_t logos_tc_mma_probe(int32_t device, int32_t n, int32_t a_in_tmem, int32_t count,
                                             int32_t accumulators, int64_t* issue_cycles_out,
                                             int64_t* complete_cycles_out);

@@ -9,6 +9,8 @@
 // tree, then warps in ascending order), so results do not depend on timing.
 #include "ops.cuh"
 
+#include <cooperative_groups.h>
+
 namespace logos {
 
 namespace {
@@ -132,15 +134,22 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target)
 }
 
 constexpr int TP_MAX_SRC = 64;  // degree x parts
+constexpr int TP_CLUSTER = 4;   // CTAs per row: at decode batch sizes a rank owns fewer rows than there are SMs
 
+// A row is spread over a cluster of TP_CLUSTER CTAs (one float4 per thread where the row is
+// short enough), so that every peer load of a row is in flight at once; the slices' sums of
+// squares meet through distributed shared memory, summed in rank order by every CTA.
 __global__ void __launch_bounds__(512)
 tp_residual_rmsnorm_kernel(float* __restrict__ h, const TpFusedArgs t, int parts, int64_t part_stride,
                            const float* __restrict__ g, int64_t rows_own, int64_t hidden, float eps, int* status) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
   __shared__ float red[32];
+  __shared__ float slice_ss;
   __shared__ uint32_t epoch_s;
   __shared__ int last_s;
   __shared__ const float* src[TP_MAX_SRC];
-  extern __shared__ float4 row_cache4[];  // hidden floats
+  extern __shared__ float4 row_cache4[];  // this CTA's slice of the row
   const int tid = threadIdx.x;
   pdl_wait();  // this rank's own GEMM has completed: its partials are in this GPU's memory
   pdl_trigger();
@@ -156,26 +165,42 @@ tp_residual_rmsnorm_kernel(float* __restrict__ h, const TpFusedArgs t, int parts
   if (tid < t.degree && !wait_flag_ge(my + tid, e)) atomicExch(status, 3010);
   __syncthreads();
 
-  const int64_t row = (int64_t)t.rank * rows_own + blockIdx.x;
-  const int64_t n4 = hidden >> 2;
-  float4* hr4 = reinterpret_cast<float4*>(h + row * hidden);
+  const unsigned crank = cluster.block_rank();
+  const int64_t row = (int64_t)t.rank * rows_own + blockIdx.x / TP_CLUSTER;
+  const int64_t per = (hidden >> 2) / TP_CLUSTER;  // float4 per CTA
+  const int64_t off4 = row * (hidden >> 2) + (int64_t)crank * per;  // this slice, in float4 units from a buffer's base
+  float4* hr4 = reinterpret_cast<float4*>(h) + off4;
   float ss = 0.f;
-  for (int64_t i = tid; i < n4; i += blockDim.x) {
+  for (int64_t i = tid; i < per; i += blockDim.x) {
     float4 v = __ldcg(hr4 + i);
-    // peers' buffers are read past L1 (ld.global.cg): the lines are rewritten every call
-#pragma unroll 4
-    for (int q = 0; q < nsrc; ++q) {
-      const float4 d = __ldcg(reinterpret_cast<const float4*>(src[q] + row * hidden) + i);
-      v.x = __fadd_rn(v.x, d.x); v.y = __fadd_rn(v.y, d.y); v.z = __fadd_rn(v.z, d.z); v.w = __fadd_rn(v.w, d.w);
+    // peers' buffers are read past L1 (ld.global.cg): the lines are rewritten every call.
+    // Eight loads are issued before their sums are taken, so a row costs few NVLink round trips.
+    for (int q0 = 0; q0 < nsrc; q0 += 8) {
+      float4 d[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        d[u] = (q0 + u < nsrc) ? __ldcg(reinterpret_cast<const float4*>(src[q0 + u]) + off4 + i)
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (q0 + u < nsrc) {
+          v.x = __fadd_rn(v.x, d[u].x); v.y = __fadd_rn(v.y, d[u].y);
+          v.z = __fadd_rn(v.z, d[u].z); v.w = __fadd_rn(v.w, d[u].w);
+        }
+      }
     }
     hr4[i] = v;
     row_cache4[i] = v;
     ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
   }
   ss = block_sum(ss, red);
-  const float inv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hidden), eps)));
-  const float4* g4 = reinterpret_cast<const float4*>(g);
-  for (int64_t i = tid; i < n4; i += blockDim.x) {
+  if (tid == 0) slice_ss = ss;
+  cluster.sync();
+  float total = 0.f;
+  for (unsigned r = 0; r < TP_CLUSTER; ++r) total += *cluster.map_shared_rank(&slice_ss, r);
+  const float inv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)hidden), eps)));
+  const float4* g4 = reinterpret_cast<const float4*>(g) + (int64_t)crank * per;
+  for (int64_t i = tid; i < per; i += blockDim.x) {
     const float4 v = row_cache4[i], gg = g4[i];
     const float o[4] = {__fmul_rn(__fmul_rn(v.x, inv), gg.x), __fmul_rn(__fmul_rn(v.y, inv), gg.y),
                         __fmul_rn(__fmul_rn(v.z, inv), gg.z), __fmul_rn(__fmul_rn(v.w, inv), gg.w)};
@@ -190,13 +215,13 @@ tp_residual_rmsnorm_kernel(float* __restrict__ h, const TpFusedArgs t, int parts
     }
     const uint2 hp = *reinterpret_cast<const uint2*>(hh), lp = *reinterpret_cast<const uint2*>(ll);
     for (int r = 0; r < t.degree; ++r) {
-      reinterpret_cast<uint2*>(t.xn_hi[r] + row * hidden)[i] = hp;
-      if (t.xn_lo[r]) reinterpret_cast<uint2*>(t.xn_lo[r] + row * hidden)[i] = lp;
+      reinterpret_cast<uint2*>(t.xn_hi[r])[off4 + i] = hp;
+      if (t.xn_lo[r]) reinterpret_cast<uint2*>(t.xn_lo[r])[off4 + i] = lp;
     }
   }
   // ---- barrier 2: the last CTA of this rank to finish tells every rank that this rank's rows
   // have been delivered, and holds the kernel until every peer's rows are here.
-  __syncthreads();
+  cluster.sync();  // also: no CTA leaves while a peer of its cluster may still read its slice_ss
   if (tid == 0) {
     __threadfence_system();
     const uint32_t ticket = atomicAdd(my + 17, 1u);
@@ -332,17 +357,35 @@ logos_status_t launch_residual_rmsnorm(float* h, const float* delta, int parts, 
 logos_status_t launch_tp_residual_rmsnorm(float* h, const TpFusedArgs& t, int parts, int64_t part_stride, const float* g,
                                           int64_t rows, int64_t hidden, float eps, int device, cudaStream_t st) {
   if (rows == 0) return LOGOS_OK;
-  if (t.degree < 2 || t.degree > 8 || rows % t.degree || (hidden & 3) || parts < 1 || t.degree * parts > TP_MAX_SRC)
+  if (t.degree < 2 || t.degree > 8 || rows % t.degree || hidden % (4 * TP_CLUSTER) || parts < 1 ||
+      t.degree * parts > TP_MAX_SRC)
     return fail(LOGOS_ERROR, "tp_residual_rmsnorm: unsupported shape (rows %lld, hidden %lld, degree %d, parts %d)",
                 (long long)rows, (long long)hidden, t.degree, parts);
   int* status = kernel_status_ptr(device);
   if (!status) return fail(LOGOS_ERROR, "tp_residual_rmsnorm: no kernel status word");
-  const size_t smem = sizeof(float) * (size_t)hidden;
-  if (smem > 48 * 1024)
-    LOGOS_CUDA_TRY(cudaFuncSetAttribute(tp_residual_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int64_t per = (hidden >> 2) / TP_CLUSTER;
   const int64_t rows_own = rows / t.degree;
-  LOGOS_CUDA_TRY(launch_kernel(tp_residual_rmsnorm_kernel, dim3((unsigned)rows_own), dim3(512), smem, st, h, t, parts,
-                               part_stride, g, rows_own, hidden, eps, status));
+  int threads = (int)(((per + 31) / 32) * 32);
+  if (threads > 512) threads = 512;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(rows_own * TP_CLUSTER));
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.dynamicSmemBytes = sizeof(float4) * (size_t)per;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = TP_CLUSTER;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_active() ? 2 : 1;
+  if (cfg.dynamicSmemBytes > 48 * 1024)
+    LOGOS_CUDA_TRY(cudaFuncSetAttribute(tp_residual_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)cfg.dynamicSmemBytes));
+  LOGOS_CUDA_TRY(cudaLaunchKernelEx(&cfg, tp_residual_rmsnorm_kernel, h, t, parts, part_stride, g, rows_own, hidden, eps,
+                                    status));
   count_launch(LK_ELEMWISE);
   return check_launch("tp_residual_rmsnorm_kernel");
 }

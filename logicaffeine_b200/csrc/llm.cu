@@ -229,7 +229,7 @@ logos_status_t build(Model* m, const void* nccl_id) {
     const int64_t total = off_flags + up(TP_FLAG_WORDS * 4);
     const char* e = getenv("LOGOS_B200_TP_FUSED");
     // opt-in until it has been measured on 2 to 8 GPUs
-    const bool want = g > 1 && g <= 8 && B % g == 0 && H % 4 == 0 && g * m->max_splits <= 64 && (e && e[0] == '1');
+    const bool want = g > 1 && g <= 8 && B % g == 0 && H % 16 == 0 && g * m->max_splits <= 64 && (e && e[0] == '1');
     if (want) LOGOS_TRY(tp_symm_alloc(&m->tp, (size_t)total, &m->symm, m->stream));
     m->tp_fused = want && m->symm.ok;
     if (m->tp_fused) {

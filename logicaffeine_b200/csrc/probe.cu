@@ -37,15 +37,25 @@ __global__ void mma_probe_kernel(long long* out, int count, int accumulators) {
   if (warp == 1) {
     long long t0 = 0, t1 = 0;
     if (elect_one()) {
+      // operands of eight consecutive MMAs are fixed at compile time (no address arithmetic in
+      // the timed loop); the accumulator index advances without a division
+      uint64_t bd[4], ad[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        bd[u] = make_desc_sw128(smem_u32(smem) + u * 32);
+        ad[u] = make_desc_sw128(smem_u32(smem) + 32768 + u * 32);
+      }
+      int acc = 0;
       t0 = clock64();
-      for (int i = 0; i < count; ++i) {
-        const uint32_t d = tb + 128 + (uint32_t)(i % accumulators) * N;  // accumulators after 128 columns of A
-        const uint64_t bd = make_desc_sw128(smem_u32(smem) + (i & 3) * 32);
-        if (A_IN_TMEM) {
-          tc_mma_f16_ts(d, tb + (uint32_t)(i & 7) * 8, bd, idesc, 1u);
-        } else {
-          const uint64_t ad = make_desc_sw128(smem_u32(smem) + 32768 + (i & 3) * 32);
-          tc_mma_f16_ss(d, ad, bd, idesc, 1u);
+      for (int i = 0; i < count; i += 8) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (i + u < count) {
+            const uint32_t d = tb + 128 + (uint32_t)acc * N;  // accumulators after 128 columns of A
+            if (A_IN_TMEM) tc_mma_f16_ts(d, tb + (uint32_t)u * 8, bd[u & 3], idesc, 1u);
+            else tc_mma_f16_ss(d, ad[u & 3], bd[u & 3], idesc, 1u);
+            acc = (acc + 1 == accumulators) ? 0 : acc + 1;
+          }
         }
       }
       t1 = clock64();

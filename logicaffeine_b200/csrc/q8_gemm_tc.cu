@@ -57,9 +57,9 @@ constexpr int TA_LIMB_COLS = 64; // TMEM columns per converted stage and copy: 1
 constexpr int CONV_WARPS = 4;
 constexpr int CONV_WARP0 = 4, DRAIN_WARP0 = CONV_WARP0 + CONV_WARPS;
 constexpr int TC_THREADS = (DRAIN_WARP0 + 8) * 32;  // 4 single-role warps, converter warps, 8 drain warps
-// Token groups an MMA warp cuts each block into (MMA N = MT / NSPLIT).  Measured: an MMA costs
-// about 45 cycles whether N is 32 or 64 once four independent accumulation chains are in
-// flight, and about 85 with two, so more, smaller MMAs lose what the extra chains gain.
+// Token groups an MMA warp cuts each block into (MMA N = MT / NSPLIT).  An isolated M=128, K=16
+// MMA with its A operand in tensor memory takes 38 cycles at N=32 and at N=64 (logos_tc_mma_probe),
+// so cutting a block into smaller MMAs only doubles the instruction count: 1 is the setting.
 #ifndef LOGOS_TC_NSPLIT
 #define LOGOS_TC_NSPLIT 1
 #endif
@@ -325,8 +325,9 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // ------------------------------------------------------------ MMA issuers
     if (kRebalance) setmaxnreg_dec<48>();
     // Two warps, one per half of a stage: warp 2 issues the first pair of Q8 blocks of every
-    // stage, warp 3 the second.  What bounds this role is the serial latency of wait -> issue ->
-    // commit, not tensor throughput, so two chains run side by side; and every barrier is
+    // stage, warp 3 the second.  What bounds the kernel is the round trip of an accumulator entry
+    // (MMAs execute -> completion seen by the drain -> tcgen05.ld -> entry released -> next
+    // stage's MMAs), so the two pairs' round trips run side by side; and every barrier is
     // waited on, phase after phase, by the same warp, which the odd/even phase test needs.
     // A warp runs its loop with all lanes (addresses and descriptors stay warp-uniform) and one
     // elected lane issues the tcgen05 instructions.  A pair owns accumulator ring entry `pr`.
@@ -354,9 +355,8 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         if (elect_one()) {
           // Per block: d = q * lo' first, then d = q * hi + d * 2^-11 (the residual plane is folded
           // in by the accumulator scaling of the MMA itself, from one copy of the weights).
-          // Back-to-back MMAs on one accumulator run at their latency, not at their throughput,
-          // so the work is cut into as many independent chains as the tile allows - two blocks x
-          // NSPLIT token groups - and the chains are issued interleaved.
+          // The two blocks' chains are issued interleaved (measured neutral: the pipe runs
+          // dependent and independent accumulations at the same rate).
 #pragma unroll
           for (int u = 0; u < 2 * LIMBS; ++u) {
 #pragma unroll
