@@ -472,12 +472,15 @@ logos_status_t launch_attn_t(const AttnArgs& a, cudaStream_t st) {
                                CU_TENSOR_MAP_SWIZZLE_128B));
   LOGOS_TRY(make_tensor_map_2d(&mv, a.v_cache, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, D, rows_total, D * 2, 64, ATT_TILE,
                                CU_TENSOR_MAP_SWIZZLE_128B));
-  // unit length: aim at ~16 units per SM over the whole (sequence, KV head, position) space
+  // Unit length: a CTA pays about a tile's worth of time for its prologue, its first load and
+  // its partial results, so units are at least four tiles where the grid still fills the GPU
+  // (two CTAs per SM, a few waves), and at most eight, which keeps the last wave short.
   int sms = sm_count(a.device);
   int64_t total_pos = a.b * a.h_kv * a.l_max;
-  int64_t ul = (total_pos + (int64_t)sms * 16 - 1) / ((int64_t)sms * 16);
+  int64_t ul = (total_pos + (int64_t)sms * 5 - 1) / ((int64_t)sms * 5);
   ul = ((ul + ATT_TILE - 1) / ATT_TILE) * ATT_TILE;
-  if (ul < 2 * ATT_TILE) ul = 2 * ATT_TILE;
+  if (ul < 4 * ATT_TILE) ul = 4 * ATT_TILE;
+  if (ul > 8 * ATT_TILE) ul = 8 * ATT_TILE;
   int max_splits = (int)((a.l_max + ul - 1) / ul);
 
   void* scratch = nullptr;

@@ -18,6 +18,7 @@
 // output rows (heads, FFN columns) and o_proj/down_proj by input columns, so
 // the only exchanges are the two sum all-reduces per layer.
 #include "ops.cuh"
+#include "q8_gemm_tc.cuh"
 #include "tp.cuh"
 
 #include <stdlib.h>
@@ -55,6 +56,8 @@ struct Model {
   ActOut att;                // [B][nq]
   ActOut ffn;                // [B][f_local]
   float* partials = nullptr; // [max_splits][B][H]
+  float* dpart = nullptr;    // split-K partials of the GEMMs with a direct output (qkv, gate/up)
+  int64_t dpart_floats = 0;
   // tensor parallelism with peer-addressable memory: partials, xn planes and flag words live in
   // one block per rank that every rank maps; the all-reduce is folded into residual + RMSNorm
   TpSymm symm;
@@ -255,6 +258,15 @@ logos_status_t build(Model* m, const void* nccl_id) {
   LOGOS_TRY(planes(&m->att, B * m->nq));
   LOGOS_TRY(planes(&m->ffn, B * m->f_local));
   if (!m->tp_fused) LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->partials), (int64_t)m->max_splits * B * H * 4));
+  {
+    // qkv and gate/up split K too when their row tiles alone would leave most SMs idle (the
+    // per-rank shapes of a TP group): room for the larger of the two sets of partials
+    const int s_qkv = gemm_pick_splits(B, m->nqkv, H, m->device), s_gu = gemm_pick_splits(B, 2 * m->f_local, H, m->device);
+    const int64_t need_qkv = s_qkv > 1 ? (int64_t)s_qkv * B * m->nqkv : 0;
+    const int64_t need_gu = s_gu > 1 ? (int64_t)s_gu * B * 2 * m->f_local : 0;
+    m->dpart_floats = need_qkv > need_gu ? need_qkv : need_gu;
+    if (m->dpart_floats > 0) LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->dpart), m->dpart_floats * 4));
+  }
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->logits), B * c.vocab * 4));
   m->history_cap = c.l_max;
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->history), m->history_cap * B * 4));
@@ -285,6 +297,30 @@ __global__ void bump_len_kernel(int32_t* seq_len, int32_t* step_counter, int b, 
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < b && seq_len[i] < l_max) seq_len[i] += 1;
   if (i == 0) *step_counter += 1;
+}
+
+// GEMM with its own output and epilogue (qkv, gate/up, lm_head): K is split, and a small kernel
+// folds the partials and applies the epilogue, where the cost model prefers that.
+logos_status_t gemm_direct(Model* m, const GemmArgs& g) {
+  ProfScope ps(m, PROF_GEMM);
+  int splits = gemm_pick_splits(g.m, g.n, g.k, m->device);
+  if (splits > 1 && (int64_t)splits * g.m * g.n <= m->dpart_floats && gemm_tc_applicable(g)) {
+    GemmArgs gp = g;
+    gp.splits = splits;
+    gp.partials = m->dpart;
+    gp.epilogue = EPI_NONE;
+    gp.c = nullptr;
+    gp.c_dtype = LOGOS_F32;
+    gp.aux = nullptr;
+    LOGOS_TRY(launch_q8_gemm(gp, m->stream));
+    LOGOS_TRY(launch_splitk_reduce(m->dpart, splits, g.c, g.c_dtype, g.c_act, g.ldc, g.aux, g.m, g.n, g.epilogue,
+                                   m->stream));
+    m->launch_counter += 2;
+    return LOGOS_OK;
+  }
+  LOGOS_TRY(launch_q8_gemm(g, m->stream));
+  m->launch_counter += 1;
+  return LOGOS_OK;
 }
 
 // GEMM producing f32 partials [splits][B][N] in m->partials; returns the split count.
@@ -373,15 +409,13 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
     LOGOS_TRY(norm_step(m, parts));
     m->launch_counter += 1;
     {
-      ProfScope ps(m, PROF_GEMM);
       GemmArgs g;
       g.a = m->xn.hi; g.a_lo = m->xn.lo; g.a_dtype = LOGOS_F16; g.lda = H;
       g.q = L.wqkv.q; g.s = L.wqkv.s;
       g.c = m->qkv; g.c_dtype = LOGOS_F32; g.ldc = m->nqkv;
       g.m = B; g.n = m->nqkv; g.k = H;
       g.device = m->device;
-      LOGOS_TRY(launch_q8_gemm(g, st));
-      m->launch_counter += 1;
+      LOGOS_TRY(gemm_direct(m, g));
     }
     LOGOS_TRY(debug_check(m, "qkv gemm", l));
     {
@@ -404,7 +438,6 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
     LOGOS_TRY(norm_step(m, parts));
     m->launch_counter += 1;
     {
-      ProfScope ps(m, PROF_GEMM);
       GemmArgs g;
       g.a = m->xn.hi; g.a_lo = m->xn.lo; g.a_dtype = LOGOS_F16; g.lda = H;
       g.q = L.wgu.q; g.s = L.wgu.s;
@@ -412,8 +445,7 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
       g.m = B; g.n = 2 * m->f_local; g.k = H;
       g.epilogue = EPI_SWIGLU;
       g.device = m->device;
-      LOGOS_TRY(launch_q8_gemm(g, st));
-      m->launch_counter += 1;
+      LOGOS_TRY(gemm_direct(m, g));
     }
     LOGOS_TRY(debug_check(m, "gate/up gemm", l));
     LOGOS_TRY(gemm_partials(m, m->ffn, L.wd, &parts));

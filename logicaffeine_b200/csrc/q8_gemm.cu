@@ -88,6 +88,8 @@ q8_gemm_simt_kernel(const void* __restrict__ a, const __half* __restrict__ a_lo,
 __global__ void splitk_reduce_kernel(const float* __restrict__ partials, int splits, void* __restrict__ c, int c_dtype,
                                      ActOut c_act, int64_t ldc, const void* __restrict__ aux, int64_t m, int64_t n,
                                      int epilogue) {
+  pdl_wait();  // the partials are the previous kernel's output: wait for it, read them past L1
+  pdl_trigger();
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (epilogue == EPI_SWIGLU) {
     int64_t half_n = n / 2;
@@ -95,8 +97,9 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partials, int spl
     int64_t mm = i / half_n, j = i - mm * half_n;
     float g = 0.f, u = 0.f;
     for (int sp = 0; sp < splits; ++sp) {
-      g = __fadd_rn(g, partials[((int64_t)sp * m + mm) * n + 2 * j]);
-      u = __fadd_rn(u, partials[((int64_t)sp * m + mm) * n + 2 * j + 1]);
+      const float2 gu = __ldcg(reinterpret_cast<const float2*>(partials + ((int64_t)sp * m + mm) * n + 2 * j));
+      g = __fadd_rn(g, gu.x);
+      u = __fadd_rn(u, gu.y);
     }
     store_out(c, c_dtype, mm * ldc + j, __fmul_rn(silu_f(g), u), c_act);
     return;
@@ -104,7 +107,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partials, int spl
   if (i >= m * n) return;
   int64_t mm = i / n, nn = i - mm * n;
   float v = 0.f;
-  for (int sp = 0; sp < splits; ++sp) v = __fadd_rn(v, partials[((int64_t)sp * m + mm) * n + nn]);
+  for (int sp = 0; sp < splits; ++sp) v = __fadd_rn(v, __ldcg(partials + ((int64_t)sp * m + mm) * n + nn));
   if (epilogue == EPI_RESIDUAL) v = __fadd_rn(v, load_act(aux, c_dtype, mm * ldc + nn));
   store_out(c, c_dtype, mm * ldc + nn, v, c_act);
 }
@@ -140,8 +143,8 @@ logos_status_t launch_splitk_reduce(const float* partials, int splits, void* c, 
                                     cudaStream_t st) {
   int64_t total = (epilogue == EPI_SWIGLU) ? m * (n / 2) : m * n;
   if (total == 0) return LOGOS_OK;
-  splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(partials, splits, c, c_dtype, c_act, ldc, aux,
-                                                                        m, n, epilogue);
+  LOGOS_CUDA_TRY(launch_kernel(splitk_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, partials, splits,
+                               c, c_dtype, c_act, ldc, aux, m, n, epilogue));
   count_launch(LK_ELEMWISE);
   return check_launch("splitk_reduce_kernel");
 }

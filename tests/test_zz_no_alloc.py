@@ -47,7 +47,7 @@ def test_fixed_scratch_attention_matches_the_allocating_entry_point_twice(llm, o
 
 
 def test_fixed_scratch_refuses_what_does_not_fit(llm):
-    # 64 sequences x 128 query heads x 5 splits x 130 floats: about 21 MiB of partials, more than the 16 MiB array
+    # 64 sequences x 128 query heads x 4 splits x 130 floats: 16.25 MiB of partials, more than the 16 MiB array
     b, hq, hkv, d, lmax = 64, 128, 8, 128, 2048
     tiny = llm.DeviceBuffer(16)
     big_q = llm.DeviceBuffer(b * hq * d * 2)
