@@ -252,3 +252,15 @@ def test_tc_mma_probe(llm):
         llm.tcMmaProbe(48, True, 16, 1)      # N not offered
     with pytest.raises(llm.LogosError):
         llm.tcMmaProbe(256, True, 16, 2)     # 512 accumulator columns do not fit beside the operand
+
+
+def test_gemm_with_one_token_equals_gemv(llm, oracle):
+    """Metamorphic: the tensor-core GEMM at M = 1 and the GEMV kernel compute the same product."""
+    O = oracle
+    n, k = 1000, 2048
+    q = O.synth_fill(O.I8, 0, 4, 21, 0, n * k).reshape(n, k)
+    s = O.synth_fill(O.F32, 1, 4, 22, 0, n * (k // 32), 1e-3, 1e-2).reshape(n, k // 32)
+    x = O.synth_fill(O.F32, 2, 4, 23, 0, k, 0.0, 1.0)
+    y = llm.q8GemvHost(q, s, x)
+    c = llm.q8GemmF32Host(x.reshape(1, k), q, s).reshape(n)
+    assert rel_l2(c, y) < 2e-6
