@@ -224,6 +224,10 @@ def op_probe(args):
             issue, done = llm.tcMmaProbe(nn, tmem, 512, accs, dev)
             rows.append({"n": nn, "a_operand": "tmem" if tmem else "smem", "accumulators": accs,
                          "cycles_per_mma": done / 512.0, "issue_cycles_per_mma": issue / 512.0})
+        for bg, what in ((1, "tcgen05.st"), (2, "tcgen05.ld"), (3, "ld.shared.v4")):
+            issue, done = llm.tcMmaProbe(64, True, 512, 2, dev, bg)
+            rows.append({"n": 64, "a_operand": "tmem", "accumulators": 2, "other_warps": what,
+                         "cycles_per_mma": done / 512.0, "issue_cycles_per_mma": issue / 512.0})
         burst = []
         for cnt in (1, 2, 4, 8, 16):
             issue, done = llm.tcMmaProbe(64, True, cnt, 2, dev)

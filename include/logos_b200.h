@@ -267,10 +267,12 @@ LOGOS_API logos_status_t logos_llm_last_timing(logos_handle_t model, double* ms_
  * `count` back-to-back tcgen05.mma kind::f16 instructions (M = 128, K = 16, N = n in
  * {32, 64, 128, 256}; A operand in tensor memory when a_in_tmem != 0, else in shared memory)
  * that alternate between `accumulators` accumulators, and cycles until their completion is
- * seen through an mbarrier.  One CTA; operand contents are irrelevant.  The Q8 GEMM's design
+ * seen through an mbarrier.  `background`: what eight other warps of the CTA do meanwhile - 0
+ * nothing, 1 tcgen05.st, 2 tcgen05.ld (both to columns the MMAs do not touch), 3 128-bit
+ * shared-memory loads.  One CTA; operand contents are irrelevant.  The Q8 GEMM's design
  * notes quote its figures (38 cycles at N = 64 with A in tensor memory on a B200). */
 LOGOS_API logos_status_t logos_tc_mma_probe(int32_t device, int32_t n, int32_t a_in_tmem, int32_t count,
-                                            int32_t accumulators, int64_t* issue_cycles_out,
+                                            int32_t accumulators, int32_t background, int64_t* issue_cycles_out,
                                             int64_t* complete_cycles_out);
 /* How the ranks of the model's tensor-parallel group exchange the partial products of the
  * row-parallel GEMMs: 0 = no group (tp_degree 1), 1 = NCCL all-reduce, 2 = folded into the

@@ -13,12 +13,14 @@ namespace {
 using namespace ptx;
 
 template <int N, bool A_IN_TMEM>
-__global__ void mma_probe_kernel(long long* out, int count, int accumulators) {
+__global__ void mma_probe_kernel(long long* out, int count, int accumulators, int background) {
   extern __shared__ uint8_t probe_smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(probe_smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t bar;
   __shared__ uint32_t slot;
+  __shared__ volatile int stop;
   const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) stop = 0;
   for (int i = tid; i < 64 * 1024 / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(smem)[i] = 0u;
   if (tid == 0) {
     mbar_init(&bar, 1);
@@ -67,7 +69,32 @@ __global__ void mma_probe_kernel(long long* out, int count, int accumulators) {
     if (elect_one()) {
       out[0] = t1 - t0;
       out[1] = seen ? t2 - t0 : -1;
+      stop = 1;
     }
+  } else if (warp >= 2 && background != 0) {
+    // Other traffic while the MMAs run (what the GEMM's converter and drain warps and its TMA
+    // loads do next to the tensor pipe); every loop is bounded and ends when the MMAs are done.
+    const int lane = tid & 31;
+    const uint32_t t_lane = tb + ((uint32_t)((warp & 3) * 32) << 16);
+    uint32_t r[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) r[i] = (uint32_t)(tid + i);
+    uint32_t sink = 0;
+    for (int it = 0; it < 200000 && !stop; ++it) {
+      if (background == 1) {         // tcgen05.st into columns the MMAs do not touch
+        uint32_t r8[8] = {r[0], r[1], r[2], r[3], r[4], r[5], r[6], r[7]};
+        tc_st_32x32b_x8(t_lane + 64 + (uint32_t)(it & 7) * 8, r8);
+        tc_wait_st();
+      } else if (background == 2) {  // tcgen05.ld from columns the MMAs do not touch
+        tc_ld_32x32b_x32(t_lane + 64, r);
+        tc_wait_ld();
+        sink += r[lane & 31];
+      } else {                       // shared-memory loads (128-bit), away from the operands
+        const uint4 v = *reinterpret_cast<const uint4*>(smem + 49152 + ((tid * 16 + it * 8192) & 16383));
+        sink += v.x;
+      }
+    }
+    if (sink == 0x12345678u) out[0] = 0;
   }
   tc_fence_before();
   __syncthreads();
@@ -78,14 +105,15 @@ __global__ void mma_probe_kernel(long long* out, int count, int accumulators) {
 }
 
 template <int N>
-logos_status_t run_probe(bool a_in_tmem, long long* dev_out, int count, int accumulators, cudaStream_t st) {
+logos_status_t run_probe(bool a_in_tmem, long long* dev_out, int count, int accumulators, int background,
+                         cudaStream_t st) {
   const size_t smem = 66 * 1024;
   if (a_in_tmem) {
     LOGOS_CUDA_TRY(cudaFuncSetAttribute(mma_probe_kernel<N, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    mma_probe_kernel<N, true><<<1, 128, smem, st>>>(dev_out, count, accumulators);
+    mma_probe_kernel<N, true><<<1, 320, smem, st>>>(dev_out, count, accumulators, background);
   } else {
     LOGOS_CUDA_TRY(cudaFuncSetAttribute(mma_probe_kernel<N, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    mma_probe_kernel<N, false><<<1, 128, smem, st>>>(dev_out, count, accumulators);
+    mma_probe_kernel<N, false><<<1, 320, smem, st>>>(dev_out, count, accumulators, background);
   }
   return check_launch("mma_probe_kernel");
 }
@@ -96,10 +124,11 @@ logos_status_t run_probe(bool a_in_tmem, long long* dev_out, int count, int accu
 using namespace logos;
 
 extern "C" logos_status_t logos_tc_mma_probe(int32_t device, int32_t n, int32_t a_in_tmem, int32_t count,
-                                             int32_t accumulators, int64_t* issue_cycles_out,
+                                             int32_t accumulators, int32_t background, int64_t* issue_cycles_out,
                                              int64_t* complete_cycles_out) {
   return guarded([&]() -> logos_status_t {
     if (!issue_cycles_out || !complete_cycles_out) return fail(LOGOS_NULL_POINTER, "logos_tc_mma_probe: null out");
+    if (background < 0 || background > 3) return fail(LOGOS_OUT_OF_BOUNDS, "logos_tc_mma_probe: background must be 0..3");
     if (count < 1 || count > 4096) return fail(LOGOS_OUT_OF_BOUNDS, "logos_tc_mma_probe: count must be 1..4096");
     if (accumulators < 1 || (int64_t)accumulators * n > 384)
       return fail(LOGOS_OUT_OF_BOUNDS, "logos_tc_mma_probe: accumulators x N must fit 384 tensor-memory columns");
@@ -109,10 +138,10 @@ extern "C" logos_status_t logos_tc_mma_probe(int32_t device, int32_t n, int32_t 
     logos_status_t rc = LOGOS_OK;
     // the second launch is the one reported: the first warms the instruction cache
     for (int rep = 0; rep < 2 && rc == LOGOS_OK; ++rep) {
-      if (n == 32) rc = run_probe<32>(a_in_tmem != 0, dev, count, accumulators, nullptr);
-      else if (n == 64) rc = run_probe<64>(a_in_tmem != 0, dev, count, accumulators, nullptr);
-      else if (n == 128) rc = run_probe<128>(a_in_tmem != 0, dev, count, accumulators, nullptr);
-      else if (n == 256) rc = run_probe<256>(a_in_tmem != 0, dev, count, accumulators, nullptr);
+      if (n == 32) rc = run_probe<32>(a_in_tmem != 0, dev, count, accumulators, background, nullptr);
+      else if (n == 64) rc = run_probe<64>(a_in_tmem != 0, dev, count, accumulators, background, nullptr);
+      else if (n == 128) rc = run_probe<128>(a_in_tmem != 0, dev, count, accumulators, background, nullptr);
+      else if (n == 256) rc = run_probe<256>(a_in_tmem != 0, dev, count, accumulators, background, nullptr);
       else rc = fail(LOGOS_OUT_OF_BOUNDS, "logos_tc_mma_probe: N must be 32, 64, 128 or 256");
     }
     long long host[2] = {0, 0};

@@ -132,11 +132,12 @@ def q8Gemm(a, q, s, c, m, n, k, epilogue=EPI_NONE, aux=None, stream=None):
          _s(stream))
 
 
-def tcMmaProbe(n, a_in_tmem=True, count=512, accumulators=2, device=0):
-    """(issue cycles, cycles until completion is seen) of `count` back-to-back tcgen05.mma M=128 K=16 N=n."""
+def tcMmaProbe(n, a_in_tmem=True, count=512, accumulators=2, device=0, background=0):
+    """(issue cycles, cycles until completion is seen) of `count` back-to-back tcgen05.mma M=128 K=16 N=n;
+    background: 0 nothing else runs, 1 tcgen05.st, 2 tcgen05.ld, 3 shared-memory loads by eight other warps."""
     issue, done = C.c_int64(), C.c_int64()
     call("logos_tc_mma_probe", int(device), int(n), 1 if a_in_tmem else 0, int(count), int(accumulators),
-         C.byref(issue), C.byref(done))
+         int(background), C.byref(issue), C.byref(done))
     return issue.value, done.value
 
 
