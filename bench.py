@@ -184,9 +184,15 @@ def gemv_probe(llm, torch, device):
             llm.q8Gemv(qs[c], ss[c], x, y, n, k, stream=sp)
         stream.synchronize()
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            for i in range(launches):
-                llm.q8Gemv(qs[i % copies], ss[i % copies], x, y, n, k, stream=stream.cuda_stream)
+        # a chain of GEMVs as a batch-1 decode would issue them: the weights of a launch are
+        # fetched while the previous launch finishes (dependent-launch scope), x and y wait
+        prev = llm.dependentLaunchScope(True)
+        try:
+            with torch.cuda.graph(graph, stream=stream):
+                for i in range(launches):
+                    llm.q8Gemv(qs[i % copies], ss[i % copies], x, y, n, k, stream=stream.cuda_stream)
+        finally:
+            llm.dependentLaunchScope(prev)
         for _ in range(3):
             graph.replay()
         stream.synchronize()
@@ -203,7 +209,8 @@ def gemv_probe(llm, torch, device):
     for b in qs + ss + [x, y]:
         b.free()
     return {"shape": "4096x4096", "us_per_launch": us, "algorithmic_bytes": nbytes, "gbs": nbytes / us / 1e3,
-            "timing": "CUDA graph of %d launches over %d rotating weight copies (> L2)" % (launches, copies)}
+            "timing": "CUDA graph of %d dependent launches (dependent-launch scope: a launch fetches its weights while "
+                      "the previous one finishes) over %d rotating weight copies (> L2)" % (launches, copies)}
 
 
 def op_probe(args):

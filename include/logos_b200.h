@@ -263,6 +263,13 @@ LOGOS_API logos_status_t logos_llm_set_seq_len(logos_handle_t model, int64_t t);
 /* Device-side time of the last logos_llm_decode_steps call, milliseconds
  * (CUDA events on the model's stream), and kernels launched per step. */
 LOGOS_API logos_status_t logos_llm_last_timing(logos_handle_t model, double* ms_out, int64_t* launches_per_step_out);
+/* Dependent-launch scope (no counterpart in the reference).  While it is open for the calling
+ * thread (on != 0), the operators it launches may start before the previous kernel of their
+ * stream has finished: they fetch their WEIGHT operands (q, s) right away and wait for the
+ * previous kernel only before touching activations and outputs.  The caller promises that no
+ * operator launched inside the scope writes weights that another one inside it reads.
+ * prev_out (may be null) receives the previous setting. */
+LOGOS_API logos_status_t logos_dependent_launch_scope(int32_t on, int32_t* prev_out);
 /* Measurement aid (no counterpart in the reference): SM cycles one thread needs to issue
  * `count` back-to-back tcgen05.mma kind::f16 instructions (M = 128, K = 16, N = n in
  * {32, 64, 128, 256}; A operand in tensor memory when a_in_tmem != 0, else in shared memory)

@@ -94,6 +94,7 @@ _SIGNATURES = {
     "logos_llm_set_seq_len": (None, [H, I64]),
     "logos_llm_last_timing": (None, [H, C.POINTER(C.c_double), C.POINTER(I64)]),
     "logos_llm_tp_exchange": (None, [H, C.POINTER(C.c_int32)]),
+    "logos_dependent_launch_scope": (None, [C.c_int32, C.POINTER(C.c_int32)]),
     "logos_tc_mma_probe": (None, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(I64),
                            C.POINTER(I64)]),
     "logos_llm_profile_step": (None, [H, C.POINTER(C.c_double)]),

@@ -58,6 +58,10 @@ q8_gemv_kernel(const int8_t* __restrict__ q, const float* __restrict__ s, const 
   const int warp = tid >> 5;
   const int chunks = (int)(k >> 4);  // 16-element chunks per row
   const int64_t kb_per_row = k >> 5;
+  // Dependent launch: the weights are read before the previous kernel of the stream has
+  // finished (the caller's scope promises nothing in it writes them); x and y wait for it.
+  pdl_trigger();
+  bool waited = false;
   bool x_ready = !X_IN_SMEM;
   for (int64_t row0 = (int64_t)blockIdx.x * GEMV_WARPS; row0 < n; row0 += (int64_t)gridDim.x * GEMV_WARPS) {
     const int64_t row = row0 + warp;
@@ -79,11 +83,15 @@ q8_gemv_kernel(const int8_t* __restrict__ q, const float* __restrict__ s, const 
           sc[u] = 0.f;
         }
       }
+      if (!waited) {
+        pdl_wait();
+        waited = true;
+      }
       if (!x_ready) {
         const float4* xg = reinterpret_cast<const float4*>(x);
         for (int i = tid; i < chunks * 4; i += GEMV_WARPS * 32) {
           int c = i >> 2, j = i & 3;
-          xs4[xs4_index(c, j)] = xg[i];
+          xs4[xs4_index(c, j)] = __ldcg(xg + i);
         }
         __syncthreads();
         x_ready = true;
@@ -98,7 +106,7 @@ q8_gemv_kernel(const int8_t* __restrict__ q, const float* __restrict__ s, const 
             x2 = xs4[xs4_index(c, 2)]; x3 = xs4[xs4_index(c, 3)];
           } else {
             const float4* xg = reinterpret_cast<const float4*>(x) + c * 4;
-            x0 = __ldg(xg); x1 = __ldg(xg + 1); x2 = __ldg(xg + 2); x3 = __ldg(xg + 3);
+            x0 = __ldcg(xg); x1 = __ldcg(xg + 1); x2 = __ldcg(xg + 2); x3 = __ldcg(xg + 3);
           }
           float p = 0.f;
           p = dot4(w[u].x, x0, p);
@@ -133,9 +141,9 @@ logos_status_t launch_q8_gemv(const int8_t* q, const float* s, const float* x, f
   if (smem <= 96 * 1024) {
     if (smem > 48 * 1024)
       LOGOS_CUDA_TRY(cudaFuncSetAttribute(q8_gemv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-    q8_gemv_kernel<true><<<grid, GEMV_WARPS * 32, smem, st>>>(q, s, x, y, n, k);
+    LOGOS_CUDA_TRY(launch_kernel(q8_gemv_kernel<true>, dim3((unsigned)grid), dim3(GEMV_WARPS * 32), smem, st, q, s, x, y, n, k));
   } else {
-    q8_gemv_kernel<false><<<grid, GEMV_WARPS * 32, 0, st>>>(q, s, x, y, n, k);
+    LOGOS_CUDA_TRY(launch_kernel(q8_gemv_kernel<false>, dim3((unsigned)grid), dim3(GEMV_WARPS * 32), 0, st, q, s, x, y, n, k));
   }
   count_launch(LK_GEMV);
   return check_launch("q8_gemv_kernel");

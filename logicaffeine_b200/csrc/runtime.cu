@@ -57,7 +57,7 @@ logos_status_t cuda_fail(cudaError_t e, const char* what) {
 static std::atomic<int64_t> g_launches[LK_KINDS];
 void count_launch(int kind, int64_t n) { g_launches[kind].fetch_add(n, std::memory_order_relaxed); }
 
-static thread_local bool g_pdl = false;
+thread_local bool g_pdl = false;
 bool pdl_active() { return g_pdl; }
 PdlScope::PdlScope(bool on) : prev(g_pdl) { g_pdl = on; }
 PdlScope::~PdlScope() { g_pdl = prev; }
@@ -262,3 +262,13 @@ logos_status_t logos_dev_free(logos_handle_t h) {
 }
 
 }  // extern "C"
+
+// Opens (on != 0) or closes a dependent-launch scope for the calling thread's later operator
+// calls; returns the previous setting through prev_out when that is not null.
+extern "C" logos_status_t logos_dependent_launch_scope(int32_t on, int32_t* prev_out) {
+  return logos::guarded([&]() -> logos_status_t {
+    if (prev_out) *prev_out = logos::g_pdl ? 1 : 0;
+    logos::g_pdl = on != 0;
+    return LOGOS_OK;
+  });
+}

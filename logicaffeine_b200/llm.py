@@ -132,6 +132,13 @@ def q8Gemm(a, q, s, c, m, n, k, epilogue=EPI_NONE, aux=None, stream=None):
          _s(stream))
 
 
+def dependentLaunchScope(on):
+    """Open or close the calling thread's dependent-launch scope; returns the previous setting."""
+    prev = C.c_int32()
+    call("logos_dependent_launch_scope", 1 if on else 0, C.byref(prev))
+    return bool(prev.value)
+
+
 def tcMmaProbe(n, a_in_tmem=True, count=512, accumulators=2, device=0, background=0):
     """(issue cycles, cycles until completion is seen) of `count` back-to-back tcgen05.mma M=128 K=16 N=n;
     background: 0 nothing else runs, 1 tcgen05.st, 2 tcgen05.ld, 3 shared-memory loads by eight other warps."""

@@ -264,3 +264,31 @@ def test_gemm_with_one_token_equals_gemv(llm, oracle):
     y = llm.q8GemvHost(q, s, x)
     c = llm.q8GemmF32Host(x.reshape(1, k), q, s).reshape(n)
     assert rel_l2(c, y) < 2e-6
+
+
+def test_gemv_chain_in_a_dependent_launch_scope(llm, oracle):
+    """Launches inside the scope may overlap their predecessor's tail; results must not change."""
+    O = oracle
+    n, k = 512, 4096
+    q = O.synth_fill(O.I8, 0, 5, 31, 0, n * k).reshape(n, k)
+    s = O.synth_fill(O.F32, 1, 5, 32, 0, n * (k // 32), 1e-3, 1e-2).reshape(n, k // 32)
+    xs = [O.synth_fill(O.F32, 2, 5, 40 + i, 0, k, 0.0, 1.0) for i in range(3)]
+    dq, ds = llm.DeviceBuffer.from_host(q), llm.DeviceBuffer.from_host(s)
+    dx = [llm.DeviceBuffer.from_host(x) for x in xs]
+    dy = [llm.DeviceBuffer(n * 4) for _ in xs]
+    want = []
+    for x_, y_ in zip(dx, dy):
+        llm.q8Gemv(dq, ds, x_, y_, n, k)
+        want.append(y_.download(np.float32, (n,)))
+    prev = llm.dependentLaunchScope(True)
+    try:
+        for rep in range(4):
+            for x_, y_ in zip(dx, dy):
+                llm.q8Gemv(dq, ds, x_, y_, n, k)
+    finally:
+        assert llm.dependentLaunchScope(prev) is True
+    llm.devSync()
+    for y_, w in zip(dy, want):
+        assert np.array_equal(y_.download(np.float32, (n,)), w)
+    for b in [dq, ds] + dx + dy:
+        b.free()
