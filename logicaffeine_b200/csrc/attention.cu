@@ -481,6 +481,12 @@ logos_status_t launch_attn_t(const AttnArgs& a, cudaStream_t st) {
   ul = ((ul + ATT_TILE - 1) / ATT_TILE) * ATT_TILE;
   if (ul < 4 * ATT_TILE) ul = 4 * ATT_TILE;
   if (ul > 8 * ATT_TILE) ul = 8 * ATT_TILE;
+  {
+    // same number of units, equal lengths: a context just past a multiple of the unit length
+    // would otherwise add one almost empty unit per (sequence, KV head), a CTA that is all prologue
+    const int64_t units = (a.l_max + ul - 1) / ul;
+    ul = (((a.l_max + units - 1) / units + ATT_TILE - 1) / ATT_TILE) * ATT_TILE;
+  }
   int max_splits = (int)((a.l_max + ul - 1) / ul);
 
   void* scratch = nullptr;
