@@ -111,34 +111,43 @@ residual_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, 
     act_store(xn, row * hidden + i, __fmul_rn(__fmul_rn(row_cache[i], inv), g[i]));
 }
 
-// ---- residual + RMSNorm with the tensor-parallel all-reduce folded in (see ops.cuh)
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// ---- residual + RMSNorm with the tensor-parallel exchange folded in (see ops.cuh)
+// Data travels between ranks as 16-byte slots {word, epoch, word, epoch}, each written by ONE
+// 16-byte store: a reader that finds both epoch words equal to the current call's number has
+// the two data words of that same store, so no flag, fence or barrier separates the payload
+// from its arrival, and every transfer is a one-way push over NVLink.
+__device__ __forceinline__ void ll_store(uint4* p, uint32_t a, uint32_t b, uint32_t epoch) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(epoch), "r"(b), "r"(epoch)
+               : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-// Bounded: false when the flag did not reach `target` within about ten seconds of SM clock (a
-// peer is another process on another GPU: it may lag by a graph instantiation or a page-in).
-__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target) {
-  if ((int32_t)(ld_acquire_sys(p) - target) >= 0) return true;
-  const long long start = clock64();
-  for (;;) {
-#pragma unroll 1
-    for (int k = 0; k < 64; ++k)
-      if ((int32_t)(ld_acquire_sys(p) - target) >= 0) return true;
-    if (clock64() - start > 20000000000ll) return false;
+// Bounded poll (about ten seconds of SM clock: the sender is another process on another GPU and
+// may lag by a graph instantiation); false when the slot never carried this epoch.
+__device__ __forceinline__ bool ll_load(const uint4* p, uint32_t epoch, uint32_t* a, uint32_t* b) {
+  uint4 v;
+  long long start = 0;
+  for (int spin = 0;; ++spin) {
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    if (v.y == epoch && v.w == epoch) {
+      *a = v.x;
+      *b = v.z;
+      return true;
+    }
+    if ((spin & 255) == 255) {
+      if (start == 0) start = clock64();
+      else if (clock64() - start > 20000000000ll) return false;
+    }
   }
 }
 
-constexpr int TP_MAX_SRC = 64;  // degree x parts
-constexpr int TP_CLUSTER = 4;   // CTAs per row: at decode batch sizes a rank owns fewer rows than there are SMs
+constexpr int TP_CLUSTER = 4;  // CTAs per row: a rank owns fewer rows than there are SMs
 
-// A row is spread over a cluster of TP_CLUSTER CTAs (one float4 per thread where the row is
-// short enough), so that every peer load of a row is in flight at once; the slices' sums of
-// squares meet through distributed shared memory, summed in rank order by every CTA.
+// grid = rows x TP_CLUSTER, cluster = the TP_CLUSTER slices of one row.  Every rank runs it:
+//   A  each CTA sums its slice of this rank's split-K partials and pushes it to the row's owner;
+//   B  the owner's CTAs wait for every rank's slice, add them (rank order) to the residual
+//      stream, reduce the sum of squares across the cluster, normalise, and push the row's
+//      activation words to every rank;
+//   C  each CTA waits for its slice of the normalised row and unpacks it into this rank's planes.
+// No CTA waits before it has pushed, so the waits cannot form a cycle.
 __global__ void __launch_bounds__(512)
 tp_residual_rmsnorm_kernel(float* __restrict__ h, const TpFusedArgs t, int parts, int64_t part_stride,
                            const float* __restrict__ g, int64_t rows_own, int64_t hidden, float eps, int* status) {
@@ -147,96 +156,114 @@ tp_residual_rmsnorm_kernel(float* __restrict__ h, const TpFusedArgs t, int parts
   __shared__ float red[32];
   __shared__ float slice_ss;
   __shared__ uint32_t epoch_s;
-  __shared__ int last_s;
-  __shared__ const float* src[TP_MAX_SRC];
   extern __shared__ float4 row_cache4[];  // this CTA's slice of the row
   const int tid = threadIdx.x;
   pdl_wait();  // this rank's own GEMM has completed: its partials are in this GPU's memory
   pdl_trigger();
-  uint32_t* my = t.flags[t.rank];
-  if (tid == 0) epoch_s = ld_acquire_sys(my + 16) + 1u;
-  const int nsrc = t.degree * parts;
-  if (tid < nsrc) src[tid] = t.partials[tid / parts] + (int64_t)(tid % parts) * part_stride;  // rank-major, then split
+  if (tid == 0) epoch_s = *reinterpret_cast<volatile uint32_t*>(t.flags + 16) + 1u;
   __syncthreads();
   const uint32_t e = epoch_s;
-  // ---- barrier 1: every rank's partials are complete.  One CTA announces this rank to all
-  // (itself included); every CTA polls its own rank's words, which are local memory.
-  if (blockIdx.x == 0 && tid < t.degree) st_release_sys(t.flags[tid] + t.rank, e);
-  if (tid < t.degree && !wait_flag_ge(my + tid, e)) atomicExch(status, 3010);
-  __syncthreads();
-
   const unsigned crank = cluster.block_rank();
-  const int64_t row = (int64_t)t.rank * rows_own + blockIdx.x / TP_CLUSTER;
-  const int64_t per = (hidden >> 2) / TP_CLUSTER;  // float4 per CTA
-  const int64_t off4 = row * (hidden >> 2) + (int64_t)crank * per;  // this slice, in float4 units from a buffer's base
-  float4* hr4 = reinterpret_cast<float4*>(h) + off4;
-  float ss = 0.f;
-  for (int64_t i = tid; i < per; i += blockDim.x) {
-    float4 v = __ldcg(hr4 + i);
-    // peers' buffers are read past L1 (ld.global.cg): the lines are rewritten every call.
-    // Eight loads are issued before their sums are taken, so a row costs few NVLink round trips.
-    for (int q0 = 0; q0 < nsrc; q0 += 8) {
-      float4 d[8];
+  const int64_t row = blockIdx.x / TP_CLUSTER;
+  const int owner = (int)(row / rows_own);
+  const int64_t row_local = row - (int64_t)owner * rows_own;
+  const bool mine = owner == t.rank;
+  const int64_t n4 = hidden >> 2, per = n4 / TP_CLUSTER;  // float4 per row, per CTA
+  const int64_t slots_per_row = hidden >> 1;               // 16-byte slots per row (two words each)
+  bool ok = true;
+
+  // ---- A: push this rank's contribution to the row's owner
+  {
+    uint4* inbox = t.inbox_part[owner] + ((int64_t)t.rank * rows_own + row_local) * slots_per_row;
+    for (int64_t i = tid; i < per; i += blockDim.x) {
+      const int64_t i4 = (int64_t)crank * per + i;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int p = 0; p < parts; ++p) {
+        const float4 d = __ldcg(reinterpret_cast<const float4*>(t.partials + (int64_t)p * part_stride + row * hidden) + i4);
+        v.x = __fadd_rn(v.x, d.x); v.y = __fadd_rn(v.y, d.y); v.z = __fadd_rn(v.z, d.z); v.w = __fadd_rn(v.w, d.w);
+      }
+      ll_store(inbox + 2 * i4, __float_as_uint(v.x), __float_as_uint(v.y), e);
+      ll_store(inbox + 2 * i4 + 1, __float_as_uint(v.z), __float_as_uint(v.w), e);
+    }
+  }
+
+  // ---- B: the owner folds, normalises and publishes
+  if (mine) {
+    float4* hr4 = reinterpret_cast<float4*>(h) + row * n4;
+    float ss = 0.f;
+    for (int64_t i = tid; i < per; i += blockDim.x) {
+      const int64_t i4 = (int64_t)crank * per + i;
+      float4 v = __ldcg(hr4 + i4);
+      for (int src = 0; src < t.degree; ++src) {
+        const uint4* in = t.inbox_part[t.rank] + ((int64_t)src * rows_own + row_local) * slots_per_row + 2 * i4;
+        uint32_t a0, a1, a2, a3;
+        if (!ll_load(in, e, &a0, &a1) || !ll_load(in + 1, e, &a2, &a3)) { ok = false; a0 = a1 = a2 = a3 = 0u; }
+        v.x = __fadd_rn(v.x, __uint_as_float(a0)); v.y = __fadd_rn(v.y, __uint_as_float(a1));
+        v.z = __fadd_rn(v.z, __uint_as_float(a2)); v.w = __fadd_rn(v.w, __uint_as_float(a3));
+      }
+      hr4[i4] = v;
+      row_cache4[i] = v;
+      ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+    ss = block_sum(ss, red);
+    if (tid == 0) slice_ss = ss;
+    cluster.sync();
+    float total = 0.f;
+    for (unsigned r = 0; r < TP_CLUSTER; ++r) total += *cluster.map_shared_rank(&slice_ss, r);
+    const float inv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)hidden), eps)));
+    const float4* g4 = reinterpret_cast<const float4*>(g);
+    for (int64_t i = tid; i < per; i += blockDim.x) {
+      const int64_t i4 = (int64_t)crank * per + i;
+      const float4 v = row_cache4[i], gg = g4[i4];
+      const float o[4] = {__fmul_rn(__fmul_rn(v.x, inv), gg.x), __fmul_rn(__fmul_rn(v.y, inv), gg.y),
+                          __fmul_rn(__fmul_rn(v.z, inv), gg.z), __fmul_rn(__fmul_rn(v.w, inv), gg.w)};
+      uint32_t pk[4];  // low half: hi plane, high half: lo plane
 #pragma unroll
-      for (int u = 0; u < 8; ++u)
-        d[u] = (q0 + u < nsrc) ? __ldcg(reinterpret_cast<const float4*>(src[q0 + u]) + off4 + i)
-                               : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        if (q0 + u < nsrc) {
-          v.x = __fadd_rn(v.x, d[u].x); v.y = __fadd_rn(v.y, d[u].y);
-          v.z = __fadd_rn(v.z, d[u].z); v.w = __fadd_rn(v.w, d[u].w);
-        }
+      for (int k = 0; k < 4; ++k) {
+        float x = o[k];
+        if (t.act_mode == LOGOS_BF16) x = __bfloat162float(__float2bfloat16_rn(x));
+        x = act_clamp(x);
+        const __half hh = __float2half_rn(x);
+        const __half ll = __float2half_rn((x - __half2float(hh)) * 2048.f);
+        pk[k] = (uint32_t)__half_as_ushort(hh) | ((uint32_t)__half_as_ushort(ll) << 16);
+      }
+      for (int r = 0; r < t.degree; ++r) {
+        uint4* out = t.inbox_xn[r] + row * slots_per_row + 2 * i4;
+        ll_store(out, pk[0], pk[1], e);
+        ll_store(out + 1, pk[2], pk[3], e);
       }
     }
-    hr4[i] = v;
-    row_cache4[i] = v;
-    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    cluster.sync();  // no CTA leaves while a peer of its cluster may still read its slice_ss
   }
-  ss = block_sum(ss, red);
-  if (tid == 0) slice_ss = ss;
-  cluster.sync();
-  float total = 0.f;
-  for (unsigned r = 0; r < TP_CLUSTER; ++r) total += *cluster.map_shared_rank(&slice_ss, r);
-  const float inv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)hidden), eps)));
-  const float4* g4 = reinterpret_cast<const float4*>(g) + (int64_t)crank * per;
-  for (int64_t i = tid; i < per; i += blockDim.x) {
-    const float4 v = row_cache4[i], gg = g4[i];
-    const float o[4] = {__fmul_rn(__fmul_rn(v.x, inv), gg.x), __fmul_rn(__fmul_rn(v.y, inv), gg.y),
-                        __fmul_rn(__fmul_rn(v.z, inv), gg.z), __fmul_rn(__fmul_rn(v.w, inv), gg.w)};
-    __half hh[4], ll[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      float x = o[k];
-      if (t.act_mode == LOGOS_BF16) x = __bfloat162float(__float2bfloat16_rn(x));
-      x = act_clamp(x);
-      hh[k] = __float2half_rn(x);
-      ll[k] = __float2half_rn((x - __half2float(hh[k])) * 2048.f);
-    }
-    const uint2 hp = *reinterpret_cast<const uint2*>(hh), lp = *reinterpret_cast<const uint2*>(ll);
-    for (int r = 0; r < t.degree; ++r) {
-      reinterpret_cast<uint2*>(t.xn_hi[r])[off4 + i] = hp;
-      if (t.xn_lo[r]) reinterpret_cast<uint2*>(t.xn_lo[r])[off4 + i] = lp;
+
+  // ---- C: unpack this CTA's slice of the normalised row into the plain planes
+  {
+    const uint4* in = t.inbox_xn[t.rank] + row * slots_per_row;
+    for (int64_t i = tid; i < per; i += blockDim.x) {
+      const int64_t i4 = (int64_t)crank * per + i;
+      uint32_t pk[4];
+      if (!ll_load(in + 2 * i4, e, &pk[0], &pk[1]) || !ll_load(in + 2 * i4 + 1, e, &pk[2], &pk[3])) {
+        ok = false;
+        pk[0] = pk[1] = pk[2] = pk[3] = 0u;
+      }
+      uint2 hi2, lo2;
+      hi2.x = (pk[0] & 0xffffu) | (pk[1] << 16);
+      hi2.y = (pk[2] & 0xffffu) | (pk[3] << 16);
+      lo2.x = (pk[0] >> 16) | (pk[1] & 0xffff0000u);
+      lo2.y = (pk[2] >> 16) | (pk[3] & 0xffff0000u);
+      reinterpret_cast<uint2*>(t.xn_hi + row * hidden)[i4] = hi2;
+      if (t.xn_lo) reinterpret_cast<uint2*>(t.xn_lo + row * hidden)[i4] = lo2;
     }
   }
-  // ---- barrier 2: the last CTA of this rank to finish tells every rank that this rank's rows
-  // have been delivered, and holds the kernel until every peer's rows are here.
-  cluster.sync();  // also: no CTA leaves while a peer of its cluster may still read its slice_ss
-  if (tid == 0) {
-    __threadfence_system();
-    const uint32_t ticket = atomicAdd(my + 17, 1u);
-    last_s = (ticket == gridDim.x - 1) ? 1 : 0;
-    if (last_s) {
-      __threadfence_system();
-      my[17] = 0u;
-    }
-  }
+  if (!ok) atomicExch(status, 3030);
+  // the last CTA to finish advances this rank's epoch
   __syncthreads();
-  if (last_s) {
-    if (tid < t.degree) st_release_sys(t.flags[tid] + 8 + t.rank, e);
-    if (tid < t.degree && !wait_flag_ge(my + 8 + tid, e)) atomicExch(status, 3020);
-    __syncthreads();
-    if (tid == 0) st_release_sys(my + 16, e);
+  if (tid == 0) {
+    const uint32_t ticket = atomicAdd(t.flags + 17, 1u);
+    if (ticket == gridDim.x - 1) {
+      t.flags[17] = 0u;
+      *reinterpret_cast<volatile uint32_t*>(t.flags + 16) = e;
+    }
   }
 }
 
@@ -357,10 +384,13 @@ logos_status_t launch_residual_rmsnorm(float* h, const float* delta, int parts, 
 logos_status_t launch_tp_residual_rmsnorm(float* h, const TpFusedArgs& t, int parts, int64_t part_stride, const float* g,
                                           int64_t rows, int64_t hidden, float eps, int device, cudaStream_t st) {
   if (rows == 0) return LOGOS_OK;
-  if (t.degree < 2 || t.degree > 8 || rows % t.degree || hidden % (4 * TP_CLUSTER) || parts < 1 ||
-      t.degree * parts > TP_MAX_SRC)
+  if (t.degree < 2 || t.degree > 8 || rows % t.degree || hidden % (4 * TP_CLUSTER) || parts < 1)
     return fail(LOGOS_ERROR, "tp_residual_rmsnorm: unsupported shape (rows %lld, hidden %lld, degree %d, parts %d)",
                 (long long)rows, (long long)hidden, t.degree, parts);
+  // every CTA must be resident at once: CTAs that wait for a peer's push must not keep the
+  // CTAs that peers wait for off the SMs
+  if (rows * TP_CLUSTER > 2 * (int64_t)sm_count(device))
+    return fail(LOGOS_ERROR, "tp_residual_rmsnorm: %lld rows are more than the grid can hold resident", (long long)rows);
   int* status = kernel_status_ptr(device);
   if (!status) return fail(LOGOS_ERROR, "tp_residual_rmsnorm: no kernel status word");
   const int64_t per = (hidden >> 2) / TP_CLUSTER;
@@ -368,7 +398,7 @@ logos_status_t launch_tp_residual_rmsnorm(float* h, const TpFusedArgs& t, int pa
   int threads = (int)(((per + 31) / 32) * 32);
   if (threads > 512) threads = 512;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(rows_own * TP_CLUSTER));
+  cfg.gridDim = dim3((unsigned)(rows * TP_CLUSTER));
   cfg.blockDim = dim3((unsigned)threads);
   cfg.dynamicSmemBytes = sizeof(float4) * (size_t)per;
   cfg.stream = st;

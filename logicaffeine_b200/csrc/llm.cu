@@ -223,16 +223,20 @@ logos_status_t build(Model* m, const void* nccl_id) {
     if (c.act_dtype == LOGOS_F32) LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&a->lo), elems * 2));
     return LOGOS_OK;
   };
-  // The block the ranks of a TP group share: [partials][xn hi][xn lo][flag words], 256-byte aligned.
+  LOGOS_TRY(planes(&m->xn, B * H));
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->partials), (int64_t)m->max_splits * B * H * 4));
+  // The block the ranks of a TP group map from each other: the two inboxes of the folded
+  // exchange ([partial rows of the rows this rank owns, from every rank] and [normalised rows],
+  // 16-byte slots of two words each) and the flag words, 256-byte aligned.
   {
     auto up = [](int64_t v) { return (v + 255) / 256 * 256; };
-    const int64_t part_bytes = up((int64_t)m->max_splits * B * H * 4), plane_bytes = up(B * H * 2);
-    const bool two = c.act_dtype == LOGOS_F32;
-    const int64_t off_hi = part_bytes, off_lo = off_hi + plane_bytes, off_flags = off_lo + (two ? plane_bytes : 0);
+    const int64_t inbox_bytes = up(B * H * 8);  // both inboxes: rows x hidden / 2 slots of 16 bytes
+    const int64_t off_xn = inbox_bytes, off_flags = 2 * inbox_bytes;
     const int64_t total = off_flags + up(TP_FLAG_WORDS * 4);
     const char* e = getenv("LOGOS_B200_TP_FUSED");
     // opt-in until it has been measured on 2 to 8 GPUs
-    const bool want = g > 1 && g <= 8 && B % g == 0 && H % 16 == 0 && g * m->max_splits <= 64 && (e && e[0] == '1');
+    const bool want = g > 1 && g <= 8 && B % g == 0 && H % 16 == 0 && B * 4 <= 2 * (int64_t)sm_count(m->device) &&
+                      (e && e[0] == '1');
     if (want) LOGOS_TRY(tp_symm_alloc(&m->tp, (size_t)total, &m->symm, m->stream));
     m->tp_fused = want && m->symm.ok;
     if (m->tp_fused) {
@@ -241,23 +245,18 @@ logos_status_t build(Model* m, const void* nccl_id) {
       m->tpf.act_mode = c.act_dtype;
       for (int k = 0; k < g; ++k) {
         char* base = static_cast<char*>(m->symm.base[k]);
-        m->tpf.partials[k] = reinterpret_cast<const float*>(base);
-        m->tpf.xn_hi[k] = reinterpret_cast<__half*>(base + off_hi);
-        m->tpf.xn_lo[k] = two ? reinterpret_cast<__half*>(base + off_lo) : nullptr;
-        m->tpf.flags[k] = reinterpret_cast<uint32_t*>(base + off_flags);
+        m->tpf.inbox_part[k] = reinterpret_cast<uint4*>(base);
+        m->tpf.inbox_xn[k] = reinterpret_cast<uint4*>(base + off_xn);
       }
-      char* mine = static_cast<char*>(m->symm.base[r]);
-      m->partials = reinterpret_cast<float*>(mine);
-      m->xn.mode = c.act_dtype;
-      m->xn.hi = reinterpret_cast<__half*>(mine + off_hi);
-      m->xn.lo = two ? reinterpret_cast<__half*>(mine + off_lo) : nullptr;
+      m->tpf.flags = reinterpret_cast<uint32_t*>(static_cast<char*>(m->symm.base[r]) + off_flags);
+      m->tpf.partials = m->partials;
+      m->tpf.xn_hi = m->xn.hi;
+      m->tpf.xn_lo = m->xn.lo;
     }
   }
-  if (!m->tp_fused) LOGOS_TRY(planes(&m->xn, B * H));
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->qkv), B * m->nqkv * 4));
   LOGOS_TRY(planes(&m->att, B * m->nq));
   LOGOS_TRY(planes(&m->ffn, B * m->f_local));
-  if (!m->tp_fused) LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->partials), (int64_t)m->max_splits * B * H * 4));
   {
     // qkv and gate/up split K too when their row tiles alone would leave most SMs idle (the
     // per-rank shapes of a TP group): room for the larger of the two sets of partials

@@ -110,18 +110,21 @@ logos_status_t launch_residual_rmsnorm(float* h, const float* delta, int parts, 
                                        cudaStream_t st);
 // The same operator for a tensor-parallel group whose ranks can address each other's memory:
 // the all-reduce of the row-parallel GEMM's partial sums is folded in.  Rank r owns rows
-// [r * rows / degree, (r + 1) * rows / degree): it adds every rank's partials for its rows to
-// its slice of the residual stream (reading the peers' buffers over NVLink), normalises them,
-// and writes the resulting activation rows into every rank's plane buffers; two flag
-// barriers (peers' partials complete; everybody's rows delivered) frame the kernel.  Only the
-// owner keeps a row of h up to date.
-constexpr int TP_FLAG_WORDS = 64;  // u32 per rank: [0..7] stage 1, [8..15] stage 2, [16] epoch, [17] CTA ticket
+// [r * rows / degree, (r + 1) * rows / degree): every rank pushes its partial sums of a row to
+// the row's owner, the owner adds them (rank order) to its slice of the residual stream,
+// normalises and pushes the resulting activation row to every rank, and every rank unpacks
+// it into its own plane buffers.  The payload travels in 16-byte slots that carry the call's
+// number (see elementwise.cu), so there is no barrier and no flag besides the data itself.
+// Only the owner keeps a row of h up to date.
+constexpr int TP_FLAG_WORDS = 64;  // u32 per rank: [16] call number (epoch), [17] CTA ticket
 struct TpFusedArgs {
   int degree = 1, rank = 0;
-  const float* partials[8] = {};  // each rank's [parts][rows][hidden] f32
-  __half* xn_hi[8] = {};          // each rank's planes [rows][hidden]
-  __half* xn_lo[8] = {};          // null in the one-plane modes
-  uint32_t* flags[8] = {};        // each rank's TP_FLAG_WORDS words, zero at creation
+  const float* partials = nullptr;  // this rank's [parts][rows][hidden] f32
+  uint4* inbox_part[8] = {};        // each rank's inbox of partial rows: [source rank][rows / degree][hidden / 2] slots
+  uint4* inbox_xn[8] = {};          // each rank's inbox of normalised rows: [rows][hidden / 2] slots
+  __half* xn_hi = nullptr;          // this rank's planes [rows][hidden]
+  __half* xn_lo = nullptr;          // null in the one-plane modes
+  uint32_t* flags = nullptr;        // this rank's TP_FLAG_WORDS words, zero at creation
   int act_mode = LOGOS_F32;
 };
 logos_status_t launch_tp_residual_rmsnorm(float* h, const TpFusedArgs& t, int parts, int64_t part_stride, const float* g,
