@@ -1,7 +1,7 @@
 """Tensor parallelism on two GPUs of one node: every rank (its own process, as under
 torchrun) builds its shard of the seeded weights, the only exchange is the sum of the partial
 products after o_proj and down_proj - folded into the residual + RMSNorm kernel over
-peer-mapped memory, or as an NCCL all-reduce (LOGOS_B200_TP_FUSED=0) - and the greedy tokens
+peer-mapped memory (the default), or as an NCCL all-reduce (LOGOS_B200_TP_FUSED=0) - and the greedy tokens
 must equal the oracle's (unsharded) ones.  Skipped when fewer than two GPUs are visible."""
 import os
 import subprocess
@@ -15,8 +15,16 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
+def _env(fused):
+    env = dict(os.environ)
+    env.pop("LOGOS_B200_TP_FUSED", None)
+    if fused != "default":
+        env["LOGOS_B200_TP_FUSED"] = fused
+    return env
+
+
 @pytest.mark.timeout(300)
-@pytest.mark.parametrize("fused", ["1", "0"])
+@pytest.mark.parametrize("fused", ["default", "0"])
 def test_tp2_tokens_match_the_oracle(llm, oracle, tmp_path, fused):
     if llm.deviceCount() < 2:
         pytest.skip("needs two GPUs")
@@ -26,7 +34,7 @@ def test_tp2_tokens_match_the_oracle(llm, oracle, tmp_path, fused):
     steps, t = 16, 7
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), str(r), "2", str(tmp_path),
                                str(steps), str(t)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
-                              env=dict(os.environ, LOGOS_B200_TP_FUSED=fused))
+                              env=_env(fused))
              for r in range(2)]
     outs = []
     try:
@@ -43,7 +51,7 @@ def test_tp2_tokens_match_the_oracle(llm, oracle, tmp_path, fused):
     ref.prefill(toks)
     want = np.array([ref.decode_step().copy() for _ in range(steps)])
     r0, r1 = (np.load(tmp_path / ("r%d.npz" % i)) for i in range(2))
-    assert int(r0["exchange"]) == int(r1["exchange"]) == (2 if fused == "1" else 1)   # no silent fall-back
+    assert int(r0["exchange"]) == int(r1["exchange"]) == (1 if fused == "0" else 2)   # no silent fall-back
     assert np.array_equal(r0["tokens"], want) and np.array_equal(r1["tokens"], want)
     assert np.array_equal(r0["logits"], r1["logits"])           # replicated lm_head on identical inputs
     # each rank holds its own KV heads: rank r's head 0 is the oracle's head r
