@@ -46,6 +46,8 @@ struct AttnParams {
   const float*  k_new_f32;
   const float*  v_new_f32;
   int64_t       kv_ld;
+  int           f32_parts;        // split-K partial copies of the f32 inputs, summed while staging
+  int64_t       f32_part_stride;
   int           fused;
   __half*       k_cache;
   __half*       v_cache;
@@ -138,6 +140,10 @@ gqa_decode_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           const float* qp = p.q_f32 + (int64_t)b * p.q_ld + (int64_t)hq * D;
           x1 = __ldcg(qp + e);
           x2 = __ldcg(qp + e + half_d);
+          for (int sp = 1; sp < p.f32_parts; ++sp) {
+            x1 = __fadd_rn(x1, __ldcg(qp + sp * p.f32_part_stride + e));
+            x2 = __fadd_rn(x2, __ldcg(qp + sp * p.f32_part_stride + e + half_d));
+          }
         }
         if (p.rotate_q) {
           float c = tab[2 * e], s = tab[2 * e + 1];
@@ -165,6 +171,11 @@ gqa_decode_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           const float* vp = p.v_new_f32 + (int64_t)b * p.kv_ld + (int64_t)kvh * D;
           k1 = __ldcg(kp + e); k2 = __ldcg(kp + e + half_d);
           v1 = __ldcg(vp + e); v2 = __ldcg(vp + e + half_d);
+          for (int sp = 1; sp < p.f32_parts; ++sp) {
+            const int64_t o = sp * p.f32_part_stride;
+            k1 = __fadd_rn(k1, __ldcg(kp + o + e)); k2 = __fadd_rn(k2, __ldcg(kp + o + e + half_d));
+            v1 = __fadd_rn(v1, __ldcg(vp + o + e)); v2 = __fadd_rn(v2, __ldcg(vp + o + e + half_d));
+          }
         }
         float c = tabn[2 * e], s = tabn[2 * e + 1];
         __half r1 = __float2half_rn(__fsub_rn(__fmul_rn(k1, c), __fmul_rn(k2, s)));
@@ -506,6 +517,8 @@ logos_status_t launch_attn_t(const AttnArgs& a, cudaStream_t st) {
   p.q_f16 = a.q_f16; p.q_f32 = a.q_f32; p.q_ld = a.q_ld; p.rotate_q = a.rotate_q;
   p.k_new_f16 = a.k_new_f16; p.v_new_f16 = a.v_new_f16; p.k_new_f32 = a.k_new_f32; p.v_new_f32 = a.v_new_f32;
   p.kv_ld = a.kv_ld;
+  p.f32_parts = a.f32_parts > 1 ? a.f32_parts : 1;
+  p.f32_part_stride = a.f32_part_stride;
   p.fused = (a.k_new_f16 || a.k_new_f32) ? 1 : 0;
   p.k_cache = a.k_cache; p.v_cache = a.v_cache; p.rope = a.rope; p.seq_len = a.seq_len;
   p.part_o = reinterpret_cast<float*>(scratch);

@@ -301,8 +301,11 @@ __global__ void bump_len_kernel(int32_t* seq_len, int32_t* step_counter, int b, 
 
 // GEMM with its own output and epilogue (qkv, gate/up, lm_head): K is split, and a small kernel
 // folds the partials and applies the epilogue, where the cost model prefers that.
-logos_status_t gemm_direct(Model* m, const GemmArgs& g) {
+// unfolded_splits (may be null): the caller's consumer folds the partials itself; it receives the
+// split count (1 = the output is in g.c as usual) and the fold kernel is not launched.
+logos_status_t gemm_direct(Model* m, const GemmArgs& g, int* unfolded_splits = nullptr) {
   ProfScope ps(m, PROF_GEMM);
+  if (unfolded_splits) *unfolded_splits = 1;
   int splits = gemm_pick_splits(g.m, g.n, g.k, m->device);
   if (splits > 1 && (int64_t)splits * g.m * g.n <= m->dpart_floats && gemm_tc_applicable(g)) {
     GemmArgs gp = g;
@@ -313,9 +316,14 @@ logos_status_t gemm_direct(Model* m, const GemmArgs& g) {
     gp.c_dtype = LOGOS_F32;
     gp.aux = nullptr;
     LOGOS_TRY(launch_q8_gemm(gp, m->stream));
+    m->launch_counter += 1;
+    if (unfolded_splits && g.epilogue == EPI_NONE && g.ldc == g.n) {
+      *unfolded_splits = splits;
+      return LOGOS_OK;
+    }
     LOGOS_TRY(launch_splitk_reduce(m->dpart, splits, g.c, g.c_dtype, g.c_act, g.ldc, g.aux, g.m, g.n, g.epilogue,
                                    m->stream));
-    m->launch_counter += 2;
+    m->launch_counter += 1;
     return LOGOS_OK;
   }
   LOGOS_TRY(launch_q8_gemm(g, m->stream));
@@ -406,6 +414,7 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
   int parts = 0;
   for (int64_t l = 0; l < c.layers; ++l) {
     Layer& L = m->layers[(size_t)l];
+    int qkv_parts = 1;
     LOGOS_TRY(norm_step(m, parts));
     m->launch_counter += 1;
     {
@@ -415,14 +424,16 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
       g.c = m->qkv; g.c_dtype = LOGOS_F32; g.ldc = m->nqkv;
       g.m = B; g.n = m->nqkv; g.k = H;
       g.device = m->device;
-      LOGOS_TRY(gemm_direct(m, g));
+      LOGOS_TRY(gemm_direct(m, g, &qkv_parts));  // split-K partials, if any, are folded by the attention kernel
     }
     LOGOS_TRY(debug_check(m, "qkv gemm", l));
     {
       ProfScope ps(m, PROF_ATTN);
       AttnArgs a;
-      a.q_f32 = m->qkv; a.q_ld = m->nqkv; a.rotate_q = 1;
-      a.k_new_f32 = m->qkv + m->nq; a.v_new_f32 = m->qkv + m->nq + m->nkv; a.kv_ld = m->nqkv;
+      const float* qkv_src = qkv_parts > 1 ? m->dpart : m->qkv;
+      a.q_f32 = qkv_src; a.q_ld = m->nqkv; a.rotate_q = 1;
+      a.k_new_f32 = qkv_src + m->nq; a.v_new_f32 = qkv_src + m->nq + m->nkv; a.kv_ld = m->nqkv;
+      a.f32_parts = qkv_parts; a.f32_part_stride = B * m->nqkv;
       a.k_cache = L.kc; a.v_cache = L.vc; a.rope = m->rope; a.seq_len = m->seq_len;
       a.bump_seq_len = 0;
       a.o_dtype = LOGOS_ACT_PLANES; a.o_act = m->att;

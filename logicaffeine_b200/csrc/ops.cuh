@@ -72,6 +72,11 @@ struct AttnArgs {
   const float*  k_new_f32 = nullptr; // f32 rows, stride kv_ld per sequence
   const float*  v_new_f32 = nullptr;
   int64_t       kv_ld = 0;
+  // The f32 inputs (q_f32, k_new_f32, v_new_f32) may be split-K partial sums: f32_parts copies,
+  // f32_part_stride floats apart, added in ascending order where the kernel stages them (the
+  // fold the GEMM's reduce kernel would have done, without its launch).
+  int           f32_parts = 1;
+  int64_t       f32_part_stride = 0;
   __half*       k_cache = nullptr;   // [B][Hkv][Lmax][D]
   __half*       v_cache = nullptr;
   const float*  rope = nullptr;      // [Lmax][D/2][2]
