@@ -95,3 +95,89 @@ def test_bench_byte_model_matches_the_survey_figures():
     w0 = dict(bench.WORKLOADS["qwen0.5b-b16"])
     layer = (14 * 64 + 2 * 2 * 64) * 896 + 896 * 14 * 64 + 3 * 4864 * 896
     assert bench.gemm_weight_bytes(w0, 1) == (24 * layer + 151936 * 896) * 1.125
+
+
+def _slot_words(values_u32, epoch):
+    """The wire format of the folded exchange: 16-byte slots {word, epoch, word, epoch}."""
+    v = np.asarray(values_u32, np.uint32).reshape(-1, 2)
+    out = np.empty((v.shape[0], 4), np.uint32)
+    out[:, 0], out[:, 2] = v[:, 0], v[:, 1]
+    out[:, 1] = out[:, 3] = epoch
+    return out
+
+
+def _exchange_worker(rank, world, port, out_dir):
+    """The folded exchange on CPU ranks: push partial rows to the row's owner, the owner folds
+    them in rank order into its slice of the residual stream and normalises, pushes the packed
+    activation words to everybody, everybody unpacks.  send/recv stand in for the NVLink pushes."""
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+    from oracle import oracle as O
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    B, H, eps, epoch = 4, 64, 1e-6, 7
+    rows_own = B // world
+    h = O.synth_fill(O.F32, 2, 3, 700, 0, B * H, 0.0, 1.0).reshape(B, H)            # same on every rank
+    part = O.synth_fill(O.F32, 2, 3, 710 + rank, 0, B * H, 0.0, 0.1).reshape(B, H)   # this rank's partial sums
+    # A: push to owners (slot format), including to oneself
+    inbox = np.zeros((world, rows_own, H // 2, 4), np.uint32)
+    pending = []
+    for owner in range(world):
+        rows = slice(owner * rows_own, (owner + 1) * rows_own)
+        msg = _slot_words(part[rows].view(np.uint32), epoch).reshape(rows_own, H // 2, 4)
+        if owner == rank:
+            inbox[rank] = msg
+        else:
+            pending.append(dist.isend(torch.from_numpy(msg.view(np.int32).copy()), owner))
+    for src in range(world):
+        if src != rank:
+            t = torch.zeros(rows_own, H // 2, 4, dtype=torch.int32)
+            dist.recv(t, src)
+            inbox[src] = t.numpy().view(np.uint32)
+    for w in pending:
+        w.wait()
+    assert np.all(inbox[:, :, :, 1] == epoch) and np.all(inbox[:, :, :, 3] == epoch)
+    # B: the owner folds in rank order, normalises, packs hi | lo << 16
+    mine = slice(rank * rows_own, (rank + 1) * rows_own)
+    hv = h[mine].copy()
+    for src in range(world):
+        vals = inbox[src][:, :, [0, 2]].reshape(rows_own, H).view(np.float32)
+        hv = (hv + vals).astype(np.float32)
+    inv = (np.float32(1.0) / np.sqrt((np.sum(hv.astype(np.float64) ** 2, 1) / H + eps))).astype(np.float32)
+    xn = (hv * inv[:, None]).astype(np.float32)
+    hi = xn.astype(np.float16)
+    lo = ((xn - hi.astype(np.float32)) * np.float32(2048.0)).astype(np.float16)
+    packed = hi.view(np.uint16).astype(np.uint32) | (lo.view(np.uint16).astype(np.uint32) << 16)
+    msg = torch.from_numpy(_slot_words(packed, epoch).view(np.int32).copy())
+    rows_words = [torch.zeros_like(msg) for _ in range(world)]
+    dist.all_gather(rows_words, msg)
+    # C: unpack every owner's rows into plain planes
+    words = np.concatenate([w.numpy().view(np.uint32)[:, [0, 2]].reshape(rows_own, H) for w in rows_words], 0)
+    hi_all = (words & 0xffff).astype(np.uint16).view(np.float16)
+    lo_all = (words >> 16).astype(np.uint16).view(np.float16)
+    np.savez(os.path.join(out_dir, "x%d.npz" % rank), hi=hi_all, lo=lo_all, h_own=hv, part=part)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_folded_exchange_scheme_equals_allreduce_then_norm(oracle, tmp_path):
+    import torch.multiprocessing as mp
+    O = oracle
+    world, B, H, eps = 2, 4, 64, 1e-6
+    mp.spawn(_exchange_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    r = [np.load(tmp_path / ("x%d.npz" % i)) for i in range(world)]
+    h = O.synth_fill(O.F32, 2, 3, 700, 0, B * H, 0.0, 1.0).reshape(B, H)
+    total = h.copy()
+    for i in range(world):
+        total = (total + r[i]["part"]).astype(np.float32)           # rank order, as the owner adds
+    inv = (np.float32(1.0) / np.sqrt((np.sum(total.astype(np.float64) ** 2, 1) / H + eps))).astype(np.float32)
+    xn = (total * inv[:, None]).astype(np.float32)
+    hi = xn.astype(np.float16)
+    lo = ((xn - hi.astype(np.float32)) * np.float32(2048.0)).astype(np.float16)
+    for i in range(world):
+        assert np.array_equal(r[i]["hi"].view(np.uint16), hi.view(np.uint16))   # every rank holds every row
+        assert np.array_equal(r[i]["lo"].view(np.uint16), lo.view(np.uint16))
+        assert np.array_equal(r[i]["h_own"], total[i * (B // world):(i + 1) * (B // world)])  # only the owner's rows of h
