@@ -285,6 +285,43 @@ LOGOS_API logos_status_t logos_tc_mma_probe(int32_t device, int32_t n, int32_t a
  * row-parallel GEMMs: 0 = no group (tp_degree 1), 1 = NCCL all-reduce, 2 = folded into the
  * residual + RMSNorm kernel over peer-mapped memory (one process per GPU, one node). */
 LOGOS_API logos_status_t logos_llm_tp_exchange(logos_handle_t model, int32_t* mode_out);
+/* ---- weight file: one flat file [256-byte header | tensors] that the library maps read-only
+ * and copies from, the device-side counterpart of the reference's memory-mapped zone
+ * (`Inside a zone called "D" mapped from "f.bin"`, crates/logicaffeine_language/src/ast/stmt.rs:405-418;
+ * Zone::new_mapped, crates/logicaffeine_system/src/memory.rs:97-103).  Regions start on
+ * 256-byte boundaries in this order: per layer attn_norm, q, k, v, o, mlp_norm, gate, up, down;
+ * then final_norm, embed and (untied only) head.  A matrix is int8 [n][k] followed by f32
+ * [n][k/32]; a norm gain is f32 [hidden].  Matrices are stored whole: a tensor-parallel rank
+ * takes its rows (q, k, v, gate, up) or columns (o, down), so one file serves every group size.
+ * A malformed or truncated file is LOGOS_DESERIALIZATION_FAILED, an unreadable one LOGOS_ERROR. */
+typedef enum {
+  LOGOS_W_ATTN_NORM = 0, LOGOS_W_Q = 1, LOGOS_W_K = 2, LOGOS_W_V = 3, LOGOS_W_O = 4, LOGOS_W_MLP_NORM = 5,
+  LOGOS_W_GATE = 6, LOGOS_W_UP = 7, LOGOS_W_DOWN = 8, LOGOS_W_FINAL_NORM = 9, LOGOS_W_EMBED = 10, LOGOS_W_HEAD = 11
+} logos_weight_tensor_t;
+/* Layout queries (no GPU needed; only the architecture fields of cfg are read): size of the
+ * file; place of one tensor (for a gain: q_off/q_bytes = the f32 vector, s_bytes = 0); the
+ * header a writer puts at offset 0. */
+LOGOS_API logos_status_t logos_llm_weights_file_bytes(const logos_llm_config_t* cfg, int64_t* bytes_out);
+LOGOS_API logos_status_t logos_llm_weights_span(const logos_llm_config_t* cfg, int64_t layer, int32_t tensor,
+                                                int64_t* q_off_out, int64_t* q_bytes_out, int64_t* s_off_out,
+                                                int64_t* s_bytes_out);
+LOGOS_API logos_status_t logos_llm_weights_header(const logos_llm_config_t* cfg, void* out_256_bytes);
+/* Map a file, validate header and length, and (cfg_out non-null) report its architecture:
+ * layers, hidden, h_q, h_kv, head_dim, ffn, vocab, tied_embeddings; other fields are untouched. */
+LOGOS_API logos_status_t logos_llm_weights_check(const char* path, logos_llm_config_t* cfg_out);
+/* Host-side read of what rank tp_rank of a group of tp_degree holds of one tensor: int8
+ * [rows][cols] into q_out and f32 [rows][cols/32] into s_out (a gain: f32 [hidden] into q_out,
+ * s_out unused).  Capacities are in bytes.  The device loader copies the same rectangles. */
+LOGOS_API logos_status_t logos_llm_weights_read_shard(const char* path, int32_t tp_degree, int32_t tp_rank, int64_t layer,
+                                                      int32_t tensor, void* q_out, int64_t q_capacity, float* s_out,
+                                                      int64_t s_capacity, int64_t* rows_out, int64_t* cols_out);
+/* Replace the model's weights and norm gains with this rank's part of the file (architecture
+ * must match the model's; the KV cache and sequence state are left alone).  The file is mapped
+ * and streamed to the GPU through two pinned staging buffers. */
+LOGOS_API logos_status_t logos_llm_load_weights(logos_handle_t model, const char* path);
+/* Write the model's weights and gains as a weight file (tp_degree 1 only: a rank of a group
+ * holds no whole matrix). */
+LOGOS_API logos_status_t logos_llm_save_weights(logos_handle_t model, const char* path);
 /* One greedy step with CUDA events around every launch group; ms_by_class_out
  * receives 4 doubles: Q8 GEMMs, attention (+merge), norms/element-wise, and
  * tensor-parallel exchange.  Advances the model like logos_llm_decode_step. */

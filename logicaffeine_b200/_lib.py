@@ -98,6 +98,15 @@ _SIGNATURES = {
     "logos_tc_mma_probe": (None, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(I64),
                            C.POINTER(I64)]),
     "logos_llm_profile_step": (None, [H, C.POINTER(C.c_double)]),
+    "logos_llm_weights_file_bytes": (None, [C.POINTER(LlmConfig), C.POINTER(I64)]),
+    "logos_llm_weights_span": (None, [C.POINTER(LlmConfig), I64, I32c, C.POINTER(I64), C.POINTER(I64), C.POINTER(I64),
+                               C.POINTER(I64)]),
+    "logos_llm_weights_header": (None, [C.POINTER(LlmConfig), PTR]),
+    "logos_llm_weights_check": (None, [C.c_char_p, C.POINTER(LlmConfig)]),
+    "logos_llm_weights_read_shard": (None, [C.c_char_p, I32c, I32c, I64, I32c, PTR, I64, PTR, I64, C.POINTER(I64),
+                                     C.POINTER(I64)]),
+    "logos_llm_load_weights": (None, [H, C.c_char_p]),
+    "logos_llm_save_weights": (None, [H, C.c_char_p]),
     "logos_llm_free": (None, [H]),
 }
 

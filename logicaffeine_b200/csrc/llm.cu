@@ -20,8 +20,13 @@
 #include "ops.cuh"
 #include "q8_gemm_tc.cuh"
 #include "tp.cuh"
+#include "weights.cuh"
 
+#include <errno.h>
+#include <fcntl.h>
 #include <stdlib.h>
+#include <string.h>
+#include <unistd.h>
 
 #include <vector>
 
@@ -48,7 +53,7 @@ struct Model {
   int64_t nq = 0, nkv = 0, nqkv = 0, f_local = 0, hkv_local = 0, hq_local = 0;
   std::vector<Layer> layers;
   Q8Mat embed, head;
-  float* ones = nullptr;
+  float* gains = nullptr;    // RMSNorm gains [2 * layers + 1][H]: attn_norm and mlp_norm of every layer, final_norm; 1 at creation
   float* rope = nullptr;
   float* h = nullptr;        // [B][H] residual stream
   ActOut xn;                 // [B][H] fp16 plane(s)
@@ -201,8 +206,8 @@ logos_status_t build(Model* m, const void* nccl_id) {
     LOGOS_TRY(gen(m, &m->head, c.vocab, 0, 0, H, 1, 0, ((uint64_t)1 << 20) + 1));
   }
 
-  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->ones), H * 4));
-  LOGOS_TRY(launch_synth_fill(m->ones, LOGOS_F32, 1, 0, 0, 0, H, 1.0f, 1.0f, m->device, m->stream));
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->gains), (2 * c.layers + 1) * H * 4));
+  LOGOS_TRY(launch_synth_fill(m->gains, LOGOS_F32, 1, 0, 0, 0, (2 * c.layers + 1) * H, 1.0f, 1.0f, m->device, m->stream));
   {
     std::vector<float> tab((size_t)(c.l_max * D));
     rope_table_host(tab.data(), c.l_max, D, (double)c.rope_theta);
@@ -386,15 +391,16 @@ logos_status_t debug_check(Model* m, const char* what, int64_t layer) {
 // Fold the pending partial sums into the residual stream and normalise: h += sum(partials),
 // xn = planes(rmsnorm(h)).  With a peer-mapped TP group the sum runs over every rank's partials
 // (the all-reduce is part of the kernel) and each rank updates only the rows it owns.
-logos_status_t norm_step(Model* m, int parts) {
+logos_status_t norm_step(Model* m, int parts, int64_t gain_row) {
   const logos_llm_config_t& c = m->cfg;
   const int64_t B = c.batch, H = c.hidden;
+  const float* g = m->gains + gain_row * H;
   if (m->tp_fused && parts > 0) {
     ProfScope ps(m, PROF_COMM);
-    return launch_tp_residual_rmsnorm(m->h, m->tpf, parts, B * H, m->ones, B, H, c.rms_eps, m->device, m->stream);
+    return launch_tp_residual_rmsnorm(m->h, m->tpf, parts, B * H, g, B, H, c.rms_eps, m->device, m->stream);
   }
   ProfScope ps(m, PROF_ELEMWISE);
-  return launch_residual_rmsnorm(m->h, m->partials, parts, B * H, m->ones, m->xn, B, H, c.rms_eps, m->stream);
+  return launch_residual_rmsnorm(m->h, m->partials, parts, B * H, g, m->xn, B, H, c.rms_eps, m->stream);
 }
 
 // One lock-step decode step on the model's stream.  tokens_in: [B] device.
@@ -415,7 +421,7 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
   for (int64_t l = 0; l < c.layers; ++l) {
     Layer& L = m->layers[(size_t)l];
     int qkv_parts = 1;
-    LOGOS_TRY(norm_step(m, parts));
+    LOGOS_TRY(norm_step(m, parts, 2 * l));
     m->launch_counter += 1;
     {
       GemmArgs g;
@@ -446,7 +452,7 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
     LOGOS_TRY(debug_check(m, "attention", l));
     LOGOS_TRY(gemm_partials(m, m->att, L.wo, &parts));
     LOGOS_TRY(debug_check(m, "o_proj gemm", l));
-    LOGOS_TRY(norm_step(m, parts));
+    LOGOS_TRY(norm_step(m, parts, 2 * l + 1));
     m->launch_counter += 1;
     {
       GemmArgs g;
@@ -463,7 +469,7 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
     LOGOS_TRY(debug_check(m, "down_proj gemm", l));
   }
   if (sample) {
-    LOGOS_TRY(norm_step(m, parts));
+    LOGOS_TRY(norm_step(m, parts, 2 * c.layers));
     GemmArgs g;
     g.a = m->xn.hi; g.a_lo = m->xn.lo; g.a_dtype = LOGOS_F16; g.lda = H;
     g.q = m->head.q; g.s = m->head.s;
@@ -528,6 +534,177 @@ logos_status_t check_cfg(const logos_llm_config_t& c) {
   if (c.act_dtype != LOGOS_F32 && c.act_dtype != LOGOS_F16 && c.act_dtype != LOGOS_BF16)
     return fail(LOGOS_ERROR, "logos_llm_create: act_dtype must be LOGOS_F32, LOGOS_F16 or LOGOS_BF16");
   return LOGOS_OK;
+}
+
+// Streams host memory to the device (and back) through two pinned buffers, so that reading the
+// next chunk out of the mapped file overlaps the copy of the previous one.
+struct Stager {
+  static constexpr size_t BYTES = (size_t)32 << 20;
+  uint8_t* buf[2] = {nullptr, nullptr};
+  cudaEvent_t ev[2] = {nullptr, nullptr};
+  bool busy[2] = {false, false};
+  int next = 0;
+  cudaStream_t st = nullptr;
+
+  logos_status_t init(cudaStream_t stream) {
+    st = stream;
+    for (int i = 0; i < 2; ++i) {
+      LOGOS_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&buf[i]), BYTES));
+      LOGOS_CUDA_TRY(cudaEventCreateWithFlags(&ev[i], cudaEventDisableTiming));
+    }
+    return LOGOS_OK;
+  }
+  ~Stager() {
+    for (int i = 0; i < 2; ++i) {
+      if (busy[i]) cudaEventSynchronize(ev[i]);
+      if (ev[i]) cudaEventDestroy(ev[i]);
+      if (buf[i]) cudaFreeHost(buf[i]);
+    }
+  }
+  // host rows of `width` bytes, src_pitch apart -> device rows dst_pitch apart
+  logos_status_t put(void* dst, size_t dst_pitch, const uint8_t* src, size_t src_pitch, size_t width, int64_t rows) {
+    if (width == 0 || rows <= 0) return LOGOS_OK;
+    if (width > BYTES) return fail(LOGOS_ERROR, "weight row of %zu bytes exceeds the staging buffer", width);
+    const int64_t per = (int64_t)(BYTES / width);
+    for (int64_t r0 = 0; r0 < rows; r0 += per) {
+      const int64_t n = rows - r0 < per ? rows - r0 : per;
+      if (busy[next]) LOGOS_CUDA_TRY(cudaEventSynchronize(ev[next]));
+      if (src_pitch == width) {
+        memcpy(buf[next], src + (size_t)r0 * src_pitch, (size_t)n * width);
+      } else {
+        for (int64_t i = 0; i < n; ++i) memcpy(buf[next] + (size_t)i * width, src + (size_t)(r0 + i) * src_pitch, width);
+      }
+      LOGOS_CUDA_TRY(cudaMemcpy2DAsync(static_cast<uint8_t*>(dst) + (size_t)r0 * dst_pitch, dst_pitch, buf[next], width, width,
+                                       (size_t)n, cudaMemcpyHostToDevice, st));
+      LOGOS_CUDA_TRY(cudaEventRecord(ev[next], st));
+      busy[next] = true;
+      next ^= 1;
+    }
+    return LOGOS_OK;
+  }
+  // device rows src_pitch apart -> `width` bytes per row written to the file at `off`, rows packed
+  logos_status_t get_to_file(int fd, int64_t off, const void* src, size_t src_pitch, size_t width, int64_t rows) {
+    if (width == 0 || rows <= 0) return LOGOS_OK;
+    if (width > BYTES) return fail(LOGOS_ERROR, "weight row of %zu bytes exceeds the staging buffer", width);
+    const int64_t per = (int64_t)(BYTES / width);
+    for (int64_t r0 = 0; r0 < rows; r0 += per) {
+      const int64_t n = rows - r0 < per ? rows - r0 : per;
+      LOGOS_CUDA_TRY(cudaMemcpy2DAsync(buf[0], width, static_cast<const uint8_t*>(src) + (size_t)r0 * src_pitch, src_pitch,
+                                       width, (size_t)n, cudaMemcpyDeviceToHost, st));
+      LOGOS_CUDA_TRY(cudaStreamSynchronize(st));
+      size_t done = 0, total = (size_t)n * width;
+      while (done < total) {
+        ssize_t k = pwrite(fd, buf[0] + done, total - done, (off_t)(off + r0 * (int64_t)width + (int64_t)done));
+        if (k < 0 && errno == EINTR) continue;
+        if (k <= 0) return fail(LOGOS_ERROR, "logos_llm_save_weights: write failed: %s", strerror(errno));
+        done += (size_t)k;
+      }
+    }
+    return LOGOS_OK;
+  }
+};
+
+// Where one tensor of the file lives in the model: device rows and their pitches, for the int8
+// part and for the scales (a gain vector: q only).
+struct TensorHome {
+  void* q = nullptr;
+  size_t q_pitch = 0;
+  void* s = nullptr;
+  size_t s_pitch = 0;
+};
+
+TensorHome tensor_home(Model* m, int64_t l, int kind) {
+  const int64_t H = m->cfg.hidden, hb = H / 32;
+  TensorHome t;
+  Layer* L = kind <= LOGOS_W_DOWN ? &m->layers[(size_t)l] : nullptr;
+  auto rows_of = [&](Q8Mat& w, int64_t row0, int64_t mul) {
+    t.q = w.q + row0 * w.k; t.q_pitch = (size_t)(mul * w.k);
+    t.s = w.s + row0 * (w.k / 32); t.s_pitch = (size_t)(mul * (w.k / 32) * 4);
+  };
+  switch (kind) {
+    case LOGOS_W_ATTN_NORM:  t.q = m->gains + (2 * l) * H; t.q_pitch = (size_t)H * 4; break;
+    case LOGOS_W_MLP_NORM:   t.q = m->gains + (2 * l + 1) * H; t.q_pitch = (size_t)H * 4; break;
+    case LOGOS_W_FINAL_NORM: t.q = m->gains + (2 * m->cfg.layers) * H; t.q_pitch = (size_t)H * 4; break;
+    case LOGOS_W_Q:    rows_of(L->wqkv, 0, 1); break;
+    case LOGOS_W_K:    rows_of(L->wqkv, m->nq, 1); break;
+    case LOGOS_W_V:    rows_of(L->wqkv, m->nq + m->nkv, 1); break;
+    case LOGOS_W_O:    rows_of(L->wo, 0, 1); break;
+    // gate row i and up row i are neighbours (rows 2i and 2i+1), which is what the SwiGLU epilogue pairs
+    case LOGOS_W_GATE: rows_of(L->wgu, 0, 2); break;
+    case LOGOS_W_UP:   rows_of(L->wgu, 0, 2); t.q = L->wgu.q + H; t.s = L->wgu.s + hb; break;
+    case LOGOS_W_DOWN: rows_of(L->wd, 0, 1); break;
+    case LOGOS_W_EMBED: rows_of(m->embed, 0, 1); break;
+    case LOGOS_W_HEAD:  rows_of(m->head, 0, 1); break;
+  }
+  return t;
+}
+
+logos_status_t same_arch(const WeightsArch& f, const WeightsArch& a, const char* who) {
+  if (f.layers != a.layers || f.hidden != a.hidden || f.h_q != a.h_q || f.h_kv != a.h_kv || f.head_dim != a.head_dim ||
+      f.ffn != a.ffn || f.vocab != a.vocab || f.tied != a.tied)
+    return fail(LOGOS_ERROR,
+                "%s: the file holds layers %lld hidden %lld heads %lld/%lld x %lld ffn %lld vocab %lld tied %d, the model "
+                "layers %lld hidden %lld heads %lld/%lld x %lld ffn %lld vocab %lld tied %d",
+                who, (long long)f.layers, (long long)f.hidden, (long long)f.h_q, (long long)f.h_kv, (long long)f.head_dim,
+                (long long)f.ffn, (long long)f.vocab, f.tied, (long long)a.layers, (long long)a.hidden, (long long)a.h_q,
+                (long long)a.h_kv, (long long)a.head_dim, (long long)a.ffn, (long long)a.vocab, a.tied);
+  return LOGOS_OK;
+}
+
+// Every tensor of the file in storage order: fn(layer, kind).
+template <class F>
+logos_status_t for_each_tensor(const WeightsArch& a, F&& fn) {
+  for (int64_t l = 0; l < a.layers; ++l)
+    for (int kind = LOGOS_W_ATTN_NORM; kind <= LOGOS_W_DOWN; ++kind) LOGOS_TRY(fn(l, kind));
+  LOGOS_TRY(fn((int64_t)0, (int)LOGOS_W_FINAL_NORM));
+  LOGOS_TRY(fn((int64_t)0, (int)LOGOS_W_EMBED));
+  if (!a.tied) LOGOS_TRY(fn((int64_t)0, (int)LOGOS_W_HEAD));
+  return LOGOS_OK;
+}
+
+logos_status_t load_weights(Model* m, const MappedWeights& w) {
+  const char* who = "logos_llm_load_weights";
+  const WeightsArch a = arch_of(m->cfg);
+  LOGOS_TRY(same_arch(w.arch, a, who));
+  LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));  // no step reads the weights while they change
+  Stager stg;
+  LOGOS_TRY(stg.init(m->stream));
+  LOGOS_TRY(for_each_tensor(a, [&](int64_t l, int kind) -> logos_status_t {
+    TensorSpan t;
+    ShardRect r;
+    LOGOS_TRY(weights_span(a, l, kind, &t, who));
+    LOGOS_TRY(weights_shard(a, kind, m->cfg.tp_degree, m->cfg.tp_rank, &r, who));
+    const TensorHome home = tensor_home(m, l, kind);
+    if (is_gain(kind)) return stg.put(home.q, home.q_pitch, w.base + t.q_off, (size_t)t.q_bytes, (size_t)t.q_bytes, 1);
+    const int64_t kb = t.k / 32;
+    LOGOS_TRY(stg.put(home.q, home.q_pitch, w.base + t.q_off + r.row0 * t.k + r.col0, (size_t)t.k, (size_t)r.cols, r.rows));
+    return stg.put(home.s, home.s_pitch, w.base + t.s_off + (r.row0 * kb + r.col0 / 32) * 4, (size_t)kb * 4,
+                   (size_t)(r.cols / 32) * 4, r.rows);
+  }));
+  LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
+  return LOGOS_OK;
+}
+
+logos_status_t save_weights(Model* m, int fd) {
+  const char* who = "logos_llm_save_weights";
+  const WeightsArch a = arch_of(m->cfg);
+  const int64_t total = weights_file_bytes(a);
+  if (ftruncate(fd, (off_t)total) != 0) return fail(LOGOS_ERROR, "%s: cannot size the file: %s", who, strerror(errno));
+  uint8_t header[256];
+  LOGOS_TRY(logos_llm_weights_header(&m->cfg, header));
+  if (pwrite(fd, header, sizeof(header), 0) != (ssize_t)sizeof(header))
+    return fail(LOGOS_ERROR, "%s: write failed: %s", who, strerror(errno));
+  LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
+  Stager stg;
+  LOGOS_TRY(stg.init(m->stream));
+  return for_each_tensor(a, [&](int64_t l, int kind) -> logos_status_t {
+    TensorSpan t;
+    LOGOS_TRY(weights_span(a, l, kind, &t, who));
+    const TensorHome home = tensor_home(m, l, kind);
+    if (is_gain(kind)) return stg.get_to_file(fd, t.q_off, home.q, home.q_pitch, (size_t)t.q_bytes, 1);
+    LOGOS_TRY(stg.get_to_file(fd, t.q_off, home.q, home.q_pitch, (size_t)t.k, t.n));
+    return stg.get_to_file(fd, t.s_off, home.s, home.s_pitch, (size_t)(t.k / 32) * 4, t.n);
+  });
 }
 
 Model* get_model(logos_handle_t h) { return static_cast<Model*>(registry_get(h, ObjKind::Model)); }
@@ -760,6 +937,35 @@ logos_status_t logos_llm_tp_exchange(logos_handle_t model, int32_t* mode_out) {
     if (!mode_out) return fail(LOGOS_NULL_POINTER, "logos_llm_tp_exchange: mode_out is null");
     *mode_out = m->tp.degree <= 1 ? 0 : (m->tp_fused ? 2 : 1);
     return LOGOS_OK;
+  });
+}
+
+logos_status_t logos_llm_load_weights(logos_handle_t model, const char* path) {
+  return guarded([&]() -> logos_status_t {
+    MODEL_OR_FAIL(m, model, "logos_llm_load_weights");
+    if (!path) return fail(LOGOS_NULL_POINTER, "logos_llm_load_weights: path is null");
+    MappedWeights w;
+    LOGOS_TRY(weights_open(path, &w, "logos_llm_load_weights"));
+    logos_status_t s = load_weights(m, w);
+    weights_close(&w);
+    return s;
+  });
+}
+
+logos_status_t logos_llm_save_weights(logos_handle_t model, const char* path) {
+  return guarded([&]() -> logos_status_t {
+    MODEL_OR_FAIL(m, model, "logos_llm_save_weights");
+    if (!path) return fail(LOGOS_NULL_POINTER, "logos_llm_save_weights: path is null");
+    if (m->cfg.tp_degree != 1)
+      return fail(LOGOS_ERROR, "logos_llm_save_weights: a rank of a tensor-parallel group holds no whole matrix (tp_degree %d)",
+                  m->cfg.tp_degree);
+    int fd = open(path, O_WRONLY | O_CREAT | O_TRUNC, 0644);
+    if (fd < 0) return fail(LOGOS_ERROR, "logos_llm_save_weights: cannot create '%s': %s", path, strerror(errno));
+    logos_status_t s = save_weights(m, fd);
+    std::string keep = s != LOGOS_OK && logos_last_error() ? logos_last_error() : "";
+    if (close(fd) != 0 && s == LOGOS_OK) s = fail(LOGOS_ERROR, "logos_llm_save_weights: close failed: %s", strerror(errno));
+    else if (s != LOGOS_OK) set_last_error(keep);
+    return s;
   });
 }
 

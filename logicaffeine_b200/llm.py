@@ -314,6 +314,14 @@ class Llm:
         call("logos_llm_tp_exchange", self.handle, C.byref(mode))
         return mode.value
 
+    def loadWeights(self, path):
+        """Replace weights and norm gains with this rank's part of a weight file (weights.py)."""
+        call("logos_llm_load_weights", self.handle, str(path).encode())
+
+    def saveWeights(self, path):
+        """Write the model's weights and gains as a weight file (tp_degree 1 only)."""
+        call("logos_llm_save_weights", self.handle, str(path).encode())
+
     def profileStep(self):
         """One step with per-class device timing: ms for (gemm, attention, elementwise, exchange)."""
         ms = (C.c_double * 4)()
@@ -346,6 +354,10 @@ def llmDecodeStep(model):
 
 def llmDecodeSteps(model, steps):
     return model.decodeSteps(steps)
+
+
+def llmLoadWeights(model, path):
+    model.loadWeights(path)
 
 
 def llmFree(model):

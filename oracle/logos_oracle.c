@@ -516,7 +516,8 @@ ORC_API void orc_swiglu(const float* gate, const float* up, float* y, int64_t co
  * rounded to the 16-bit activation type, fp16 KV cache, f32 logits, argmax
  * with the lowest index winning ties.  Weight streams: layer*16 + {0:q 1:k 2:v
  * 3:o 4:gate 5:up 6:down}; embedding (1<<20); lm_head (1<<20)+1.  Norm gains
- * are 1. */
+ * [2*layers+1][hidden] (attn_norm and mlp_norm per layer, final_norm) are 1 until
+ * orc_llm_set_tensor replaces them. */
 typedef struct {
   int64_t layers, hidden, h_q, h_kv, head_dim, ffn, vocab, l_max, batch;
   float rms_eps, rope_theta;
@@ -538,7 +539,7 @@ typedef struct {
   q8mat embed, head;
   uint16_t **kc, **vc; /* per layer [B][Hkv][Lmax][D] */
   float* rope;
-  float* ones;
+  float* gains;
   int32_t* seq_len;
   int32_t* tokens;
   float* logits;
@@ -587,9 +588,8 @@ ORC_API void* orc_llm_create(const orc_llm_config_t* cfg) {
   if (!cfg->tied_embeddings) M->head = make_mat(cfg->vocab, H, cfg->seed, ((uint64_t)1 << 20) + 1, cfg->init_std);
   M->rope = (float*)malloc(sizeof(float) * (size_t)(cfg->l_max * D));
   orc_rope_table(M->rope, cfg->l_max, D, (double)cfg->rope_theta);
-  int64_t mx = H > F ? H : F;
-  M->ones = (float*)malloc(sizeof(float) * (size_t)mx);
-  for (int64_t i = 0; i < mx; ++i) M->ones[i] = 1.0f;
+  M->gains = (float*)malloc(sizeof(float) * (size_t)((2 * L + 1) * H));
+  for (int64_t i = 0; i < (2 * L + 1) * H; ++i) M->gains[i] = 1.0f;
   M->seq_len = (int32_t*)calloc((size_t)cfg->batch, 4);
   M->tokens = (int32_t*)calloc((size_t)cfg->batch, 4);
   M->logits = (float*)calloc((size_t)(cfg->batch * cfg->vocab), 4);
@@ -608,7 +608,7 @@ ORC_API void orc_llm_free(void* model) {
   free(M->kc); free(M->vc);
   free_mat(&M->embed);
   if (!M->cfg.tied_embeddings) free_mat(&M->head);
-  free(M->rope); free(M->ones); free(M->seq_len); free(M->tokens); free(M->logits); free(M->h);
+  free(M->rope); free(M->gains); free(M->seq_len); free(M->tokens); free(M->logits); free(M->h);
   free(M);
 }
 
@@ -641,7 +641,7 @@ static void llm_step(orc_llm* M, int sample) {
       M->h[i * H + e] = M->embed.s[t * (H / 32) + e / 32] * (float)M->embed.q[t * H + e];
   }
   for (int64_t l = 0; l < c->layers; ++l) {
-    orc_rmsnorm(M->h, M->ones, xn, B, H, c->rms_eps);
+    orc_rmsnorm(M->h, M->gains + (2 * l) * H, xn, B, H, c->rms_eps);
     round_rows(xn, B * H, act);
     orc_q8_gemm_f32(xn, ORC_F32, M->wq[l].q, M->wq[l].s, qf, B, nq, H);
     orc_q8_gemm_f32(xn, ORC_F32, M->wk[l].q, M->wk[l].s, kf, B, nkv, H);
@@ -662,7 +662,7 @@ static void llm_step(orc_llm* M, int sample) {
     round_rows(att, B * nq, act);
     orc_q8_gemm_f32(att, ORC_F32, M->wo[l].q, M->wo[l].s, delta, B, H, nq);
     for (int64_t i = 0; i < B * H; ++i) M->h[i] = M->h[i] + delta[i];
-    orc_rmsnorm(M->h, M->ones, xn, B, H, c->rms_eps);
+    orc_rmsnorm(M->h, M->gains + (2 * l + 1) * H, xn, B, H, c->rms_eps);
     round_rows(xn, B * H, act);
     orc_q8_gemm_f32(xn, ORC_F32, M->wg[l].q, M->wg[l].s, gate, B, F, H);
     orc_q8_gemm_f32(xn, ORC_F32, M->wu[l].q, M->wu[l].s, up, B, F, H);
@@ -673,7 +673,7 @@ static void llm_step(orc_llm* M, int sample) {
   }
   for (int64_t i = 0; i < B; ++i) M->seq_len[i] += 1;
   if (sample) {
-    orc_rmsnorm(M->h, M->ones, xn, B, H, c->rms_eps);
+    orc_rmsnorm(M->h, M->gains + (2 * c->layers) * H, xn, B, H, c->rms_eps);
     round_rows(xn, B * H, act);
     const q8mat* hd = c->tied_embeddings ? &M->embed : &M->head;
     orc_q8_gemm_f32(xn, ORC_F32, hd->q, hd->s, M->logits, B, c->vocab, H);
@@ -686,6 +686,58 @@ static void llm_step(orc_llm* M, int sample) {
     }
   }
   free(xn); free(qf); free(kf); free(vf); free(qh); free(att); free(delta); free(gate); free(up); free(len1);
+}
+
+/* One tensor of the model, named as the weight file names them: 0 attn_norm, 1 q, 2 k, 3 v,
+ * 4 o, 5 mlp_norm, 6 gate, 7 up, 8 down, 9 final_norm, 10 embed, 11 head.  A matrix is int8
+ * [n][k] plus f32 [n][k/32]; a gain is f32 [hidden] behind `q`.  Returns 0, or -1 for a
+ * tensor the model does not have. */
+static int llm_tensor(orc_llm* M, int64_t layer, int kind, q8mat** mat, float** gain) {
+  const orc_llm_config_t* c = &M->cfg;
+  *mat = NULL;
+  *gain = NULL;
+  if (kind <= 8 && (layer < 0 || layer >= c->layers)) return -1;
+  switch (kind) {
+    case 0: *gain = M->gains + (2 * layer) * c->hidden; return 0;
+    case 5: *gain = M->gains + (2 * layer + 1) * c->hidden; return 0;
+    case 9: *gain = M->gains + (2 * c->layers) * c->hidden; return 0;
+    case 1: *mat = &M->wq[layer]; return 0;
+    case 2: *mat = &M->wk[layer]; return 0;
+    case 3: *mat = &M->wv[layer]; return 0;
+    case 4: *mat = &M->wo[layer]; return 0;
+    case 6: *mat = &M->wg[layer]; return 0;
+    case 7: *mat = &M->wu[layer]; return 0;
+    case 8: *mat = &M->wd[layer]; return 0;
+    case 10: *mat = &M->embed; return 0;
+    case 11: if (c->tied_embeddings) return -1; *mat = &M->head; return 0;
+    default: return -1;
+  }
+}
+ORC_API int orc_llm_set_tensor(void* model, int64_t layer, int kind, const void* q, const float* s) {
+  orc_llm* M = (orc_llm*)model;
+  q8mat* mat;
+  float* gain;
+  if (llm_tensor(M, layer, kind, &mat, &gain) != 0) return -1;
+  if (gain) {
+    memcpy(gain, q, sizeof(float) * (size_t)M->cfg.hidden);
+  } else {
+    memcpy(mat->q, q, (size_t)(mat->n * mat->k));
+    memcpy(mat->s, s, sizeof(float) * (size_t)(mat->n * (mat->k / 32)));
+  }
+  return 0;
+}
+ORC_API int orc_llm_get_tensor(void* model, int64_t layer, int kind, void* q, float* s) {
+  orc_llm* M = (orc_llm*)model;
+  q8mat* mat;
+  float* gain;
+  if (llm_tensor(M, layer, kind, &mat, &gain) != 0) return -1;
+  if (gain) {
+    memcpy(q, gain, sizeof(float) * (size_t)M->cfg.hidden);
+  } else {
+    memcpy(q, mat->q, (size_t)(mat->n * mat->k));
+    memcpy(s, mat->s, sizeof(float) * (size_t)(mat->n * (mat->k / 32)));
+  }
+  return 0;
 }
 
 ORC_API void orc_llm_prefill(void* model, const int32_t* tokens, int64_t t) {

@@ -227,6 +227,39 @@ class Llm:
         lib().orc_llm_read_kv(self._h, C.c_int64(layer), _p(k), _p(v))
         return k, v
 
+    def _tensor_shape(self, kind):
+        c = self.cfg
+        nq, nkv = c.h_q * c.head_dim, c.h_kv * c.head_dim
+        return {1: (nq, c.hidden), 2: (nkv, c.hidden), 3: (nkv, c.hidden), 4: (c.hidden, nq), 6: (c.ffn, c.hidden),
+                7: (c.ffn, c.hidden), 8: (c.hidden, c.ffn), 10: (c.vocab, c.hidden), 11: (c.vocab, c.hidden)}.get(kind)
+
+    def get_tensor(self, layer, kind):
+        """A tensor by the weight file's numbering (0 attn_norm, 1 q, 2 k, 3 v, 4 o, 5 mlp_norm, 6 gate,
+        7 up, 8 down, 9 final_norm, 10 embed, 11 head): (q, s) for a matrix, an f32 vector for a gain."""
+        shape = self._tensor_shape(kind)
+        if shape is None:
+            g = np.empty(self.cfg.hidden, np.float32)
+            if lib().orc_llm_get_tensor(self._h, C.c_int64(layer), C.c_int(kind), _p(g), None) != 0:
+                raise KeyError((layer, kind))
+            return g
+        q = np.empty(shape, np.int8)
+        s = np.empty((shape[0], shape[1] // 32), np.float32)
+        if lib().orc_llm_get_tensor(self._h, C.c_int64(layer), C.c_int(kind), _p(q), _p(s)) != 0:
+            raise KeyError((layer, kind))
+        return q, s
+
+    def set_tensor(self, layer, kind, q, s=None):
+        shape = self._tensor_shape(kind)
+        if shape is None:
+            g = np.ascontiguousarray(q, np.float32).reshape(self.cfg.hidden)
+            rc = lib().orc_llm_set_tensor(self._h, C.c_int64(layer), C.c_int(kind), _p(g), None)
+        else:
+            q = np.ascontiguousarray(q, np.int8).reshape(shape)
+            s = np.ascontiguousarray(s, np.float32).reshape(shape[0], shape[1] // 32)
+            rc = lib().orc_llm_set_tensor(self._h, C.c_int64(layer), C.c_int(kind), _p(q), _p(s))
+        if rc != 0:
+            raise KeyError((layer, kind))
+
     def read_logits(self):
         out = np.empty((self.cfg.batch, self.cfg.vocab), np.float32)
         lib().orc_llm_read_logits(self._h, _p(out))

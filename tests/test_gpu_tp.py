@@ -23,18 +23,10 @@ def _env(fused):
     return env
 
 
-@pytest.mark.timeout(300)
-@pytest.mark.parametrize("fused", ["default", "0"])
-def test_tp2_tokens_match_the_oracle(llm, oracle, tmp_path, fused):
-    if llm.deviceCount() < 2:
-        pytest.skip("needs two GPUs")
-    sys.path.insert(0, HERE)
-    from tp_worker import CFG
-    O = oracle
-    steps, t = 16, 7
+def _run_ranks(tmp_path, steps, t, fused, extra=()):
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), str(r), "2", str(tmp_path),
-                               str(steps), str(t)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
-                              env=_env(fused))
+                               str(steps), str(t)] + list(extra), stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                              text=True, env=_env(fused))
              for r in range(2)]
     outs = []
     try:
@@ -46,11 +38,50 @@ def test_tp2_tokens_match_the_oracle(llm, oracle, tmp_path, fused):
                 p.kill()
     for r, p in enumerate(procs):
         assert p.returncode == 0, "rank %d failed:\n%s" % (r, outs[r][-2000:] if r < len(outs) else "")
+    return tuple(np.load(tmp_path / ("r%d.npz" % i)) for i in range(2))
+
+
+@pytest.mark.timeout(300)
+def test_tp2_ranks_load_their_shards_from_one_file(llm, oracle, tmp_path):
+    """The ranks are created from another seed and take their rows / columns out of one file
+    of whole matrices; tokens equal the oracle's run on the file's weights and gains."""
+    if llm.deviceCount() < 2:
+        pytest.skip("needs two GPUs")
+    sys.path.insert(0, HERE)
+    from tp_worker import CFG
+    from logicaffeine_b200 import weights as W
+    O = oracle
+    steps, t = 12, 5
+    ref = O.Llm(tp_degree=1, tp_rank=0, device=0, act_dtype=O.F32, **CFG)
+    rng = np.random.default_rng(11)
+    gains = {key: rng.uniform(0.5, 1.5, CFG["hidden"]).astype(np.float32)
+             for key in W.tensors(CFG) if key[1] in W.GAINS}
+    path = tmp_path / "model.q8w"
+    W.writeWeightsFile(path, CFG, lambda l, k: gains[(l, k)] if k in W.GAINS else ref.get_tensor(l, k))
+    for (l, k), g in gains.items():
+        ref.set_tensor(l, k, g)
+    r0, r1 = _run_ranks(tmp_path, steps, t, "default", [str(path)])
+    toks = O.synth_fill(O.I32, 3, 9, 999, 0, CFG["batch"] * t, 0.0, float(CFG["vocab"])).reshape(CFG["batch"], t)
+    ref.prefill(toks)
+    want = np.array([ref.decode_step().copy() for _ in range(steps)])
+    assert np.array_equal(r0["tokens"], want) and np.array_equal(r1["tokens"], want)
+    ref.close()
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("fused", ["default", "0"])
+def test_tp2_tokens_match_the_oracle(llm, oracle, tmp_path, fused):
+    if llm.deviceCount() < 2:
+        pytest.skip("needs two GPUs")
+    sys.path.insert(0, HERE)
+    from tp_worker import CFG
+    O = oracle
+    steps, t = 16, 7
+    r0, r1 = _run_ranks(tmp_path, steps, t, fused)
     toks = O.synth_fill(O.I32, 3, 9, 999, 0, CFG["batch"] * t, 0.0, float(CFG["vocab"])).reshape(CFG["batch"], t)
     ref = O.Llm(tp_degree=1, tp_rank=0, device=0, act_dtype=O.F32, **CFG)
     ref.prefill(toks)
     want = np.array([ref.decode_step().copy() for _ in range(steps)])
-    r0, r1 = (np.load(tmp_path / ("r%d.npz" % i)) for i in range(2))
     assert int(r0["exchange"]) == int(r1["exchange"]) == (1 if fused == "0" else 2)   # no silent fall-back
     assert np.array_equal(r0["tokens"], want) and np.array_equal(r1["tokens"], want)
     assert np.array_equal(r0["logits"], r1["logits"])           # replicated lm_head on identical inputs

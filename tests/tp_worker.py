@@ -1,5 +1,6 @@
 """One tensor-parallel rank as its own process (used by test_gpu_tp.py):
-    python tests/tp_worker.py RANK WORLD OUT_DIR STEPS PROMPT_LEN
+    python tests/tp_worker.py RANK WORLD OUT_DIR STEPS PROMPT_LEN [WEIGHT_FILE]
+With WEIGHT_FILE the model is created from another seed and every rank loads its shard of the file.
 Rank 0 makes the NCCL id and publishes it in OUT_DIR; every rank writes its tokens, its
 first layer's KV cache and the last logits to OUT_DIR/rRANK.npz."""
 import faulthandler
@@ -37,7 +38,11 @@ def main():
     with open(id_path, "rb") as f:
         uid = f.read()
     toks = O.synth_fill(O.I32, 3, 9, 999, 0, CFG["batch"] * t, 0.0, float(CFG["vocab"])).reshape(CFG["batch"], t)
-    m = llm.Llm(nccl_unique_id=uid, tp_degree=world, tp_rank=rank, device=rank, **CFG)
+    weight_file = sys.argv[6] if len(sys.argv) > 6 else None
+    cfg = dict(CFG, seed=CFG["seed"] + 100) if weight_file else CFG
+    m = llm.Llm(nccl_unique_id=uid, tp_degree=world, tp_rank=rank, device=rank, **cfg)
+    if weight_file:
+        m.loadWeights(weight_file)
     m.prefill(toks)
     got = m.decodeSteps(steps)
     k, v = m.readKv(0)
