@@ -111,6 +111,7 @@ LOGOS_API logos_status_t logos_launch_counts(int64_t* out8);
  *   kind 1: f32 uniform in [a,b)                 (dst f32)
  *   kind 2: normal, mean a, std b                (dst f32 / f16 / bf16 by `dtype`)
  *   kind 3: int32 uniform in [0,(int)b)          (dst i32)
+ *   kind 4: standard Gumbel -ln(-ln u)           (dst f32; the noise of temperature sampling)
  * `first_index` offsets the counter (element i uses first_index+i). */
 LOGOS_API logos_status_t logos_synth_fill(logos_handle_t dst, int64_t dst_offset_bytes, int32_t dtype, int32_t kind,
                                 uint64_t seed, uint64_t stream, int64_t first_index, int64_t count,
@@ -260,6 +261,13 @@ LOGOS_API logos_status_t logos_llm_read_seq_len(logos_handle_t model, int32_t* s
 /* Rewind every sequence to length t (t <= current length): decode can be re-run
  * from a prefilled state. */
 LOGOS_API logos_status_t logos_llm_set_seq_len(logos_handle_t model, int64_t t);
+/* Temperature sampling instead of greedy argmax: the next token of sequence b at position p
+ * is argmax_i(logit_i / temperature + G(seed, b, p * vocab + i)) with G the generator's Gumbel
+ * variate (logos_synth_fill kind 4), i.e. a draw from softmax(logits / temperature) that is a
+ * pure function of (seed, sequence, position): the same on every rank of a tensor-parallel
+ * group, under graph replay, and in the CPU oracle.  temperature 0 (the state after create)
+ * is greedy.  Takes effect from the next step. */
+LOGOS_API logos_status_t logos_llm_set_sampling(logos_handle_t model, float temperature, uint64_t seed);
 /* Device-side time of the last logos_llm_decode_steps call, milliseconds
  * (CUDA events on the model's stream), and kernels launched per step. */
 LOGOS_API logos_status_t logos_llm_last_timing(logos_handle_t model, double* ms_out, int64_t* launches_per_step_out);

@@ -8,6 +8,7 @@
 // Row reductions run in a fixed shape (per-thread strided partials, shuffle
 // tree, then warps in ascending order), so results do not depend on timing.
 #include "ops.cuh"
+#include "synth.cuh"
 
 #include <cooperative_groups.h>
 
@@ -281,7 +282,8 @@ __global__ void act_split_kernel(const float* __restrict__ x, ActOut o, int64_t 
 // so a captured step needs no per-step pointer.
 __global__ void argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ tokens,
                               int32_t* __restrict__ history, const int32_t* __restrict__ step_counter,
-                              int64_t history_rows, int64_t vocab) {
+                              int64_t history_rows, int64_t vocab, const SamplingParams* __restrict__ sampling,
+                              const int32_t* __restrict__ positions) {
   __shared__ float bv[32];
   __shared__ int bi[32];
   pdl_wait();
@@ -290,8 +292,13 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int32_t* __restr
   const float* lr = logits + row * vocab;
   float best = -INFINITY;
   int idx = 0x7fffffff;
+  const bool sample = sampling && positions && __ldcg(&sampling->enabled) != 0;
+  const float inv_t = sample ? __ldcg(&sampling->inv_temperature) : 1.f;
+  const uint64_t seed = sample ? __ldcg(&sampling->seed) : 0ull;
+  const uint64_t first = sample ? (uint64_t)__ldcg(positions + row) * (uint64_t)vocab : 0ull;
   for (int64_t i = threadIdx.x; i < vocab; i += blockDim.x) {
     float v = __ldcg(lr + i);
+    if (sample) v = __fadd_rn(__fmul_rn(v, inv_t), synth::gumbel_f32(seed, (uint64_t)row, first + (uint64_t)i));
     if (v > best || (v == best && (int)i < idx)) {
       best = v;
       idx = (int)i;
@@ -422,10 +429,10 @@ logos_status_t launch_tp_residual_rmsnorm(float* h, const TpFusedArgs& t, int pa
 
 logos_status_t launch_argmax(const float* logits, int32_t* tokens, int32_t* history_or_null,
                              const int32_t* step_counter_or_null, int64_t history_rows, int64_t rows, int64_t vocab,
-                             cudaStream_t st) {
+                             const SamplingParams* sampling_or_null, const int32_t* positions_or_null, cudaStream_t st) {
   if (rows == 0) return LOGOS_OK;
   LOGOS_CUDA_TRY(launch_kernel(argmax_kernel, dim3((unsigned)rows), dim3(1024), 0, st, logits, tokens, history_or_null,
-                               step_counter_or_null, history_rows, vocab));
+                               step_counter_or_null, history_rows, vocab, sampling_or_null, positions_or_null));
   count_launch(LK_ELEMWISE);
   return check_launch("argmax_kernel");
 }

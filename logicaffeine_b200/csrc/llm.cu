@@ -72,6 +72,7 @@ struct Model {
   float* logits = nullptr;   // [B][V]
   int32_t* tokens = nullptr; // [B] current input / last output
   int32_t* seq_len = nullptr;
+  SamplingParams* sampling = nullptr;  // device: temperature sampling state (zeroed = greedy)
   int32_t* history = nullptr; // [history_cap][B] token log of the current decode_steps call
   int64_t  history_cap = 0;
   int32_t* step_counter = nullptr;  // device: steps taken since the current decode_steps call began
@@ -279,6 +280,8 @@ logos_status_t build(Model* m, const void* nccl_id) {
   LOGOS_CUDA_TRY(cudaMemsetAsync(m->step_counter, 0, 256, m->stream));
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->tokens), B * 4));
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->seq_len), B * 4));
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->sampling), 256));
+  LOGOS_CUDA_TRY(cudaMemsetAsync(m->sampling, 0, 256, m->stream));
   LOGOS_CUDA_TRY(cudaMemsetAsync(m->tokens, 0, (size_t)B * 4, m->stream));
   LOGOS_CUDA_TRY(cudaMemsetAsync(m->seq_len, 0, (size_t)B * 4, m->stream));
   LOGOS_CUDA_TRY(cudaMemsetAsync(m->logits, 0, (size_t)(B * c.vocab) * 4, m->stream));
@@ -481,8 +484,9 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
       LOGOS_TRY(launch_q8_gemm(g, st));
     }
     ProfScope ps(m, PROF_ELEMWISE);
+    // seq_len still holds the position of the token this step consumed (bump_len_kernel runs last)
     LOGOS_TRY(launch_argmax(m->logits, m->tokens, log_tokens ? m->history : nullptr, m->step_counter, m->history_cap, B,
-                            c.vocab, st));
+                            c.vocab, m->sampling, m->seq_len, st));
     m->launch_counter += 3;
   }
   ProfScope ps_tail(m, PROF_ELEMWISE);
@@ -917,6 +921,21 @@ logos_status_t logos_llm_set_seq_len(logos_handle_t model, int64_t t) {
     if (t < 0 || t > m->cfg.l_max) return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_set_seq_len: t outside [0,l_max]");
     std::vector<int32_t> len((size_t)m->cfg.batch, (int32_t)t);
     LOGOS_CUDA_TRY(cudaMemcpyAsync(m->seq_len, len.data(), len.size() * 4, cudaMemcpyHostToDevice, m->stream));
+    LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    return LOGOS_OK;
+  });
+}
+
+logos_status_t logos_llm_set_sampling(logos_handle_t model, float temperature, uint64_t seed) {
+  return guarded([&]() -> logos_status_t {
+    MODEL_OR_FAIL(m, model, "logos_llm_set_sampling");
+    if (!(temperature >= 0.0f) || temperature > 1e6f)
+      return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_set_sampling: temperature %g outside [0, 1e6]", (double)temperature);
+    SamplingParams p;
+    p.enabled = temperature > 0.0f ? 1 : 0;
+    p.inv_temperature = p.enabled ? 1.0f / temperature : 1.0f;
+    p.seed = seed;
+    LOGOS_CUDA_TRY(cudaMemcpyAsync(m->sampling, &p, sizeof(p), cudaMemcpyHostToDevice, m->stream));
     LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
     return LOGOS_OK;
   });

@@ -138,9 +138,17 @@ logos_status_t launch_tp_residual_rmsnorm(float* h, const TpFusedArgs& t, int pa
 logos_status_t launch_bf16_to_f16(const __nv_bfloat16* x, __half* y, int64_t count, cudaStream_t st);
 // f32 [count] -> activation planes
 logos_status_t launch_act_split(const float* x, ActOut o, int64_t count, cudaStream_t st);
-// tokens[row] = argmax(logits[row]) with the lowest index winning ties
+// Sampling state of a model, in device memory so that a captured step follows changes to it.
+struct SamplingParams {
+  float inv_temperature;  // 1 / T
+  int32_t enabled;        // 0: plain argmax
+  uint64_t seed;
+};
+// tokens[row] = argmax(logits[row]) with the lowest index winning ties.  With sampling enabled
+// (sampling_or_null and positions non-null) the compared value is
+// logit * inv_temperature + gumbel(seed, row, positions[row] * vocab + index).
 logos_status_t launch_argmax(const float* logits, int32_t* tokens, int32_t* history_or_null,
                              const int32_t* step_counter_or_null, int64_t history_rows, int64_t rows, int64_t vocab,
-                             cudaStream_t st);
+                             const SamplingParams* sampling_or_null, const int32_t* positions_or_null, cudaStream_t st);
 
 }  // namespace logos

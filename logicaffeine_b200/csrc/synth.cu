@@ -24,6 +24,8 @@ __global__ void synth_fill_kernel(void* dst, int dtype, int kind, uint64_t seed,
       if (dtype == LOGOS_F32) reinterpret_cast<float*>(dst)[i] = v;
       else if (dtype == LOGOS_F16) reinterpret_cast<__half*>(dst)[i] = __float2half_rn(v);
       else reinterpret_cast<__nv_bfloat16*>(dst)[i] = __float2bfloat16_rn(v);
+    } else if (kind == 4) {
+      reinterpret_cast<float*>(dst)[i] = synth::gumbel_f32(seed, stream, idx);
     } else {
       reinterpret_cast<int32_t*>(dst)[i] = synth::uniform_i32(seed, stream, idx, (uint32_t)b);
     }
@@ -153,6 +155,7 @@ logos_status_t logos_synth_fill(logos_handle_t dst, int64_t dst_offset_bytes, in
         if (dtype != LOGOS_I32) return fail(LOGOS_ERROR, "logos_synth_fill: kind 3 writes i32");
         if (!(b >= 1.0f)) return fail(LOGOS_OUT_OF_BOUNDS, "logos_synth_fill: kind 3 needs b >= 1");
         break;
+      case 4: esz = 4; if (dtype != LOGOS_F32) return fail(LOGOS_ERROR, "logos_synth_fill: kind 4 writes f32"); break;
       default: return fail(LOGOS_ERROR, "logos_synth_fill: unknown kind %d", kind);
     }
     if (dst_offset_bytes % esz) return fail(LOGOS_ERROR, "logos_synth_fill: offset not aligned to the element size");

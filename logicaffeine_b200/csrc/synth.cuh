@@ -103,6 +103,37 @@ __device__ __forceinline__ float normal_f32(uint64_t seed, uint64_t stream, uint
   return __fmul_rn(r, (idx & 1ull) ? sq : cq);
 }
 
+// ln of a positive normal float: the exponent comes off by bits, the mantissa (folded into
+// (0.707, 1.414]) goes through the same atanh series as above.
+__device__ __forceinline__ float ln_pos(float x) {
+  const int bits = __float_as_int(x);
+  int e = (bits >> 23) - 127;
+  float m = __int_as_float((bits & 0x007FFFFF) | 0x3F800000);
+  if (m > 1.41421354f) {
+    m = __fmul_rn(m, 0.5f);
+    e += 1;
+  }
+  float t = __fdiv_rn(__fsub_rn(m, 1.0f), __fadd_rn(m, 1.0f));
+  float t2 = __fmul_rn(t, t);
+  float p = 0.111111111f;
+  p = __fadd_rn(__fmul_rn(p, t2), 0.142857143f);
+  p = __fadd_rn(__fmul_rn(p, t2), 0.2f);
+  p = __fadd_rn(__fmul_rn(p, t2), 0.333333343f);
+  p = __fadd_rn(__fmul_rn(p, t2), 1.0f);
+  float ln_m = __fmul_rn(__fmul_rn(2.0f, t), p);
+  return __fadd_rn(ln_m, __fmul_rn((float)e, 0.693147182f));
+}
+
+// Standard Gumbel variate -ln(-ln u) with u = (2k + 1) * 2^-24 for a 23-bit k, so u lies strictly
+// inside (0, 1) and both logarithms see a positive normal number.  argmax(logit / T + gumbel)
+// draws from softmax(logit / T).
+__device__ __forceinline__ float gumbel_f32(uint64_t seed, uint64_t stream, uint64_t idx) {
+  const uint32_t k = (uint32_t)(ctr_hash(seed, stream, idx) >> 41);
+  const float u = __fmul_rn((float)(2u * k + 1u), 5.9604644775390625e-08f);  // * 2^-24, exact
+  const float l = -ln_pos(u);
+  return -ln_pos(l);
+}
+
 __device__ __forceinline__ float normal_scaled(uint64_t seed, uint64_t stream, uint64_t idx, float mean, float std) {
   return __fadd_rn(mean, __fmul_rn(std, normal_f32(seed, stream, idx)));
 }

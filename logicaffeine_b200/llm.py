@@ -302,6 +302,10 @@ class Llm:
     def setSeqLen(self, t):
         call("logos_llm_set_seq_len", self.handle, int(t))
 
+    def setSampling(self, temperature, seed=0):
+        """Temperature sampling by Gumbel-max on the seeded generator; temperature 0 is greedy."""
+        call("logos_llm_set_sampling", self.handle, float(temperature), int(seed))
+
     def lastTiming(self):
         ms = C.c_double()
         launches = C.c_int64()

@@ -169,6 +169,39 @@ static inline float gen_normal(uint64_t seed, uint64_t stream, uint64_t idx) {
   return r * ((idx & 1ull) ? sq : cq);
 }
 
+/* ln of a positive normal float (exponent by bits, atanh series on the mantissa) and the
+ * standard Gumbel variate -ln(-ln u), u = (2k+1) * 2^-24 for a 23-bit k. */
+static inline float ln_pos(float x) {
+  uint32_t bits;
+  memcpy(&bits, &x, 4);
+  int e = (int)(bits >> 23) - 127;
+  uint32_t mb = (bits & 0x007FFFFFu) | 0x3F800000u;
+  float m;
+  memcpy(&m, &mb, 4);
+  if (m > 1.41421354f) {
+    m = m * 0.5f;
+    e += 1;
+  }
+  float num = m - 1.0f, den = m + 1.0f;
+  float t = num / den;
+  float t2 = t * t;
+  float p = 0.111111111f;
+  p = p * t2; p = p + 0.142857143f;
+  p = p * t2; p = p + 0.2f;
+  p = p * t2; p = p + 0.333333343f;
+  p = p * t2; p = p + 1.0f;
+  float two_t = 2.0f * t;
+  float ln_m = two_t * p;
+  float ek = (float)e * 0.693147182f;
+  return ln_m + ek;
+}
+static inline float gen_gumbel(uint64_t seed, uint64_t stream, uint64_t idx) {
+  uint32_t k = (uint32_t)(ctr_hash(seed, stream, idx) >> 41);
+  float u = (float)(2u * k + 1u) * 5.9604644775390625e-08f;
+  float l = -ln_pos(u);
+  return -ln_pos(l);
+}
+
 ORC_API void orc_synth_fill(void* dst, int dtype, int kind, uint64_t seed, uint64_t stream,
                             int64_t first, int64_t count, float a, float b) {
 #pragma omp parallel for schedule(static)
@@ -185,6 +218,8 @@ ORC_API void orc_synth_fill(void* dst, int dtype, int kind, uint64_t seed, uint6
       if (dtype == ORC_F32) ((float*)dst)[i] = v;
       else if (dtype == ORC_F16) ((uint16_t*)dst)[i] = f2h(v);
       else ((uint16_t*)dst)[i] = f2bf(v);
+    } else if (kind == 4) {
+      ((float*)dst)[i] = gen_gumbel(seed, stream, idx);
     } else {
       uint32_t r = (uint32_t)(ctr_hash(seed, stream, idx) >> 32);
       ((int32_t*)dst)[i] = (int32_t)(r % (uint32_t)b);
@@ -544,6 +579,9 @@ typedef struct {
   int32_t* tokens;
   float* logits;
   float* h; /* residual stream [B][H] */
+  int sampling; /* 0: greedy argmax */
+  float inv_temperature;
+  uint64_t sample_seed;
 } orc_llm;
 
 static q8mat make_mat(int64_t n, int64_t k, uint64_t seed, uint64_t stream, float std) {
@@ -616,6 +654,34 @@ static void round_rows(float* x, int64_t n, int act_dtype) {
   for (int64_t i = 0; i < n; ++i) x[i] = round_act(x[i], act_dtype);
 }
 
+/* Next token per row: argmax with the lowest index winning ties; with sampling enabled the
+ * compared value is logit * inv_temperature + gumbel(seed, row, position * vocab + index)
+ * (Gumbel-max: a draw from softmax(logits / temperature) that depends only on seed, row and
+ * position). */
+ORC_API void orc_sample_rows(const float* logits, int64_t rows, int64_t vocab, int enabled, float inv_temperature,
+                             uint64_t seed, const int32_t* positions, int32_t* tokens) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < rows; ++i) {
+    const float* lg = logits + i * vocab;
+    uint64_t first = enabled ? (uint64_t)positions[i] * (uint64_t)vocab : 0;
+    int64_t best = 0;
+    float best_v = 0.0f;
+    for (int64_t v = 0; v < vocab; ++v) {
+      float x = lg[v];
+      if (enabled) {
+        float scaled = x * inv_temperature;
+        float g = gen_gumbel(seed, (uint64_t)i, first + (uint64_t)v);
+        x = scaled + g;
+      }
+      if (v == 0 || x > best_v) {
+        best = v;
+        best_v = x;
+      }
+    }
+    tokens[i] = (int32_t)best;
+  }
+}
+
 /* One step for all sequences.  `sample` 0 skips the lm_head (prompt tokens). */
 static void llm_step(orc_llm* M, int sample) {
   const orc_llm_config_t* c = &M->cfg;
@@ -677,13 +743,8 @@ static void llm_step(orc_llm* M, int sample) {
     round_rows(xn, B * H, act);
     const q8mat* hd = c->tied_embeddings ? &M->embed : &M->head;
     orc_q8_gemm_f32(xn, ORC_F32, hd->q, hd->s, M->logits, B, c->vocab, H);
-    for (int64_t i = 0; i < B; ++i) {
-      const float* lg = M->logits + i * c->vocab;
-      int64_t best = 0;
-      for (int64_t v = 1; v < c->vocab; ++v)
-        if (lg[v] > lg[best]) best = v;
-      M->tokens[i] = (int32_t)best;
-    }
+    for (int64_t i = 0; i < B; ++i) len1[i] = M->seq_len[i] - 1; /* position of the token just consumed */
+    orc_sample_rows(M->logits, B, c->vocab, M->sampling, M->inv_temperature, M->sample_seed, len1, M->tokens);
   }
   free(xn); free(qf); free(kf); free(vf); free(qh); free(att); free(delta); free(gate); free(up); free(len1);
 }
@@ -738,6 +799,14 @@ ORC_API int orc_llm_get_tensor(void* model, int64_t layer, int kind, void* q, fl
     memcpy(s, mat->s, sizeof(float) * (size_t)(mat->n * (mat->k / 32)));
   }
   return 0;
+}
+
+/* temperature 0 = greedy */
+ORC_API void orc_llm_set_sampling(void* model, float temperature, uint64_t seed) {
+  orc_llm* M = (orc_llm*)model;
+  M->sampling = temperature > 0.0f ? 1 : 0;
+  M->inv_temperature = M->sampling ? 1.0f / temperature : 1.0f;
+  M->sample_seed = seed;
 }
 
 ORC_API void orc_llm_prefill(void* model, const int32_t* tokens, int64_t t) {

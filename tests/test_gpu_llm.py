@@ -107,3 +107,43 @@ def test_synth_kv_matches_oracle_and_decodes(llm, oracle):
     assert np.array_equal(got, want)
     gpu.free()
     ref.close()
+
+
+def test_temperature_sampling_tokens_match_the_oracle(llm, oracle):
+    """Gumbel-max on the seeded generator: the draw is a pure function of (seed, sequence,
+    position), so the GPU (eager first step, then the replayed graph) and the oracle pick the
+    same tokens; switching back to temperature 0 under the captured graph is greedy again."""
+    O = oracle
+    t, steps = 5, 24
+    toks = O.synth_fill(O.I32, 3, SMALL["seed"], 999, 0, SMALL["batch"] * t, 0.0, float(SMALL["vocab"]))
+    toks = toks.reshape(SMALL["batch"], t)
+    ref = O.Llm(tp_degree=1, tp_rank=0, device=0, act_dtype=O.F32, **SMALL)
+    gpu = llm.Llm(act_dtype=llm.F32, **SMALL)
+    greedy_ref = O.Llm(tp_degree=1, tp_rank=0, device=0, act_dtype=O.F32, **SMALL)
+    greedy_ref.prefill(toks)
+    greedy = np.array([greedy_ref.decode_step().copy() for _ in range(steps)])
+    for m, setter in ((ref, ref.set_sampling), (gpu, gpu.setSampling)):
+        setter(0.9, 1234)
+        m.prefill(toks)
+    want = np.array([ref.decode_step().copy() for _ in range(steps)])
+    got = gpu.decodeSteps(steps)
+    assert np.array_equal(got, want)
+    assert not np.array_equal(want, greedy)
+    # other seed: other tokens, still equal
+    ref.set_sampling(0.9, 99)
+    gpu.setSampling(0.9, 99)
+    ref.prefill(toks)
+    gpu.prefill(toks)
+    want2 = np.array([ref.decode_step().copy() for _ in range(steps)])
+    got2 = gpu.decodeSteps(steps)
+    assert np.array_equal(got2, want2) and not np.array_equal(want2, want)
+    # back to greedy under the captured step
+    gpu.setSampling(0.0, 0)
+    gpu.prefill(toks)
+    assert np.array_equal(gpu.decodeSteps(steps), greedy)
+    with pytest.raises(llm.LogosError) as e:
+        gpu.setSampling(-1.0, 0)
+    assert e.value.status == 4
+    gpu.free()
+    ref.close()
+    greedy_ref.close()

@@ -22,7 +22,8 @@ def test_generator_matches_oracle_bit_for_bit(llm, oracle):
     n = 100_003
     for dtype, kind, npdt, a, b in ((llm.I8, 0, np.int8, 0.0, 0.0), (llm.F32, 1, np.float32, 1e-3, 1e-2),
                                     (llm.F32, 2, np.float32, 0.0, 1.0), (llm.F16, 2, np.uint16, 0.0, 1.0),
-                                    (llm.BF16, 2, np.uint16, 0.5, 0.02), (llm.I32, 3, np.int32, 0.0, 151936.0)):
+                                    (llm.BF16, 2, np.uint16, 0.5, 0.02), (llm.I32, 3, np.int32, 0.0, 151936.0),
+                                    (llm.F32, 4, np.float32, 0.0, 0.0)):     # 4: Gumbel (temperature sampling)
         buf = llm.DeviceBuffer(n * np.dtype(npdt).itemsize)
         llm.synthFill(buf, dtype, kind, 42, 5, 7, n, a, b)
         got = buf.download(npdt, (n,))

@@ -1,0 +1,76 @@
+"""Temperature sampling in the oracle: the Gumbel variate of the seeded generator has the right
+distribution, Gumbel-max draws follow softmax(logits / T), temperature 0 is the plain argmax,
+and a draw depends on (seed, row, position) only."""
+import numpy as np
+
+
+def test_gumbel_variate_moments_and_range(oracle):
+    O = oracle
+    g = O.synth_fill(O.F32, 4, 12, 3, 0, 400000)
+    assert np.isfinite(g).all()
+    # u = (2k+1) * 2^-24 lies strictly inside (0,1): -ln(-ln u) is bounded on both sides
+    assert g.min() > -3.0 and g.max() < 17.0
+    assert abs(g.mean() - 0.5772157) < 0.01                    # Euler-Mascheroni
+    assert abs(g.var() - np.pi ** 2 / 6) < 0.03
+    again = O.synth_fill(O.F32, 4, 12, 3, 0, 400000)
+    assert np.array_equal(g, again)
+    other = O.synth_fill(O.F32, 4, 12, 4, 0, 1000)
+    assert not np.array_equal(g[:1000], other)
+    # a window of the same stream is the same values
+    assert np.array_equal(O.synth_fill(O.F32, 4, 12, 3, 1000, 500), g[1000:1500])
+
+
+def test_gumbel_max_draws_follow_the_softmax(oracle):
+    O = oracle
+    logits = np.array([0.0, 1.0, 2.0, -1.0, 0.5, 2.5, -3.0, 1.5], np.float32)
+    n = 40000
+    for temperature in (1.0, 0.5, 2.0):
+        rows = np.tile(logits, (n, 1))
+        # every row its own stream, every row its own position: n independent draws
+        tok = O.sample_rows(rows, temperature, seed=9, positions=np.arange(n) % 1000)
+        freq = np.bincount(tok, minlength=8) / n
+        p = np.exp(logits.astype(np.float64) / temperature)
+        p /= p.sum()
+        sigma = np.sqrt(p * (1 - p) / n)
+        assert np.all(np.abs(freq - p) < 5 * sigma + 1e-4), (temperature, freq, p)
+
+
+def test_temperature_zero_is_argmax_with_lowest_index_on_ties(oracle):
+    O = oracle
+    x = np.array([[1.0, 3.0, 3.0, 2.0], [5.0, 5.0, 5.0, 5.0], [-1.0, -2.0, -0.5, -0.5]], np.float32)
+    assert O.sample_rows(x, 0.0, seed=1, positions=[0, 0, 0]).tolist() == [1, 0, 2]
+
+
+def test_a_draw_depends_on_seed_row_and_position_only(oracle):
+    O = oracle
+    rng = np.random.default_rng(0)
+    x = rng.normal(size=(6, 512)).astype(np.float32)
+    pos = np.array([3, 4, 5, 6, 7, 8], np.int32)
+    a = O.sample_rows(x, 1.0, 5, pos)
+    assert np.array_equal(a, O.sample_rows(x, 1.0, 5, pos))
+    # the same logits in the same row at the same position give the same token whatever the other rows hold
+    y = x.copy()
+    y[1:] = rng.normal(size=(5, 512)).astype(np.float32)
+    assert O.sample_rows(y, 1.0, 5, pos)[0] == a[0]
+    # another seed or other positions move the draws
+    assert not np.array_equal(a, O.sample_rows(x, 1.0, 6, pos))
+    assert not np.array_equal(a, O.sample_rows(x, 1.0, 5, pos + 1))
+
+
+def test_oracle_model_samples_reproducibly(oracle):
+    O = oracle
+    cfg = dict(layers=2, hidden=128, h_q=4, h_kv=2, head_dim=64, ffn=256, vocab=320, l_max=32, batch=3,
+               rms_eps=1e-6, rope_theta=1e6, tied_embeddings=1, seed=2, init_std=0.02)
+    toks = O.synth_fill(O.I32, 3, 2, 999, 0, 3 * 4, 0.0, 320.0).reshape(3, 4)
+
+    def run(temperature, seed):
+        m = O.Llm(tp_degree=1, tp_rank=0, device=0, act_dtype=O.F32, **cfg)
+        m.set_sampling(temperature, seed)
+        m.prefill(toks)
+        out = np.array([m.decode_step().copy() for _ in range(8)])
+        m.close()
+        return out
+
+    greedy, a, b, c = run(0.0, 1), run(1.0, 1), run(1.0, 1), run(1.0, 2)
+    assert np.array_equal(a, b)
+    assert not np.array_equal(a, greedy) and not np.array_equal(a, c)
