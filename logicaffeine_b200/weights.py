@@ -113,6 +113,24 @@ def writeWeightsFile(path, cfg, get_tensor):
     return total
 
 
+def q8QuantizeHost(w):
+    """Q8 blocks of a float matrix on the host, for converting a float checkpoint into a weight
+    file: per 32 elements along k, s = max|w| / 127 (f32 division), q = round-half-even(w / s),
+    an all-zero block stores s = 0.  The same rule, bit for bit, as the library's
+    logos_q8_quantize kernel.  Returns (q int8 [n][k], s f32 [n][k/32])."""
+    w = np.ascontiguousarray(w, np.float32)
+    n, k = w.shape
+    if k % 32:
+        raise ValueError("k = %d is not a multiple of the Q8 block 32" % k)
+    blocks = w.reshape(n, k // 32, 32)
+    amax = np.abs(blocks).max(axis=2)
+    s = (amax / np.float32(127.0)).astype(np.float32)
+    safe = np.where(amax > 0, s, np.float32(1.0)).astype(np.float32)
+    q = np.rint((blocks / safe[:, :, None]).astype(np.float32))
+    q = np.where(amax[:, :, None] > 0, np.clip(q, -127, 127), 0).astype(np.int8)
+    return q.reshape(n, k), s
+
+
 def _cfg_struct(cfg):
     if isinstance(cfg, LlmConfig):
         return cfg

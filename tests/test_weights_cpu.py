@@ -170,3 +170,17 @@ def test_oracle_tensors_round_trip_and_gains_are_used(oracle):
         a.get_tensor(5, W.Q)
     for m in (a, b, c):
         m.close()
+
+
+def test_host_quantiser_equals_the_oracle_bit_for_bit(oracle):
+    O = oracle
+    w = O.synth_fill(O.F32, 2, 7, 1, 0, 96 * 256, 0.0, 0.02).reshape(96, 256)
+    w[5, 32:64] = 0.0                       # an all-zero block
+    w[6, 0] = 3.0                           # an outlier that sets its block's scale
+    w[7, :32] = np.float32(1e-30)           # tiny values: the scale is subnormal-free but small
+    q, s = W.q8QuantizeHost(w)
+    q0, s0 = O.q8_quantize(w)
+    assert np.array_equal(q, q0)
+    assert np.array_equal(s.view(np.uint32), s0.view(np.uint32))
+    with pytest.raises(ValueError):
+        W.q8QuantizeHost(np.zeros((2, 40), np.float32))
