@@ -242,6 +242,32 @@ def op_probe(args):
         print(json.dumps({"op": "mma_probe", "kind": "tcgen05.mma kind::f16 M=128 K=16", "steady": rows,
                           "burst_n64_tmem": burst}), flush=True)
         return
+    if args.op == "weights":
+        # weight file: save the workload's model (seeded weights), then time loading the file back
+        # (host wall clock around the call; the file was just written, so it comes from the page cache)
+        import tempfile
+        from logicaffeine_b200 import weights as W
+        cfg = {k: v for k, v in WORKLOADS[args.workload].items() if k != "ctx"}
+        cfg.update(batch=1, l_max=64, seed=0, init_std=0.02)
+        model = llm.Llm(**cfg)
+        with tempfile.TemporaryDirectory() as tmp:
+            path = os.path.join(tmp, "model.q8w")
+            t0 = time.perf_counter()
+            model.saveWeights(path)
+            t_save = time.perf_counter() - t0
+            size = os.path.getsize(path)
+            assert size == W.weightsFileBytes(cfg)
+            loads = []
+            for _ in range(3):
+                t0 = time.perf_counter()
+                model.loadWeights(path)
+                loads.append(time.perf_counter() - t0)
+        model.free()
+        print(json.dumps({"op": "weights", "workload": args.workload, "file_bytes": size, "save_s": t_save,
+                          "load_s": loads, "load_gbs": size / min(loads) / 1e9,
+                          "how": "mmap + two pinned 32 MiB staging buffers + cudaMemcpy2DAsync, page cache hot"}),
+              flush=True)
+        return
     if args.op == "q8_gemm":
         a = llm.DeviceBuffer(m * k * 4, dev)
         c = llm.DeviceBuffer(m * n * 4, dev)
@@ -320,7 +346,7 @@ def main():
     ap.add_argument("--prefill", default="synthetic-kv", choices=["synthetic-kv", "prompt"])
     ap.add_argument("--act", default="f32", choices=["f32", "f16", "bf16"])
     ap.add_argument("--no-extras", action="store_true", help="skip the CPU baseline and the GEMV probe")
-    ap.add_argument("--op", default="decode", choices=["decode", "q8_gemm", "q8_gemv", "attention", "mma_probe"],
+    ap.add_argument("--op", default="decode", choices=["decode", "q8_gemm", "q8_gemv", "attention", "mma_probe", "weights"],
                     help="time one operator instead of the decode loop (attention: --m sequences, --n context)")
     ap.add_argument("--m", type=int, default=64)
     ap.add_argument("--n", type=int, default=18944)
