@@ -241,6 +241,12 @@ LOGOS_API logos_status_t logos_llm_create(const logos_llm_config_t* cfg, const v
 /* Process t prompt tokens per sequence ([B][T] row-major, host) and fill the KV
  * cache; sequence lengths become t.  Starts from an empty cache. */
 LOGOS_API logos_status_t logos_llm_prefill(logos_handle_t model, const int32_t* tokens_host, int64_t t);
+/* Prompts of different lengths: sequence b consumes tokens_host[b][0 .. lens_host[b]) of a
+ * [B][t_max] array, 0 <= lens_host[b] <= t_max.  Afterwards its length is lens_host[b] and its
+ * current token is the one chosen after its last prompt token (token 0 for an empty prompt);
+ * decode steps then run all sequences in lock step, each at its own position. */
+LOGOS_API logos_status_t logos_llm_prefill_ragged(logos_handle_t model, const int32_t* tokens_host, int64_t t_max,
+                                                  const int32_t* lens_host);
 /* Fill the KV cache for positions [0,t) with seeded N(0,1) fp16 values instead
  * of running a prompt (measurement of decode at a given context length). */
 LOGOS_API logos_status_t logos_llm_synth_kv(logos_handle_t model, int64_t t, uint64_t seed);

@@ -283,12 +283,14 @@ __global__ void act_split_kernel(const float* __restrict__ x, ActOut o, int64_t 
 __global__ void argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ tokens,
                               int32_t* __restrict__ history, const int32_t* __restrict__ step_counter,
                               int64_t history_rows, int64_t vocab, const SamplingParams* __restrict__ sampling,
-                              const int32_t* __restrict__ positions) {
+                              const int32_t* __restrict__ positions, const int32_t* __restrict__ only_ending,
+                              int prompt_step) {
   __shared__ float bv[32];
   __shared__ int bi[32];
   pdl_wait();
   pdl_trigger();
   const int64_t row = blockIdx.x;
+  if (only_ending && only_ending[row] - 1 != prompt_step) return;  // this sequence's prompt does not end here
   const float* lr = logits + row * vocab;
   float best = -INFINITY;
   int idx = 0x7fffffff;
@@ -429,10 +431,12 @@ logos_status_t launch_tp_residual_rmsnorm(float* h, const TpFusedArgs& t, int pa
 
 logos_status_t launch_argmax(const float* logits, int32_t* tokens, int32_t* history_or_null,
                              const int32_t* step_counter_or_null, int64_t history_rows, int64_t rows, int64_t vocab,
-                             const SamplingParams* sampling_or_null, const int32_t* positions_or_null, cudaStream_t st) {
+                             const SamplingParams* sampling_or_null, const int32_t* positions_or_null,
+                             const int32_t* only_ending_or_null, int prompt_step, cudaStream_t st) {
   if (rows == 0) return LOGOS_OK;
   LOGOS_CUDA_TRY(launch_kernel(argmax_kernel, dim3((unsigned)rows), dim3(1024), 0, st, logits, tokens, history_or_null,
-                               step_counter_or_null, history_rows, vocab, sampling_or_null, positions_or_null));
+                               step_counter_or_null, history_rows, vocab, sampling_or_null, positions_or_null,
+                               only_ending_or_null, prompt_step));
   count_launch(LK_ELEMWISE);
   return check_launch("argmax_kernel");
 }

@@ -299,11 +299,13 @@ __global__ void sum_partials_kernel(float* __restrict__ p, int parts, int64_t st
   p[i] = v;
 }
 
-__global__ void bump_len_kernel(int32_t* seq_len, int32_t* step_counter, int b, int l_max) {
+// prompt_len (ragged prompts, null otherwise): only sequences with prompt_step < prompt_len[i] advance
+__global__ void bump_len_kernel(int32_t* seq_len, int32_t* step_counter, int b, int l_max,
+                                const int32_t* __restrict__ prompt_len, int prompt_step) {
   pdl_wait();
   pdl_trigger();
   int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < b && seq_len[i] < l_max) seq_len[i] += 1;
+  if (i < b && seq_len[i] < l_max && (!prompt_len || prompt_step < prompt_len[i])) seq_len[i] += 1;
   if (i == 0) *step_counter += 1;
 }
 
@@ -407,7 +409,12 @@ logos_status_t norm_step(Model* m, int parts, int64_t gain_row) {
 }
 
 // One lock-step decode step on the model's stream.  tokens_in: [B] device.
-logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_tokens) {
+// prompt_len ([B] device, ragged prompts only) with prompt_step: sequences whose prompt is over
+// (prompt_step >= prompt_len[i]) run through the step without advancing - their K/V row lands at
+// their next free position and is overwritten when they do advance - and only sequences whose
+// prompt ends at this step take the sampled token.
+logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_tokens,
+                    const int32_t* prompt_len = nullptr, int prompt_step = 0) {
   const logos_llm_config_t& c = m->cfg;
   const int64_t B = c.batch, H = c.hidden, D = c.head_dim;
   cudaStream_t st = m->stream;
@@ -486,12 +493,12 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
     ProfScope ps(m, PROF_ELEMWISE);
     // seq_len still holds the position of the token this step consumed (bump_len_kernel runs last)
     LOGOS_TRY(launch_argmax(m->logits, m->tokens, log_tokens ? m->history : nullptr, m->step_counter, m->history_cap, B,
-                            c.vocab, m->sampling, m->seq_len, st));
+                            c.vocab, m->sampling, m->seq_len, prompt_len, prompt_step, st));
     m->launch_counter += 3;
   }
   ProfScope ps_tail(m, PROF_ELEMWISE);
   LOGOS_CUDA_TRY(launch_kernel(bump_len_kernel, dim3((unsigned)((B + 127) / 128)), dim3(128), 0, st, m->seq_len,
-                               m->step_counter, (int)B, (int)c.l_max));
+                               m->step_counter, (int)B, (int)c.l_max, prompt_len, prompt_step));
   LOGOS_TRY(check_launch("bump_len_kernel"));
   m->launch_counter += 1;
   m->launches_per_step = m->launch_counter;
@@ -770,6 +777,51 @@ logos_status_t logos_llm_prefill(logos_handle_t model, const int32_t* tokens_hos
     LOGOS_CUDA_TRY(cudaMemcpyAsync(m->prompt, tr.data(), tr.size() * 4, cudaMemcpyHostToDevice, m->stream));
     LOGOS_CUDA_TRY(cudaMemsetAsync(m->seq_len, 0, (size_t)B * 4, m->stream));
     for (int64_t p = 0; p < t; ++p) LOGOS_TRY(step(m, m->prompt + p * B, p == t - 1, false));
+    LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    return LOGOS_OK;
+  });
+}
+
+logos_status_t logos_llm_prefill_ragged(logos_handle_t model, const int32_t* tokens_host, int64_t t_max,
+                                        const int32_t* lens_host) {
+  return guarded([&]() -> logos_status_t {
+    MODEL_OR_FAIL(m, model, "logos_llm_prefill_ragged");
+    if (!tokens_host || !lens_host) return fail(LOGOS_NULL_POINTER, "logos_llm_prefill_ragged: null argument");
+    const int64_t B = m->cfg.batch;
+    if (t_max <= 0 || t_max > m->cfg.l_max)
+      return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_prefill_ragged: t_max=%lld outside [1,%lld]", (long long)t_max,
+                  (long long)m->cfg.l_max);
+    int64_t longest = 0;
+    for (int64_t b = 0; b < B; ++b) {
+      if (lens_host[b] < 0 || lens_host[b] > t_max)
+        return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_prefill_ragged: length %d of sequence %lld outside [0,%lld]", lens_host[b],
+                    (long long)b, (long long)t_max);
+      if (lens_host[b] > longest) longest = lens_host[b];
+      for (int64_t p = 0; p < lens_host[b]; ++p)
+        if (tokens_host[b * t_max + p] < 0 || tokens_host[b * t_max + p] >= m->cfg.vocab)
+          return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_prefill_ragged: token id %d outside the vocabulary",
+                      tokens_host[b * t_max + p]);
+    }
+    // device: [longest][B] prompt tokens (0 past a sequence's end), then the [B] lengths
+    const int64_t need = (longest + 1) * B;
+    if (m->prompt_cap < need) {
+      LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->prompt), need * 4));
+      m->prompt_cap = need;
+    }
+    std::vector<int32_t> tr((size_t)need, 0);
+    for (int64_t b = 0; b < B; ++b) {
+      for (int64_t p = 0; p < lens_host[b]; ++p) tr[(size_t)(p * B + b)] = tokens_host[b * t_max + p];
+      tr[(size_t)(longest * B + b)] = lens_host[b];
+    }
+    LOGOS_CUDA_TRY(cudaMemcpyAsync(m->prompt, tr.data(), tr.size() * 4, cudaMemcpyHostToDevice, m->stream));
+    LOGOS_CUDA_TRY(cudaMemsetAsync(m->seq_len, 0, (size_t)B * 4, m->stream));
+    LOGOS_CUDA_TRY(cudaMemsetAsync(m->tokens, 0, (size_t)B * 4, m->stream));  // an empty prompt leaves token 0
+    const int32_t* lens_dev = m->prompt + longest * B;
+    for (int64_t p = 0; p < longest; ++p) {
+      bool ends_here = false;
+      for (int64_t b = 0; b < B; ++b) ends_here = ends_here || lens_host[b] - 1 == p;
+      LOGOS_TRY(step(m, m->prompt + p * B, ends_here, false, lens_dev, (int)p));
+    }
     LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
     return LOGOS_OK;
   });

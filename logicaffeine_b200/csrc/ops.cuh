@@ -147,8 +147,10 @@ struct SamplingParams {
 // tokens[row] = argmax(logits[row]) with the lowest index winning ties.  With sampling enabled
 // (sampling_or_null and positions non-null) the compared value is
 // logit * inv_temperature + gumbel(seed, row, positions[row] * vocab + index).
+// only_ending_or_null (ragged prompts): a row is written only if only_ending[row] - 1 == prompt_step.
 logos_status_t launch_argmax(const float* logits, int32_t* tokens, int32_t* history_or_null,
                              const int32_t* step_counter_or_null, int64_t history_rows, int64_t rows, int64_t vocab,
-                             const SamplingParams* sampling_or_null, const int32_t* positions_or_null, cudaStream_t st);
+                             const SamplingParams* sampling_or_null, const int32_t* positions_or_null,
+                             const int32_t* only_ending_or_null, int prompt_step, cudaStream_t st);
 
 }  // namespace logos

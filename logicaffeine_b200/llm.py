@@ -264,6 +264,13 @@ class Llm:
         assert tokens.shape[0] == self.cfg.batch
         call("logos_llm_prefill", self.handle, _host_ptr(tokens), int(tokens.shape[1]))
 
+    def prefillRagged(self, tokens, lens):
+        """tokens [B][t_max]; sequence b consumes tokens[b, :lens[b]] (0 <= lens[b] <= t_max)."""
+        tokens = np.ascontiguousarray(tokens, np.int32)
+        lens = np.ascontiguousarray(lens, np.int32)
+        assert tokens.shape[0] == self.cfg.batch and lens.shape == (self.cfg.batch,)
+        call("logos_llm_prefill_ragged", self.handle, _host_ptr(tokens), int(tokens.shape[1]), _host_ptr(lens))
+
     def synthKv(self, t, seed=0):
         call("logos_llm_synth_kv", self.handle, int(t), int(seed))
 

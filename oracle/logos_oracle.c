@@ -682,8 +682,12 @@ ORC_API void orc_sample_rows(const float* logits, int64_t rows, int64_t vocab, i
   }
 }
 
-/* One step for all sequences.  `sample` 0 skips the lm_head (prompt tokens). */
-static void llm_step(orc_llm* M, int sample) {
+/* One step for all sequences.  `sample` 0 skips the lm_head (prompt tokens).  With `lens`
+ * (ragged prompts, step p of the prefill): only sequences with p < lens[i] advance, and only
+ * those whose prompt ends here (lens[i] - 1 == p) take the sampled token; the others keep
+ * theirs.  A sequence that does not advance still runs through the step - its K/V row lands
+ * at its next free position and is overwritten when the sequence does advance. */
+static void llm_step(orc_llm* M, int sample, const int32_t* lens, int64_t p) {
   const orc_llm_config_t* c = &M->cfg;
   int64_t B = c->batch, H = c->hidden, D = c->head_dim, F = c->ffn;
   int64_t nq = c->h_q * D, nkv = c->h_kv * D;
@@ -737,14 +741,19 @@ static void llm_step(orc_llm* M, int sample) {
     orc_q8_gemm_f32(gate, ORC_F32, M->wd[l].q, M->wd[l].s, delta, B, H, F);
     for (int64_t i = 0; i < B * H; ++i) M->h[i] = M->h[i] + delta[i];
   }
-  for (int64_t i = 0; i < B; ++i) M->seq_len[i] += 1;
+  for (int64_t i = 0; i < B; ++i)
+    if (!lens || p < lens[i]) M->seq_len[i] += 1;
   if (sample) {
     orc_rmsnorm(M->h, M->gains + (2 * c->layers) * H, xn, B, H, c->rms_eps);
     round_rows(xn, B * H, act);
     const q8mat* hd = c->tied_embeddings ? &M->embed : &M->head;
     orc_q8_gemm_f32(xn, ORC_F32, hd->q, hd->s, M->logits, B, c->vocab, H);
-    for (int64_t i = 0; i < B; ++i) len1[i] = M->seq_len[i] - 1; /* position of the token just consumed */
-    orc_sample_rows(M->logits, B, c->vocab, M->sampling, M->inv_temperature, M->sample_seed, len1, M->tokens);
+    int32_t* tok = (int32_t*)malloc(4 * (size_t)B);
+    for (int64_t i = 0; i < B; ++i) len1[i] = M->seq_len[i] > 0 ? M->seq_len[i] - 1 : 0; /* position of the token just consumed */
+    orc_sample_rows(M->logits, B, c->vocab, M->sampling, M->inv_temperature, M->sample_seed, len1, tok);
+    for (int64_t i = 0; i < B; ++i)
+      if (!lens || lens[i] - 1 == p) M->tokens[i] = tok[i];
+    free(tok);
   }
   free(xn); free(qf); free(kf); free(vf); free(qh); free(att); free(delta); free(gate); free(up); free(len1);
 }
@@ -815,8 +824,31 @@ ORC_API void orc_llm_prefill(void* model, const int32_t* tokens, int64_t t) {
   for (int64_t i = 0; i < B; ++i) M->seq_len[i] = 0;
   for (int64_t p = 0; p < t; ++p) {
     for (int64_t i = 0; i < B; ++i) M->tokens[i] = tokens[i * t + p];
-    llm_step(M, p == t - 1);
+    llm_step(M, p == t - 1, NULL, 0);
   }
+}
+/* Prompts of different lengths: sequence i consumes tokens[i][0 .. lens[i]) of a [B][t_max]
+ * array (0 <= lens[i] <= t_max); afterwards its length is lens[i] and its current token is the
+ * one sampled after its last prompt token (token 0 for an empty prompt). */
+ORC_API void orc_llm_prefill_ragged(void* model, const int32_t* tokens, int64_t t_max, const int32_t* lens) {
+  orc_llm* M = (orc_llm*)model;
+  int64_t B = M->cfg.batch;
+  int32_t* next = (int32_t*)calloc((size_t)B, 4);
+  for (int64_t i = 0; i < B; ++i) M->seq_len[i] = 0;
+  for (int64_t p = 0; p < t_max; ++p) {
+    int ends_here = 0, active = 0;
+    for (int64_t i = 0; i < B; ++i) {
+      M->tokens[i] = p < lens[i] ? tokens[i * t_max + p] : 0;
+      if (lens[i] - 1 == p) ends_here = 1;
+      if (p < lens[i]) active = 1;
+    }
+    if (!active) break;
+    llm_step(M, ends_here, lens, p);
+    for (int64_t i = 0; i < B; ++i)
+      if (lens[i] - 1 == p) next[i] = M->tokens[i];
+  }
+  memcpy(M->tokens, next, 4 * (size_t)B);
+  free(next);
 }
 /* Fill positions [0,t) of every layer's cache with seeded N(0,1) fp16 values
  * (streams 2l for K, 2l+1 for V, index = flat index in the [B][Hkv][Lmax][D]
@@ -841,7 +873,7 @@ ORC_API void orc_llm_set_tokens(void* model, const int32_t* tokens) {
 }
 ORC_API void orc_llm_decode_step(void* model, int32_t* next_tokens) {
   orc_llm* M = (orc_llm*)model;
-  llm_step(M, 1);
+  llm_step(M, 1, NULL, 0);
   if (next_tokens) memcpy(next_tokens, M->tokens, 4 * (size_t)M->cfg.batch);
 }
 ORC_API void orc_llm_read_kv(void* model, int64_t layer, uint16_t* k, uint16_t* v) {

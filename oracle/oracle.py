@@ -221,6 +221,12 @@ class Llm:
         tokens = np.ascontiguousarray(tokens, np.int32)
         lib().orc_llm_prefill(self._h, _p(tokens), C.c_int64(tokens.shape[1]))
 
+    def prefill_ragged(self, tokens, lens):
+        """tokens [B][t_max]; sequence i consumes tokens[i, :lens[i]]."""
+        tokens = np.ascontiguousarray(tokens, np.int32)
+        lens = np.ascontiguousarray(lens, np.int32)
+        lib().orc_llm_prefill_ragged(self._h, _p(tokens), C.c_int64(tokens.shape[1]), _p(lens))
+
     def synth_kv(self, t, seed=0):
         lib().orc_llm_synth_kv(self._h, C.c_int64(t), C.c_uint64(seed))
 

@@ -147,3 +147,39 @@ def test_temperature_sampling_tokens_match_the_oracle(llm, oracle):
     gpu.free()
     ref.close()
     greedy_ref.close()
+
+
+def test_ragged_prompts_tokens_lengths_and_kv(llm, oracle):
+    """Prompts of 9, 1, 5 and 0 tokens in one batch: every sequence ends up at its own length with
+    the token chosen after its own last prompt token, and lock-step decode from there equals the
+    oracle's (each sequence at its own position)."""
+    O = oracle
+    t_max, steps = 9, 20
+    lens = np.array([9, 1, 5, 0], np.int32)
+    toks = O.synth_fill(O.I32, 3, SMALL["seed"], 999, 0, SMALL["batch"] * t_max, 0.0, float(SMALL["vocab"]))
+    toks = toks.reshape(SMALL["batch"], t_max)
+    ref = O.Llm(tp_degree=1, tp_rank=0, device=0, act_dtype=O.F32, **SMALL)
+    gpu = llm.Llm(act_dtype=llm.F32, **SMALL)
+    ref.prefill_ragged(toks, lens)
+    gpu.prefillRagged(toks, lens)
+    assert np.array_equal(gpu.readSeqLen(), lens) and np.array_equal(ref.read_seq_len(), lens)
+    want = np.array([ref.decode_step().copy() for _ in range(steps)])
+    got = gpu.decodeSteps(steps)
+    assert np.array_equal(got, want)
+    assert np.array_equal(gpu.readSeqLen(), lens + steps)
+    k, v = gpu.readKv(0)
+    kr, vr = ref.read_kv(0)
+    for b, n in enumerate(lens + steps):
+        assert np.array_equal(k[b, :, :n] != 0, kr[b, :, :n] != 0)
+        assert rel_l2(O.f16_to_f32(k[b, :, :n]), O.f16_to_f32(kr[b, :, :n])) < 2e-4
+        assert rel_l2(O.f16_to_f32(v[b, :, :n]), O.f16_to_f32(vr[b, :, :n])) < 2e-4
+    # equal lengths: the same as the plain prefill
+    gpu.prefillRagged(toks, np.full(4, t_max, np.int32))
+    a = gpu.decodeSteps(8)
+    gpu.prefill(toks)
+    assert np.array_equal(gpu.decodeSteps(8), a)
+    with pytest.raises(llm.LogosError) as e:
+        gpu.prefillRagged(toks, np.array([1, 2, 3, 10], np.int32))
+    assert e.value.status == 4
+    gpu.free()
+    ref.close()

@@ -74,3 +74,35 @@ def test_oracle_model_samples_reproducibly(oracle):
     greedy, a, b, c = run(0.0, 1), run(1.0, 1), run(1.0, 1), run(1.0, 2)
     assert np.array_equal(a, b)
     assert not np.array_equal(a, greedy) and not np.array_equal(a, c)
+
+
+def test_oracle_ragged_prompts_equal_each_sequence_alone(oracle):
+    """Sequences of a batch do not interact: a ragged batch gives every sequence the tokens it
+    gets when it is run alone with its own prompt; equal lengths equal the plain prefill."""
+    O = oracle
+    cfg = dict(layers=2, hidden=128, h_q=4, h_kv=2, head_dim=64, ffn=256, vocab=320, l_max=32,
+               rms_eps=1e-6, rope_theta=1e6, tied_embeddings=1, seed=2, init_std=0.02)
+    lens = np.array([6, 1, 3, 0], np.int32)
+    toks = O.synth_fill(O.I32, 3, 2, 999, 0, 4 * 6, 0.0, 320.0).reshape(4, 6)
+
+    def decode(m, n):
+        return np.array([m.decode_step().copy() for _ in range(n)])
+
+    m = O.Llm(tp_degree=1, tp_rank=0, device=0, act_dtype=O.F32, batch=4, **cfg)
+    m.prefill_ragged(toks, lens)
+    assert np.array_equal(m.read_seq_len(), lens)
+    batch = decode(m, 6)
+    assert np.array_equal(m.read_seq_len(), lens + 6)
+    for b in range(4):
+        one = O.Llm(tp_degree=1, tp_rank=0, device=0, act_dtype=O.F32, batch=1, **cfg)
+        if lens[b]:
+            one.prefill(toks[b:b + 1, :lens[b]])
+        else:
+            one.set_tokens(np.zeros(1, np.int32))            # an empty prompt starts from token 0
+        assert np.array_equal(decode(one, 6)[:, 0], batch[:, b]), b
+        one.close()
+    m.prefill_ragged(toks, np.full(4, 6, np.int32))
+    same = decode(m, 4)
+    m.prefill(toks)
+    assert np.array_equal(decode(m, 4), same)
+    m.close()
