@@ -244,7 +244,9 @@ LOGOS_API logos_status_t logos_llm_prefill(logos_handle_t model, const int32_t* 
 /* Prompts of different lengths: sequence b consumes tokens_host[b][0 .. lens_host[b]) of a
  * [B][t_max] array, 0 <= lens_host[b] <= t_max.  Afterwards its length is lens_host[b] and its
  * current token is the one chosen after its last prompt token (token 0 for an empty prompt);
- * decode steps then run all sequences in lock step, each at its own position. */
+ * decode steps then run all sequences in lock step, each at its own position.
+ * lens_host[b] == -1 leaves sequence b as it is (cache, length, current token): a finished
+ * sequence's slot takes a new prompt while the others of the running batch keep their state. */
 LOGOS_API logos_status_t logos_llm_prefill_ragged(logos_handle_t model, const int32_t* tokens_host, int64_t t_max,
                                                   const int32_t* lens_host);
 /* Fill the KV cache for positions [0,t) with seeded N(0,1) fp16 values instead

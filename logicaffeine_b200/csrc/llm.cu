@@ -793,8 +793,8 @@ logos_status_t logos_llm_prefill_ragged(logos_handle_t model, const int32_t* tok
                   (long long)m->cfg.l_max);
     int64_t longest = 0;
     for (int64_t b = 0; b < B; ++b) {
-      if (lens_host[b] < 0 || lens_host[b] > t_max)
-        return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_prefill_ragged: length %d of sequence %lld outside [0,%lld]", lens_host[b],
+      if (lens_host[b] < -1 || lens_host[b] > t_max)
+        return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_prefill_ragged: length %d of sequence %lld outside [-1,%lld]", lens_host[b],
                     (long long)b, (long long)t_max);
       if (lens_host[b] > longest) longest = lens_host[b];
       for (int64_t p = 0; p < lens_host[b]; ++p)
@@ -814,8 +814,16 @@ logos_status_t logos_llm_prefill_ragged(logos_handle_t model, const int32_t* tok
       tr[(size_t)(longest * B + b)] = lens_host[b];
     }
     LOGOS_CUDA_TRY(cudaMemcpyAsync(m->prompt, tr.data(), tr.size() * 4, cudaMemcpyHostToDevice, m->stream));
-    LOGOS_CUDA_TRY(cudaMemsetAsync(m->seq_len, 0, (size_t)B * 4, m->stream));
-    LOGOS_CUDA_TRY(cudaMemsetAsync(m->tokens, 0, (size_t)B * 4, m->stream));  // an empty prompt leaves token 0
+    // restarted sequences begin empty with token 0 (what an empty prompt leaves); length -1 keeps a
+    // sequence's cache, length and current token
+    std::vector<int32_t> len_now((size_t)B), tok_now((size_t)B);
+    LOGOS_CUDA_TRY(cudaMemcpyAsync(len_now.data(), m->seq_len, (size_t)B * 4, cudaMemcpyDeviceToHost, m->stream));
+    LOGOS_CUDA_TRY(cudaMemcpyAsync(tok_now.data(), m->tokens, (size_t)B * 4, cudaMemcpyDeviceToHost, m->stream));
+    LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    for (int64_t b = 0; b < B; ++b)
+      if (lens_host[b] >= 0) len_now[(size_t)b] = tok_now[(size_t)b] = 0;
+    LOGOS_CUDA_TRY(cudaMemcpyAsync(m->seq_len, len_now.data(), (size_t)B * 4, cudaMemcpyHostToDevice, m->stream));
+    LOGOS_CUDA_TRY(cudaMemcpyAsync(m->tokens, tok_now.data(), (size_t)B * 4, cudaMemcpyHostToDevice, m->stream));
     const int32_t* lens_dev = m->prompt + longest * B;
     for (int64_t p = 0; p < longest; ++p) {
       bool ends_here = false;

@@ -265,7 +265,8 @@ class Llm:
         call("logos_llm_prefill", self.handle, _host_ptr(tokens), int(tokens.shape[1]))
 
     def prefillRagged(self, tokens, lens):
-        """tokens [B][t_max]; sequence b consumes tokens[b, :lens[b]] (0 <= lens[b] <= t_max)."""
+        """tokens [B][t_max]; sequence b consumes tokens[b, :lens[b]] (0 <= lens[b] <= t_max);
+        lens[b] == -1 keeps sequence b as it is while other slots take new prompts."""
         tokens = np.ascontiguousarray(tokens, np.int32)
         lens = np.ascontiguousarray(lens, np.int32)
         assert tokens.shape[0] == self.cfg.batch and lens.shape == (self.cfg.batch,)

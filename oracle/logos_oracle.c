@@ -829,12 +829,16 @@ ORC_API void orc_llm_prefill(void* model, const int32_t* tokens, int64_t t) {
 }
 /* Prompts of different lengths: sequence i consumes tokens[i][0 .. lens[i]) of a [B][t_max]
  * array (0 <= lens[i] <= t_max); afterwards its length is lens[i] and its current token is the
- * one sampled after its last prompt token (token 0 for an empty prompt). */
+ * one sampled after its last prompt token (token 0 for an empty prompt).  lens[i] == -1 keeps
+ * sequence i as it is (cache, length, current token). */
 ORC_API void orc_llm_prefill_ragged(void* model, const int32_t* tokens, int64_t t_max, const int32_t* lens) {
   orc_llm* M = (orc_llm*)model;
   int64_t B = M->cfg.batch;
   int32_t* next = (int32_t*)calloc((size_t)B, 4);
-  for (int64_t i = 0; i < B; ++i) M->seq_len[i] = 0;
+  for (int64_t i = 0; i < B; ++i) {
+    if (lens[i] < 0) next[i] = M->tokens[i];
+    else M->seq_len[i] = 0;
+  }
   for (int64_t p = 0; p < t_max; ++p) {
     int ends_here = 0, active = 0;
     for (int64_t i = 0; i < B; ++i) {

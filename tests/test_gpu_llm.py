@@ -173,6 +173,16 @@ def test_ragged_prompts_tokens_lengths_and_kv(llm, oracle):
         assert np.array_equal(k[b, :, :n] != 0, kr[b, :, :n] != 0)
         assert rel_l2(O.f16_to_f32(k[b, :, :n]), O.f16_to_f32(kr[b, :, :n])) < 2e-4
         assert rel_l2(O.f16_to_f32(v[b, :, :n]), O.f16_to_f32(vr[b, :, :n])) < 2e-4
+    # slot 2 finishes and takes a new prompt; the other sequences of the running batch keep their state
+    fresh = np.zeros((4, t_max), np.int32)
+    fresh[2, :4] = [17, 3, 900, 41]
+    keep = np.array([-1, -1, 4, -1], np.int32)
+    ref.prefill_ragged(fresh, keep)
+    gpu.prefillRagged(fresh, keep)
+    after = np.array([lens[0] + steps, lens[1] + steps, 4, lens[3] + steps], np.int32)
+    assert np.array_equal(gpu.readSeqLen(), after) and np.array_equal(ref.read_seq_len(), after)
+    want = np.array([ref.decode_step().copy() for _ in range(10)])
+    assert np.array_equal(gpu.decodeSteps(10), want)
     # equal lengths: the same as the plain prefill
     gpu.prefillRagged(toks, np.full(4, t_max, np.int32))
     a = gpu.decodeSteps(8)
@@ -180,6 +190,9 @@ def test_ragged_prompts_tokens_lengths_and_kv(llm, oracle):
     assert np.array_equal(gpu.decodeSteps(8), a)
     with pytest.raises(llm.LogosError) as e:
         gpu.prefillRagged(toks, np.array([1, 2, 3, 10], np.int32))
+    assert e.value.status == 4
+    with pytest.raises(llm.LogosError) as e:
+        gpu.prefillRagged(toks, np.array([1, 2, 3, -2], np.int32))
     assert e.value.status == 4
     gpu.free()
     ref.close()

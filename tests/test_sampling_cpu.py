@@ -101,6 +101,20 @@ def test_oracle_ragged_prompts_equal_each_sequence_alone(oracle):
             one.set_tokens(np.zeros(1, np.int32))            # an empty prompt starts from token 0
         assert np.array_equal(decode(one, 6)[:, 0], batch[:, b]), b
         one.close()
+    # a slot takes a new prompt in a running batch: the others carry on as if nothing happened
+    m.prefill_ragged(toks, lens)
+    head = decode(m, 3)
+    fresh = np.zeros((4, 6), np.int32)
+    fresh[1, :2] = [7, 300]
+    m.prefill_ragged(fresh, np.array([-1, 2, -1, -1], np.int32))
+    assert np.array_equal(m.read_seq_len(), [lens[0] + 3, 2, lens[2] + 3, lens[3] + 3])
+    tail = decode(m, 3)
+    for b in (0, 2, 3):
+        assert np.array_equal(np.concatenate([head[:, b], tail[:, b]]), batch[:, b]), b
+    one = O.Llm(tp_degree=1, tp_rank=0, device=0, act_dtype=O.F32, batch=1, **cfg)
+    one.prefill(fresh[1:2, :2])
+    assert np.array_equal(decode(one, 3)[:, 0], tail[:, 1])
+    one.close()
     m.prefill_ragged(toks, np.full(4, 6, np.int32))
     same = decode(m, 4)
     m.prefill(toks)
