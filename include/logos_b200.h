@@ -274,8 +274,10 @@ LOGOS_API logos_status_t logos_llm_set_seq_len(logos_handle_t model, int64_t t);
  * variate (logos_synth_fill kind 4), i.e. a draw from softmax(logits / temperature) that is a
  * pure function of (seed, sequence, position): the same on every rank of a tensor-parallel
  * group, under graph replay, and in the CPU oracle.  temperature 0 (the state after create)
- * is greedy.  Takes effect from the next step. */
-LOGOS_API logos_status_t logos_llm_set_sampling(logos_handle_t model, float temperature, uint64_t seed);
+ * is greedy.  top_k > 0 restricts the draw to the logits that reach the k-th largest of their
+ * sequence (ties at that value included; 0 or >= vocab: no filter).  Takes effect from the
+ * next step. */
+LOGOS_API logos_status_t logos_llm_set_sampling(logos_handle_t model, float temperature, int64_t top_k, uint64_t seed);
 /* Device-side time of the last logos_llm_decode_steps call, milliseconds
  * (CUDA events on the model's stream), and kernels launched per step. */
 LOGOS_API logos_status_t logos_llm_last_timing(logos_handle_t model, double* ms_out, int64_t* launches_per_step_out);

@@ -93,7 +93,7 @@ _SIGNATURES = {
     "logos_llm_read_logits": (None, [H, PTR]),
     "logos_llm_read_seq_len": (None, [H, PTR]),
     "logos_llm_set_seq_len": (None, [H, I64]),
-    "logos_llm_set_sampling": (None, [H, FLT, U64]),
+    "logos_llm_set_sampling": (None, [H, FLT, I64, U64]),
     "logos_llm_last_timing": (None, [H, C.POINTER(C.c_double), C.POINTER(I64)]),
     "logos_llm_tp_exchange": (None, [H, C.POINTER(C.c_int32)]),
     "logos_dependent_launch_scope": (None, [C.c_int32, C.POINTER(C.c_int32)]),

@@ -278,6 +278,48 @@ __global__ void act_split_kernel(const float* __restrict__ x, ActOut o, int64_t 
   if (i < count) act_store(o, i, x[i]);
 }
 
+// Order-preserving map of a float onto unsigned integers, and back.
+__device__ __forceinline__ uint32_t float_key(float x) {
+  const uint32_t u = __float_as_uint(x);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_float(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+// The k-th largest value of row[0 .. n) (1 <= k <= n), by the whole block: radix select on the
+// ordered keys, eight bits a round, each round one pass over the row and one 256-bin histogram.
+__device__ float block_kth_largest(const float* __restrict__ row, int64_t n, int k) {
+  __shared__ unsigned hist[256];
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_k;
+  uint32_t prefix = 0u, mask = 0u;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0u;
+    __syncthreads();
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+      const uint32_t key = float_key(__ldcg(row + i));
+      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int cum = 0, b = 255;
+      for (; b > 0; --b) {
+        if (cum + (int)hist[b] >= k) break;
+        cum += (int)hist[b];
+      }
+      s_prefix = prefix | ((uint32_t)b << shift);
+      s_k = k - cum;
+    }
+    __syncthreads();
+    prefix = s_prefix;
+    k = s_k;
+    mask |= 255u << shift;
+    __syncthreads();
+  }
+  return key_float(prefix);
+}
+
 // history (optional): row `*step_counter` of a [history_rows][rows] log also receives the ids,
 // so a captured step needs no per-step pointer.
 __global__ void argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ tokens,
@@ -298,8 +340,12 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int32_t* __restr
   const float inv_t = sample ? __ldcg(&sampling->inv_temperature) : 1.f;
   const uint64_t seed = sample ? __ldcg(&sampling->seed) : 0ull;
   const uint64_t first = sample ? (uint64_t)__ldcg(positions + row) * (uint64_t)vocab : 0ull;
+  const int top_k = sample ? __ldcg(&sampling->top_k) : 0;
+  // candidates: everything, or the logits that reach the row's k-th largest (ties at it included)
+  const float least = (top_k > 0 && (int64_t)top_k < vocab) ? block_kth_largest(lr, vocab, top_k) : -INFINITY;
   for (int64_t i = threadIdx.x; i < vocab; i += blockDim.x) {
     float v = __ldcg(lr + i);
+    if (v < least) continue;
     if (sample) v = __fadd_rn(__fmul_rn(v, inv_t), synth::gumbel_f32(seed, (uint64_t)row, first + (uint64_t)i));
     if (v > best || (v == best && (int)i < idx)) {
       best = v;

@@ -986,15 +986,18 @@ logos_status_t logos_llm_set_seq_len(logos_handle_t model, int64_t t) {
   });
 }
 
-logos_status_t logos_llm_set_sampling(logos_handle_t model, float temperature, uint64_t seed) {
+logos_status_t logos_llm_set_sampling(logos_handle_t model, float temperature, int64_t top_k, uint64_t seed) {
   return guarded([&]() -> logos_status_t {
     MODEL_OR_FAIL(m, model, "logos_llm_set_sampling");
     if (!(temperature >= 0.0f) || temperature > 1e6f)
       return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_set_sampling: temperature %g outside [0, 1e6]", (double)temperature);
+    if (top_k < 0) return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_set_sampling: top_k %lld is negative", (long long)top_k);
     SamplingParams p;
     p.enabled = temperature > 0.0f ? 1 : 0;
     p.inv_temperature = p.enabled ? 1.0f / temperature : 1.0f;
     p.seed = seed;
+    p.top_k = top_k >= m->cfg.vocab ? 0 : (int32_t)top_k;  // the whole vocabulary: no filter
+    p.reserved = 0;
     LOGOS_CUDA_TRY(cudaMemcpyAsync(m->sampling, &p, sizeof(p), cudaMemcpyHostToDevice, m->stream));
     LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
     return LOGOS_OK;

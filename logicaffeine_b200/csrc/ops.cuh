@@ -143,10 +143,13 @@ struct SamplingParams {
   float inv_temperature;  // 1 / T
   int32_t enabled;        // 0: plain argmax
   uint64_t seed;
+  int32_t top_k;          // > 0: only logits >= the k-th largest of their row are candidates
+  int32_t reserved;
 };
 // tokens[row] = argmax(logits[row]) with the lowest index winning ties.  With sampling enabled
 // (sampling_or_null and positions non-null) the compared value is
-// logit * inv_temperature + gumbel(seed, row, positions[row] * vocab + index).
+// logit * inv_temperature + gumbel(seed, row, positions[row] * vocab + index), over the logits
+// that are >= the row's top_k-th largest when top_k is set.
 // only_ending_or_null (ragged prompts): a row is written only if only_ending[row] - 1 == prompt_step.
 logos_status_t launch_argmax(const float* logits, int32_t* tokens, int32_t* history_or_null,
                              const int32_t* step_counter_or_null, int64_t history_rows, int64_t rows, int64_t vocab,

@@ -310,9 +310,10 @@ class Llm:
     def setSeqLen(self, t):
         call("logos_llm_set_seq_len", self.handle, int(t))
 
-    def setSampling(self, temperature, seed=0):
-        """Temperature sampling by Gumbel-max on the seeded generator; temperature 0 is greedy."""
-        call("logos_llm_set_sampling", self.handle, float(temperature), int(seed))
+    def setSampling(self, temperature, seed=0, top_k=0):
+        """Temperature sampling by Gumbel-max on the seeded generator, over the top_k largest logits
+        when top_k > 0; temperature 0 is greedy."""
+        call("logos_llm_set_sampling", self.handle, float(temperature), int(top_k), int(seed))
 
     def lastTiming(self):
         ms = C.c_double()

@@ -580,6 +580,7 @@ typedef struct {
   float* logits;
   float* h; /* residual stream [B][H] */
   int sampling; /* 0: greedy argmax */
+  int64_t top_k; /* > 0: only logits >= the k-th largest of the row are candidates */
   float inv_temperature;
   uint64_t sample_seed;
 } orc_llm;
@@ -658,27 +659,42 @@ static void round_rows(float* x, int64_t n, int act_dtype) {
  * compared value is logit * inv_temperature + gumbel(seed, row, position * vocab + index)
  * (Gumbel-max: a draw from softmax(logits / temperature) that depends only on seed, row and
  * position). */
+static int cmp_float_desc(const void* a, const void* b) {
+  float x = *(const float*)a, y = *(const float*)b;
+  return (x < y) - (x > y);
+}
+/* top_k > 0 (with sampling enabled): only logits >= the k-th largest of the row are candidates
+ * (ties at that value included); 0 or >= vocab: all of them. */
 ORC_API void orc_sample_rows(const float* logits, int64_t rows, int64_t vocab, int enabled, float inv_temperature,
-                             uint64_t seed, const int32_t* positions, int32_t* tokens) {
+                             int64_t top_k, uint64_t seed, const int32_t* positions, int32_t* tokens) {
 #pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < rows; ++i) {
     const float* lg = logits + i * vocab;
     uint64_t first = enabled ? (uint64_t)positions[i] * (uint64_t)vocab : 0;
-    int64_t best = 0;
+    float least = -INFINITY;
+    if (enabled && top_k > 0 && top_k < vocab) {
+      float* sorted = (float*)malloc(sizeof(float) * (size_t)vocab);
+      memcpy(sorted, lg, sizeof(float) * (size_t)vocab);
+      qsort(sorted, (size_t)vocab, sizeof(float), cmp_float_desc);
+      least = sorted[top_k - 1];
+      free(sorted);
+    }
+    int64_t best = -1;
     float best_v = 0.0f;
     for (int64_t v = 0; v < vocab; ++v) {
       float x = lg[v];
+      if (x < least) continue;
       if (enabled) {
         float scaled = x * inv_temperature;
         float g = gen_gumbel(seed, (uint64_t)i, first + (uint64_t)v);
         x = scaled + g;
       }
-      if (v == 0 || x > best_v) {
+      if (best < 0 || x > best_v) {
         best = v;
         best_v = x;
       }
     }
-    tokens[i] = (int32_t)best;
+    tokens[i] = (int32_t)(best < 0 ? 0 : best);
   }
 }
 
@@ -750,7 +766,7 @@ static void llm_step(orc_llm* M, int sample, const int32_t* lens, int64_t p) {
     orc_q8_gemm_f32(xn, ORC_F32, hd->q, hd->s, M->logits, B, c->vocab, H);
     int32_t* tok = (int32_t*)malloc(4 * (size_t)B);
     for (int64_t i = 0; i < B; ++i) len1[i] = M->seq_len[i] > 0 ? M->seq_len[i] - 1 : 0; /* position of the token just consumed */
-    orc_sample_rows(M->logits, B, c->vocab, M->sampling, M->inv_temperature, M->sample_seed, len1, tok);
+    orc_sample_rows(M->logits, B, c->vocab, M->sampling, M->inv_temperature, M->top_k, M->sample_seed, len1, tok);
     for (int64_t i = 0; i < B; ++i)
       if (!lens || lens[i] - 1 == p) M->tokens[i] = tok[i];
     free(tok);
@@ -811,8 +827,9 @@ ORC_API int orc_llm_get_tensor(void* model, int64_t layer, int kind, void* q, fl
 }
 
 /* temperature 0 = greedy */
-ORC_API void orc_llm_set_sampling(void* model, float temperature, uint64_t seed) {
+ORC_API void orc_llm_set_sampling(void* model, float temperature, int64_t top_k, uint64_t seed) {
   orc_llm* M = (orc_llm*)model;
+  M->top_k = top_k;
   M->sampling = temperature > 0.0f ? 1 : 0;
   M->inv_temperature = M->sampling ? 1.0f / temperature : 1.0f;
   M->sample_seed = seed;

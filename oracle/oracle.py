@@ -153,16 +153,17 @@ def gqa_decode_attn_fused(q_raw, k_new, v_new, k_cache, v_cache, tab, seq_len, s
     return o
 
 
-def sample_rows(logits, temperature, seed, positions):
-    """Next token per row by Gumbel-max on the seeded generator (temperature 0: plain argmax)."""
+def sample_rows(logits, temperature, seed, positions, top_k=0):
+    """Next token per row by Gumbel-max on the seeded generator (temperature 0: plain argmax),
+    over the logits that reach the row's top_k-th largest when top_k > 0."""
     logits = np.ascontiguousarray(logits, np.float32)
     rows, vocab = logits.shape
     pos = np.ascontiguousarray(positions, np.int32)
     out = np.empty(rows, np.int32)
     on = 1 if temperature > 0 else 0
     inv = np.float32(1.0) / np.float32(temperature) if on else np.float32(1.0)
-    lib().orc_sample_rows(_p(logits), C.c_int64(rows), C.c_int64(vocab), C.c_int(on), C.c_float(inv), C.c_uint64(seed),
-                          _p(pos), _p(out))
+    lib().orc_sample_rows(_p(logits), C.c_int64(rows), C.c_int64(vocab), C.c_int(on), C.c_float(inv), C.c_int64(top_k),
+                          C.c_uint64(seed), _p(pos), _p(out))
     return out
 
 
@@ -279,8 +280,8 @@ class Llm:
         if rc != 0:
             raise KeyError((layer, kind))
 
-    def set_sampling(self, temperature, seed=0):
-        lib().orc_llm_set_sampling(self._h, C.c_float(temperature), C.c_uint64(seed))
+    def set_sampling(self, temperature, seed=0, top_k=0):
+        lib().orc_llm_set_sampling(self._h, C.c_float(temperature), C.c_int64(top_k), C.c_uint64(seed))
 
     def read_logits(self):
         out = np.empty((self.cfg.batch, self.cfg.vocab), np.float32)

@@ -137,12 +137,26 @@ def test_temperature_sampling_tokens_match_the_oracle(llm, oracle):
     want2 = np.array([ref.decode_step().copy() for _ in range(steps)])
     got2 = gpu.decodeSteps(steps)
     assert np.array_equal(got2, want2) and not np.array_equal(want2, want)
+    # top-k: a hot temperature over the 6 largest logits of each sequence (negative logits included in the ordering)
+    ref.set_sampling(3.0, 7, top_k=6)
+    gpu.setSampling(3.0, 7, top_k=6)
+    ref.prefill(toks)
+    gpu.prefill(toks)
+    want3 = np.array([ref.decode_step().copy() for _ in range(steps)])
+    assert np.array_equal(gpu.decodeSteps(steps), want3)
+    ref.set_sampling(3.0, 7)
+    ref.prefill(toks)
+    unfiltered = np.array([ref.decode_step().copy() for _ in range(steps)])
+    assert not np.array_equal(want3, unfiltered)
     # back to greedy under the captured step
     gpu.setSampling(0.0, 0)
     gpu.prefill(toks)
     assert np.array_equal(gpu.decodeSteps(steps), greedy)
     with pytest.raises(llm.LogosError) as e:
         gpu.setSampling(-1.0, 0)
+    assert e.value.status == 4
+    with pytest.raises(llm.LogosError) as e:
+        gpu.setSampling(1.0, 0, top_k=-3)
     assert e.value.status == 4
     gpu.free()
     ref.close()

@@ -120,3 +120,26 @@ def test_oracle_ragged_prompts_equal_each_sequence_alone(oracle):
     m.prefill(toks)
     assert np.array_equal(decode(m, 4), same)
     m.close()
+
+
+def test_top_k_restricts_the_draw_to_the_k_largest_with_ties(oracle):
+    O = oracle
+    logits = np.array([0.0, 1.0, 2.0, -1.0, 0.5, 2.5, -3.0, 1.5], np.float32)
+    n = 30000
+    rows = np.tile(logits, (n, 1))
+    tok = O.sample_rows(rows, 1.0, seed=3, positions=np.arange(n) % 997, top_k=3)
+    assert set(np.unique(tok)) == {2, 5, 7}                       # 2.0, 2.5, 1.5
+    p = np.exp(logits[[2, 5, 7]].astype(np.float64))
+    p /= p.sum()
+    freq = np.array([(tok == i).mean() for i in (2, 5, 7)])
+    assert np.all(np.abs(freq - p) < 5 * np.sqrt(p * (1 - p) / n) + 1e-4)
+    # ties at the k-th largest value are all candidates; k = 1 is the argmax whatever the noise
+    tied = np.tile(np.array([1.0, 3.0, 2.0, 2.0, 0.0], np.float32), (4000, 1))
+    assert set(np.unique(O.sample_rows(tied, 1.0, 5, np.arange(4000), top_k=2))) == {1, 2, 3}
+    assert set(np.unique(O.sample_rows(tied, 5.0, 5, np.arange(4000), top_k=1))) == {1}
+    # k >= vocabulary or 0: no filter, the same draws
+    base = O.sample_rows(rows[:500], 1.0, 3, np.arange(500))
+    assert np.array_equal(O.sample_rows(rows[:500], 1.0, 3, np.arange(500), top_k=8), base)
+    assert np.array_equal(O.sample_rows(rows[:500], 1.0, 3, np.arange(500), top_k=100), base)
+    # temperature 0 ignores top_k
+    assert O.sample_rows(rows[:3], 0.0, 3, [0, 0, 0], top_k=3).tolist() == [5, 5, 5]
