@@ -61,6 +61,17 @@ def test_null_and_invalid_handles(llm):
     assert lib.logos_q8_gemv(None, None, None, None, 4, 32, None) == 3
     assert lib.logos_q8_gemv(None, None, None, None, 4, 33, None) == 4  # K not a multiple of 32
     assert lib.logos_llm_create(None, None, None) == 3
+    # model-level entry points added later: the handle is checked before anything else
+    for call in (lambda h: lib.logos_llm_load_weights(h, b"/nonexistent"),
+                 lambda h: lib.logos_llm_save_weights(h, b"/nonexistent"),
+                 lambda h: lib.logos_llm_set_sampling(h, 1.0, 0, 0),
+                 lambda h: lib.logos_llm_prefill_ragged(h, None, 1, None)):
+        assert call(None) == 3
+        assert call(C.c_void_p(777)) == 6
+    assert lib.logos_llm_weights_check(None, None) == 3
+    assert lib.logos_llm_weights_file_bytes(None, None) == 3
+    assert lib.logos_llm_weights_header(None, None) == 3
+    assert lib.logos_llm_weights_read_shard(None, 1, 0, 0, 1, None, 0, None, 0, None, None) == 3
     assert lib.logos_get_last_error() == lib.logos_last_error()
 
 
