@@ -702,7 +702,10 @@ ORC_API void orc_sample_rows(const float* logits, int64_t rows, int64_t vocab, i
  * (ragged prompts, step p of the prefill): only sequences with p < lens[i] advance, and only
  * those whose prompt ends here (lens[i] - 1 == p) take the sampled token; the others keep
  * theirs.  A sequence that does not advance still runs through the step - its K/V row lands
- * at its next free position and is overwritten when the sequence does advance. */
+ * at its next free position and is overwritten when the sequence does advance.
+ * A sequence whose cache is full (length == l_max) still steps: its query is rotated for the
+ * last position, nothing is appended, it attends over the l_max cached rows and its length
+ * stays. */
 static void llm_step(orc_llm* M, int sample, const int32_t* lens, int64_t p) {
   const orc_llm_config_t* c = &M->cfg;
   int64_t B = c->batch, H = c->hidden, D = c->head_dim, F = c->ffn;
@@ -719,6 +722,8 @@ static void llm_step(orc_llm* M, int sample, const int32_t* lens, int64_t p) {
   float* gate = (float*)malloc(sizeof(float) * (size_t)(B * F));
   float* up = (float*)malloc(sizeof(float) * (size_t)(B * F));
   int32_t* len1 = (int32_t*)malloc(4 * (size_t)B);
+  int32_t* pos0 = (int32_t*)malloc(4 * (size_t)B); /* lengths when the step began = positions of the consumed tokens */
+  for (int64_t i = 0; i < B; ++i) pos0[i] = M->seq_len[i];
 
   /* embedding row = dequantised Q8 row */
   for (int64_t i = 0; i < B; ++i) {
@@ -733,10 +738,12 @@ static void llm_step(orc_llm* M, int sample, const int32_t* lens, int64_t p) {
     orc_q8_gemm_f32(xn, ORC_F32, M->wk[l].q, M->wk[l].s, kf, B, nkv, H);
     orc_q8_gemm_f32(xn, ORC_F32, M->wv[l].q, M->wv[l].s, vf, B, nkv, H);
     for (int64_t i = 0; i < B; ++i) {
-      int64_t pos = M->seq_len[i];
+      int64_t pos = pos0[i];
+      int full = pos >= c->l_max;
+      if (full) pos = c->l_max - 1;
       const float* tab = M->rope + pos * (D / 2) * 2;
       for (int64_t h = 0; h < c->h_q; ++h) rope_row_f16out(qf + (i * c->h_q + h) * D, tab, D, qh + (i * c->h_q + h) * D);
-      for (int64_t h = 0; h < c->h_kv; ++h) {
+      for (int64_t h = 0; h < c->h_kv && !full; ++h) {
         uint16_t* kd = M->kc[l] + ((i * c->h_kv + h) * c->l_max + pos) * D;
         uint16_t* vd = M->vc[l] + ((i * c->h_kv + h) * c->l_max + pos) * D;
         rope_row_f16out(kf + (i * c->h_kv + h) * D, tab, D, kd);
@@ -758,20 +765,19 @@ static void llm_step(orc_llm* M, int sample, const int32_t* lens, int64_t p) {
     for (int64_t i = 0; i < B * H; ++i) M->h[i] = M->h[i] + delta[i];
   }
   for (int64_t i = 0; i < B; ++i)
-    if (!lens || p < lens[i]) M->seq_len[i] += 1;
+    if ((!lens || p < lens[i]) && M->seq_len[i] < c->l_max) M->seq_len[i] += 1;
   if (sample) {
     orc_rmsnorm(M->h, M->gains + (2 * c->layers) * H, xn, B, H, c->rms_eps);
     round_rows(xn, B * H, act);
     const q8mat* hd = c->tied_embeddings ? &M->embed : &M->head;
     orc_q8_gemm_f32(xn, ORC_F32, hd->q, hd->s, M->logits, B, c->vocab, H);
     int32_t* tok = (int32_t*)malloc(4 * (size_t)B);
-    for (int64_t i = 0; i < B; ++i) len1[i] = M->seq_len[i] > 0 ? M->seq_len[i] - 1 : 0; /* position of the token just consumed */
-    orc_sample_rows(M->logits, B, c->vocab, M->sampling, M->inv_temperature, M->top_k, M->sample_seed, len1, tok);
+    orc_sample_rows(M->logits, B, c->vocab, M->sampling, M->inv_temperature, M->top_k, M->sample_seed, pos0, tok);
     for (int64_t i = 0; i < B; ++i)
       if (!lens || lens[i] - 1 == p) M->tokens[i] = tok[i];
     free(tok);
   }
-  free(xn); free(qf); free(kf); free(vf); free(qh); free(att); free(delta); free(gate); free(up); free(len1);
+  free(xn); free(qf); free(kf); free(vf); free(qh); free(att); free(delta); free(gate); free(up); free(len1); free(pos0);
 }
 
 /* One tensor of the model, named as the weight file names them: 0 attn_norm, 1 q, 2 k, 3 v,

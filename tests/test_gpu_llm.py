@@ -210,3 +210,30 @@ def test_ragged_prompts_tokens_lengths_and_kv(llm, oracle):
     assert e.value.status == 4
     gpu.free()
     ref.close()
+
+
+@pytest.mark.parametrize("temperature", [0.0, 1.0])
+def test_decode_past_a_full_cache(llm, oracle, temperature):
+    """The maximum size: once a sequence fills its cache (length == l_max) a step appends nothing,
+    rotates the query for the last position, attends over all l_max rows and leaves the length;
+    tokens still equal the oracle's, greedy and sampled."""
+    O = oracle
+    cfg = dict(SMALL, l_max=16)
+    toks = O.synth_fill(O.I32, 3, 6, 999, 0, cfg["batch"] * 10, 0.0, float(cfg["vocab"])).reshape(cfg["batch"], 10)
+    lens = np.array([10, 7, 10, 3], np.int32)
+    ref = O.Llm(tp_degree=1, tp_rank=0, device=0, act_dtype=O.F32, **cfg)
+    gpu = llm.Llm(act_dtype=llm.F32, **cfg)
+    ref.set_sampling(temperature, 5)
+    gpu.setSampling(temperature, 5)
+    ref.prefill_ragged(toks, lens)
+    gpu.prefillRagged(toks, lens)
+    want = np.array([ref.decode_step().copy() for _ in range(11)])   # sequences 0 and 2 are full after 6 steps
+    got = gpu.decodeSteps(11)
+    assert np.array_equal(got, want)
+    full = np.minimum(lens + 11, 16)
+    assert np.array_equal(gpu.readSeqLen(), full) and np.array_equal(ref.read_seq_len(), full)
+    k, v = gpu.readKv(cfg["layers"] - 1)
+    kr, vr = ref.read_kv(cfg["layers"] - 1)
+    assert rel_l2(O.f16_to_f32(k), O.f16_to_f32(kr)) < 1e-3 and rel_l2(O.f16_to_f32(v), O.f16_to_f32(vr)) < 1e-3
+    gpu.free()
+    ref.close()

@@ -143,3 +143,20 @@ def test_top_k_restricts_the_draw_to_the_k_largest_with_ties(oracle):
     assert np.array_equal(O.sample_rows(rows[:500], 1.0, 3, np.arange(500), top_k=100), base)
     # temperature 0 ignores top_k
     assert O.sample_rows(rows[:3], 0.0, 3, [0, 0, 0], top_k=3).tolist() == [5, 5, 5]
+
+
+def test_oracle_steps_past_a_full_cache(oracle):
+    O = oracle
+    cfg = dict(layers=2, hidden=128, h_q=4, h_kv=2, head_dim=64, ffn=256, vocab=320, l_max=8, batch=2,
+               rms_eps=1e-6, rope_theta=1e6, tied_embeddings=1, seed=2, init_std=0.02)
+    toks = O.synth_fill(O.I32, 3, 2, 999, 0, 2 * 6, 0.0, 320.0).reshape(2, 6)
+    m = O.Llm(tp_degree=1, tp_rank=0, device=0, act_dtype=O.F32, **cfg)
+    m.prefill_ragged(toks, np.array([6, 2], np.int32))
+    k_before = None
+    for step in range(7):
+        m.decode_step()
+        if step == 1:                                   # sequence 0 is full now (6 + 2)
+            k_before = m.read_kv(0)[0][0].copy()
+    assert m.read_seq_len().tolist() == [8, 8]
+    assert np.array_equal(m.read_kv(0)[0][0], k_before)   # a full sequence's cache is not written again
+    m.close()
