@@ -230,7 +230,7 @@ typedef struct {
   int32_t act_dtype;         /* precision of GEMM inputs: LOGOS_F32 (default: no rounding), LOGOS_F16 or LOGOS_BF16 */
   uint64_t seed;             /* random-init weights: N(0, init_std) -> Q8 blocks of 32 */
   float   init_std;
-  int32_t reserved;
+  int32_t qkv_bias;          /* 1: the q, k and v projections add a bias vector (Qwen2); N(0, init_std) at creation */
 } logos_llm_config_t;
 
 /* 128-byte NCCL unique id for the tensor-parallel group (rank 0 makes it, the
@@ -307,14 +307,16 @@ LOGOS_API logos_status_t logos_llm_tp_exchange(logos_handle_t model, int32_t* mo
  * and copies from, the device-side counterpart of the reference's memory-mapped zone
  * (`Inside a zone called "D" mapped from "f.bin"`, crates/logicaffeine_language/src/ast/stmt.rs:405-418;
  * Zone::new_mapped, crates/logicaffeine_system/src/memory.rs:97-103).  Regions start on
- * 256-byte boundaries in this order: per layer attn_norm, q, k, v, o, mlp_norm, gate, up, down;
+ * 256-byte boundaries in this order: per layer attn_norm, q, k, v, (q_bias, k_bias, v_bias: f32
+ * vectors, only with qkv_bias, header flag bit 0), o, mlp_norm, gate, up, down;
  * then final_norm, embed and (untied only) head.  A matrix is int8 [n][k] followed by f32
  * [n][k/32]; a norm gain is f32 [hidden].  Matrices are stored whole: a tensor-parallel rank
  * takes its rows (q, k, v, gate, up) or columns (o, down), so one file serves every group size.
  * A malformed or truncated file is LOGOS_DESERIALIZATION_FAILED, an unreadable one LOGOS_ERROR. */
 typedef enum {
   LOGOS_W_ATTN_NORM = 0, LOGOS_W_Q = 1, LOGOS_W_K = 2, LOGOS_W_V = 3, LOGOS_W_O = 4, LOGOS_W_MLP_NORM = 5,
-  LOGOS_W_GATE = 6, LOGOS_W_UP = 7, LOGOS_W_DOWN = 8, LOGOS_W_FINAL_NORM = 9, LOGOS_W_EMBED = 10, LOGOS_W_HEAD = 11
+  LOGOS_W_GATE = 6, LOGOS_W_UP = 7, LOGOS_W_DOWN = 8, LOGOS_W_FINAL_NORM = 9, LOGOS_W_EMBED = 10, LOGOS_W_HEAD = 11,
+  LOGOS_W_Q_BIAS = 12, LOGOS_W_K_BIAS = 13, LOGOS_W_V_BIAS = 14 /* only with cfg.qkv_bias; stored after v */
 } logos_weight_tensor_t;
 /* Layout queries (no GPU needed; only the architecture fields of cfg are read): size of the
  * file; place of one tensor (for a gain: q_off/q_bytes = the f32 vector, s_bytes = 0); the
@@ -325,7 +327,7 @@ LOGOS_API logos_status_t logos_llm_weights_span(const logos_llm_config_t* cfg, i
                                                 int64_t* s_bytes_out);
 LOGOS_API logos_status_t logos_llm_weights_header(const logos_llm_config_t* cfg, void* out_256_bytes);
 /* Map a file, validate header and length, and (cfg_out non-null) report its architecture:
- * layers, hidden, h_q, h_kv, head_dim, ffn, vocab, tied_embeddings; other fields are untouched. */
+ * layers, hidden, h_q, h_kv, head_dim, ffn, vocab, tied_embeddings, qkv_bias; other fields are untouched. */
 LOGOS_API logos_status_t logos_llm_weights_check(const char* path, logos_llm_config_t* cfg_out);
 /* Host-side read of what rank tp_rank of a group of tp_degree holds of one tensor: int8
  * [rows][cols] into q_out and f32 [rows][cols/32] into s_out (a gain: f32 [hidden] into q_out,

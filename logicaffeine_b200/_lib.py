@@ -38,7 +38,7 @@ class LlmConfig(C.Structure):
         ("rms_eps", C.c_float), ("rope_theta", C.c_float),
         ("tied_embeddings", C.c_int32), ("tp_degree", C.c_int32), ("tp_rank", C.c_int32),
         ("device", C.c_int32), ("act_dtype", C.c_int32),
-        ("seed", C.c_uint64), ("init_std", C.c_float), ("reserved", C.c_int32),
+        ("seed", C.c_uint64), ("init_std", C.c_float), ("qkv_bias", C.c_int32),
     ]
 
 

@@ -48,6 +48,9 @@ struct AttnParams {
   int64_t       kv_ld;
   int           f32_parts;        // split-K partial copies of the f32 inputs, summed while staging
   int64_t       f32_part_stride;
+  const float*  q_bias;           // f32 inputs only: added after the partial copies (null = none)
+  const float*  k_bias;
+  const float*  v_bias;
   int           fused;
   __half*       k_cache;
   __half*       v_cache;
@@ -144,6 +147,10 @@ gqa_decode_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             x1 = __fadd_rn(x1, __ldcg(qp + sp * p.f32_part_stride + e));
             x2 = __fadd_rn(x2, __ldcg(qp + sp * p.f32_part_stride + e + half_d));
           }
+          if (p.q_bias) {
+            x1 = __fadd_rn(x1, __ldg(p.q_bias + hq * D + e));
+            x2 = __fadd_rn(x2, __ldg(p.q_bias + hq * D + e + half_d));
+          }
         }
         if (p.rotate_q) {
           float c = tab[2 * e], s = tab[2 * e + 1];
@@ -175,6 +182,12 @@ gqa_decode_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             const int64_t o = sp * p.f32_part_stride;
             k1 = __fadd_rn(k1, __ldcg(kp + o + e)); k2 = __fadd_rn(k2, __ldcg(kp + o + e + half_d));
             v1 = __fadd_rn(v1, __ldcg(vp + o + e)); v2 = __fadd_rn(v2, __ldcg(vp + o + e + half_d));
+          }
+          if (p.k_bias) {
+            k1 = __fadd_rn(k1, __ldg(p.k_bias + kvh * D + e)); k2 = __fadd_rn(k2, __ldg(p.k_bias + kvh * D + e + half_d));
+          }
+          if (p.v_bias) {
+            v1 = __fadd_rn(v1, __ldg(p.v_bias + kvh * D + e)); v2 = __fadd_rn(v2, __ldg(p.v_bias + kvh * D + e + half_d));
           }
         }
         float c = tabn[2 * e], s = tabn[2 * e + 1];
@@ -519,6 +532,7 @@ logos_status_t launch_attn_t(const AttnArgs& a, cudaStream_t st) {
   p.kv_ld = a.kv_ld;
   p.f32_parts = a.f32_parts > 1 ? a.f32_parts : 1;
   p.f32_part_stride = a.f32_part_stride;
+  p.q_bias = a.q_bias; p.k_bias = a.k_bias; p.v_bias = a.v_bias;
   p.fused = (a.k_new_f16 || a.k_new_f32) ? 1 : 0;
   p.k_cache = a.k_cache; p.v_cache = a.v_cache; p.rope = a.rope; p.seq_len = a.seq_len;
   p.part_o = reinterpret_cast<float*>(scratch);

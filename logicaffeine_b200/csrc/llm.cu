@@ -42,6 +42,7 @@ struct Q8Mat {
 
 struct Layer {
   Q8Mat wqkv, wo, wgu, wd;
+  float* bqkv = nullptr;  // cfg.qkv_bias only: f32 [nqkv], the biases of this rank's q | k | v rows
   __half *kc = nullptr, *vc = nullptr;
 };
 
@@ -193,6 +194,14 @@ logos_status_t build(Model* m, const void* nccl_id) {
     LOGOS_TRY(gen(m, &L.wgu, m->f_local, r * m->f_local, 0, H, 2, 0, st + 4));
     LOGOS_TRY(gen(m, &L.wgu, m->f_local, r * m->f_local, 0, H, 2, 1, st + 5));
     LOGOS_TRY(gen(m, &L.wd, H, 0, r * m->f_local, c.ffn, 1, 0, st + 6));
+    if (c.qkv_bias) {  // streams 7, 8, 9 of the layer, valued by the row's index in the whole projection
+      LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&L.bqkv), m->nqkv * 4));
+      LOGOS_TRY(launch_synth_fill(L.bqkv, LOGOS_F32, 2, c.seed, st + 7, r * m->nq, m->nq, 0.f, c.init_std, m->device, m->stream));
+      LOGOS_TRY(launch_synth_fill(L.bqkv + m->nq, LOGOS_F32, 2, c.seed, st + 8, r * m->nkv, m->nkv, 0.f, c.init_std, m->device,
+                                  m->stream));
+      LOGOS_TRY(launch_synth_fill(L.bqkv + m->nq + m->nkv, LOGOS_F32, 2, c.seed, st + 9, r * m->nkv, m->nkv, 0.f, c.init_std,
+                                  m->device, m->stream));
+    }
     LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&L.kc), kv_elems * 2));
     LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&L.vc), kv_elems * 2));
     LOGOS_CUDA_TRY(cudaMemsetAsync(L.kc, 0, (size_t)kv_elems * 2, m->stream));
@@ -450,6 +459,9 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
       a.q_f32 = qkv_src; a.q_ld = m->nqkv; a.rotate_q = 1;
       a.k_new_f32 = qkv_src + m->nq; a.v_new_f32 = qkv_src + m->nq + m->nkv; a.kv_ld = m->nqkv;
       a.f32_parts = qkv_parts; a.f32_part_stride = B * m->nqkv;
+      if (L.bqkv) {
+        a.q_bias = L.bqkv; a.k_bias = L.bqkv + m->nq; a.v_bias = L.bqkv + m->nq + m->nkv;
+      }
       a.k_cache = L.kc; a.v_cache = L.vc; a.rope = m->rope; a.seq_len = m->seq_len;
       a.bump_seq_len = 0;
       a.o_dtype = LOGOS_ACT_PLANES; a.o_act = m->att;
@@ -542,6 +554,7 @@ logos_status_t check_cfg(const logos_llm_config_t& c) {
   if (c.head_dim != 64 && c.head_dim != 128) return fail(LOGOS_ERROR, "logos_llm_create: head_dim must be 64 or 128");
   if (c.hidden % 32 || (c.ffn / c.tp_degree) % 32 || ((c.h_q / c.tp_degree) * c.head_dim) % 32)
     return fail(LOGOS_ERROR, "logos_llm_create: hidden, ffn/tp and q width/tp must be multiples of the Q8 block 32");
+  if (c.qkv_bias != 0 && c.qkv_bias != 1) return fail(LOGOS_ERROR, "logos_llm_create: qkv_bias must be 0 or 1");
   if (c.act_dtype != LOGOS_F32 && c.act_dtype != LOGOS_F16 && c.act_dtype != LOGOS_BF16)
     return fail(LOGOS_ERROR, "logos_llm_create: act_dtype must be LOGOS_F32, LOGOS_F16 or LOGOS_BF16");
   return LOGOS_OK;
@@ -627,7 +640,7 @@ struct TensorHome {
 TensorHome tensor_home(Model* m, int64_t l, int kind) {
   const int64_t H = m->cfg.hidden, hb = H / 32;
   TensorHome t;
-  Layer* L = kind <= LOGOS_W_DOWN ? &m->layers[(size_t)l] : nullptr;
+  Layer* L = (kind <= LOGOS_W_DOWN || kind >= LOGOS_W_Q_BIAS) ? &m->layers[(size_t)l] : nullptr;
   auto rows_of = [&](Q8Mat& w, int64_t row0, int64_t mul) {
     t.q = w.q + row0 * w.k; t.q_pitch = (size_t)(mul * w.k);
     t.s = w.s + row0 * (w.k / 32); t.s_pitch = (size_t)(mul * (w.k / 32) * 4);
@@ -636,6 +649,9 @@ TensorHome tensor_home(Model* m, int64_t l, int kind) {
     case LOGOS_W_ATTN_NORM:  t.q = m->gains + (2 * l) * H; t.q_pitch = (size_t)H * 4; break;
     case LOGOS_W_MLP_NORM:   t.q = m->gains + (2 * l + 1) * H; t.q_pitch = (size_t)H * 4; break;
     case LOGOS_W_FINAL_NORM: t.q = m->gains + (2 * m->cfg.layers) * H; t.q_pitch = (size_t)H * 4; break;
+    case LOGOS_W_Q_BIAS: t.q = L->bqkv; t.q_pitch = (size_t)m->nq * 4; break;
+    case LOGOS_W_K_BIAS: t.q = L->bqkv + m->nq; t.q_pitch = (size_t)m->nkv * 4; break;
+    case LOGOS_W_V_BIAS: t.q = L->bqkv + m->nq + m->nkv; t.q_pitch = (size_t)m->nkv * 4; break;
     case LOGOS_W_Q:    rows_of(L->wqkv, 0, 1); break;
     case LOGOS_W_K:    rows_of(L->wqkv, m->nq, 1); break;
     case LOGOS_W_V:    rows_of(L->wqkv, m->nq + m->nkv, 1); break;
@@ -652,21 +668,26 @@ TensorHome tensor_home(Model* m, int64_t l, int kind) {
 
 logos_status_t same_arch(const WeightsArch& f, const WeightsArch& a, const char* who) {
   if (f.layers != a.layers || f.hidden != a.hidden || f.h_q != a.h_q || f.h_kv != a.h_kv || f.head_dim != a.head_dim ||
-      f.ffn != a.ffn || f.vocab != a.vocab || f.tied != a.tied)
+      f.ffn != a.ffn || f.vocab != a.vocab || f.tied != a.tied || f.qkv_bias != a.qkv_bias)
     return fail(LOGOS_ERROR,
-                "%s: the file holds layers %lld hidden %lld heads %lld/%lld x %lld ffn %lld vocab %lld tied %d, the model "
-                "layers %lld hidden %lld heads %lld/%lld x %lld ffn %lld vocab %lld tied %d",
+                "%s: the file holds layers %lld hidden %lld heads %lld/%lld x %lld ffn %lld vocab %lld tied %d qkv_bias %d, "
+                "the model layers %lld hidden %lld heads %lld/%lld x %lld ffn %lld vocab %lld tied %d qkv_bias %d",
                 who, (long long)f.layers, (long long)f.hidden, (long long)f.h_q, (long long)f.h_kv, (long long)f.head_dim,
-                (long long)f.ffn, (long long)f.vocab, f.tied, (long long)a.layers, (long long)a.hidden, (long long)a.h_q,
-                (long long)a.h_kv, (long long)a.head_dim, (long long)a.ffn, (long long)a.vocab, a.tied);
+                (long long)f.ffn, (long long)f.vocab, f.tied, f.qkv_bias, (long long)a.layers, (long long)a.hidden,
+                (long long)a.h_q, (long long)a.h_kv, (long long)a.head_dim, (long long)a.ffn, (long long)a.vocab, a.tied,
+                a.qkv_bias);
   return LOGOS_OK;
 }
 
 // Every tensor of the file in storage order: fn(layer, kind).
 template <class F>
 logos_status_t for_each_tensor(const WeightsArch& a, F&& fn) {
-  for (int64_t l = 0; l < a.layers; ++l)
-    for (int kind = LOGOS_W_ATTN_NORM; kind <= LOGOS_W_DOWN; ++kind) LOGOS_TRY(fn(l, kind));
+  for (int64_t l = 0; l < a.layers; ++l) {
+    for (int kind = LOGOS_W_ATTN_NORM; kind <= LOGOS_W_V; ++kind) LOGOS_TRY(fn(l, kind));
+    if (a.qkv_bias)
+      for (int kind = LOGOS_W_Q_BIAS; kind <= LOGOS_W_V_BIAS; ++kind) LOGOS_TRY(fn(l, kind));
+    for (int kind = LOGOS_W_O; kind <= LOGOS_W_DOWN; ++kind) LOGOS_TRY(fn(l, kind));
+  }
   LOGOS_TRY(fn((int64_t)0, (int)LOGOS_W_FINAL_NORM));
   LOGOS_TRY(fn((int64_t)0, (int)LOGOS_W_EMBED));
   if (!a.tied) LOGOS_TRY(fn((int64_t)0, (int)LOGOS_W_HEAD));
@@ -686,7 +707,8 @@ logos_status_t load_weights(Model* m, const MappedWeights& w) {
     LOGOS_TRY(weights_span(a, l, kind, &t, who));
     LOGOS_TRY(weights_shard(a, kind, m->cfg.tp_degree, m->cfg.tp_rank, &r, who));
     const TensorHome home = tensor_home(m, l, kind);
-    if (is_gain(kind)) return stg.put(home.q, home.q_pitch, w.base + t.q_off, (size_t)t.q_bytes, (size_t)t.q_bytes, 1);
+    if (is_vector(kind))  // a gain whole, a bias this rank's slice
+      return stg.put(home.q, home.q_pitch, w.base + t.q_off + r.col0 * 4, (size_t)r.cols * 4, (size_t)r.cols * 4, 1);
     const int64_t kb = t.k / 32;
     LOGOS_TRY(stg.put(home.q, home.q_pitch, w.base + t.q_off + r.row0 * t.k + r.col0, (size_t)t.k, (size_t)r.cols, r.rows));
     return stg.put(home.s, home.s_pitch, w.base + t.s_off + (r.row0 * kb + r.col0 / 32) * 4, (size_t)kb * 4,
@@ -712,7 +734,7 @@ logos_status_t save_weights(Model* m, int fd) {
     TensorSpan t;
     LOGOS_TRY(weights_span(a, l, kind, &t, who));
     const TensorHome home = tensor_home(m, l, kind);
-    if (is_gain(kind)) return stg.get_to_file(fd, t.q_off, home.q, home.q_pitch, (size_t)t.q_bytes, 1);
+    if (is_vector(kind)) return stg.get_to_file(fd, t.q_off, home.q, home.q_pitch, (size_t)t.q_bytes, 1);
     LOGOS_TRY(stg.get_to_file(fd, t.q_off, home.q, home.q_pitch, (size_t)t.k, t.n));
     return stg.get_to_file(fd, t.s_off, home.s, home.s_pitch, (size_t)(t.k / 32) * 4, t.n);
   });

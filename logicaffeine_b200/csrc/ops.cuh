@@ -77,6 +77,11 @@ struct AttnArgs {
   // fold the GEMM's reduce kernel would have done, without its launch).
   int           f32_parts = 1;
   int64_t       f32_part_stride = 0;
+  // Bias vectors of the q, k and v projections (f32 [Hq*D], [Hkv*D], [Hkv*D]; f32 inputs only),
+  // added after the partial copies where the kernel stages its inputs.  Null = none.
+  const float*  q_bias = nullptr;
+  const float*  k_bias = nullptr;
+  const float*  v_bias = nullptr;
   __half*       k_cache = nullptr;   // [B][Hkv][Lmax][D]
   __half*       v_cache = nullptr;
   const float*  rope = nullptr;      // [Lmax][D/2][2]

@@ -24,14 +24,15 @@ void walk(const WeightsArch& a, int64_t layer, int kind, TensorSpan* out) {
   const int64_t H = a.hidden, nq = a.h_q * a.head_dim, nkv = a.h_kv * a.head_dim, F = a.ffn;
   int64_t off = (int64_t)sizeof(WeightsHeader);
   bool found = false;
-  auto gain = [&](int64_t l, int k) {
+  auto vec = [&](int64_t l, int k, int64_t len) {
     if (found) return;
     if (l == layer && k == kind) {
-      out->q_off = off; out->q_bytes = H * 4; out->s_off = 0; out->s_bytes = 0; out->n = 1; out->k = H;
+      out->q_off = off; out->q_bytes = len * 4; out->s_off = 0; out->s_bytes = 0; out->n = 1; out->k = len;
       found = true;
     }
-    off = align_up(off + H * 4);
+    off = align_up(off + len * 4);
   };
+  auto gain = [&](int64_t l, int k) { vec(l, k, H); };
   auto mat = [&](int64_t l, int k, int64_t n, int64_t kk) {
     if (found) return;
     const int64_t qb = n * kk, sb = n * (kk / 32) * 4;
@@ -46,6 +47,11 @@ void walk(const WeightsArch& a, int64_t layer, int kind, TensorSpan* out) {
     mat(l, LOGOS_W_Q, nq, H);
     mat(l, LOGOS_W_K, nkv, H);
     mat(l, LOGOS_W_V, nkv, H);
+    if (a.qkv_bias) {
+      vec(l, LOGOS_W_Q_BIAS, nq);
+      vec(l, LOGOS_W_K_BIAS, nkv);
+      vec(l, LOGOS_W_V_BIAS, nkv);
+    }
     mat(l, LOGOS_W_O, H, nq);
     gain(l, LOGOS_W_MLP_NORM);
     mat(l, LOGOS_W_GATE, F, H);
@@ -64,6 +70,7 @@ WeightsArch arch_of(const logos_llm_config_t& c) {
   WeightsArch a;
   a.layers = c.layers; a.hidden = c.hidden; a.h_q = c.h_q; a.h_kv = c.h_kv; a.head_dim = c.head_dim;
   a.ffn = c.ffn; a.vocab = c.vocab; a.tied = c.tied_embeddings ? 1 : 0;
+  a.qkv_bias = c.qkv_bias ? 1 : 0;
   return a;
 }
 
@@ -79,7 +86,10 @@ logos_status_t check_arch(const WeightsArch& a, const char* who) {
   return LOGOS_OK;
 }
 
-bool is_gain(int kind) { return kind == LOGOS_W_ATTN_NORM || kind == LOGOS_W_MLP_NORM || kind == LOGOS_W_FINAL_NORM; }
+bool is_vector(int kind) {
+  return kind == LOGOS_W_ATTN_NORM || kind == LOGOS_W_MLP_NORM || kind == LOGOS_W_FINAL_NORM || kind == LOGOS_W_Q_BIAS ||
+         kind == LOGOS_W_K_BIAS || kind == LOGOS_W_V_BIAS;
+}
 
 int64_t weights_file_bytes(const WeightsArch& a) {
   TensorSpan end;
@@ -88,8 +98,9 @@ int64_t weights_file_bytes(const WeightsArch& a) {
 }
 
 logos_status_t weights_span(const WeightsArch& a, int64_t layer, int kind, TensorSpan* out, const char* who) {
-  if (kind < LOGOS_W_ATTN_NORM || kind > LOGOS_W_HEAD) return fail(LOGOS_OUT_OF_BOUNDS, "%s: tensor kind %d", who, kind);
-  const bool per_layer = kind <= LOGOS_W_DOWN;
+  if (kind < LOGOS_W_ATTN_NORM || kind > LOGOS_W_V_BIAS) return fail(LOGOS_OUT_OF_BOUNDS, "%s: tensor kind %d", who, kind);
+  const bool per_layer = kind <= LOGOS_W_DOWN || kind >= LOGOS_W_Q_BIAS;
+  if (kind >= LOGOS_W_Q_BIAS && !a.qkv_bias) return fail(LOGOS_ERROR, "%s: the architecture has no q/k/v biases", who);
   if (per_layer && (layer < 0 || layer >= a.layers))
     return fail(LOGOS_OUT_OF_BOUNDS, "%s: layer %lld of %lld", who, (long long)layer, (long long)a.layers);
   if (kind == LOGOS_W_HEAD && a.tied) return fail(LOGOS_ERROR, "%s: tied embeddings: the file has no separate lm_head", who);
@@ -117,6 +128,9 @@ logos_status_t weights_shard(const WeightsArch& a, int kind, int g, int r, Shard
     case LOGOS_W_ATTN_NORM:
     case LOGOS_W_MLP_NORM:
     case LOGOS_W_FINAL_NORM: s = {0, 1, 0, H}; break;
+    case LOGOS_W_Q_BIAS: s = {0, 1, r * (nq / g), nq / g}; break;
+    case LOGOS_W_K_BIAS:
+    case LOGOS_W_V_BIAS: s = {0, 1, r * (nkv / g), nkv / g}; break;
     default: return fail(LOGOS_OUT_OF_BOUNDS, "%s: tensor kind %d", who, kind);
   }
   *out = s;
@@ -155,7 +169,10 @@ logos_status_t weights_open(const char* path, MappedWeights* out, const char* wh
     WeightsArch a;
     a.layers = h.layers; a.hidden = h.hidden; a.h_q = h.h_q; a.h_kv = h.h_kv; a.head_dim = h.head_dim;
     a.ffn = h.ffn; a.vocab = h.vocab; a.tied = h.tied_embeddings ? 1 : 0;
-    if (check_arch(a, who) != LOGOS_OK) {
+    a.qkv_bias = (h.flags & 1u) ? 1 : 0;
+    if (h.flags & ~1u) {
+      s = fail(LOGOS_DESERIALIZATION_FAILED, "%s: '%s' sets header flags 0x%x this library does not know", who, path, h.flags);
+    } else if (check_arch(a, who) != LOGOS_OK) {
       s = fail(LOGOS_DESERIALIZATION_FAILED, "%s: '%s' names an architecture this library cannot hold", who, path);
     } else {
       const int64_t need = weights_file_bytes(a);
@@ -221,6 +238,7 @@ logos_status_t logos_llm_weights_header(const logos_llm_config_t* cfg, void* out
     h.layers = a.layers; h.hidden = a.hidden; h.h_q = a.h_q; h.h_kv = a.h_kv; h.head_dim = a.head_dim;
     h.ffn = a.ffn; h.vocab = a.vocab; h.tied_embeddings = (uint32_t)a.tied;
     h.block = 32;
+    h.flags = a.qkv_bias ? 1u : 0u;
     h.file_bytes = (uint64_t)weights_file_bytes(a);
     memcpy(out_256_bytes, &h, sizeof(h));
     return LOGOS_OK;
@@ -236,6 +254,7 @@ logos_status_t logos_llm_weights_check(const char* path, logos_llm_config_t* cfg
       cfg_out->layers = w.arch.layers; cfg_out->hidden = w.arch.hidden; cfg_out->h_q = w.arch.h_q;
       cfg_out->h_kv = w.arch.h_kv; cfg_out->head_dim = w.arch.head_dim; cfg_out->ffn = w.arch.ffn;
       cfg_out->vocab = w.arch.vocab; cfg_out->tied_embeddings = w.arch.tied;
+      cfg_out->qkv_bias = w.arch.qkv_bias;
     }
     weights_close(&w);
     return LOGOS_OK;
@@ -255,9 +274,9 @@ logos_status_t logos_llm_weights_read_shard(const char* path, int32_t tp_degree,
     logos_status_t s = weights_span(w.arch, layer, tensor, &t, who);
     if (s == LOGOS_OK) s = weights_shard(w.arch, tensor, tp_degree, tp_rank, &r, who);
     if (s == LOGOS_OK) {
-      if (is_gain(tensor)) {
-        if (q_capacity < t.q_bytes) s = fail(LOGOS_OUT_OF_BOUNDS, "%s: the gain vector needs %lld bytes", who, (long long)t.q_bytes);
-        else memcpy(q_out, w.base + t.q_off, (size_t)t.q_bytes);
+      if (is_vector(tensor)) {  // a gain is whole on every rank, a bias is the rank's slice
+        if (q_capacity < r.cols * 4) s = fail(LOGOS_OUT_OF_BOUNDS, "%s: the vector needs %lld bytes", who, (long long)(r.cols * 4));
+        else memcpy(q_out, w.base + t.q_off + r.col0 * 4, (size_t)r.cols * 4);
       } else if (!s_out) {
         s = fail(LOGOS_NULL_POINTER, "%s: s_out is null", who);
       } else if (q_capacity < r.rows * r.cols || s_capacity < r.rows * (r.cols / 32) * 4) {

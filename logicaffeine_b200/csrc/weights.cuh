@@ -9,6 +9,7 @@
 //   per layer l = 0..layers-1, in this order:
 //     attn_norm  f32 [hidden]
 //     q  k  v    each: int8 [rows][hidden] then f32 [rows][hidden/32]   (rows = h_q*D, h_kv*D, h_kv*D)
+//     q_bias  k_bias  v_bias   f32 [rows] each, present only when header flag bit 0 (qkv_bias) is set
 //     o          int8 [hidden][h_q*D]     then f32 [hidden][h_q*D/32]
 //     mlp_norm   f32 [hidden]
 //     gate  up   each: int8 [ffn][hidden] then f32 [ffn][hidden/32]
@@ -38,17 +39,20 @@ struct WeightsHeader {
   uint32_t tied_embeddings;
   uint32_t block;       // elements per scale along K: 32
   uint64_t file_bytes;  // header + payload, as laid out above
-  uint8_t  pad[256 - 8 - 4 - 4 - 7 * 8 - 4 - 4 - 8];
+  uint32_t flags;       // bit 0: q/k/v bias vectors are present
+  uint8_t  pad[256 - 8 - 4 - 4 - 7 * 8 - 4 - 4 - 8 - 4];
 };
 static_assert(sizeof(WeightsHeader) == 256, "the header is 256 bytes");
 
 struct WeightsArch {
   int64_t layers = 0, hidden = 0, h_q = 0, h_kv = 0, head_dim = 0, ffn = 0, vocab = 0;
   int32_t tied = 0;
+  int32_t qkv_bias = 0;
 };
 
 // One tensor's place in the file.  Matrices: q_off/q_bytes = the int8 part [n][k], s_off/s_bytes
-// = the scales [n][k/32].  Gain vectors: q_off/q_bytes = the f32 vector, n = 1, k = hidden, no scales.
+// = the scales [n][k/32].  Vectors (gains, biases): q_off/q_bytes = the f32 vector, n = 1,
+// k = its length, no scales.
 struct TensorSpan {
   int64_t q_off = 0, q_bytes = 0, s_off = 0, s_bytes = 0, n = 0, k = 0;
 };
@@ -60,7 +64,7 @@ struct ShardRect {
 
 WeightsArch arch_of(const logos_llm_config_t& c);
 logos_status_t check_arch(const WeightsArch& a, const char* who);
-bool is_gain(int kind);
+bool is_vector(int kind);
 // kind: logos_weight_tensor_t.  layer is ignored for final_norm, embed and head.
 logos_status_t weights_span(const WeightsArch& a, int64_t layer, int kind, TensorSpan* out, const char* who);
 int64_t weights_file_bytes(const WeightsArch& a);

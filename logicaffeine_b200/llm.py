@@ -248,7 +248,7 @@ class Llm:
 
     def __init__(self, nccl_unique_id=None, **cfg):
         defaults = dict(rms_eps=1e-6, rope_theta=1e6, tied_embeddings=1, tp_degree=1, tp_rank=0, device=0,
-                        act_dtype=F32, seed=0, init_std=0.02, reserved=0)
+                        act_dtype=F32, seed=0, init_std=0.02, qkv_bias=0)
         defaults.update(cfg)
         self.cfg = LlmConfig(**defaults)
         h = _lib.H()

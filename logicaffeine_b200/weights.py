@@ -8,8 +8,10 @@ crates/logicaffeine_system/src/memory.rs:97-103): the bytes on disk are the byte
 in HBM, there is nothing to parse.
 
 Regions start on 256-byte boundaries, in this order: per layer attn_norm, q, k, v,
-o, mlp_norm, gate, up, down; then final_norm, embed and (untied only) head.  A
-matrix is int8 [n][k] followed by f32 [n][k/32]; a gain is f32 [hidden].
+(q_bias, k_bias, v_bias when the architecture has them: header flag bit 0), o,
+mlp_norm, gate, up, down; then final_norm, embed and (untied only) head.  A matrix
+is int8 [n][k] followed by f32 [n][k/32]; a gain is f32 [hidden], a bias f32 [rows
+of its projection].
 
 `layout()` restates the arithmetic in Python, independently of the library's
 `logos_llm_weights_span`; the tests hold the two against each other.
@@ -21,9 +23,12 @@ import numpy as np
 
 from ._lib import LlmConfig, call
 
-ATTN_NORM, Q, K, V, O, MLP_NORM, GATE, UP, DOWN, FINAL_NORM, EMBED, HEAD = range(12)
-TENSOR_NAMES = ("attn_norm", "q", "k", "v", "o", "mlp_norm", "gate", "up", "down", "final_norm", "embed", "head")
+ATTN_NORM, Q, K, V, O, MLP_NORM, GATE, UP, DOWN, FINAL_NORM, EMBED, HEAD, Q_BIAS, K_BIAS, V_BIAS = range(15)
+TENSOR_NAMES = ("attn_norm", "q", "k", "v", "o", "mlp_norm", "gate", "up", "down", "final_norm", "embed", "head",
+                "q_bias", "k_bias", "v_bias")
 GAINS = (ATTN_NORM, MLP_NORM, FINAL_NORM)
+BIASES = (Q_BIAS, K_BIAS, V_BIAS)
+VECTORS = GAINS + BIASES
 MAGIC = b"LOGOSQ8W"
 VERSION = 1
 HEADER_BYTES = 256
@@ -36,17 +41,19 @@ def _up(v):
 
 
 def _arch(cfg):
-    """(layers, hidden, h_q, h_kv, head_dim, ffn, vocab, tied) from a dict or an LlmConfig."""
+    """(layers, hidden, h_q, h_kv, head_dim, ffn, vocab, tied, qkv_bias) from a dict or an LlmConfig."""
     get = (lambda k: cfg[k]) if isinstance(cfg, dict) else (lambda k: getattr(cfg, k))
     tied = cfg.get("tied_embeddings", 1) if isinstance(cfg, dict) else cfg.tied_embeddings
-    return tuple(int(get(k)) for k in _ARCH) + (1 if tied else 0,)
+    bias = cfg.get("qkv_bias", 0) if isinstance(cfg, dict) else cfg.qkv_bias
+    return tuple(int(get(k)) for k in _ARCH) + (1 if tied else 0, 1 if bias else 0)
 
 
 def shape(cfg, kind):
-    """(n, k) of a whole tensor; a gain is (1, hidden)."""
-    _, hidden, h_q, h_kv, d, ffn, vocab, _ = _arch(cfg)
+    """(n, k) of a whole tensor; a vector is (1, length)."""
+    _, hidden, h_q, h_kv, d, ffn, vocab, _, _ = _arch(cfg)
     return {
         ATTN_NORM: (1, hidden), MLP_NORM: (1, hidden), FINAL_NORM: (1, hidden),
+        Q_BIAS: (1, h_q * d), K_BIAS: (1, h_kv * d), V_BIAS: (1, h_kv * d),
         Q: (h_q * d, hidden), K: (h_kv * d, hidden), V: (h_kv * d, hidden), O: (hidden, h_q * d),
         GATE: (ffn, hidden), UP: (ffn, hidden), DOWN: (hidden, ffn), EMBED: (vocab, hidden), HEAD: (vocab, hidden),
     }[kind]
@@ -54,8 +61,9 @@ def shape(cfg, kind):
 
 def tensors(cfg):
     """(layer, kind) of every tensor in storage order (layer is 0 for the model-level ones)."""
-    layers, tied = _arch(cfg)[0], _arch(cfg)[7]
-    out = [(l, kind) for l in range(layers) for kind in range(ATTN_NORM, DOWN + 1)]
+    layers, tied, bias = _arch(cfg)[0], _arch(cfg)[7], _arch(cfg)[8]
+    per_layer = [ATTN_NORM, Q, K, V] + (list(BIASES) if bias else []) + [O, MLP_NORM, GATE, UP, DOWN]
+    out = [(l, kind) for l in range(layers) for kind in per_layer]
     out += [(0, FINAL_NORM), (0, EMBED)]
     if not tied:
         out.append((0, HEAD))
@@ -68,7 +76,7 @@ def layout(cfg):
     spans = {}
     for layer, kind in tensors(cfg):
         n, k = shape(cfg, kind)
-        if kind in GAINS:
+        if kind in VECTORS:
             spans[(layer, kind)] = (off, k * 4, 0, 0)
             off = _up(off + k * 4)
         else:
@@ -79,15 +87,16 @@ def layout(cfg):
 
 
 def header(cfg):
-    layers, hidden, h_q, h_kv, d, ffn, vocab, tied = _arch(cfg)
+    layers, hidden, h_q, h_kv, d, ffn, vocab, tied, bias = _arch(cfg)
     _, total = layout(cfg)
-    h = MAGIC + struct.pack("<II7qIIQ", VERSION, HEADER_BYTES, layers, hidden, h_q, h_kv, d, ffn, vocab, tied, 32, total)
+    h = MAGIC + struct.pack("<II7qIIQI", VERSION, HEADER_BYTES, layers, hidden, h_q, h_kv, d, ffn, vocab, tied, 32, total,
+                            bias)
     return h + bytes(HEADER_BYTES - len(h))
 
 
 def writeWeightsFile(path, cfg, get_tensor):
     """Write a weight file.  get_tensor(layer, kind) returns (q int8 [n][k], s f32 [n][k/32]) for a
-    matrix and an f32 [hidden] vector for a gain (None: all ones)."""
+    matrix and an f32 vector for a gain (None: all ones) or a bias (None: all zeros)."""
     spans, total = layout(cfg)
     with open(path, "wb") as f:
         f.truncate(total)
@@ -95,8 +104,9 @@ def writeWeightsFile(path, cfg, get_tensor):
         for (layer, kind), (q_off, q_bytes, s_off, s_bytes) in spans.items():
             n, k = shape(cfg, kind)
             got = get_tensor(layer, kind)
-            if kind in GAINS:
-                g = np.ones(k, np.float32) if got is None else np.ascontiguousarray(got, np.float32).reshape(k)
+            if kind in VECTORS:
+                default = np.ones if kind in GAINS else np.zeros
+                g = default(k, np.float32) if got is None else np.ascontiguousarray(got, np.float32).reshape(k)
                 f.seek(q_off)
                 f.write(g.tobytes())
                 continue
@@ -165,16 +175,18 @@ def weightsCheck(path):
     call("logos_llm_weights_check", str(path).encode(), C.byref(cfg))
     out = {k: int(getattr(cfg, k)) for k in _ARCH}
     out["tied_embeddings"] = int(cfg.tied_embeddings)
+    out["qkv_bias"] = int(cfg.qkv_bias)
     return out
 
 
 def weightsReadShard(path, layer, kind, tp_degree=1, tp_rank=0):
     """What one rank of a tensor-parallel group holds of a tensor, read on the host:
-    (q int8 [rows][cols], s f32 [rows][cols/32]), or an f32 vector for a gain."""
+    (q int8 [rows][cols], s f32 [rows][cols/32]), or an f32 vector for a gain (whole) or a
+    bias (the rank's slice)."""
     arch = weightsCheck(path)
     n, k = shape(arch, kind)
-    if kind in GAINS:
-        g = np.empty(k, np.float32)
+    if kind in VECTORS:
+        g = np.empty(k // tp_degree if kind in BIASES else k, np.float32)
         call("logos_llm_weights_read_shard", str(path).encode(), int(tp_degree), int(tp_rank), int(layer), int(kind),
              g.ctypes.data_as(C.c_void_p), g.nbytes, None, 0, None, None)
         return g

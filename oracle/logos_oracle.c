@@ -559,7 +559,7 @@ typedef struct {
   int32_t tied_embeddings, tp_degree, tp_rank, device, act_dtype;
   uint64_t seed;
   float init_std;
-  int32_t reserved;
+  int32_t qkv_bias; /* 1: the q, k and v projections add a bias vector (Qwen2) */
 } orc_llm_config_t;
 
 typedef struct {
@@ -571,6 +571,7 @@ typedef struct {
 typedef struct {
   orc_llm_config_t cfg;
   q8mat *wq, *wk, *wv, *wo, *wg, *wu, *wd;
+  float **bq, **bk, **bv; /* per layer, only with cfg.qkv_bias: f32 [h_q*D], [h_kv*D], [h_kv*D] */
   q8mat embed, head;
   uint16_t **kc, **vc; /* per layer [B][Hkv][Lmax][D] */
   float* rope;
@@ -608,6 +609,8 @@ ORC_API void* orc_llm_create(const orc_llm_config_t* cfg) {
   M->wv = calloc((size_t)L, sizeof(q8mat)); M->wo = calloc((size_t)L, sizeof(q8mat));
   M->wg = calloc((size_t)L, sizeof(q8mat)); M->wu = calloc((size_t)L, sizeof(q8mat));
   M->wd = calloc((size_t)L, sizeof(q8mat));
+  M->bq = calloc((size_t)L, sizeof(float*)); M->bk = calloc((size_t)L, sizeof(float*));
+  M->bv = calloc((size_t)L, sizeof(float*));
   M->kc = calloc((size_t)L, sizeof(uint16_t*));
   M->vc = calloc((size_t)L, sizeof(uint16_t*));
   for (int64_t l = 0; l < L; ++l) {
@@ -619,6 +622,14 @@ ORC_API void* orc_llm_create(const orc_llm_config_t* cfg) {
     M->wg[l] = make_mat(F, H, cfg->seed, st + 4, cfg->init_std);
     M->wu[l] = make_mat(F, H, cfg->seed, st + 5, cfg->init_std);
     M->wd[l] = make_mat(H, F, cfg->seed, st + 6, cfg->init_std);
+    if (cfg->qkv_bias) { /* streams 7, 8, 9 of the layer: N(0, init_std) */
+      M->bq[l] = (float*)malloc(sizeof(float) * (size_t)nq);
+      M->bk[l] = (float*)malloc(sizeof(float) * (size_t)nkv);
+      M->bv[l] = (float*)malloc(sizeof(float) * (size_t)nkv);
+      orc_synth_fill(M->bq[l], ORC_F32, 2, cfg->seed, st + 7, 0, nq, 0.0f, cfg->init_std);
+      orc_synth_fill(M->bk[l], ORC_F32, 2, cfg->seed, st + 8, 0, nkv, 0.0f, cfg->init_std);
+      orc_synth_fill(M->bv[l], ORC_F32, 2, cfg->seed, st + 9, 0, nkv, 0.0f, cfg->init_std);
+    }
     size_t kv = (size_t)(cfg->batch * cfg->h_kv * cfg->l_max * D);
     M->kc[l] = (uint16_t*)calloc(kv, 2);
     M->vc[l] = (uint16_t*)calloc(kv, 2);
@@ -641,9 +652,11 @@ ORC_API void orc_llm_free(void* model) {
   for (int64_t l = 0; l < M->cfg.layers; ++l) {
     free_mat(&M->wq[l]); free_mat(&M->wk[l]); free_mat(&M->wv[l]); free_mat(&M->wo[l]);
     free_mat(&M->wg[l]); free_mat(&M->wu[l]); free_mat(&M->wd[l]);
+    free(M->bq[l]); free(M->bk[l]); free(M->bv[l]);
     free(M->kc[l]); free(M->vc[l]);
   }
   free(M->wq); free(M->wk); free(M->wv); free(M->wo); free(M->wg); free(M->wu); free(M->wd);
+  free(M->bq); free(M->bk); free(M->bv);
   free(M->kc); free(M->vc);
   free_mat(&M->embed);
   if (!M->cfg.tied_embeddings) free_mat(&M->head);
@@ -737,6 +750,12 @@ static void llm_step(orc_llm* M, int sample, const int32_t* lens, int64_t p) {
     orc_q8_gemm_f32(xn, ORC_F32, M->wq[l].q, M->wq[l].s, qf, B, nq, H);
     orc_q8_gemm_f32(xn, ORC_F32, M->wk[l].q, M->wk[l].s, kf, B, nkv, H);
     orc_q8_gemm_f32(xn, ORC_F32, M->wv[l].q, M->wv[l].s, vf, B, nkv, H);
+    if (c->qkv_bias)
+      for (int64_t i = 0; i < B; ++i) {
+        for (int64_t j = 0; j < nq; ++j) qf[i * nq + j] = qf[i * nq + j] + M->bq[l][j];
+        for (int64_t j = 0; j < nkv; ++j) kf[i * nkv + j] = kf[i * nkv + j] + M->bk[l][j];
+        for (int64_t j = 0; j < nkv; ++j) vf[i * nkv + j] = vf[i * nkv + j] + M->bv[l][j];
+      }
     for (int64_t i = 0; i < B; ++i) {
       int64_t pos = pos0[i];
       int full = pos >= c->l_max;
@@ -781,18 +800,22 @@ static void llm_step(orc_llm* M, int sample, const int32_t* lens, int64_t p) {
 }
 
 /* One tensor of the model, named as the weight file names them: 0 attn_norm, 1 q, 2 k, 3 v,
- * 4 o, 5 mlp_norm, 6 gate, 7 up, 8 down, 9 final_norm, 10 embed, 11 head.  A matrix is int8
- * [n][k] plus f32 [n][k/32]; a gain is f32 [hidden] behind `q`.  Returns 0, or -1 for a
- * tensor the model does not have. */
-static int llm_tensor(orc_llm* M, int64_t layer, int kind, q8mat** mat, float** gain) {
+ * 4 o, 5 mlp_norm, 6 gate, 7 up, 8 down, 9 final_norm, 10 embed, 11 head, 12 q_bias, 13 k_bias,
+ * 14 v_bias.  A matrix is int8 [n][k] plus f32 [n][k/32]; a vector (gain [hidden], bias [rows of
+ * its projection]) is f32 behind `q`.  Returns 0, or -1 for a tensor the model does not have. */
+static int llm_tensor(orc_llm* M, int64_t layer, int kind, q8mat** mat, float** gain, int64_t* gain_len) {
   const orc_llm_config_t* c = &M->cfg;
   *mat = NULL;
   *gain = NULL;
-  if (kind <= 8 && (layer < 0 || layer >= c->layers)) return -1;
+  *gain_len = c->hidden;
+  if ((kind <= 8 || kind >= 12) && (layer < 0 || layer >= c->layers)) return -1;
   switch (kind) {
     case 0: *gain = M->gains + (2 * layer) * c->hidden; return 0;
     case 5: *gain = M->gains + (2 * layer + 1) * c->hidden; return 0;
     case 9: *gain = M->gains + (2 * c->layers) * c->hidden; return 0;
+    case 12: if (!c->qkv_bias) return -1; *gain = M->bq[layer]; *gain_len = c->h_q * c->head_dim; return 0;
+    case 13: if (!c->qkv_bias) return -1; *gain = M->bk[layer]; *gain_len = c->h_kv * c->head_dim; return 0;
+    case 14: if (!c->qkv_bias) return -1; *gain = M->bv[layer]; *gain_len = c->h_kv * c->head_dim; return 0;
     case 1: *mat = &M->wq[layer]; return 0;
     case 2: *mat = &M->wk[layer]; return 0;
     case 3: *mat = &M->wv[layer]; return 0;
@@ -809,9 +832,10 @@ ORC_API int orc_llm_set_tensor(void* model, int64_t layer, int kind, const void*
   orc_llm* M = (orc_llm*)model;
   q8mat* mat;
   float* gain;
-  if (llm_tensor(M, layer, kind, &mat, &gain) != 0) return -1;
+  int64_t gain_len;
+  if (llm_tensor(M, layer, kind, &mat, &gain, &gain_len) != 0) return -1;
   if (gain) {
-    memcpy(gain, q, sizeof(float) * (size_t)M->cfg.hidden);
+    memcpy(gain, q, sizeof(float) * (size_t)gain_len);
   } else {
     memcpy(mat->q, q, (size_t)(mat->n * mat->k));
     memcpy(mat->s, s, sizeof(float) * (size_t)(mat->n * (mat->k / 32)));
@@ -822,9 +846,10 @@ ORC_API int orc_llm_get_tensor(void* model, int64_t layer, int kind, void* q, fl
   orc_llm* M = (orc_llm*)model;
   q8mat* mat;
   float* gain;
-  if (llm_tensor(M, layer, kind, &mat, &gain) != 0) return -1;
+  int64_t gain_len;
+  if (llm_tensor(M, layer, kind, &mat, &gain, &gain_len) != 0) return -1;
   if (gain) {
-    memcpy(q, gain, sizeof(float) * (size_t)M->cfg.hidden);
+    memcpy(q, gain, sizeof(float) * (size_t)gain_len);
   } else {
     memcpy(q, mat->q, (size_t)(mat->n * mat->k));
     memcpy(s, mat->s, sizeof(float) * (size_t)(mat->n * (mat->k / 32)));

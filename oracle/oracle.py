@@ -31,7 +31,7 @@ class LlmConfig(C.Structure):
         ("rms_eps", C.c_float), ("rope_theta", C.c_float),
         ("tied_embeddings", C.c_int32), ("tp_degree", C.c_int32), ("tp_rank", C.c_int32),
         ("device", C.c_int32), ("act_dtype", C.c_int32),
-        ("seed", C.c_uint64), ("init_std", C.c_float), ("reserved", C.c_int32),
+        ("seed", C.c_uint64), ("init_std", C.c_float), ("qkv_bias", C.c_int32),
     ]
 
 
@@ -253,12 +253,17 @@ class Llm:
         return {1: (nq, c.hidden), 2: (nkv, c.hidden), 3: (nkv, c.hidden), 4: (c.hidden, nq), 6: (c.ffn, c.hidden),
                 7: (c.ffn, c.hidden), 8: (c.hidden, c.ffn), 10: (c.vocab, c.hidden), 11: (c.vocab, c.hidden)}.get(kind)
 
+    def _vector_len(self, kind):
+        c = self.cfg
+        return {12: c.h_q * c.head_dim, 13: c.h_kv * c.head_dim, 14: c.h_kv * c.head_dim}.get(kind, c.hidden)
+
     def get_tensor(self, layer, kind):
         """A tensor by the weight file's numbering (0 attn_norm, 1 q, 2 k, 3 v, 4 o, 5 mlp_norm, 6 gate,
-        7 up, 8 down, 9 final_norm, 10 embed, 11 head): (q, s) for a matrix, an f32 vector for a gain."""
+        7 up, 8 down, 9 final_norm, 10 embed, 11 head, 12 q_bias, 13 k_bias, 14 v_bias): (q, s) for a matrix,
+        an f32 vector for a gain or a bias."""
         shape = self._tensor_shape(kind)
         if shape is None:
-            g = np.empty(self.cfg.hidden, np.float32)
+            g = np.empty(self._vector_len(kind), np.float32)
             if lib().orc_llm_get_tensor(self._h, C.c_int64(layer), C.c_int(kind), _p(g), None) != 0:
                 raise KeyError((layer, kind))
             return g
@@ -271,7 +276,7 @@ class Llm:
     def set_tensor(self, layer, kind, q, s=None):
         shape = self._tensor_shape(kind)
         if shape is None:
-            g = np.ascontiguousarray(q, np.float32).reshape(self.cfg.hidden)
+            g = np.ascontiguousarray(q, np.float32).reshape(self._vector_len(kind))
             rc = lib().orc_llm_set_tensor(self._h, C.c_int64(layer), C.c_int(kind), _p(g), None)
         else:
             q = np.ascontiguousarray(q, np.int8).reshape(shape)

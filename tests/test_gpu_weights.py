@@ -117,3 +117,47 @@ def test_mismatched_and_unreadable_files_are_refused(llm, oracle, tmp_path):
     gpu.prefill(toks)                                   # untouched by the refused loads
     assert np.array_equal(gpu.decodeSteps(4), before)
     gpu.free()
+
+
+def test_biased_model_saves_loads_and_decodes(llm, oracle, tmp_path):
+    """q/k/v bias vectors (Qwen2): the seeded biases of a created model are the oracle's, they sit
+    in the file between v and o, and a model that loads other biases decodes the oracle's tokens
+    (the attention kernel adds them where it stages q and the new k/v row)."""
+    O = oracle
+    cfg = dict(CFG, qkv_bias=1)
+    t, steps = 6, 16
+    toks = _prompt(O, t)
+    ref = _oracle(O, qkv_bias=1)
+    W.writeWeightsFile(tmp_path / "want.q8w", cfg, lambda l, k: None if k in W.GAINS else ref.get_tensor(l, k))
+    gpu = llm.Llm(**cfg)
+    gpu.saveWeights(tmp_path / "got.q8w")
+    assert (tmp_path / "got.q8w").read_bytes() == (tmp_path / "want.q8w").read_bytes()
+    ref.prefill(toks)
+    gpu.prefill(toks)
+    want = np.array([ref.decode_step().copy() for _ in range(steps)])
+    assert np.array_equal(gpu.decodeSteps(steps), want)
+    plain = llm.Llm(**CFG)                     # the biases matter
+    plain.prefill(toks)
+    assert not np.array_equal(plain.decodeSteps(steps), want)
+    with pytest.raises(LogosError) as e:       # a file with biases does not fit a model without
+        plain.loadWeights(tmp_path / "want.q8w")
+    assert e.value.status == 1 and "qkv_bias" in str(e.value)
+    plain.free()
+
+    rng = np.random.default_rng(5)
+    nq, nkv = CFG["h_q"] * CFG["head_dim"], CFG["h_kv"] * CFG["head_dim"]
+    for layer in range(CFG["layers"]):
+        for kind, n in ((W.Q_BIAS, nq), (W.K_BIAS, nkv), (W.V_BIAS, nkv)):
+            ref.set_tensor(layer, kind, rng.uniform(-0.5, 0.5, n).astype(np.float32))
+    W.writeWeightsFile(tmp_path / "other.q8w", cfg, lambda l, k: None if k in W.GAINS else ref.get_tensor(l, k))
+    gpu.loadWeights(tmp_path / "other.q8w")
+    ref.prefill(toks)
+    gpu.prefill(toks)
+    want2 = np.array([ref.decode_step().copy() for _ in range(steps)])
+    got2 = gpu.decodeSteps(steps)
+    assert np.array_equal(got2, want2) and not np.array_equal(want2, want)
+    k, _ = gpu.readKv(0)
+    kr, _ = ref.read_kv(0)
+    assert rel_l2(O.f16_to_f32(k), O.f16_to_f32(kr)) < 2e-4
+    gpu.free()
+    ref.close()

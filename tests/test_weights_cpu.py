@@ -27,7 +27,8 @@ def _write_from(model, path, cfg, gains=None):
 
 @pytest.mark.parametrize("cfg", [ARCH, dict(ARCH, tied_embeddings=1, layers=3, hidden=96, ffn=160, vocab=77),
                                  dict(layers=64, hidden=5120, h_q=64, h_kv=8, head_dim=128, ffn=27648, vocab=152064,
-                                      tied_embeddings=0)])
+                                      tied_embeddings=0),
+                                 dict(ARCH, qkv_bias=1), dict(ARCH, qkv_bias=1, tied_embeddings=1, layers=5)])
 def test_layout_of_the_library_equals_the_python_restatement(cfg):
     spans, total = W.layout(cfg)
     assert W.weightsFileBytes(cfg) == total
@@ -55,8 +56,11 @@ def test_span_and_size_reject_bad_arguments():
         W.weightsSpan(ARCH, 2, W.Q)                  # layer out of range
     assert e.value.status == 4
     with pytest.raises(LogosError) as e:
-        W.weightsSpan(ARCH, 0, 12)                   # no such tensor
+        W.weightsSpan(ARCH, 0, 15)                   # no such tensor
     assert e.value.status == 4
+    with pytest.raises(LogosError) as e:
+        W.weightsSpan(ARCH, 0, W.Q_BIAS)             # this architecture has no biases
+    assert e.value.status == 1
     with pytest.raises(LogosError) as e:
         W.weightsSpan(dict(ARCH, tied_embeddings=1), 0, W.HEAD)
     assert e.value.status == 1
@@ -78,7 +82,7 @@ def test_written_file_checks_out_and_shards_are_the_generator_slices(oracle, tmp
     gains[(0, W.FINAL_NORM)] = rng.uniform(0.5, 1.5, ARCH["hidden"]).astype(np.float32)
     total = _write_from(ref, path, ARCH, gains)
     assert os.path.getsize(path) == total == W.weightsFileBytes(ARCH)
-    assert W.weightsCheck(path) == ARCH
+    assert W.weightsCheck(path) == dict(ARCH, qkv_bias=0)
     H, D, F = ARCH["hidden"], ARCH["head_dim"], ARCH["ffn"]
     nq, nkv = ARCH["h_q"] * D, ARCH["h_kv"] * D
     std, seed = MODEL["init_std"], MODEL["seed"]
@@ -184,3 +188,49 @@ def test_host_quantiser_equals_the_oracle_bit_for_bit(oracle):
     assert np.array_equal(s.view(np.uint32), s0.view(np.uint32))
     with pytest.raises(ValueError):
         W.q8QuantizeHost(np.zeros((2, 40), np.float32))
+
+
+def test_bias_vectors_in_the_file_and_their_shards(oracle, tmp_path):
+    O = oracle
+    arch = dict(ARCH, qkv_bias=1)
+    ref = _oracle_model(O, qkv_bias=1)
+    plain = _oracle_model(O)
+    path = tmp_path / "biased.q8w"
+    W.writeWeightsFile(path, arch, lambda l, k: None if k in W.GAINS else ref.get_tensor(l, k))
+    assert W.weightsCheck(path) == arch
+    assert os.path.getsize(path) > W.weightsFileBytes(ARCH)
+    nq, nkv = ARCH["h_q"] * ARCH["head_dim"], ARCH["h_kv"] * ARCH["head_dim"]
+    for layer in range(ARCH["layers"]):
+        for kind, n, stream in ((W.Q_BIAS, nq, 7), (W.K_BIAS, nkv, 8), (W.V_BIAS, nkv, 9)):
+            whole = O.synth_fill(O.F32, 2, MODEL["seed"], layer * 16 + stream, 0, n, 0.0, MODEL["init_std"])
+            assert np.array_equal(ref.get_tensor(layer, kind), whole)
+            assert np.array_equal(W.weightsReadShard(path, layer, kind), whole)
+            for r in range(2):       # a rank's slice = the generator started at the rank's first row
+                part = O.synth_fill(O.F32, 2, MODEL["seed"], layer * 16 + stream, r * (n // 2), n // 2, 0.0, MODEL["init_std"])
+                assert np.array_equal(W.weightsReadShard(path, layer, kind, 2, r), part)
+        # the matrices sit where the layout says, biases in between
+        q, s = W.weightsReadShard(path, layer, W.O)
+        wq, ws = ref.get_tensor(layer, W.O)
+        assert np.array_equal(q, wq) and np.array_equal(s, ws)
+    with pytest.raises(KeyError):
+        plain.get_tensor(0, W.Q_BIAS)
+    # the biases are used: same weights, other logits
+    toks = O.synth_fill(O.I32, 3, 1, 999, 0, MODEL["batch"] * 4, 0.0, float(MODEL["vocab"])).reshape(MODEL["batch"], 4)
+    ref.prefill(toks)
+    plain.prefill(toks)
+    assert not np.array_equal(ref.read_logits(), plain.read_logits())
+    # zero biases = no biases, bit for bit
+    for layer in range(ARCH["layers"]):
+        for kind, n in ((W.Q_BIAS, nq), (W.K_BIAS, nkv), (W.V_BIAS, nkv)):
+            ref.set_tensor(layer, kind, np.zeros(n, np.float32))
+    ref.prefill(toks)
+    assert np.array_equal(ref.read_logits(), plain.read_logits())
+    # unknown header flags are refused
+    data = bytearray(path.read_bytes())
+    data[88] |= 2
+    (tmp_path / "flags.q8w").write_bytes(bytes(data))
+    with pytest.raises(LogosError) as e:
+        W.weightsCheck(tmp_path / "flags.q8w")
+    assert e.value.status == 5
+    ref.close()
+    plain.close()
