@@ -39,6 +39,8 @@ def _worker(rank, world, port, out_dir):
 
     # row-sharded projections: this rank's slice of the output columns
     q_loc = O.q8_gemm_f32(x, O.F32, *mat(nq, H, 0, row0=rank * nq))
+    # the rank's slice of the projection's bias: the generator's window at the rank's first row
+    q_loc = (q_loc + O.synth_fill(O.F32, 2, seed, 7, rank * nq, nq, 0.0, std)).astype(np.float32)
     k_loc = O.q8_gemm_f32(x, O.F32, *mat(nkv, H, 1, row0=rank * nkv))
     g_loc = O.q8_gemm_f32(x, O.F32, *mat(f, H, 4, row0=rank * f))
     u_loc = O.q8_gemm_f32(x, O.F32, *mat(f, H, 5, row0=rank * f))
@@ -68,6 +70,7 @@ def test_two_rank_sharding_matches_unsharded(oracle, tmp_path):
     x = O.synth_fill(O.F32, 2, seed, 500, 0, B * H, 0.0, 1.0).reshape(B, H)
     full = lambda n, k, st: O.q8_synth_weights(n, k, seed, st, std)
     q = O.q8_gemm_f32(x, O.F32, *full(HQ * D, H, 0))
+    q = (q + O.synth_fill(O.F32, 2, seed, 7, 0, HQ * D, 0.0, std)).astype(np.float32)
     kk = O.q8_gemm_f32(x, O.F32, *full(HKV * D, H, 1))
     act = O.swiglu(O.q8_gemm_f32(x, O.F32, *full(F, H, 4)), O.q8_gemm_f32(x, O.F32, *full(F, H, 5)))
     o = O.q8_gemm_f32(q, O.F32, *full(H, HQ * D, 3))
