@@ -122,3 +122,17 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(ImportError):
         _lib.load()
+
+
+def test_ctypes_signatures_have_the_headers_arity():
+    """Every prototype in the public header against the ctypes table: same set of names, same
+    number of parameters (a mismatch would corrupt the call, not fail it)."""
+    import re
+    with open(_lib.HEADER_PATH) as f:
+        text = re.sub(r"/\*.*?\*/", "", f.read(), flags=re.S)
+    protos = dict(re.findall(r"LOGOS_API[^;(]*?\b(logos_[a-z0-9_]+)\s*\(([^;]*?)\)\s*;", text, flags=re.S))
+    assert set(protos) == set(_lib._SIGNATURES)
+    for name, params in protos.items():
+        params = " ".join(params.split())
+        n = 0 if params in ("", "void") else params.count(",") + 1
+        assert n == len(_lib._SIGNATURES[name][1]), (name, params)
