@@ -76,6 +76,49 @@ def gen_normal(seed, stream, idx):
     return f32(r * (sq if idx & 1 else cq))
 
 
+def ln_pos(x):
+    """ln of a positive normal float32: exponent by bits, atanh series on the mantissa."""
+    bits = int(np.array([x], f32).view(np.uint32)[0])
+    e = (bits >> 23) - 127
+    m = np.array([(bits & 0x007FFFFF) | 0x3F800000], np.uint32).view(f32)[0]
+    if m > f32(1.41421354):
+        m = f32(m * f32(0.5))
+        e += 1
+    t = f32(f32(m - f32(1.0)) / f32(m + f32(1.0)))
+    t2 = f32(t * t)
+    p = f32(0.111111111)
+    for c in (0.142857143, 0.2, 0.333333343, 1.0):
+        p = f32(f32(p * t2) + f32(c))
+    ln_m = f32(f32(f32(2.0) * t) * p)
+    return f32(ln_m + f32(f32(e) * f32(0.693147182)))
+
+
+def gen_gumbel(seed, stream, idx):
+    """-ln(-ln u), u = (2k+1) * 2^-24 from the top 23 bits of the hash."""
+    k = ctr_hash(seed, stream, idx) >> 41
+    u = f32(f32(2 * k + 1) * f32(5.9604644775390625e-08))
+    return f32(-ln_pos(f32(-ln_pos(u))))
+
+
+def sample_rows(logits, inv_t, top_k, seed, positions):
+    """Gumbel-max over the logits that reach the row's top_k-th largest (0: all of them)."""
+    rows, vocab = logits.shape
+    out = np.zeros(rows, np.int32)
+    for i in range(rows):
+        least = -np.inf
+        if 0 < top_k < vocab:
+            least = np.sort(logits[i])[::-1][top_k - 1]
+        best, best_v = -1, None
+        for v in range(vocab):
+            if logits[i, v] < least:
+                continue
+            x = f32(f32(logits[i, v] * inv_t) + gen_gumbel(seed, i, int(positions[i]) * vocab + v))
+            if best < 0 or x > best_v:
+                best, best_v = v, x
+        out[i] = best
+    return out
+
+
 # ------------------------------------------------------------------ 16-bit floats
 def to_bf16_bits(a):
     u = np.ascontiguousarray(a, f32).view(np.uint32).astype(np.uint64)
@@ -217,6 +260,19 @@ def main():
     ub = rng.normal(0, 2, 200).astype(f32)
     out["swi_g"], out["swi_u"] = ga, ub
     out["swi_y"] = ga.astype(np.float64) / (1.0 + np.exp(-ga.astype(np.float64))) * ub.astype(np.float64)
+
+    # Gumbel variate and Gumbel-max sampling (its own generator: the arrays above stay as they were)
+    rng2 = np.random.default_rng(20240608)
+    out["gen_gumbel"] = np.array([gen_gumbel(7, 3, int(i)) for i in idx], f32)
+    out["gen_gumbel_run"] = np.array([gen_gumbel(0, 12, i) for i in range(256)], f32)
+    lg = (rng2.normal(0, 2, (5, 40))).astype(f32)
+    lg[3, 7] = lg[3, 9]                                   # a tie inside the row
+    pos = np.array([0, 1, 33, 4096, 12], np.int32)
+    inv_t = f32(f32(1.0) / f32(0.7))
+    out["samp_logits"], out["samp_pos"], out["samp_temperature"] = lg, pos, np.array([0.7], f32)
+    out["samp_tokens"] = sample_rows(lg, inv_t, 0, 21, pos)
+    out["samp_tokens_top4"] = sample_rows(lg, inv_t, 4, 21, pos)
+    out["samp_tokens_top1"] = sample_rows(lg, inv_t, 1, 21, pos)
 
     np.savez_compressed(os.path.join(HERE, "golden.npz"), **out)
     print("wrote golden.npz with", len(out), "arrays")

@@ -158,3 +158,20 @@ def test_model_is_deterministic_and_kv_grows(oracle):
         runs.append((np.array(out), k, v))
         m.close()
     assert np.array_equal(runs[0][0], runs[1][0]) and np.array_equal(runs[0][1], runs[1][1])
+
+
+def test_gumbel_bits_and_sampled_tokens(oracle, golden):
+    """The sampler's noise and its choices against the independent numpy restatement: the Gumbel
+    variate bit for bit, and the chosen token per row with all logits, the top 4 and the top 1."""
+    O = oracle
+    for j, i in enumerate(golden["gen_idx"]):
+        g = O.synth_fill(O.F32, 4, 7, 3, int(i), 1)[0]
+        assert g.view(np.uint32) == golden["gen_gumbel"][j].view(np.uint32)
+    run = O.synth_fill(O.F32, 4, 0, 12, 0, 256)
+    assert np.array_equal(run.view(np.uint32), golden["gen_gumbel_run"].view(np.uint32))
+    lg, pos, t = golden["samp_logits"], golden["samp_pos"], float(golden["samp_temperature"][0])
+    assert np.array_equal(O.sample_rows(lg, t, 21, pos), golden["samp_tokens"])
+    assert np.array_equal(O.sample_rows(lg, t, 21, pos, top_k=4), golden["samp_tokens_top4"])
+    assert np.array_equal(O.sample_rows(lg, t, 21, pos, top_k=1), golden["samp_tokens_top1"])
+    # top 1 is the row's largest logit whatever the noise (lowest index on the tie in row 3)
+    assert np.array_equal(golden["samp_tokens_top1"], lg.argmax(1))
