@@ -184,6 +184,77 @@ def attention64(q16, kc16, vc16, seq_len, scale):
     return out
 
 
+# ------------------------------------------------------------------ the decode model, in float64
+def synth_matrix(n, k, seed, stream, std):
+    """Q8 blocks of the seeded N(0, std) matrix: element (r, c) is value r * k + c of its stream."""
+    w = np.array([[f32(f32(std) * gen_normal(seed, stream, r * k + c)) for c in range(k)] for r in range(n)], f32)
+    return q8_quantize(w)
+
+
+def synth_vector(n, seed, stream, std):
+    return np.array([f32(f32(std) * gen_normal(seed, stream, i)) for i in range(n)], f32)
+
+
+class Model64:
+    """The batched greedy decode step restated with float64 sums: f32 residual stream values are
+    kept in float64 here, the KV cache and the rotated query are rounded to fp16 exactly as the
+    arithmetic defines them.  Weight streams per layer l: 16 l + {0 q, 1 k, 2 v, 3 o, 4 gate,
+    5 up, 6 down, 7 q_bias, 8 k_bias, 9 v_bias}; embedding 1 << 20 (tied lm_head)."""
+
+    def __init__(self, cfg, gains):
+        self.c = c = dict(cfg)
+        H, D = c["hidden"], c["head_dim"]
+        nq, nkv, F = c["h_q"] * D, c["h_kv"] * D, c["ffn"]
+        mat = lambda n, k, st: dequant64(*synth_matrix(n, k, c["seed"], st, c["init_std"]))
+        self.layers = []
+        for l in range(c["layers"]):
+            st = 16 * l
+            L = dict(q=mat(nq, H, st), k=mat(nkv, H, st + 1), v=mat(nkv, H, st + 2), o=mat(H, nq, st + 3),
+                     g=mat(F, H, st + 4), u=mat(F, H, st + 5), d=mat(H, F, st + 6))
+            for j, (name, n) in enumerate((("bq", nq), ("bk", nkv), ("bv", nkv))):
+                L[name] = synth_vector(n, c["seed"], st + 7 + j, c["init_std"]).astype(np.float64)
+            self.layers.append(L)
+        eq, es = synth_matrix(c["vocab"], H, c["seed"], 1 << 20, c["init_std"])
+        self.embed_f32 = (eq.reshape(c["vocab"], H // 32, 32).astype(f32) * es[:, :, None]).astype(f32).reshape(c["vocab"], H)
+        self.head = dequant64(eq, es)
+        self.gains = gains.astype(np.float64)            # [2 layers + 1][hidden]
+        self.tab = rope_table(c["l_max"], D, c["rope_theta"])
+        B = c["batch"]
+        self.kc = np.zeros((c["layers"], B, c["h_kv"], c["l_max"], D), np.uint16)
+        self.vc = np.zeros_like(self.kc)
+        self.len = np.zeros(B, np.int64)
+
+    def norm(self, h, g):
+        return h / np.sqrt((h ** 2).mean(1, keepdims=True) + float(f32(self.c["rms_eps"]))) * g
+
+    def step(self, tokens):
+        c = self.c
+        B, D, hq, hkv = c["batch"], c["head_dim"], c["h_q"], c["h_kv"]
+        h = self.embed_f32[tokens].astype(np.float64)
+        scale = f32(1.0) / np.sqrt(f32(D))
+        for l, L in enumerate(self.layers):
+            x = self.norm(h, self.gains[2 * l])
+            q = x @ L["q"].T + L["bq"]
+            k = x @ L["k"].T + L["bk"]
+            v = x @ L["v"].T + L["bv"]
+            q16 = np.zeros((B, hq, D), np.uint16)
+            for i in range(B):
+                pos = int(self.len[i])
+                for j in range(hq):
+                    q16[i, j] = rope_f16(q[i, j * D:(j + 1) * D].astype(f32), self.tab[pos])
+                for j in range(hkv):
+                    self.kc[l, i, j, pos] = rope_f16(k[i, j * D:(j + 1) * D].astype(f32), self.tab[pos])
+                    self.vc[l, i, j, pos] = v[i, j * D:(j + 1) * D].astype(f32).astype(np.float16).view(np.uint16)
+            att = attention64(q16, self.kc[l], self.vc[l], self.len + 1, scale).reshape(B, hq * D)
+            h = h + att @ L["o"].T
+            x = self.norm(h, self.gains[2 * l + 1])
+            g, u = x @ L["g"].T, x @ L["u"].T
+            h = h + (g / (1.0 + np.exp(-g)) * u) @ L["d"].T
+        self.len += 1
+        logits = self.norm(h, self.gains[2 * c["layers"]]) @ self.head.T
+        return logits
+
+
 def main():
     rng = np.random.default_rng(20240607)
     out = {}
@@ -273,6 +344,30 @@ def main():
     out["samp_tokens"] = sample_rows(lg, inv_t, 0, 21, pos)
     out["samp_tokens_top4"] = sample_rows(lg, inv_t, 4, 21, pos)
     out["samp_tokens_top1"] = sample_rows(lg, inv_t, 1, 21, pos)
+
+    # a tiny decode model end to end: seeded weights and biases, gains that are not 1, a 3-token
+    # prompt per sequence, then 5 greedy steps
+    cfg = dict(layers=2, hidden=64, h_q=2, h_kv=1, head_dim=64, ffn=96, vocab=48, l_max=10, batch=2, rms_eps=1e-6,
+               rope_theta=1e6, seed=13, init_std=0.05)
+    gains = rng2.uniform(0.5, 1.5, (2 * cfg["layers"] + 1, cfg["hidden"])).astype(f32)
+    prompt = rng2.integers(0, cfg["vocab"], (cfg["batch"], 3)).astype(np.int32)
+    m = Model64(cfg, gains)
+    for p in range(3):
+        logits = m.step(prompt[:, p])
+    toks = []
+    for _ in range(5):
+        nxt = logits.argmax(1).astype(np.int32)
+        toks.append(nxt)
+        logits = m.step(nxt)
+    out["model_cfg"] = np.array([cfg[k] for k in ("layers", "hidden", "h_q", "h_kv", "head_dim", "ffn", "vocab", "l_max",
+                                                  "batch", "seed")], np.int64)
+    out["model_std"] = np.array([cfg["init_std"]], f32)
+    out["model_gains"], out["model_prompt"] = gains, prompt
+    out["model_tokens"] = np.array(toks, np.int32)                 # [5][B]: the tokens steps 1..5 consume
+    out["model_logits"] = logits                                    # after the 5th of them
+    out["model_k0"], out["model_v0"] = m.kc[0], m.vc[0]             # layer 0 cache, fp16 bits
+    sl = np.sort(logits, 1)
+    out["model_margin"] = sl[:, -1] - sl[:, -2]
 
     np.savez_compressed(os.path.join(HERE, "golden.npz"), **out)
     print("wrote golden.npz with", len(out), "arrays")

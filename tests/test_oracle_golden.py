@@ -175,3 +175,35 @@ def test_gumbel_bits_and_sampled_tokens(oracle, golden):
     assert np.array_equal(O.sample_rows(lg, t, 21, pos, top_k=1), golden["samp_tokens_top1"])
     # top 1 is the row's largest logit whatever the noise (lowest index on the tie in row 3)
     assert np.array_equal(golden["samp_tokens_top1"], lg.argmax(1))
+
+
+def test_decode_model_against_the_float64_restatement(oracle, golden):
+    """The whole model (seeded Q8 weights and q/k/v biases, gains that are not 1, RoPE positions,
+    fp16 KV append, GQA attention, SwiGLU, residuals, tied lm_head, greedy choice) against the
+    numpy model of tests/golden/make_golden.py, which shares no code with the oracle."""
+    O = oracle
+    names = ("layers", "hidden", "h_q", "h_kv", "head_dim", "ffn", "vocab", "l_max", "batch", "seed")
+    cfg = {k: int(v) for k, v in zip(names, golden["model_cfg"])}
+    m = O.Llm(tp_degree=1, tp_rank=0, device=0, act_dtype=O.F32, rms_eps=1e-6, rope_theta=1e6, tied_embeddings=1,
+              init_std=float(golden["model_std"][0]), qkv_bias=1, **cfg)
+    gains = golden["model_gains"]
+    for l in range(cfg["layers"]):
+        m.set_tensor(l, 0, gains[2 * l])
+        m.set_tensor(l, 5, gains[2 * l + 1])
+    m.set_tensor(0, 9, gains[2 * cfg["layers"]])
+    m.prefill(golden["model_prompt"])
+    want = golden["model_tokens"]                       # [5][B]: the tokens steps 1..5 consume
+    assert np.array_equal(m.read_logits().argmax(1), want[0])
+    outs = np.array([m.decode_step().copy() for _ in range(5)])
+    assert np.array_equal(outs[:4], want[1:])
+    assert np.array_equal(outs[4], golden["model_logits"].argmax(1))
+    assert rel_l2(m.read_logits(), golden["model_logits"]) < 1e-4
+    assert golden["model_margin"].min() > 1e-2          # the choices above were not near ties
+    k, v = m.read_kv(0)
+    n = 3 + 5
+    assert m.read_seq_len().tolist() == [n] * cfg["batch"]
+    for got, ref in ((k, golden["model_k0"]), (v, golden["model_v0"])):
+        assert not got[:, :, n:].any() and not ref[:, :, n:].any()
+        assert np.mean(got[:, :, :n] != ref[:, :, :n]) < 0.02        # fp16 values on a rounding boundary may flip
+        assert rel_l2(O.f16_to_f32(got), O.f16_to_f32(ref)) < 1e-3
+    m.close()
