@@ -20,7 +20,9 @@
  * index order, and the order is part of the definition.
  *
  * Independent cross-check: tests/golden/make_golden.py restates the same
- * operators in numpy float64 and commits small input/output vectors.
+ * operators, the sampler and the whole decode model in numpy (float64 sums,
+ * explicit float32 steps where bits are defined) and commits small
+ * input/output vectors; tests/test_oracle_golden.py holds this file to them.
  */
 #include <math.h>
 #include <stdint.h>
