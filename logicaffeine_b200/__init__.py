@@ -1,5 +1,6 @@
 """logicaffeine_b200 — the Q8 LLM-decode hot path as sm_100a CUDA kernels behind
 logicaffeine's native-operator C ABI.  `logicaffeine_b200.llm` is the host-side
-mirror of the operator family; `logicaffeine_b200.build` compiles the library."""
+mirror of the operator family; `logicaffeine_b200.weights` writes and inspects weight files;
+`logicaffeine_b200.build` compiles the library."""
 
-__all__ = ["llm", "build"]
+__all__ = ["llm", "weights", "build"]
