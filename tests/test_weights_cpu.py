@@ -234,3 +234,27 @@ def test_bias_vectors_in_the_file_and_their_shards(oracle, tmp_path):
     assert e.value.status == 5
     ref.close()
     plain.close()
+
+
+def test_layout_property_random_architectures():
+    """Random architectures: the library's spans equal the Python restatement's for every tensor,
+    regions are aligned, ordered and disjoint, and the file ends within one alignment unit of the last."""
+    from hypothesis import given, settings, strategies as stg
+
+    @settings(max_examples=40, deadline=None)
+    @given(layers=stg.integers(1, 4), hb=stg.integers(1, 6), hkv=stg.sampled_from([1, 2, 4]), grp=stg.integers(1, 4),
+           d=stg.sampled_from([64, 128]), fb=stg.integers(1, 9), vocab=stg.integers(1, 500), tied=stg.booleans(),
+           bias=stg.booleans())
+    def check(layers, hb, hkv, grp, d, fb, vocab, tied, bias):
+        cfg = dict(layers=layers, hidden=32 * hb, h_q=hkv * grp, h_kv=hkv, head_dim=d, ffn=32 * hkv * fb, vocab=vocab,
+                   tied_embeddings=int(tied), qkv_bias=int(bias))
+        spans, total = W.layout(cfg)
+        assert W.weightsFileBytes(cfg) == total
+        end = 256
+        for (layer, kind), span in spans.items():
+            assert W.weightsSpan(cfg, layer, kind) == span
+            q_off, q_bytes, s_off, s_bytes = span
+            assert q_off % 256 == 0 and q_off >= end and (s_bytes == 0 or (s_off % 256 == 0 and s_off >= q_off + q_bytes))
+            end = max(q_off + q_bytes, s_off + s_bytes)
+        assert end <= total < end + 256
+    check()
