@@ -223,25 +223,6 @@ def op_probe(args):
     stream = torch.cuda.Stream()
     sp = stream.cuda_stream
     m, n, k, reps, copies = args.m, args.n, args.k, args.reps, args.copies
-    if args.op == "mma_probe":
-        # cycles per tcgen05.mma (M=128, K=16) by N, operand source and accumulator count
-        rows = []
-        for nn, tmem, accs in ((32, True, 2), (64, True, 1), (64, True, 2), (64, True, 4), (128, True, 2),
-                               (256, True, 1), (64, False, 2), (128, False, 2)):
-            issue, done = llm.tcMmaProbe(nn, tmem, 512, accs, dev)
-            rows.append({"n": nn, "a_operand": "tmem" if tmem else "smem", "accumulators": accs,
-                         "cycles_per_mma": done / 512.0, "issue_cycles_per_mma": issue / 512.0})
-        for bg, what in ((1, "tcgen05.st"), (2, "tcgen05.ld"), (3, "ld.shared.v4")):
-            issue, done = llm.tcMmaProbe(64, True, 512, 2, dev, bg)
-            rows.append({"n": 64, "a_operand": "tmem", "accumulators": 2, "other_warps": what,
-                         "cycles_per_mma": done / 512.0, "issue_cycles_per_mma": issue / 512.0})
-        burst = []
-        for cnt in (1, 2, 4, 8, 16):
-            issue, done = llm.tcMmaProbe(64, True, cnt, 2, dev)
-            burst.append({"count": cnt, "issue_cycles": issue, "complete_cycles": done})
-        print(json.dumps({"op": "mma_probe", "kind": "tcgen05.mma kind::f16 M=128 K=16", "steady": rows,
-                          "burst_n64_tmem": burst}), flush=True)
-        return
     if args.op == "weights":
         # weight file: save the workload's model (seeded weights), then time loading the file back
         # (host wall clock around the call; the file was just written, so it comes from the page cache)
@@ -346,7 +327,7 @@ def main():
     ap.add_argument("--prefill", default="synthetic-kv", choices=["synthetic-kv", "prompt"])
     ap.add_argument("--act", default="f32", choices=["f32", "f16", "bf16"])
     ap.add_argument("--no-extras", action="store_true", help="skip the CPU baseline and the GEMV probe")
-    ap.add_argument("--op", default="decode", choices=["decode", "q8_gemm", "q8_gemv", "attention", "mma_probe", "weights"],
+    ap.add_argument("--op", default="decode", choices=["decode", "q8_gemm", "q8_gemv", "attention", "weights"],
                     help="time one operator instead of the decode loop (attention: --m sequences, --n context)")
     ap.add_argument("--m", type=int, default=64)
     ap.add_argument("--n", type=int, default=18944)

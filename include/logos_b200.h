@@ -40,24 +40,44 @@
 extern "C" {
 #endif
 
-/* ffi.rs:196-209 */
+/* Status codes: the Rust enum LogosStatus (ffi.rs:196-209) with the enumerator spelling of
+ * the C header the reference generates (ffi.rs:1364-1375).  A translation unit that also
+ * includes such a generated header defines LOGOS_B200_NO_RUNTIME_DECLS first: the typedefs and
+ * the unprefixed runtime functions below then come from that header alone. */
+#ifndef LOGOS_B200_NO_RUNTIME_DECLS
 typedef enum {
-  LOGOS_OK = 0,
-  LOGOS_ERROR = 1,
-  LOGOS_REFINEMENT_VIOLATION = 2,
-  LOGOS_NULL_POINTER = 3,
-  LOGOS_OUT_OF_BOUNDS = 4,
-  LOGOS_DESERIALIZATION_FAILED = 5,
-  LOGOS_INVALID_HANDLE = 6,
-  LOGOS_CONTAINS_NULL_BYTE = 7,
-  LOGOS_THREAD_PANIC = 8,
-  LOGOS_MEMORY_EXHAUSTED = 9
+  LOGOS_STATUS_OK = 0,
+  LOGOS_STATUS_ERROR = 1,
+  LOGOS_STATUS_REFINEMENT_VIOLATION = 2,
+  LOGOS_STATUS_NULL_POINTER = 3,
+  LOGOS_STATUS_OUT_OF_BOUNDS = 4,
+  LOGOS_STATUS_DESERIALIZATION_FAILED = 5,
+  LOGOS_STATUS_INVALID_HANDLE = 6,
+  LOGOS_STATUS_CONTAINS_NULL_BYTE = 7,
+  LOGOS_STATUS_THREAD_PANIC = 8,
+  LOGOS_STATUS_MEMORY_EXHAUSTED = 9
 } logos_status_t;
+#endif
+/* short spellings used inside this library */
+#define LOGOS_OK LOGOS_STATUS_OK
+#define LOGOS_ERROR LOGOS_STATUS_ERROR
+#define LOGOS_REFINEMENT_VIOLATION LOGOS_STATUS_REFINEMENT_VIOLATION
+#define LOGOS_NULL_POINTER LOGOS_STATUS_NULL_POINTER
+#define LOGOS_OUT_OF_BOUNDS LOGOS_STATUS_OUT_OF_BOUNDS
+#define LOGOS_DESERIALIZATION_FAILED LOGOS_STATUS_DESERIALIZATION_FAILED
+#define LOGOS_INVALID_HANDLE LOGOS_STATUS_INVALID_HANDLE
+#define LOGOS_CONTAINS_NULL_BYTE LOGOS_STATUS_CONTAINS_NULL_BYTE
+#define LOGOS_THREAD_PANIC LOGOS_STATUS_THREAD_PANIC
+#define LOGOS_MEMORY_EXHAUSTED LOGOS_STATUS_MEMORY_EXHAUSTED
 
-/* ffi.rs:212 — an id, not an address */
+/* ffi.rs:212 and :1376 — an id, not an address */
+#ifndef LOGOS_B200_NO_RUNTIME_DECLS
 typedef void* logos_handle_t;
+#endif
 
-#define LOGOS_ABI_VERSION 1u
+#ifndef LOGOS_ABI_VERSION
+#define LOGOS_ABI_VERSION 1 /* ffi.rs:275, :1382 */
+#endif
 
 #if defined(__GNUC__)
 #define LOGOS_API __attribute__((visibility("default")))
@@ -74,12 +94,31 @@ typedef enum {
   LOGOS_I32 = 4
 } logos_dtype_t;
 
-/* ---- runtime (names identical to the reference preamble, ffi.rs:1377-1384) ---- */
+/* ---- runtime ----
+ * The library's own copies carry the logos_b200_ prefix.  Every LOGOS program with C exports
+ * defines logos_last_error, logos_get_last_error, logos_clear_error, logos_free_string,
+ * logos_version and logos_abi_version itself (#[no_mangle], ffi.rs:234-285), so inside such a
+ * program the unprefixed names resolve to the PROGRAM's error store, not to this library's:
+ * a host that is (or links) a LOGOS program reads this library's errors through the prefixed
+ * names.  The unprefixed names (the reference preamble's, ffi.rs:1377-1384) are exported as
+ * weak symbols for stand-alone C / Python hosts; the library never calls through them. */
+LOGOS_API const char* logos_b200_last_error(void);     /* valid until the next failing call on this thread */
+LOGOS_API const char* logos_b200_get_last_error(void); /* alias, as in the reference */
+LOGOS_API void logos_b200_clear_error(void);
+/* Releases a string the library handed out with ownership.  No entry point hands one out
+ * today (error text stays owned by the library), so this only accepts NULL or such a future
+ * string; it exists because the reference's C boundary has it (ffi.rs:268-273, :1380). */
+LOGOS_API void logos_b200_free_string(char* str);
+LOGOS_API uint32_t logos_b200_abi_version(void);
+LOGOS_API const char* logos_b200_version(void);
+#ifndef LOGOS_B200_NO_RUNTIME_DECLS
 LOGOS_API const char* logos_last_error(void);
 LOGOS_API const char* logos_get_last_error(void);
 LOGOS_API void logos_clear_error(void);
+LOGOS_API void logos_free_string(char* str);
 LOGOS_API uint32_t logos_abi_version(void);
 LOGOS_API const char* logos_version(void);
+#endif
 /* number of CUDA devices visible to the library; 0 when there is none */
 LOGOS_API int32_t logos_device_count(void);
 
@@ -91,10 +130,16 @@ LOGOS_API logos_status_t logos_dev_memset(logos_handle_t dst, int32_t byte_value
 /* raw device address and size of a buffer, for hosts that share it with other CUDA code */
 LOGOS_API logos_status_t logos_dev_ptr(logos_handle_t h, void** out_ptr, int64_t* out_bytes);
 LOGOS_API logos_status_t logos_dev_sync(int32_t device);
+/* free and total bytes of device memory as the driver reports them (cudaMemGetInfo) */
+LOGOS_API logos_status_t logos_dev_mem_info(int32_t device, int64_t* free_out, int64_t* total_out);
 LOGOS_API logos_status_t logos_dev_free(logos_handle_t h);
 /* Every device-side wait in the library is bounded; a kernel that gives up
- * stores a non-zero code in a per-device status word instead of hanging.  This
- * reads and clears it (0 = nothing reported).  Call after a synchronisation. */
+ * stores a non-zero code in a status word instead of hanging, and later kernels that
+ * share the word do no work on top of it.  This reads and clears the device's words
+ * (the per-device one, and the one logos_gqa_decode_attn_fixed_scratch keeps inside the
+ * library image once that entry point has run on the device); 0 = nothing reported.
+ * Call after a synchronisation.  The first call on a device allocates the 256-byte
+ * per-device word; later calls allocate nothing. */
 LOGOS_API logos_status_t logos_kernel_status(int32_t device, int32_t* out_code);
 
 /* Kernel launches this process has made through the library, by kind:
@@ -139,7 +184,10 @@ LOGOS_API logos_status_t logos_q8_gemv(logos_handle_t q /*i8 [N][K]*/, logos_han
  * epilogue 0: plain.  1: C = bf16(acc + aux[m,n]) with aux bf16 [M][N] (residual).
  * 2: rows of q interleave gate (even) and up (odd); C is [M][N/2] =
  *    bf16( silu(acc_gate) * acc_up ).
- * Uses the library's per-device scratch when the shape asks for split-K. */
+ * The stand-alone operators logos_q8_gemm, logos_q8_gemm_f32 and logos_gqa_decode_attn(_fused)
+ * keep activation planes, split-K and split-KV partials in one library-owned scratch block per
+ * device, grown on demand and shared by every caller on that device: calls that use it must
+ * be ordered on the GPU (one stream, or events).  A model (logos_llm_*) owns its own. */
 LOGOS_API logos_status_t logos_q8_gemm(logos_handle_t a /*bf16 [M][K]*/, logos_handle_t q, logos_handle_t s,
                              logos_handle_t c /*bf16*/, int64_t m, int64_t n, int64_t k,
                              int32_t epilogue, logos_handle_t aux_or_null, void* stream_or_null);
@@ -150,11 +198,6 @@ LOGOS_API logos_status_t logos_q8_gemm(logos_handle_t a /*bf16 [M][K]*/, logos_h
 LOGOS_API logos_status_t logos_q8_gemm_f32(logos_handle_t a /*f32 [M][K]*/, logos_handle_t q, logos_handle_t s,
                                  logos_handle_t c /*f32 [M][N]*/, int64_t m, int64_t n, int64_t k,
                                  void* stream_or_null);
-
-/* Tracing aid: with a device buffer of at least 64*16 int64 set, CTA (0,0,0) of every
- * tcgen05 GEMM launch stores SM-clock timestamps of its pipeline roles per 128-column
- * K stage ([stage][16]); NULL turns tracing off. */
-LOGOS_API logos_status_t logos_gemm_trace_buffer(logos_handle_t buf_or_null);
 
 /* Same contract as logos_q8_gemm, always on the plain SIMT kernel (no tensor
  * cores, no split-K): the on-device cross-check the tests hold the tcgen05
@@ -195,10 +238,13 @@ LOGOS_API logos_status_t logos_gqa_decode_attn(logos_handle_t q, logos_handle_t 
  * partials need more (b * h_q * ceil(l_max / unit) * (d + 2) * 4 bytes) is refused with
  * LOGOS_OUT_OF_BOUNDS and a message giving both sizes.  The call itself makes no
  * cudaMalloc / cudaFree.  The first call on a device looks up the array's device address;
- * make that first call outside any stream capture.  All calls share the one array and its
- * status word (the word is cleared at the start of every call; the partials are always
- * written before they are read), so two calls that overlap on the GPU race: keep calls on
- * this entry point ordered, for instance on one stream. */
+ * make that first call outside any stream capture.  All calls share the one array and one
+ * status word.  Nothing is cleared between calls: the partials are always written before
+ * they are read, and the status word is zero until a bounded wait inside the kernel gives up,
+ * after which calls on this entry point leave `o` untouched until logos_kernel_status has
+ * reported and cleared the code (call logos_kernel_status once at start-up if it must not
+ * allocate later).  Two calls that overlap on the GPU race on the array: keep calls on this
+ * entry point ordered, for instance on one stream. */
 LOGOS_API logos_status_t logos_gqa_decode_attn_fixed_scratch(logos_handle_t q, logos_handle_t k_cache,
                                      logos_handle_t v_cache, logos_handle_t seq_len, logos_handle_t o,
                                      int64_t b, int64_t h_q, int64_t h_kv, int64_t d, int64_t l_max,
@@ -288,17 +334,6 @@ LOGOS_API logos_status_t logos_llm_last_timing(logos_handle_t model, double* ms_
  * operator launched inside the scope writes weights that another one inside it reads.
  * prev_out (may be null) receives the previous setting. */
 LOGOS_API logos_status_t logos_dependent_launch_scope(int32_t on, int32_t* prev_out);
-/* Measurement aid (no counterpart in the reference): SM cycles one thread needs to issue
- * `count` back-to-back tcgen05.mma kind::f16 instructions (M = 128, K = 16, N = n in
- * {32, 64, 128, 256}; A operand in tensor memory when a_in_tmem != 0, else in shared memory)
- * that alternate between `accumulators` accumulators, and cycles until their completion is
- * seen through an mbarrier.  `background`: what eight other warps of the CTA do meanwhile - 0
- * nothing, 1 tcgen05.st, 2 tcgen05.ld (both to columns the MMAs do not touch), 3 128-bit
- * shared-memory loads.  One CTA; operand contents are irrelevant.  The Q8 GEMM's design
- * notes quote its figures (38 cycles at N = 64 with A in tensor memory on a B200). */
-LOGOS_API logos_status_t logos_tc_mma_probe(int32_t device, int32_t n, int32_t a_in_tmem, int32_t count,
-                                            int32_t accumulators, int32_t background, int64_t* issue_cycles_out,
-                                            int64_t* complete_cycles_out);
 /* How the ranks of the model's tensor-parallel group exchange the partial products of the
  * row-parallel GEMMs: 0 = no group (tp_degree 1), 1 = NCCL all-reduce, 2 = folded into the
  * residual + RMSNorm kernel over peer-mapped memory (one process per GPU, one node). */

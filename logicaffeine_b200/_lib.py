@@ -51,6 +51,13 @@ PTR = C.c_void_p
 
 # name -> (restype, argtypes); restype None means logos_status_t
 _SIGNATURES = {
+    "logos_b200_last_error": (C.c_char_p, []),
+    "logos_b200_get_last_error": (C.c_char_p, []),
+    "logos_b200_clear_error": (None.__class__, []),
+    "logos_b200_free_string": (None.__class__, [C.c_char_p]),
+    "logos_b200_abi_version": (C.c_uint32, []),
+    "logos_b200_version": (C.c_char_p, []),
+    "logos_free_string": (None.__class__, [C.c_char_p]),
     "logos_last_error": (C.c_char_p, []),
     "logos_get_last_error": (C.c_char_p, []),
     "logos_clear_error": (None.__class__, []),
@@ -63,6 +70,7 @@ _SIGNATURES = {
     "logos_dev_memset": (None, [H, I32c, I64]),
     "logos_dev_ptr": (None, [H, C.POINTER(PTR), C.POINTER(I64)]),
     "logos_dev_sync": (None, [I32c]),
+    "logos_dev_mem_info": (None, [I32c, C.POINTER(I64), C.POINTER(I64)]),
     "logos_dev_free": (None, [H]),
     "logos_kernel_status": (None, [I32c, C.POINTER(I32c)]),
     "logos_launch_counts": (None, [C.POINTER(I64)]),
@@ -72,7 +80,6 @@ _SIGNATURES = {
     "logos_q8_gemv": (None, [H, H, H, H, I64, I64, PTR]),
     "logos_q8_gemm": (None, [H, H, H, H, I64, I64, I64, I32c, H, PTR]),
     "logos_q8_gemm_f32": (None, [H, H, H, H, I64, I64, I64, PTR]),
-    "logos_gemm_trace_buffer": (None, [H]),
     "logos_q8_gemm_simt": (None, [H, H, H, H, I64, I64, I64, I32c, H, PTR]),
     "logos_rope_table": (None, [PTR, I64, I64, C.c_double]),
     "logos_kv_append_rope": (None, [H, H, H, H, H, H, I64, I64, I64, I64, PTR]),
@@ -97,8 +104,6 @@ _SIGNATURES = {
     "logos_llm_last_timing": (None, [H, C.POINTER(C.c_double), C.POINTER(I64)]),
     "logos_llm_tp_exchange": (None, [H, C.POINTER(C.c_int32)]),
     "logos_dependent_launch_scope": (None, [C.c_int32, C.POINTER(C.c_int32)]),
-    "logos_tc_mma_probe": (None, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(I64),
-                           C.POINTER(I64)]),
     "logos_llm_profile_step": (None, [H, C.POINTER(C.c_double)]),
     "logos_llm_weights_file_bytes": (None, [C.POINTER(LlmConfig), C.POINTER(I64)]),
     "logos_llm_weights_span": (None, [C.POINTER(LlmConfig), I64, I32c, C.POINTER(I64), C.POINTER(I64), C.POINTER(I64),
@@ -148,7 +153,7 @@ def load():
 
 def check(status):
     if status != 0:
-        msg = load().logos_last_error()
+        msg = load().logos_b200_last_error()
         raise LogosError(status, msg.decode() if msg else "(no message)")
 
 

@@ -75,7 +75,7 @@ def build(force=False, verbose=False):
         raise RuntimeError("nvcc failed")
     objs = [os.path.join(OBJ, os.path.basename(s)[:-3] + ".o") for s in srcs]
     if force or jobs or _newer(LIB, objs):
-        cmd = [nvcc, "-ccbin", _host_cxx()] + ARCH + ["-shared", "-o", LIB] + objs + ["-ldl"]
+        cmd = [nvcc, "-ccbin", _host_cxx()] + ARCH + ["-shared", "-Xlinker", "-Bsymbolic-functions", "-o", LIB] + objs + ["-ldl"]
         subprocess.check_call(cmd)
     return LIB
 

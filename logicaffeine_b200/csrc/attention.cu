@@ -488,17 +488,11 @@ constexpr size_t attn_smem_bytes() {
          2 * ATT_STAGES * 8 + 64;
 }
 
-template <int D>
-logos_status_t launch_attn_t(const AttnArgs& a, cudaStream_t st) {
-  const int64_t rows_total = a.b * a.h_kv * a.l_max;
-  CUtensorMap mk, mv;
-  LOGOS_TRY(make_tensor_map_2d(&mk, a.k_cache, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, D, rows_total, D * 2, 64, ATT_TILE,
-                               CU_TENSOR_MAP_SWIZZLE_128B));
-  LOGOS_TRY(make_tensor_map_2d(&mv, a.v_cache, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, D, rows_total, D * 2, 64, ATT_TILE,
-                               CU_TENSOR_MAP_SWIZZLE_128B));
-  // Unit length: a CTA pays about a tile's worth of time for its prologue, its first load and
-  // its partial results, so units are at least four tiles where the grid still fills the GPU
-  // (two CTAs per SM, a few waves), and at most eight, which keeps the last wave short.
+// Unit length and units per (sequence, KV head): a CTA pays about a tile's worth of time for its
+// prologue, its first load and its partial results, so units are at least four tiles where the
+// grid still fills the GPU (two CTAs per SM, a few waves), and at most eight, which keeps the
+// last wave short.
+void attn_plan(const AttnArgs& a, int64_t* unit_len, int* max_splits) {
   int sms = sm_count(a.device);
   int64_t total_pos = a.b * a.h_kv * a.l_max;
   int64_t ul = (total_pos + (int64_t)sms * 5 - 1) / ((int64_t)sms * 5);
@@ -511,7 +505,21 @@ logos_status_t launch_attn_t(const AttnArgs& a, cudaStream_t st) {
     const int64_t units = (a.l_max + ul - 1) / ul;
     ul = (((a.l_max + units - 1) / units + ATT_TILE - 1) / ATT_TILE) * ATT_TILE;
   }
-  int max_splits = (int)((a.l_max + ul - 1) / ul);
+  *unit_len = ul;
+  *max_splits = (int)((a.l_max + ul - 1) / ul);
+}
+
+template <int D>
+logos_status_t launch_attn_t(const AttnArgs& a, cudaStream_t st) {
+  const int64_t rows_total = a.b * a.h_kv * a.l_max;
+  CUtensorMap mk, mv;
+  LOGOS_TRY(make_tensor_map_2d(&mk, a.k_cache, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, D, rows_total, D * 2, 64, ATT_TILE,
+                               CU_TENSOR_MAP_SWIZZLE_128B));
+  LOGOS_TRY(make_tensor_map_2d(&mv, a.v_cache, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, D, rows_total, D * 2, 64, ATT_TILE,
+                               CU_TENSOR_MAP_SWIZZLE_128B));
+  int64_t ul = 0;
+  int max_splits = 0;
+  attn_plan(a, &ul, &max_splits);
 
   void* scratch = nullptr;
   int64_t po_bytes = a.b * a.h_q * max_splits * D * (int64_t)sizeof(float);
@@ -576,6 +584,13 @@ void rope_table_host(float* out, int64_t l_max, int64_t d, double theta) {
     }
 }
 
+int64_t attn_scratch_bytes(const AttnArgs& a) {
+  int64_t ul = 0;
+  int max_splits = 0;
+  attn_plan(a, &ul, &max_splits);
+  return a.b * a.h_q * max_splits * (a.d + 2) * (int64_t)sizeof(float);
+}
+
 logos_status_t launch_gqa_decode_attn(const AttnArgs& a, cudaStream_t st) {
   if (a.b == 0 || a.h_q == 0) return LOGOS_OK;
   if (a.h_kv <= 0 || a.h_q % a.h_kv) return fail(LOGOS_ERROR, "attention: h_q must be a multiple of h_kv");
@@ -638,6 +653,25 @@ logos_status_t static_scratch_for(int device, StaticAddr* out) {
 }
 }  // namespace
 
+// The fixed-scratch entry point's own status word, for logos_kernel_status: copies the eight
+// words out (and zeroes them when asked) if that entry point has run on `device`; *used tells
+// whether it has.  A device-to-host copy of eight words: no allocation here either.
+logos_status_t static_attn_status_read(int device, int words_out[8], bool clear, bool* used) {
+  *used = false;
+  if (device < 0 || device >= kMaxStaticDevices) return LOGOS_OK;
+  StaticAddr sa;
+  {
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    sa = g_static_addr[device];
+  }
+  if (!sa.ready) return LOGOS_OK;
+  LOGOS_CUDA_TRY(cudaSetDevice(device));
+  LOGOS_CUDA_TRY(cudaMemcpy(words_out, sa.status, sizeof(int) * 8, cudaMemcpyDeviceToHost));
+  if (clear && words_out[0] != 0) LOGOS_CUDA_TRY(cudaMemset(sa.status, 0, sizeof(int) * 8));
+  *used = true;
+  return LOGOS_OK;
+}
+
 }  // namespace logos
 
 using namespace logos;
@@ -664,10 +698,10 @@ logos_status_t logos_gqa_decode_attn_fixed_scratch(logos_handle_t q, logos_handl
     StaticAddr sa;
     LOGOS_TRY(static_scratch_for(dev, &sa));
     cudaStream_t st = as_stream(stream_or_null);
-    // The status word is shared by every call on this path and keeps the last call's value:
-    // it has to start at zero.  The partials need no clearing: every entry the merge reads is
-    // written by this call first.
-    LOGOS_CUDA_TRY(cudaMemsetAsync(sa.status, 0, sizeof(int) * 8, st));
+    // Nothing in the array has to be cleared.  The partials: every entry the merge reads is
+    // written by this call first.  The status word starts at zero with the library image and is
+    // sticky like the per-device one: a kernel that gave up leaves its code there, later calls
+    // on this entry point do no work on top of it, and logos_kernel_status reports and clears it.
     a.q_f16 = qp; a.k_cache = kc; a.v_cache = vc; a.seq_len = sl; a.o = op; a.o_dtype = LOGOS_F16;
     a.b = b; a.h_q = h_q; a.h_kv = h_kv; a.d = d; a.l_max = l_max; a.scale = softmax_scale; a.device = dev;
     a.ext_scratch = sa.scratch;

@@ -14,9 +14,11 @@
 namespace logos {
 
 // ---------------------------------------------------------------- errors
-// Per-thread message store, read through logos_last_error(); same contract as
+// Per-thread message store, read through logos_b200_last_error(); same contract as
 // the reference's thread-keyed store (crates/logicaffeine_compile/src/codegen/ffi.rs:214-251).
 void set_last_error(const std::string& msg);
+const char* last_error_text();  // null when the calling thread has no pending message
+void clear_last_error();
 logos_status_t fail(logos_status_t code, const char* fmt, ...);
 logos_status_t cuda_fail(cudaError_t e, const char* what);
 
@@ -76,8 +78,12 @@ logos_status_t buf_ptr(logos_handle_t h, int64_t elems, const char* name, T** ou
   return LOGOS_OK;
 }
 
-// Per-device scratch the library owns (split-K partials, attention partials).
-// Grows on demand, outside any stream capture; freed at process exit.
+// Per-device scratch the library owns, for the stand-alone operators (activation planes and
+// split-K partials of logos_q8_gemm*, split-KV partials of logos_gqa_decode_attn*).  One block
+// per (device, slot), shared by every caller on that device: calls that use it must be ordered
+// on the GPU (one stream, or the caller's own events).  Grows on demand, outside any stream
+// capture; outgrown blocks are kept until the process exits.  A model never uses it: what a
+// captured decode step points at is owned by the model.
 logos_status_t scratch_get(int32_t device, int slot, int64_t bytes, void** out);
 
 int sm_count(int device);

@@ -121,11 +121,14 @@ __device__ __forceinline__ void ll_store(uint4* p, uint32_t a, uint32_t b, uint3
   asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(epoch), "r"(b), "r"(epoch)
                : "memory");
 }
-// Bounded poll (about ten seconds of SM clock: the sender is another process on another GPU and
-// may lag by a graph instantiation); false when the slot never carried this epoch.
-__device__ __forceinline__ bool ll_load(const uint4* p, uint32_t epoch, uint32_t* a, uint32_t* b) {
+// Bounded poll.  The sender is another process on another GPU and may lag (by a graph
+// instantiation, say), so a thread's waits of one kernel share ONE budget of about four seconds
+// of SM clock counted from the thread's first unsuccessful poll: `*deadline` is 0 until then.
+// False when the slot did not carry this epoch in time; the caller then stops waiting
+// altogether (a launch with a dead peer costs one budget, not one per slot).
+constexpr long long kPeerWaitCycles = 8000000000ll;
+__device__ __forceinline__ bool ll_load(const uint4* p, uint32_t epoch, uint32_t* a, uint32_t* b, long long* deadline) {
   uint4 v;
-  long long start = 0;
   for (int spin = 0;; ++spin) {
     asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     if (v.y == epoch && v.w == epoch) {
@@ -134,8 +137,9 @@ __device__ __forceinline__ bool ll_load(const uint4* p, uint32_t epoch, uint32_t
       return true;
     }
     if ((spin & 255) == 255) {
-      if (start == 0) start = clock64();
-      else if (clock64() - start > 20000000000ll) return false;
+      const long long now = clock64();
+      if (*deadline == 0) *deadline = now + kPeerWaitCycles;
+      else if (now > *deadline) return false;
     }
   }
 }
@@ -171,7 +175,12 @@ tp_residual_rmsnorm_kernel(float* __restrict__ h, const TpFusedArgs t, int parts
   const bool mine = owner == t.rank;
   const int64_t n4 = hidden >> 2, per = n4 / TP_CLUSTER;  // float4 per row, per CTA
   const int64_t slots_per_row = hidden >> 1;               // 16-byte slots per row (two words each)
-  bool ok = true;
+  // A code left behind by an earlier kernel (a wait that gave up, here or in a GEMM) means the
+  // ranks are no longer in step: push as usual, so that no peer waits for this rank longer
+  // than it must, but wait for nobody.
+  bool ok = *reinterpret_cast<volatile int*>(status) == 0;
+  const bool ok_at_entry = ok;
+  long long deadline = 0;
 
   // ---- A: push this rank's contribution to the row's owner
   {
@@ -198,7 +207,10 @@ tp_residual_rmsnorm_kernel(float* __restrict__ h, const TpFusedArgs t, int parts
       for (int src = 0; src < t.degree; ++src) {
         const uint4* in = t.inbox_part[t.rank] + ((int64_t)src * rows_own + row_local) * slots_per_row + 2 * i4;
         uint32_t a0, a1, a2, a3;
-        if (!ll_load(in, e, &a0, &a1) || !ll_load(in + 1, e, &a2, &a3)) { ok = false; a0 = a1 = a2 = a3 = 0u; }
+        if (!ok || !ll_load(in, e, &a0, &a1, &deadline) || !ll_load(in + 1, e, &a2, &a3, &deadline)) {
+          ok = false;
+          a0 = a1 = a2 = a3 = 0u;
+        }
         v.x = __fadd_rn(v.x, __uint_as_float(a0)); v.y = __fadd_rn(v.y, __uint_as_float(a1));
         v.z = __fadd_rn(v.z, __uint_as_float(a2)); v.w = __fadd_rn(v.w, __uint_as_float(a3));
       }
@@ -243,7 +255,8 @@ tp_residual_rmsnorm_kernel(float* __restrict__ h, const TpFusedArgs t, int parts
     for (int64_t i = tid; i < per; i += blockDim.x) {
       const int64_t i4 = (int64_t)crank * per + i;
       uint32_t pk[4];
-      if (!ll_load(in + 2 * i4, e, &pk[0], &pk[1]) || !ll_load(in + 2 * i4 + 1, e, &pk[2], &pk[3])) {
+      if (!ok || !ll_load(in + 2 * i4, e, &pk[0], &pk[1], &deadline) ||
+          !ll_load(in + 2 * i4 + 1, e, &pk[2], &pk[3], &deadline)) {
         ok = false;
         pk[0] = pk[1] = pk[2] = pk[3] = 0u;
       }
@@ -256,7 +269,7 @@ tp_residual_rmsnorm_kernel(float* __restrict__ h, const TpFusedArgs t, int parts
       if (t.xn_lo) reinterpret_cast<uint2*>(t.xn_lo + row * hidden)[i4] = lo2;
     }
   }
-  if (!ok) atomicExch(status, 3030);
+  if (!ok && ok_at_entry) atomicCAS(status, 0, 3030);
   // the last CTA to finish advances this rank's epoch
   __syncthreads();
   if (tid == 0) {
@@ -395,7 +408,10 @@ logos_status_t launch_rmsnorm_f32(const float* x, const float* g, float* y, int6
 logos_status_t launch_swiglu_f32(const float* gate, const float* up, float* y, int64_t count, cudaStream_t st) {
   if (count == 0) return LOGOS_OK;
   int64_t want = (count + 255) / 256;
-  int grid = (int)(want < 148 * 8 ? want : 148 * 8);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int64_t cap = (int64_t)sm_count(dev) * 8;
+  int grid = (int)(want < cap ? want : cap);
   swiglu_f32_kernel<<<grid, 256, 0, st>>>(gate, up, y, count);
   count_launch(LK_ELEMWISE);
   return check_launch("swiglu_f32_kernel");

@@ -64,6 +64,8 @@ struct Model {
   float* partials = nullptr; // [max_splits][B][H]
   float* dpart = nullptr;    // split-K partials of the GEMMs with a direct output (qkv, gate/up)
   int64_t dpart_floats = 0;
+  void*  attn_scratch = nullptr;  // split-KV partials of the attention kernel: owned here, so the captured step
+  int64_t attn_scratch_bytes = 0; // never points at the library's shared scratch
   // tensor parallelism with peer-addressable memory: partials, xn planes and flag words live in
   // one block per rank that every rank maps; the all-reduce is folded into residual + RMSNorm
   TpSymm symm;
@@ -282,6 +284,12 @@ logos_status_t build(Model* m, const void* nccl_id) {
     m->dpart_floats = need_qkv > need_gu ? need_qkv : need_gu;
     if (m->dpart_floats > 0) LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->dpart), m->dpart_floats * 4));
   }
+  {
+    AttnArgs a;
+    a.b = B; a.h_q = m->hq_local; a.h_kv = m->hkv_local; a.d = D; a.l_max = c.l_max; a.device = m->device;
+    m->attn_scratch_bytes = attn_scratch_bytes(a);
+    LOGOS_TRY(dmalloc(m, &m->attn_scratch, m->attn_scratch_bytes));
+  }
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->logits), B * c.vocab * 4));
   m->history_cap = c.l_max;
   LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->history), m->history_cap * B * 4));
@@ -396,7 +404,7 @@ logos_status_t debug_check(Model* m, const char* what, int64_t layer) {
   int code = 0;
   LOGOS_TRY(kernel_status_read(m->device, &code, false));
   if (code != 0) {
-    std::string detail = logos_last_error() ? logos_last_error() : "";
+    std::string detail = last_error_text() ? last_error_text() : "";
     return fail(LOGOS_ERROR, "kernel status %d first seen after %s of layer %lld [%s]", code, what, (long long)layer, detail.c_str());
   }
   return LOGOS_OK;
@@ -468,6 +476,7 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
       a.b = B; a.h_q = m->hq_local; a.h_kv = m->hkv_local; a.d = D; a.l_max = c.l_max;
       a.scale = 1.0f / sqrtf((float)D);
       a.device = m->device;
+      a.ext_scratch = m->attn_scratch; a.ext_scratch_bytes = m->attn_scratch_bytes;
       LOGOS_TRY(launch_gqa_decode_attn(a, st));
       m->launch_counter += 2;
     }
@@ -770,7 +779,7 @@ logos_status_t logos_llm_create(const logos_llm_config_t* cfg, const void* nccl_
     m->device = cfg->device;
     logos_status_t s = build(m, nccl_unique_id_or_null);
     if (s != LOGOS_OK) {
-      std::string keep = logos_last_error() ? logos_last_error() : "";
+      std::string keep = last_error_text() ? last_error_text() : "";
       destroy(m);
       set_last_error(keep);
       return s;
@@ -902,8 +911,9 @@ logos_status_t logos_llm_decode_steps(logos_handle_t model, int64_t steps, int32
     LOGOS_CUDA_TRY(cudaMemsetAsync(m->step_counter, 0, sizeof(int32_t), m->stream));
     LOGOS_CUDA_TRY(cudaEventRecord(m->ev0, m->stream));
     for (int64_t i = 0; i < steps; ++i) {
-      // The first step of a model runs eagerly (it sizes the library's scratch buffers); after
-      // that one step is captured once and replayed: all of its arguments are device-resident.
+      // The first step of a model runs eagerly; after that one step is captured once and
+      // replayed: all of its arguments are device-resident and every buffer it names is owned
+      // by the model.
       if (!m->step_graph && !m->graph_failed && m->eager_sample_steps >= 1 && graphs_enabled()) {
         cudaGraph_t graph = nullptr;
         bool good = cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
@@ -1066,7 +1076,7 @@ logos_status_t logos_llm_save_weights(logos_handle_t model, const char* path) {
     int fd = open(path, O_WRONLY | O_CREAT | O_TRUNC, 0644);
     if (fd < 0) return fail(LOGOS_ERROR, "logos_llm_save_weights: cannot create '%s': %s", path, strerror(errno));
     logos_status_t s = save_weights(m, fd);
-    std::string keep = s != LOGOS_OK && logos_last_error() ? logos_last_error() : "";
+    std::string keep = s != LOGOS_OK && last_error_text() ? last_error_text() : "";
     if (close(fd) != 0 && s == LOGOS_OK) s = fail(LOGOS_ERROR, "logos_llm_save_weights: close failed: %s", strerror(errno));
     else if (s != LOGOS_OK) set_last_error(keep);
     return s;

@@ -94,12 +94,17 @@ struct AttnArgs {
   float         scale = 1.f;
   int           device = 0;
   // Caller-provided scratch for the split-KV partials and the status word (both device
-  // addresses).  Null = the library's own per-device scratch, allocated on first use.
+  // addresses).  Null = the library's own per-device scratch, allocated on first use and shared
+  // by every stand-alone call on the device (a model passes its own: a captured step must not
+  // point at memory another caller can outgrow).
   void*         ext_scratch = nullptr;
   int64_t       ext_scratch_bytes = 0;
   int*          ext_status = nullptr;
 };
 logos_status_t launch_gqa_decode_attn(const AttnArgs& a, cudaStream_t st);
+// Bytes of split-KV scratch a call with these extents (b, h_q, h_kv, d, l_max, device) needs:
+// what a caller that passes ext_scratch has to provide.
+int64_t attn_scratch_bytes(const AttnArgs& a);
 logos_status_t launch_kv_append_rope(__half* k_cache, __half* v_cache, const __half* k_new, const __half* v_new,
                                      const float* rope, int32_t* seq_len, int64_t b, int64_t h_kv, int64_t d,
                                      int64_t l_max, int device, cudaStream_t st);

@@ -229,10 +229,11 @@ static logos_status_t gemm_abi(logos_handle_t a, logos_handle_t q, logos_handle_
 
 extern "C" {
 
-// Tracing: when a buffer of at least 64*16 int64 is set, CTA (0,0,0) of every tcgen05 GEMM
-// launch stores SM-clock timestamps of its pipeline roles per K stage ([stage][16]); null turns
-// it off.  A development aid for reading where a stage's time goes.
-logos_status_t logos_gemm_trace_buffer(logos_handle_t buf_or_null) {
+#ifdef LOGOS_TC_TRACE
+// Development builds only: CTA (0,0,0) of every tcgen05 GEMM launch stores SM-clock timestamps of
+// its pipeline roles per K stage ([stage][16]) into this buffer of at least 64*16 int64; null
+// turns it off.
+__attribute__((visibility("default"))) logos_status_t logos_gemm_trace_buffer(logos_handle_t buf_or_null) {
   return guarded([&]() -> logos_status_t {
     if (!buf_or_null) {
       gemm_set_trace(nullptr);
@@ -244,6 +245,7 @@ logos_status_t logos_gemm_trace_buffer(logos_handle_t buf_or_null) {
     return LOGOS_OK;
   });
 }
+#endif
 
 // f32 activations, f32 output: the form the decode step uses internally (the
 // activations are split into two fp16 planes so the tensor-core product keeps

@@ -51,18 +51,9 @@ constexpr int RAW_PREFETCH = 12;  // L2 prefetch distance of the weight stream, 
 constexpr int ACT_STAGES = 4;
 constexpr int TA_STAGES = 4;
 constexpr int TA_LIMB_COLS = 64; // TMEM columns per converted stage and copy: 128 fp16 per row
-// 4 or 8.  Eight converter warps halve the conversion time of a stage but measured no faster
-// overall (the MMA -> drain -> MMA hand-off is what bounds a stage), so four is the default;
-// with eight the kernel rebalances registers between its warpgroups (20 warps x 96 at launch).
-constexpr int CONV_WARPS = 4;
+constexpr int CONV_WARPS = 4;     // one per TMEM lane quarter
 constexpr int CONV_WARP0 = 4, DRAIN_WARP0 = CONV_WARP0 + CONV_WARPS;
 constexpr int TC_THREADS = (DRAIN_WARP0 + 8) * 32;  // 4 single-role warps, converter warps, 8 drain warps
-// Token groups an MMA warp cuts each block into (MMA N = MT / NSPLIT).  An isolated M=128, K=16
-// MMA with its A operand in tensor memory takes 38 cycles at N=32 and at N=64 (logos_tc_mma_probe),
-// so cutting a block into smaller MMAs only doubles the instruction count: 1 is the setting.
-#ifndef LOGOS_TC_NSPLIT
-#define LOGOS_TC_NSPLIT 1
-#endif
 constexpr int ACC_PAIRS = 2;     // TMEM accumulator ring: each entry holds two Q8 blocks
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int RAW_BYTES = TC_ROWS * TC_KSTAGE;  // 16 KB
@@ -107,7 +98,9 @@ struct TcParams {
   int items;        // work items: row tiles x splits
   int store_mode;
   int* status;
-  long long* trace;  // optional: SM-clock timestamps of CTA (0,0,0), first item, [stage][16]
+#ifdef LOGOS_TC_TRACE
+  long long* trace;  // SM-clock timestamps of CTA (0,0,0), first item, [stage][16]
+#endif
 };
 
 // Work item w = (row tile, K split): the splits of a tile are neighbours.
@@ -128,11 +121,18 @@ __device__ __forceinline__ void tc_report(int* status, int code, int stage, int 
   }
 }
 
-// Timestamp slot `ev` of stage `i` (tracing only; CTA 0, its first item, one lane per role).
+// Timestamp slot `ev` of stage `i` (development builds with -DLOGOS_TC_TRACE only; CTA 0, its
+// first item, one lane per role).  Compiled out otherwise.
+#ifdef LOGOS_TC_TRACE
 #define TC_TRACE(i, ev)                                                                          \
   do {                                                                                           \
     if (trace_on && (i) < 64) p.trace[(i) * 16 + (ev)] = clock64();                              \
   } while (0)
+#define TC_TRACE_ITEM(w) trace_on = cta0 && (w) == 0
+#else
+#define TC_TRACE(i, ev) do { } while (0)
+#define TC_TRACE_ITEM(w) do { } while (0)
+#endif
 
 __device__ __forceinline__ float silu_f(float g) { return __fdiv_rn(g, 1.0f + expf(-g)); }
 
@@ -215,8 +215,10 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const int warp = tid >> 5;
   const int64_t m0 = (int64_t)blockIdx.z * MT;
   const int items = p.items;
+#ifdef LOGOS_TC_TRACE
   const bool cta0 = p.trace && blockIdx.x == 0 && blockIdx.z == 0;
   bool trace_on = cta0;
+#endif
 
   if (tid == 0) TC_TRACE(63, 0);  // kernel entry
   // a kernel that gave up earlier left a code behind: do not start new work on top of it
@@ -257,23 +259,18 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
   bool ok = true;
   if (tid == 0) TC_TRACE(63, 1);  // set-up done
-  // With 20 warps the launch grants 96 registers each; the single-role and converter
-  // warpgroups hand most of theirs back and the two drain warpgroups take them (the first
-  // statement of every role below).
-  constexpr bool kRebalance = (CONV_WARPS == 8);
 
   // Every role walks the same sequence of (item, stage) pairs; `gs` counts stages across items
   // and alone decides ring slots and barrier phases, so the rings never drain between items.
   if (warp == 0) {
     // ------------------------------------------------------------ weight producer
-    if (kRebalance) setmaxnreg_dec<48>();
     if (lane == 0) {
       const uint64_t pol = policy_evict_first();
       int gs = 0;
       for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
         const TcItem it = tc_item(p, w);
         const int n0 = it.tile * TC_ROWS, nst = it.nst, st_begin = it.st_begin;
-        trace_on = cta0 && w == 0;
+        TC_TRACE_ITEM(w);
         // The smem ring alone (RAW_STAGES x 16 KB per SM) does not cover HBM latency under load:
         // L2 prefetches run RAW_PREFETCH stages ahead of the TMA loads.  They start only after
         // the item's first loads are on their way, so that nothing queues in front of those.
@@ -295,7 +292,6 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ activation producer
-    if (kRebalance) setmaxnreg_dec<48>();
     if (lane == 0) {
       pdl_wait();  // the activations are the previous kernel's output
       const uint64_t pol = policy_evict_last();
@@ -303,7 +299,7 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
         const TcItem it = tc_item(p, w);
         const int nst = it.nst, st_begin = it.st_begin;
-        trace_on = cta0 && w == 0;
+        TC_TRACE_ITEM(w);
         for (int i = 0; i < nst; ++i, ++gs) {
           const int st = gs % ACT_STAGES;
           const uint32_t ph = (uint32_t)(gs / ACT_STAGES) & 1u;
@@ -323,7 +319,6 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
   } else if (warp == 2 || warp == 3) {
     // ------------------------------------------------------------ MMA issuers
-    if (kRebalance) setmaxnreg_dec<48>();
     // Two warps, one per half of a stage: warp 2 issues the first pair of Q8 blocks of every
     // stage, warp 3 the second.  What bounds the kernel is the round trip of an accumulator entry
     // (MMAs execute -> completion seen by the drain -> tcgen05.ld -> entry released -> next
@@ -331,15 +326,15 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // waited on, phase after phase, by the same warp, which the odd/even phase test needs.
     // A warp runs its loop with all lanes (addresses and descriptors stay warp-uniform) and one
     // elected lane issues the tcgen05 instructions.  A pair owns accumulator ring entry `pr`.
-    constexpr int NSPLIT = LOGOS_TC_NSPLIT <= MT / 16 ? LOGOS_TC_NSPLIT : MT / 16;  // token groups per block
-    constexpr int MN = MT / NSPLIT;                  // tokens per MMA (MMA N, a multiple of 16)
+    constexpr int NSPLIT = 1;   // an M=128, K=16 MMA costs the same at N=32 and N=64: one MMA per block and plane
+    constexpr int MN = MT;      // tokens per MMA (MMA N, a multiple of 16)
     constexpr uint32_t idesc = make_idesc_f16(0, 0, TC_ROWS, MN);
     static_assert(ACC_PAIRS == 2, "one accumulator ring entry per MMA warp");
     const int pr = warp - 2;
     int gs = 0;
     for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
       const int nst = tc_item(p, w).nst;
-      trace_on = cta0 && w == 0;
+      TC_TRACE_ITEM(w);
       for (int i = 0; i < nst && ok; ++i, ++gs) {
         const int ts = gs % TA_STAGES, as = gs % ACT_STAGES;
         const uint32_t tph = (uint32_t)(gs / TA_STAGES) & 1u, aph = (uint32_t)(gs / ACT_STAGES) & 1u;
@@ -390,7 +385,6 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // ------------------------------------------------------------ converters: int8 smem -> fp16 TMEM
     // One or two warps per lane quarter; each converts its share of the stage's eight 16-byte
     // chunks per row.
-    if (kRebalance) setmaxnreg_dec<64>();
     const int qd = warp & 3;
     const int chalf = (warp - CONV_WARP0) >> 2;
     const uint32_t row = qd * 32 + lane;
@@ -398,7 +392,7 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     int gs = 0;
     for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
       const int nst = tc_item(p, w).nst;
-      trace_on = cta0 && w == 0;
+      TC_TRACE_ITEM(w);
       for (int i = 0; i < nst; ++i, ++gs) {
         const int rs = gs % RAW_STAGES, ts = gs % TA_STAGES;
         const uint32_t rph = (uint32_t)(gs / RAW_STAGES) & 1u, tph = (uint32_t)(gs / TA_STAGES) & 1u;
@@ -438,7 +432,6 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // Two warps per lane quarter, each owning half of the token columns.  Blocks are taken two
     // at a time so one tcgen05.wait::ld covers both loads: the TMEM read latency, not the
     // arithmetic, is what bounds this role.
-    if (kRebalance) setmaxnreg_inc<144>();
     const int qd = warp & 3;
     const int half = (warp - DRAIN_WARP0) >> 2;
     constexpr int HC = MT / 2;  // token columns per drain warp
@@ -454,7 +447,7 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       const TcItem it = tc_item(p, w);
       const int nst = it.nst, st_begin = it.st_begin;
       const int64_t n0 = (int64_t)it.tile * TC_ROWS;
-      trace_on = cta0 && w == 0;
+      TC_TRACE_ITEM(w);
       const int64_t n = n0 + nl;
       const bool n_ok = n < p.n;
       const float* srow = p.s + (n_ok ? n : 0) * kb_per_row;
@@ -487,8 +480,10 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           tc_ld_cols<HC>(t_lane + (pr * 2 + 1) * MT, b1);
           tc_wait_ld();
           if (warp == DRAIN_WARP0 && lane == 0) TC_TRACE(i, pr == 0 ? 9 : 14);
+#ifdef LOGOS_TC_TRACE
           if (trace_on && lane == 0 && i < 64)  // the last of the eight drain warps to get here
             atomicMax(reinterpret_cast<unsigned long long*>(&p.trace[i * 16 + (pr == 0 ? 3 : 15)]), (unsigned long long)clock64());
+#endif
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[pr]);
@@ -606,7 +601,9 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
   tc_fence_before();
   __syncthreads();
+#ifdef LOGOS_TC_TRACE
   if (tid == 0) { trace_on = cta0; TC_TRACE(63, 4); }
+#endif
   if (warp == 3) {
     __syncwarp();
     tc_fence_after();
@@ -615,7 +612,9 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 }
 
 // ---------------------------------------------------------------- host side
+#ifdef LOGOS_TC_TRACE
 long long* g_trace = nullptr;  // set through logos_gemm_trace_buffer; null = tracing off
+#endif
 
 struct MapKey {
   const void* base;
@@ -684,12 +683,14 @@ logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
   if (tiles * p.splits > INT32_MAX) return fail(LOGOS_OUT_OF_BOUNDS, "q8_gemm: too many work items");
   p.items = (int)(tiles * p.splits);
   p.status = kernel_status_ptr(g.device);
+#ifdef LOGOS_TC_TRACE
   p.trace = g_trace;
   if (g_trace) {
     // optional filter: trace only launches whose grid has this many row tiles
     static const char* f = getenv("LOGOS_B200_TRACE_TILES");
     if (f && atoi(f) != (int)tiles) p.trace = nullptr;
   }
+#endif
   if (!p.status) return fail(LOGOS_ERROR, "q8_gemm: no kernel status word");
   if (p.splits > p.stages_total) return fail(LOGOS_ERROR, "q8_gemm: more K splits than 128-column stages");
 
@@ -732,8 +733,7 @@ logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
 
   LOGOS_CUDA_TRY(cudaFuncSetAttribute(q8_gemm_tc_kernel<MT, LIMBS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
   // persistent CTAs: one per SM at most, each takes items blockIdx.x, blockIdx.x + gridDim.x, ...
-  static const bool one_item_ctas = getenv("LOGOS_B200_GEMM_ONE_ITEM_CTAS") != nullptr;
-  const int sms = one_item_ctas ? INT32_MAX : sm_count(g.device);
+  const int sms = sm_count(g.device);
   dim3 grid((unsigned)(p.items < sms ? p.items : sms), 1u, (unsigned)((g.m + MT - 1) / MT));
   LOGOS_CUDA_TRY(launch_kernel(q8_gemm_tc_kernel<MT, LIMBS>, grid, dim3(TC_THREADS), Cfg::SMEM, st, mq, mhi, mlo, mo0, mo1, p));
   count_launch(LK_GEMM_TC);
@@ -742,7 +742,9 @@ logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
 
 }  // namespace
 
+#ifdef LOGOS_TC_TRACE
 void gemm_set_trace(long long* buf) { g_trace = buf; }
+#endif
 
 bool gemm_tc_applicable(const GemmArgs& g) {
   if (g.a_dtype != LOGOS_F16) return false;

@@ -7,6 +7,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -29,6 +30,7 @@ uint64_t g_counter = 0;
 struct Scratch {
   void*   ptr = nullptr;
   int64_t bytes = 0;
+  std::vector<void*> retired;  // outgrown blocks: kept, since launches already enqueued may still use them
 };
 std::mutex g_scratch_mu;
 std::unordered_map<uint64_t, Scratch> g_scratch;
@@ -37,6 +39,11 @@ std::unordered_map<uint64_t, Scratch> g_scratch;
 void set_last_error(const std::string& msg) {
   t_error = msg;
   t_has_error = true;
+}
+const char* last_error_text() { return t_has_error ? t_error.c_str() : nullptr; }
+void clear_last_error() {
+  t_has_error = false;
+  t_error.clear();
 }
 
 logos_status_t fail(logos_status_t code, const char* fmt, ...) {
@@ -110,14 +117,24 @@ logos_status_t scratch_get(int32_t device, int slot, int64_t bytes, void** out) 
     int prev = 0;
     LOGOS_CUDA_TRY(cudaGetDevice(&prev));
     LOGOS_CUDA_TRY(cudaSetDevice(device));
-    if (s.ptr) {
-      LOGOS_CUDA_TRY(cudaDeviceSynchronize());
-      LOGOS_CUDA_TRY(cudaFree(s.ptr));
-      s.ptr = nullptr;
-      s.bytes = 0;
+    // An outgrown block is never freed: kernels already enqueued (on any stream) may still
+    // write to it.  Growing at least geometrically bounds what the retired blocks hold to the
+    // size of the live one.
+    int64_t want = bytes > 2 * s.bytes ? bytes : 2 * s.bytes;
+    want = (want + 255) & ~int64_t(255);
+    void* fresh = nullptr;
+    cudaError_t e = cudaMalloc(&fresh, want);
+    if (e != cudaSuccess && want > bytes) {  // no room for the doubled block: take what is needed
+      cudaGetLastError();
+      want = (bytes + 255) & ~int64_t(255);
+      e = cudaMalloc(&fresh, want);
     }
-    int64_t want = (bytes + 255) & ~int64_t(255);
-    LOGOS_CUDA_TRY(cudaMalloc(&s.ptr, want));
+    if (e != cudaSuccess) {
+      cudaSetDevice(prev);
+      return cuda_fail(e, "cudaMalloc (library scratch)");
+    }
+    if (s.ptr) s.retired.push_back(s.ptr);
+    s.ptr = fresh;
     s.bytes = want;
     LOGOS_CUDA_TRY(cudaSetDevice(prev));
   }
@@ -143,14 +160,23 @@ using namespace logos;
 
 extern "C" {
 
-const char* logos_last_error(void) { return t_has_error ? t_error.c_str() : nullptr; }
-const char* logos_get_last_error(void) { return logos_last_error(); }
-void logos_clear_error(void) {
-  t_has_error = false;
-  t_error.clear();
-}
-uint32_t logos_abi_version(void) { return LOGOS_ABI_VERSION; }
-const char* logos_version(void) { return "0.1.0-b200"; }
+const char* logos_b200_last_error(void) { return last_error_text(); }
+const char* logos_b200_get_last_error(void) { return last_error_text(); }
+void logos_b200_clear_error(void) { clear_last_error(); }
+// Strings handed out with ownership would come from malloc; none is handed out today.
+void logos_b200_free_string(char* str) { free(str); }
+uint32_t logos_b200_abi_version(void) { return LOGOS_ABI_VERSION; }
+const char* logos_b200_version(void) { return "0.2.0-b200"; }
+
+// The reference preamble's names, for hosts that do not define them themselves.  Weak: a LOGOS
+// program that links this library statically keeps its own definitions without a clash.
+#define LOGOS_WEAK __attribute__((weak, visibility("default")))
+LOGOS_WEAK const char* logos_last_error(void) { return last_error_text(); }
+LOGOS_WEAK const char* logos_get_last_error(void) { return last_error_text(); }
+LOGOS_WEAK void logos_clear_error(void) { clear_last_error(); }
+LOGOS_WEAK void logos_free_string(char* str) { free(str); }
+LOGOS_WEAK uint32_t logos_abi_version(void) { return LOGOS_ABI_VERSION; }
+LOGOS_WEAK const char* logos_version(void) { return logos_b200_version(); }
 
 int32_t logos_device_count(void) {
   int n = 0;
@@ -233,6 +259,19 @@ logos_status_t logos_dev_ptr(logos_handle_t h, void** out_ptr, int64_t* out_byte
     LOGOS_TRY(buf_resolve(h, 0, 0, "logos_dev_ptr", &b));
     *out_ptr = b->ptr;
     if (out_bytes) *out_bytes = b->bytes;
+    return LOGOS_OK;
+  });
+}
+
+logos_status_t logos_dev_mem_info(int32_t device, int64_t* free_out, int64_t* total_out) {
+  return guarded([&]() -> logos_status_t {
+    int n = logos_device_count();
+    if (device < 0 || device >= n) return fail(LOGOS_OUT_OF_BOUNDS, "logos_dev_mem_info: device %d of %d", device, n);
+    LOGOS_CUDA_TRY(cudaSetDevice(device));
+    size_t f = 0, t = 0;
+    LOGOS_CUDA_TRY(cudaMemGetInfo(&f, &t));
+    if (free_out) *free_out = (int64_t)f;
+    if (total_out) *total_out = (int64_t)t;
     return LOGOS_OK;
   });
 }

@@ -86,12 +86,25 @@ int* kernel_status_ptr(int device) {
   return p;
 }
 
+logos_status_t static_attn_status_read(int device, int words_out[8], bool clear, bool* used);  // attention.cu
+
 logos_status_t kernel_status_read(int device, int* out, bool clear) {
   int* p = kernel_status_ptr(device);
   if (!p) return fail(LOGOS_ERROR, "no kernel status word (no CUDA device?)");
   LOGOS_CUDA_TRY(cudaSetDevice(device));
   int words[8];
   LOGOS_CUDA_TRY(cudaMemcpy(words, p, sizeof(words), cudaMemcpyDeviceToHost));
+  if (words[0] == 0) {
+    // the word of the entry point that keeps its scratch inside the library image
+    int sw[8];
+    bool used = false;
+    LOGOS_TRY(static_attn_status_read(device, sw, clear, &used));
+    if (used && sw[0] != 0) {
+      *out = sw[0];
+      set_last_error("device-side wait gave up in logos_gqa_decode_attn_fixed_scratch: code " + std::to_string(sw[0]));
+      return LOGOS_OK;
+    }
+  }
   *out = words[0];
   if (words[0] != 0) {
     // where the first kernel to give up was: block (x, y), K stage, stages of that block, warp

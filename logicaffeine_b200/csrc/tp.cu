@@ -3,9 +3,9 @@
 // The library does not link NCCL: the first tensor-parallel model resolves
 // libnccl.so.2 with dlopen (the copy the host process already loaded, e.g.
 // the one bundled with PyTorch, wins by soname), so single-GPU users carry no
-// NCCL dependency.  Only sum all-reduce and all-gather are used: partial
-// o_proj / down_proj outputs, and the per-rank (max, index) pairs of a
-// vocabulary-sharded lm_head.
+// NCCL dependency.  Only sum all-reduce (partial o_proj / down_proj outputs when the
+// exchange is not folded into the norm kernel) and all-gather (the ranks' CUDA-IPC
+// handles at set-up) are used.
 #include "tp.cuh"
 
 #include <dlfcn.h>

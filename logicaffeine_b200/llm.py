@@ -27,7 +27,14 @@ def deviceCount():
 
 
 def abiVersion():
-    return int(load().logos_abi_version())
+    return int(load().logos_b200_abi_version())
+
+
+def devMemInfo(device=0):
+    """(free, total) bytes of device memory as the driver reports them."""
+    f, t = C.c_int64(), C.c_int64()
+    call("logos_dev_mem_info", int(device), C.byref(f), C.byref(t))
+    return f.value, t.value
 
 
 def _host_ptr(a):
@@ -137,15 +144,6 @@ def dependentLaunchScope(on):
     prev = C.c_int32()
     call("logos_dependent_launch_scope", 1 if on else 0, C.byref(prev))
     return bool(prev.value)
-
-
-def tcMmaProbe(n, a_in_tmem=True, count=512, accumulators=2, device=0, background=0):
-    """(issue cycles, cycles until completion is seen) of `count` back-to-back tcgen05.mma M=128 K=16 N=n;
-    background: 0 nothing else runs, 1 tcgen05.st, 2 tcgen05.ld, 3 shared-memory loads by eight other warps."""
-    issue, done = C.c_int64(), C.c_int64()
-    call("logos_tc_mma_probe", int(device), int(n), 1 if a_in_tmem else 0, int(count), int(accumulators),
-         int(background), C.byref(issue), C.byref(done))
-    return issue.value, done.value
 
 
 def q8GemmF32(a, q, s, c, m, n, k, stream=None):

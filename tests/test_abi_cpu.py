@@ -33,8 +33,32 @@ def test_status_codes_match_the_reference_enum():
     want = {"OK": 0, "ERROR": 1, "REFINEMENT_VIOLATION": 2, "NULL_POINTER": 3, "OUT_OF_BOUNDS": 4,
             "DESERIALIZATION_FAILED": 5, "INVALID_HANDLE": 6, "CONTAINS_NULL_BYTE": 7, "THREAD_PANIC": 8,
             "MEMORY_EXHAUSTED": 9}
+    # the enumerator spelling of the C header the reference generates
+    # (crates/logicaffeine_compile/src/codegen/ffi.rs:1364-1375): LOGOS_STATUS_<NAME> = <code>
     for k, v in want.items():
-        assert re.search(r"LOGOS_%s\s*=\s*%d\b" % (k, v), text), k
+        assert re.search(r"\bLOGOS_STATUS_%s\s*=\s*%d\b" % (k, v), text), k
+        assert re.search(r"#define\s+LOGOS_%s\s+LOGOS_STATUS_%s\b" % (k, k), text), k
+    assert re.search(r"typedef\s+void\s*\*\s*logos_handle_t\s*;", text)
+    assert re.search(r"#define\s+LOGOS_ABI_VERSION\s+1\b", text)
+
+
+def test_runtime_names_of_the_reference_preamble_and_the_library_prefix(llm):
+    """The preamble names of ffi.rs:1377-1384 are exported (weak) next to the library's own
+    logos_b200_ copies; both read the same per-thread store; logos_free_string takes NULL."""
+    import subprocess
+    lib = _lib.load()
+    out = subprocess.run(["nm", "-D", "--defined-only", _lib.LIB_PATH], capture_output=True, text=True).stdout
+    kinds = {l.split()[-1]: l.split()[-2] for l in out.splitlines() if len(l.split()) >= 3}
+    for n in ("last_error", "get_last_error", "clear_error", "free_string", "abi_version", "version"):
+        assert kinds.get("logos_" + n) == "W", (n, kinds.get("logos_" + n))
+        assert kinds.get("logos_b200_" + n) == "T", (n, kinds.get("logos_b200_" + n))
+    assert lib.logos_dev_alloc(16, 0, None) == 3
+    assert lib.logos_b200_last_error() == lib.logos_last_error() == lib.logos_b200_get_last_error()
+    lib.logos_b200_clear_error()
+    assert lib.logos_last_error() is None and lib.logos_b200_last_error() is None
+    lib.logos_free_string(None)
+    lib.logos_b200_free_string(None)
+    assert lib.logos_b200_abi_version() == lib.logos_abi_version() == 1
 
 
 def test_version_and_abi(llm):

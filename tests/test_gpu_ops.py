@@ -243,18 +243,6 @@ def test_out_of_bounds_buffers_are_refused(llm):
     assert e.value.status in (3, 6)
 
 
-def test_tc_mma_probe(llm):
-    """The measurement aid behind the GEMM's design note: runs, and the figures are sane."""
-    issue, done = llm.tcMmaProbe(64, True, 256, 2)
-    assert 0 < issue <= done
-    per = done / 256.0
-    assert 16.0 <= per <= 400.0, per          # the arithmetic alone is 32 cycles; measured about 85
-    with pytest.raises(llm.LogosError):
-        llm.tcMmaProbe(48, True, 16, 1)      # N not offered
-    with pytest.raises(llm.LogosError):
-        llm.tcMmaProbe(256, True, 16, 2)     # 512 accumulator columns do not fit beside the operand
-
-
 def test_gemm_with_one_token_equals_gemv(llm, oracle):
     """Metamorphic: the tensor-core GEMM at M = 1 and the GEMV kernel compute the same product."""
     O = oracle

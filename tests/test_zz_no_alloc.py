@@ -35,11 +35,23 @@ def test_fixed_scratch_attention_matches_the_allocating_entry_point_twice(llm, o
         got_buf = llm.DeviceBuffer(b * hq * d * 2)
         llm.gqaDecodeAttn(dq, dkc, dvc, dseq, want_buf, b, hq, hkv, d, lmax, scale)
         want = want_buf.download(np.uint16, (b, hq, d))
+        assert llm.kernelStatus() == 0   # also the status reader's own one-off allocation, before memory is measured
         for call in range(2):
             got_buf.memset(0xFF)
+            llm.devSync()
+            free_before, _ = llm.devMemInfo()
             llm.gqaDecodeAttnFixedScratch(dq, dkc, dvc, dseq, got_buf, b, hq, hkv, d, lmax, scale)
+            llm.devSync()
+            free_after, _ = llm.devMemInfo()
+            # the very first call on a device may load the kernels' module; every later call must
+            # not lower the driver's free-memory figure: no allocation, no growth
+            if call == 1:
+                assert free_after >= free_before, (free_before, free_after)
             got = got_buf.download(np.uint16, (b, hq, d))
             assert np.array_equal(got, want), "call %d differs from logos_gqa_decode_attn" % call
+            # reads the fixed-scratch path's own status word (and the per-device one): a bounded
+            # wait that gave up inside these kernels would show here
+            assert llm.kernelStatus() == 0
         ref = O.gqa_decode_attn(q, kc, vc, seq, scale)
         a, r = O.f16_to_f32(want), O.f16_to_f32(ref)
         assert np.linalg.norm(a - r) / np.linalg.norm(r) < 1e-3   # and both agree with the oracle
