@@ -45,6 +45,11 @@ WORKLOADS = {
 }
 
 
+# crc32 of the tokens of 8 greedy steps from the benchmark's fixed start state, as the unsharded
+# model (N = 1) decodes them on a B200; a tensor-parallel run must print the same value.
+EXPECTED_TOKENS_CRC = {}
+
+
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -116,46 +121,81 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_sample(w, ctx, reps, threads=None):
-    """The oracle on one decoder layer of the workload, one step at context `ctx`;
-    returns (tokens/s extrapolated to the full depth, seconds per layer-step, threads)."""
+def host_threads():
+    """Threads the CPU legs use: every core this process may run on.  Set explicitly, because
+    launchers such as torch.distributed.run export OMP_NUM_THREADS=1 to their children."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def cpu_sample(w, ctx, warm=2, runs=5):
+    """The oracle on a bounded sample of one decode step of the workload at context `ctx`: ONE
+    decoder layer (all four Q8 GEMMs, attention over the full context, norms) and the lm_head
+    GEMM, each timed `runs` times after `warm` untimed passes.  A full step is
+    layers x (layer time) + (head time); the embedding gather and the argmax are not in the
+    sample (below 0.1 % of a step).  Returns a dict with the extrapolated tokens/s and the
+    statistics of the sample."""
     from oracle import oracle as O
-    if threads:
-        O.set_threads(threads)
-    m = O.Llm(layers=1, hidden=w["hidden"], h_q=w["h_q"], h_kv=w["h_kv"], head_dim=w["head_dim"], ffn=w["ffn"],
-              vocab=1024, l_max=ctx + reps + 2, batch=w["batch"], rms_eps=1e-6, rope_theta=1e6, tied_embeddings=1,
+    O.set_threads(host_threads())
+    B, H = w["batch"], w["hidden"]
+    m = O.Llm(layers=1, hidden=H, h_q=w["h_q"], h_kv=w["h_kv"], head_dim=w["head_dim"], ffn=w["ffn"],
+              vocab=1024, l_max=ctx + warm + runs + 2, batch=B, rms_eps=1e-6, rope_theta=1e6, tied_embeddings=1,
               tp_degree=1, tp_rank=0, device=0, act_dtype=O.F32, seed=0, init_std=0.02)
     m.synth_kv(ctx, 1)
-    m.set_tokens(np.arange(w["batch"], dtype=np.int32) % 1024)
-    m.decode_step()  # warm
-    times = []
-    for _ in range(reps):
+    m.set_tokens(np.arange(B, dtype=np.int32) % 1024)
+    layer = []
+    for i in range(warm + runs):
         t0 = time.perf_counter()
         m.decode_step()
-        times.append(time.perf_counter() - t0)
+        if i >= warm:
+            layer.append(time.perf_counter() - t0)
     m.close()
-    t_layer = float(np.median(times))
-    return w["batch"] / (t_layer * w["layers"]), t_layer, O.threads()
+    # lm_head: [B x hidden] f32 activations x the [vocab x hidden] Q8 matrix
+    V = w["vocab"]
+    q, s_ = O.q8_synth_weights(V, H, 0, 77, 0.02)
+    a = O.synth_fill(O.F32, 2, 0, 78, 0, B * H, 0.0, 1.0).reshape(B, H)
+    head = []
+    for i in range(warm + runs):
+        t0 = time.perf_counter()
+        O.q8_gemm_f32(a, O.F32, q, s_)
+        if i >= warm:
+            head.append(time.perf_counter() - t0)
+    del q, s_
+    steps = [w["layers"] * tl + th for tl, th in zip(layer, head)]
+    med = float(np.median(steps))
+    return {
+        "tokens_per_s": B / med, "step_s": med, "step_s_min": float(min(steps)), "step_s_max": float(max(steps)),
+        "cv": float(np.std(steps) / np.mean(steps)), "layer_s": float(np.median(layer)), "head_s": float(np.median(head)),
+        "sample_s": float(np.median(layer) + np.median(head)), "threads": O.threads(), "warm": warm, "runs": runs,
+        "sample": "oracle, %d threads: 1 of %d decoder layers (4 Q8 GEMMs + attention at context %d + norms) and the "
+                  "lm_head GEMM, batch %d, warm-up %d, median of %d runs (min %.3f s, max %.3f s, cv %.3f per "
+                  "extrapolated step); step = %d x layer + head" %
+                  (O.threads(), w["layers"], ctx, B, warm, runs, min(steps), max(steps),
+                   float(np.std(steps) / np.mean(steps)), w["layers"]),
+    }
 
 
 def run_reference(args, w, rank):
     """CPU arm: the oracle (a port: the reference holds no implementation of this path)."""
     if rank != 0:
         return
-    reps = max(1, args.steps)
-    for _ in range(max(0, min(args.warmup, 1))):
-        cpu_sample(w, w["ctx"], 1)
+    runs = max(1, min(args.steps, 10))
+    warm = max(0, min(args.warmup, 2))
     t0 = time.perf_counter()
-    tps, t_layer, threads = cpu_sample(w, w["ctx"], reps)
-    sample = "1 of %d decoder layers x 1 decode step at context %d, batch %d, per timed step; scaled by the layer " \
-             "count; lm_head (2%% of the weights) not in the sample" % (w["layers"], w["ctx"], w["batch"])
+    c = cpu_sample(w, w["ctx"], warm, runs)
+    tps = c["tokens_per_s"]
     line = {
         "impl": "reference", "metric": "Q8 decode tokens/s", "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": reps, "warmup": args.warmup, "ms_per_step": t_layer * w["layers"] * 1e3, "higher_is_better": True,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": c["step_s"] * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "int8 weights x f32 activations, f32 accumulate",
         "data": "synthetic", "config": {"workload": args.workload, "batch": w["batch"], "context": w["ctx"]},
-        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": c["threads"], "kind": "port", "sample": c["sample"]},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        # ms_per_step is the extrapolated time of a whole decode step; what ran per timed pass is the sample
+        "extrapolated": True, "sample_ms_per_run": c["sample_s"] * 1e3, "timed_runs": runs,
+        "step_ms_min": c["step_s_min"] * 1e3, "step_ms_max": c["step_s_max"] * 1e3, "cv": c["cv"],
         "wall_s": time.perf_counter() - t0,
     }
     print(json.dumps(line), flush=True)
@@ -309,8 +349,31 @@ def op_probe(args):
             e1.record(stream)
             stream.synchronize()
             times.append(e0.elapsed_time(e1) * 1e3)
+    sustained = None
+    if args.sustain > 0:
+        # back-to-back launches for `sustain` seconds with the clock sampler running: the figure a
+        # kernel reaches inside a long step under the power cap, and time x clock (SM cycles per
+        # launch), which separates "fewer cycles" from "a higher clock"
+        sampler = ClockSampler(dev)
+        sampler.start()
+        with torch.cuda.stream(stream):
+            n_launch, t_end = 0, time.perf_counter() + args.sustain
+            e0.record(stream)
+            while time.perf_counter() < t_end:
+                for _ in range(64):
+                    run(n_launch)
+                    n_launch += 1
+                stream.synchronize() if n_launch % 1024 == 0 else None
+            e1.record(stream)
+            stream.synchronize()
+        clk = sampler.stop()
+        us_s = e0.elapsed_time(e1) * 1e3 / n_launch
+        sustained = {"seconds": args.sustain, "launches": n_launch, "us_per_launch": us_s, "gbs": nbytes / us_s / 1e3,
+                     "frac": nbytes / us_s / 1e3 / peak, "clocks": clk,
+                     "sm_cycles_per_launch": us_s * clk["sm_mhz"] if clk.get("sm_mhz") else None}
     us = float(np.median(times))
     print(json.dumps({"op": args.op, "m": m, "n": n, "k": k, "us_median": us, "us_min": float(min(times)),
+                      "sustained": sustained,
                       "algorithmic_bytes": nbytes, "gbs": nbytes / us / 1e3, "frac": nbytes / us / 1e3 / peak,
                       "peak_kind": "of " + peak_kind, "status": llm.kernelStatus(dev),
                       "timing": "CUDA events around single launches (includes launch latency), %d rotating weight "
@@ -337,6 +400,8 @@ def main():
     ap.add_argument("--d", type=int, default=128)
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--copies", type=int, default=3)
+    ap.add_argument("--sustain", type=float, default=0.0,
+                    help="--op only: also run the operator back to back for this many seconds with clock sampling")
     args = ap.parse_args()
     if args.op != "decode":
         op_probe(args)
@@ -363,13 +428,17 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
+    uid_bytes = None
+
+    def make_uid():
+        """A fresh NCCL id for one tensor-parallel group, made by rank 0 and carried to the others."""
+        if world == 1:
+            return None
+        t = torch.zeros(128, dtype=torch.uint8, device="cuda")
         if rank == 0:
-            uid.copy_(torch.frombuffer(bytearray(llm.tpUniqueId()), dtype=torch.uint8))
-        dist.broadcast(uid, 0)
-        uid_bytes = bytes(uid.cpu().numpy().tobytes())
-    else:
-        uid_bytes = None
+            t.copy_(torch.frombuffer(bytearray(llm.tpUniqueId()), dtype=torch.uint8))
+        dist.broadcast(t, 0)
+        return bytes(t.cpu().numpy().tobytes())
 
     def barrier():
         torch.cuda.synchronize()
@@ -386,6 +455,46 @@ def main():
 
     ctx, B, K, W = w.pop("ctx"), w["batch"], args.steps, args.warmup
     act = {"f32": llm.F32, "f16": llm.F16, "bf16": llm.BF16}[args.act]
+
+    # ---- verify before timing (N > 1): the workload's architecture at depth 2 and a short
+    # context, sharded over the N ranks, must decode the tokens the unsharded model decodes on
+    # rank 0's GPU (that unsharded GPU path is what the parity tests hold to the CPU oracle)
+    tp_parity = None
+    if world > 1:
+        pcfg = dict(w, layers=2, l_max=32, rms_eps=1e-6, rope_theta=1e6, seed=4, init_std=0.02, act_dtype=act)
+        prng = np.random.default_rng(4)
+        prompt = prng.integers(0, w["vocab"], (B, 3)).astype(np.int32)
+        psteps = 8
+        shard = llm.Llm(nccl_unique_id=make_uid(), tp_degree=tp, tp_rank=rank, device=local_rank, **pcfg)
+        shard.prefill(prompt)
+        mine = shard.decodeSteps(psteps)
+        mode = {0: "none", 1: "nccl all-reduce", 2: "folded into residual+rmsnorm over peer memory"}[shard.tpExchange()]
+        shard.free()
+        allt = torch.zeros((world, psteps, B), dtype=torch.int32, device="cuda")
+        dist.all_gather_into_tensor(allt, torch.from_numpy(np.ascontiguousarray(mine)).cuda())
+        allt = allt.cpu().numpy()
+        same = bool((allt == allt[0]).all())
+        ok = same
+        if rank == 0:
+            whole = llm.Llm(tp_degree=1, tp_rank=0, device=local_rank, **pcfg)
+            whole.prefill(prompt)
+            want = whole.decodeSteps(psteps)
+            whole.free()
+            ok = same and bool(np.array_equal(allt[0], want))
+        tp_parity = {"ok": ok, "steps": psteps, "mode": mode, "ranks_identical": same,
+                     "model": "the workload's architecture at 2 layers, batch %d, 3-token prompts" % B,
+                     "reference": "the unsharded model decoded on rank 0's GPU"}
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device="cuda")
+        dist.broadcast(flag, 0)
+        if int(flag.item()) != 1:
+            if rank == 0:
+                print(json.dumps({"metric": "Q8 decode tokens/s", "value": None, "n_gpus": world, "tp_parity": tp_parity,
+                                  "error": "tensor-parallel tokens differ from the unsharded model: nothing was timed"}),
+                      flush=True)
+            dist.destroy_process_group()
+            raise SystemExit(1)
+
+    uid_bytes = make_uid()
     t_setup = time.perf_counter()
     model = llm.Llm(nccl_unique_id=uid_bytes, tp_degree=tp, tp_rank=rank, device=local_rank, act_dtype=act,
                     l_max=ctx + K + 8, rms_eps=1e-6, rope_theta=1e6, seed=0, init_std=0.02, **w)
@@ -436,6 +545,13 @@ def main():
     e2e = {"value": B * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(B * 4),
            "d2h_bytes_per_step": int(B * 4)}
 
+    # ---- tokens of 8 greedy steps from the fixed start state (seeded weights, seeded KV fill up
+    # to the context, seeded first tokens): one checksum that every N must reproduce
+    import zlib
+    rewind()
+    crc_tokens = model.decodeSteps(8)
+    tokens_crc = "%08x" % (zlib.crc32(np.ascontiguousarray(crc_tokens).tobytes()) & 0xFFFFFFFF)
+
     # ---- per-class device time of a step (events inside the library), mid-run context
     rewind()
     model.decodeSteps(max(1, K // 2), read_back=False)
@@ -473,7 +589,12 @@ def main():
         "kernels_ms_per_step": cls,
         "attention": {"achieved": attn_gbs, "unit": "GB/s", "frac": attn_gbs / peak, "context": mid_len},
         "clocks": clocks, "setup_s": setup_s, "launch_counts": llm.launchCounts(),
+        "tokens_crc": tokens_crc, "tp_parity": tp_parity,
     }
+    expect = EXPECTED_TOKENS_CRC.get((args.workload, args.act, args.prefill))
+    if expect is not None:
+        line["tokens_crc_expected"] = expect
+        line["tokens_crc_ok"] = tokens_crc == expect
 
     if rank == 0 and world == 1 and not args.no_extras:
         try:
@@ -482,11 +603,9 @@ def main():
             line["q8_gemv"]["frac_of_8000_nominal"] = line["q8_gemv"]["gbs"] / 8000.0
         except Exception as e:  # the probe is an extra; the headline stands without it
             line["q8_gemv"] = {"error": str(e)}
-        tps, t_layer, threads = cpu_sample(dict(w), ctx, 5)
-        line["cpu_baseline"] = {
-            "value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
-            "sample": "oracle on 1 of %d decoder layers x 1 decode step at context %d, batch %d, median of 5; scaled "
-                      "by the layer count; lm_head not in the sample" % (w["layers"], ctx, B)}
+        c = cpu_sample(dict(w), ctx, warm=1, runs=3)
+        line["cpu_baseline"] = {"value": c["tokens_per_s"], "unit": "tokens/s", "cores": c["threads"], "kind": "port",
+                                "sample": c["sample"]}
     model.free()
     if rank == 0:
         print(json.dumps(line), flush=True)

@@ -237,3 +237,36 @@ def test_decode_past_a_full_cache(llm, oracle, temperature):
     assert rel_l2(O.f16_to_f32(k), O.f16_to_f32(kr)) < 1e-3 and rel_l2(O.f16_to_f32(v), O.f16_to_f32(vr)) < 1e-3
     gpu.free()
     ref.close()
+
+
+def test_captured_step_survives_a_larger_stand_alone_call(llm, oracle):
+    """A model's captured decode step points only at memory the model owns: a stand-alone
+    attention call with a much larger shape (which makes the library's shared scratch grow)
+    between two decode calls must not disturb the replayed graph."""
+    O = oracle
+    t, steps = 6, 10
+    toks = O.synth_fill(O.I32, 3, SMALL["seed"], 999, 0, SMALL["batch"] * t, 0.0, float(SMALL["vocab"]))
+    toks = toks.reshape(SMALL["batch"], t)
+    ref = O.Llm(tp_degree=1, tp_rank=0, device=0, act_dtype=O.F32, **SMALL)
+    ref.prefill(toks)
+    want = np.array([ref.decode_step().copy() for _ in range(steps)])
+    gpu = llm.Llm(**SMALL)
+    gpu.prefill(toks)
+    got = [gpu.decodeSteps(3)]                       # eager first step, then the captured graph
+    for b, hq, hkv, d, lmax in ((8, 28, 4, 128, 1500), (16, 32, 8, 128, 2500)):   # each outgrows the last scratch
+        q = llm.DeviceBuffer(b * hq * d * 2)
+        cache = llm.DeviceBuffer(b * hkv * lmax * d * 2)
+        o = llm.DeviceBuffer(b * hq * d * 2)
+        seq = llm.DeviceBuffer.from_host(np.full(b, lmax - 1, np.int32))
+        q.memset(0)
+        cache.memset(0)
+        llm.gqaDecodeAttn(q, cache, cache, seq, o, b, hq, hkv, d, lmax, 0.1)
+        llm.devSync()
+        got.append(gpu.decodeSteps(3))               # the replayed graph, after the scratch moved
+        for x in (q, cache, o, seq):
+            x.free()
+    got.append(gpu.decodeSteps(steps - 9))
+    assert np.array_equal(np.concatenate(got), want)
+    assert llm.kernelStatus() == 0
+    gpu.free()
+    ref.close()

@@ -137,6 +137,25 @@ def test_q8_gemm_config1_slice(llm, oracle):
         assert rel_l2(c, ref) < TOL
 
 
+def test_q8_gemm_config1_full_size(llm, oracle):
+    """Config 1 as BASELINE.json states it: M=64 tokens x K=3584 x N=18944 (Qwen-7B FFN up-proj),
+    bf16 activations, bf16 output, compared with the oracle's bf16-rounded result and, before
+    the rounding hides it, with the oracle's f32 sums."""
+    O = oracle
+    m, n, k = 64, 18944, 3584
+    a, q, s = _gemm_inputs(O, m, n, k, seed=1)
+    c_bits = llm.q8GemmHost(a, q, s)
+    assert llm.kernelStatus() == 0
+    c = O.bf16_to_f32(c_bits)
+    ref_bits = O.q8_gemm(a, q, s)
+    ref = O.bf16_to_f32(ref_bits)
+    assert rel_l2(c, ref) < TOL
+    assert np.mean(c_bits != ref_bits) < 5e-3          # only last-place bf16 flips
+    assert rel_l2(c, O.q8_gemm_f32(a, O.BF16, q, s)) < 3e-3   # bf16 output rounding alone is ~1.7e-3
+    # every row tile and every token took part: no row or column of the output is left at zero
+    assert (np.abs(c).max(axis=0) > 0).all() and (np.abs(c).max(axis=1) > 0).all()
+
+
 def _attn_inputs(O, b, hq, hkv, d, lmax, lens, seed=0):
     kc = O.synth_fill(O.F16, 2, seed, 20, 0, b * hkv * lmax * d, 0.0, 1.0).reshape(b, hkv, lmax, d)
     vc = O.synth_fill(O.F16, 2, seed, 21, 0, b * hkv * lmax * d, 0.0, 1.0).reshape(b, hkv, lmax, d)
@@ -201,6 +220,30 @@ def test_gqa_decode_attn_fused_kv_bit_exact(llm, oracle, b, hq, hkv, d, lmax, le
     assert np.array_equal(dvc.download(np.uint16, vc.shape), vc)
     assert np.array_equal(dseq.download(np.int32, (b,)), seq)
     assert rel_l2(o, ref) < 1e-3
+
+
+def test_gqa_decode_attn_config2_full_size(llm, oracle):
+    """Config 2 as BASELINE.json states it: batch 32, 28 query / 4 KV heads, head_dim 128, 4096
+    cached positions, one token appended per sequence with RoPE theta 1e6: the KV cache after the
+    call is bit-equal to the oracle's, the lengths advance, the output is within tolerance."""
+    O = oracle
+    b, hq, hkv, d, ctx = 32, 28, 4, 128, 4096
+    lmax = ctx + 1
+    q, kn, vn, kc, vc, seq = _attn_inputs(O, b, hq, hkv, d, lmax, [ctx] * b, seed=5)
+    tab = O.rope_table(lmax, d, 1e6)
+    scale = 1.0 / np.sqrt(d)
+    dq, dkn, dvn, dkc, dvc, dtab, dseq = (_dev(llm, x) for x in (q, kn, vn, kc, vc, tab, seq))
+    do = llm.DeviceBuffer(b * hq * d * 2)
+    llm.gqaDecodeAttnFused(dq, dkn, dvn, dkc, dvc, dtab, dseq, do, b, hq, hkv, d, lmax, scale)
+    o = O.f16_to_f32(do.download(np.uint16, (b, hq, d)))
+    ref = O.f16_to_f32(O.gqa_decode_attn_fused(q, kn, vn, kc, vc, tab, seq, scale))   # appends to kc, vc, seq in place
+    assert llm.kernelStatus() == 0
+    assert np.array_equal(dkc.download(np.uint16, kc.shape), kc)
+    assert np.array_equal(dvc.download(np.uint16, vc.shape), vc)
+    assert np.array_equal(dseq.download(np.int32, (b,)), seq) and (seq == ctx + 1).all()
+    assert rel_l2(o, ref) < 1e-3
+    for x in (dq, dkn, dvn, dkc, dvc, dtab, dseq, do):
+        x.free()
 
 
 def test_gqa_golden(llm, oracle, golden):
