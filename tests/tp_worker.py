@@ -1,7 +1,9 @@
 """One tensor-parallel rank as its own process (used by test_gpu_tp.py and test_gpu_config4.py):
-    python tests/tp_worker.py RANK WORLD OUT_DIR STEPS PROMPT_LEN [WEIGHT_FILE | cfg=NAME]
+    python tests/tp_worker.py RANK WORLD OUT_DIR STEPS PROMPT_LEN [cfg=NAME] [force=NPZ] [WEIGHT_FILE]
 With WEIGHT_FILE the model is created from another seed and every rank loads its shard of the file;
-cfg=NAME picks one of CONFIGS (default "toy").
+cfg=NAME picks one of CONFIGS (default "toy"); force=NPZ names a file whose array "inputs" [STEPS][B]
+holds the token every step consumes (teacher forcing: a near-tie that flips one argmax then does
+not change what the later steps are compared on).
 Rank 0 makes the NCCL id and publishes it in OUT_DIR; every rank writes its tokens, its
 first layer's KV cache and the last logits to OUT_DIR/rRANK.npz."""
 import faulthandler
@@ -39,8 +41,13 @@ def prompt_tokens(cfg, t):
 def main():
     global CFG
     rank, world, out_dir, steps, t = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], int(sys.argv[4]), int(sys.argv[5])
-    if len(sys.argv) > 6 and sys.argv[6].startswith("cfg="):
-        CFG = CONFIGS[sys.argv.pop(6)[4:]]
+    forced = None
+    while len(sys.argv) > 6 and "=" in sys.argv[6]:
+        key, val = sys.argv.pop(6).split("=", 1)
+        if key == "cfg":
+            CFG = CONFIGS[val]
+        elif key == "force":
+            forced = np.load(val)["inputs"]
     id_path = os.path.join(out_dir, "nccl_id.bin")
     if rank == 0:
         with open(id_path + ".tmp", "wb") as f:
@@ -60,7 +67,13 @@ def main():
     if weight_file:
         m.loadWeights(weight_file)
     m.prefill(toks)
-    got = m.decodeSteps(steps)
+    if forced is None:
+        got = m.decodeSteps(steps)
+    else:
+        got = np.zeros((steps, CFG["batch"]), np.int32)
+        for i in range(steps):
+            m.setTokens(forced[i])
+            got[i] = m.decodeStep()
     k, v = m.readKv(0)
     np.savez(os.path.join(out_dir, "r%d.npz" % rank), tokens=got, k=k, v=v, logits=m.readLogits(), exchange=m.tpExchange(),
              status=llm.kernelStatus(rank))
