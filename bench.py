@@ -516,7 +516,7 @@ def main():
     uid_bytes = make_uid()
     t_setup = time.perf_counter()
     model = llm.Llm(nccl_unique_id=uid_bytes, tp_degree=tp, tp_rank=rank, device=local_rank, act_dtype=act,
-                    l_max=ctx + K + 8, rms_eps=1e-6, rope_theta=1e6, seed=0, init_std=0.02, **w)
+                    l_max=ctx + max(K, 512) + 8, rms_eps=1e-6, rope_theta=1e6, seed=0, init_std=0.02, **w)
     tok_pinned = torch.empty(B, dtype=torch.int32).pin_memory()
     out_pinned = torch.empty(B, dtype=torch.int32).pin_memory()
     rng = np.random.default_rng(0)
@@ -580,12 +580,14 @@ def main():
     tokens_check = None
     if args.write_token_golden and rank == 0 and world == 1 and args.prefill == "synthetic-kv":
         with open(args.write_token_golden, "w") as f:
-            json.dump({"workload": args.workload, "context": ctx, "steps": 8, "inputs": "numpy default_rng(7) ids per step",
+            json.dump({"workload": args.workload, "context": ctx, "l_max": ctx + max(K, 512) + 8, "steps": 8, "inputs": "numpy default_rng(7) ids per step",
                        "made_by": "python bench.py --write-token-golden PATH (N = 1, B200)", "tokens": chk.tolist()}, f)
     if os.path.exists(gfile) and args.prefill == "synthetic-kv":
         with open(gfile) as f:
-            want = np.array(json.load(f)["tokens"], np.int32)
-        if want.shape == chk.shape:
+            gold = json.load(f)
+        want = np.array(gold["tokens"], np.int32)
+        # the seeded KV fill is indexed by position in the [B][Hkv][l_max][D] cache, so the list holds for one l_max
+        if want.shape == chk.shape and gold.get("l_max") == ctx + max(K, 512) + 8:
             agree = int((want == chk).sum())
             # decisions are independent (inputs are fixed), so an f32 re-association can flip a
             # near-tie here and there; a wrong exchange or shard would agree nowhere

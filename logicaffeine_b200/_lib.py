@@ -9,7 +9,8 @@ import os
 import re
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "liblogos_b200.so")
+# LOGOS_B200_LIBRARY names another build of the same library (same header), e.g. one compiled with other flags
+LIB_PATH = os.environ.get("LOGOS_B200_LIBRARY") or os.path.join(_HERE, "liblogos_b200.so")
 HEADER_PATH = os.path.join(_HERE, "..", "include", "logos_b200.h")
 
 # LogosStatus (crates/logicaffeine_compile/src/codegen/ffi.rs:196-209)

@@ -58,13 +58,23 @@ __global__ void swiglu_f32_kernel(const float* __restrict__ gate, const float* _
 }
 
 __global__ void embed_kernel(const int32_t* __restrict__ tokens, const int8_t* __restrict__ q,
-                             const float* __restrict__ s, float* __restrict__ h, int64_t hidden) {
+                             const float* __restrict__ s, float* __restrict__ h, int64_t hidden, int tiled) {
   pdl_wait();
   pdl_trigger();
   int64_t row = blockIdx.x;
   int64_t t = __ldcg(tokens + row);
-  const int8_t* qr = q + t * hidden;
+  if (tiled) {
+    // element (t, e) of the tile-major form: tile (t / 128, e / 128), row t % 128, byte e % 128;
+    // its scale: the same tile's [128 rows][4] block, row t % 128, entry (e % 128) / 32
+    const int64_t tile0 = ((t >> 7) * (hidden >> 7) * 128 + (t & 127));
+    const int8_t* base = q + tile0 * 128;
+    const float* sbase = s + tile0 * 4;
+    for (int64_t e = threadIdx.x; e < hidden; e += blockDim.x)
+      h[row * hidden + e] = __fmul_rn(sbase[(e >> 7) * 512 + ((e & 127) >> 5)], (float)base[(e >> 7) * 16384 + (e & 127)]);
+    return;
+  }
   const float* sr = s + t * (hidden / 32);
+  const int8_t* qr = q + t * hidden;
   for (int64_t e = threadIdx.x; e < hidden; e += blockDim.x)
     h[row * hidden + e] = __fmul_rn(sr[e >> 5], (float)qr[e]);
 }
@@ -418,9 +428,9 @@ logos_status_t launch_swiglu_f32(const float* gate, const float* up, float* y, i
 }
 
 logos_status_t launch_embed(const int32_t* tokens, const int8_t* q, const float* s, float* h, int64_t rows,
-                            int64_t hidden, cudaStream_t st) {
+                            int64_t hidden, int tiled, cudaStream_t st) {
   if (rows == 0) return LOGOS_OK;
-  LOGOS_CUDA_TRY(launch_kernel(embed_kernel, dim3((unsigned)rows), dim3(256), 0, st, tokens, q, s, h, hidden));
+  LOGOS_CUDA_TRY(launch_kernel(embed_kernel, dim3((unsigned)rows), dim3(256), 0, st, tokens, q, s, h, hidden, tiled));
   count_launch(LK_ELEMWISE);
   return check_launch("embed_kernel");
 }

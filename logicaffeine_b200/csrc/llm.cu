@@ -28,16 +28,21 @@
 #include <string.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <vector>
 
 namespace logos {
 
 namespace {
 
+// int8 [n][k] + f32 [n][k/32].  q is allocated for ceil128(n) rows and is either row-major (as
+// generated, loaded and saved) or tile-major (as the GEMM streams it, see launch_q8_retile);
+// matrices whose K is not a multiple of 128 stay row-major (the SIMT kernel takes them).
 struct Q8Mat {
   int8_t* q = nullptr;
   float*  s = nullptr;
   int64_t n = 0, k = 0;
+  bool tiled = false;
 };
 
 struct Layer {
@@ -134,8 +139,8 @@ logos_status_t dmalloc(Model* m, void** p, int64_t bytes) {
 logos_status_t alloc_mat(Model* m, Q8Mat* w, int64_t n, int64_t k) {
   w->n = n;
   w->k = k;
-  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&w->q), n * k));
-  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&w->s), n * (k / 32) * (int64_t)sizeof(float)));
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&w->q), ((n + 127) / 128 * 128) * k));
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&w->s), ((n + 127) / 128 * 128) * (k / 32) * (int64_t)sizeof(float)));
   return LOGOS_OK;
 }
 
@@ -154,6 +159,52 @@ void destroy(Model* m) {
   if (m->ev1) cudaEventDestroy(m->ev1);
   if (m->stream) cudaStreamDestroy(m->stream);
   delete m;
+}
+
+bool tiling_enabled() {
+  const char* e = getenv("LOGOS_B200_TILED_WEIGHTS");
+  return !(e && e[0] == '0');
+}
+
+// Every GEMM weight of the model into the tile-major layout (or back to row-major, which is what
+// the generator, the weight-file loader and the writer address).  One pass per matrix through a
+// scratch buffer of the largest matrix's size, allocated for the call.
+logos_status_t set_layout(Model* m, bool tiled) {
+  if (tiled && !tiling_enabled()) return LOGOS_OK;
+  std::vector<Q8Mat*> mats;
+  for (Layer& L : m->layers) {
+    mats.push_back(&L.wqkv); mats.push_back(&L.wo); mats.push_back(&L.wgu); mats.push_back(&L.wd);
+  }
+  mats.push_back(&m->embed);
+  if (!m->cfg.tied_embeddings) mats.push_back(&m->head);
+  int64_t biggest = 0;
+  for (Q8Mat* w : mats)
+    if (w->k % 128 == 0 && w->tiled != tiled) biggest = std::max(biggest, ((w->n + 127) / 128 * 128) * w->k);
+  if (biggest == 0) return LOGOS_OK;
+  int8_t* tmp = nullptr;
+  LOGOS_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&tmp), (size_t)biggest));
+  logos_status_t rc = LOGOS_OK;
+  for (Q8Mat* w : mats) {
+    if (w->k % 128 || w->tiled == tiled) continue;
+    const int64_t bytes = (tiled ? (w->n + 127) / 128 * 128 : w->n) * w->k;
+    rc = launch_q8_retile(w->q, tmp, w->n, w->k, tiled, m->device, m->stream);
+    if (rc != LOGOS_OK) break;
+    if (cudaMemcpyAsync(w->q, tmp, (size_t)bytes, cudaMemcpyDeviceToDevice, m->stream) != cudaSuccess) {
+      rc = fail(LOGOS_ERROR, "set_layout: device copy failed");
+      break;
+    }
+    rc = launch_q8_retile_scales(w->s, reinterpret_cast<float*>(tmp), w->n, w->k, tiled, m->device, m->stream);
+    if (rc != LOGOS_OK) break;
+    if (cudaMemcpyAsync(w->s, tmp, (size_t)(bytes / 8), cudaMemcpyDeviceToDevice, m->stream) != cudaSuccess) {
+      rc = fail(LOGOS_ERROR, "set_layout: device copy failed");
+      break;
+    }
+    w->tiled = tiled;
+  }
+  cudaStreamSynchronize(m->stream);
+  cudaFree(tmp);
+  if (m->cfg.tied_embeddings) m->head = m->embed;
+  return rc;
 }
 
 logos_status_t gen(Model* m, Q8Mat* w, int64_t n, int64_t row0, int64_t col0, int64_t k_total, int64_t mul, int64_t add,
@@ -303,7 +354,7 @@ logos_status_t build(Model* m, const void* nccl_id) {
   LOGOS_CUDA_TRY(cudaMemsetAsync(m->seq_len, 0, (size_t)B * 4, m->stream));
   LOGOS_CUDA_TRY(cudaMemsetAsync(m->logits, 0, (size_t)(B * c.vocab) * 4, m->stream));
   LOGOS_CUDA_TRY(cudaStreamSynchronize(m->stream));
-  return LOGOS_OK;
+  return set_layout(m, true);
 }
 
 __global__ void sum_partials_kernel(float* __restrict__ p, int parts, int64_t stride, int64_t count) {
@@ -363,7 +414,7 @@ logos_status_t gemm_partials(Model* m, const ActOut& a, const Q8Mat& w, int* spl
   const int64_t B = m->cfg.batch;
   GemmArgs g;
   g.a = a.hi; g.a_lo = a.lo; g.a_dtype = LOGOS_F16; g.lda = w.k;
-  g.q = w.q; g.s = w.s;
+  g.q = w.q; g.s = w.s; g.q_tiled = w.tiled;
   g.m = B; g.n = w.n; g.k = w.k;
   g.device = m->device;
   int splits = gemm_pick_splits(B, w.n, w.k, m->device);
@@ -441,7 +492,7 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
   PdlScope pdl(pdl_enabled());
   {
     ProfScope ps(m, PROF_ELEMWISE);
-    LOGOS_TRY(launch_embed(tokens_in, m->embed.q, m->embed.s, m->h, B, H, st));
+    LOGOS_TRY(launch_embed(tokens_in, m->embed.q, m->embed.s, m->h, B, H, m->embed.tiled ? 1 : 0, st));
   }
   m->launch_counter += 1;
   int parts = 0;
@@ -453,7 +504,7 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
     {
       GemmArgs g;
       g.a = m->xn.hi; g.a_lo = m->xn.lo; g.a_dtype = LOGOS_F16; g.lda = H;
-      g.q = L.wqkv.q; g.s = L.wqkv.s;
+      g.q = L.wqkv.q; g.s = L.wqkv.s; g.q_tiled = L.wqkv.tiled;
       g.c = m->qkv; g.c_dtype = LOGOS_F32; g.ldc = m->nqkv;
       g.m = B; g.n = m->nqkv; g.k = H;
       g.device = m->device;
@@ -488,7 +539,7 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
     {
       GemmArgs g;
       g.a = m->xn.hi; g.a_lo = m->xn.lo; g.a_dtype = LOGOS_F16; g.lda = H;
-      g.q = L.wgu.q; g.s = L.wgu.s;
+      g.q = L.wgu.q; g.s = L.wgu.s; g.q_tiled = L.wgu.tiled;
       g.c_dtype = LOGOS_ACT_PLANES; g.c_act = m->ffn; g.ldc = m->f_local;
       g.m = B; g.n = 2 * m->f_local; g.k = H;
       g.epilogue = EPI_SWIGLU;
@@ -503,7 +554,7 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
     LOGOS_TRY(norm_step(m, parts, 2 * c.layers));
     GemmArgs g;
     g.a = m->xn.hi; g.a_lo = m->xn.lo; g.a_dtype = LOGOS_F16; g.lda = H;
-    g.q = m->head.q; g.s = m->head.s;
+    g.q = m->head.q; g.s = m->head.s; g.q_tiled = m->head.tiled;
     g.c = m->logits; g.c_dtype = LOGOS_F32; g.ldc = c.vocab;
     g.m = B; g.n = c.vocab; g.k = H;
     g.device = m->device;
@@ -1060,9 +1111,13 @@ logos_status_t logos_llm_load_weights(logos_handle_t model, const char* path) {
     if (!path) return fail(LOGOS_NULL_POINTER, "logos_llm_load_weights: path is null");
     MappedWeights w;
     LOGOS_TRY(weights_open(path, &w, "logos_llm_load_weights"));
-    logos_status_t s = load_weights(m, w);
+    logos_status_t s = set_layout(m, false);   // the loader addresses rows
+    if (s == LOGOS_OK) s = load_weights(m, w);
     weights_close(&w);
-    return s;
+    std::string keep = s != LOGOS_OK && last_error_text() ? last_error_text() : "";
+    logos_status_t t = set_layout(m, true);
+    if (s != LOGOS_OK) set_last_error(keep);
+    return s != LOGOS_OK ? s : t;
   });
 }
 
@@ -1075,8 +1130,13 @@ logos_status_t logos_llm_save_weights(logos_handle_t model, const char* path) {
                   m->cfg.tp_degree);
     int fd = open(path, O_WRONLY | O_CREAT | O_TRUNC, 0644);
     if (fd < 0) return fail(LOGOS_ERROR, "logos_llm_save_weights: cannot create '%s': %s", path, strerror(errno));
-    logos_status_t s = save_weights(m, fd);
+    logos_status_t s = set_layout(m, false);   // the writer addresses rows
+    if (s == LOGOS_OK) s = save_weights(m, fd);
     std::string keep = s != LOGOS_OK && last_error_text() ? last_error_text() : "";
+    {
+      logos_status_t t = set_layout(m, true);
+      if (s == LOGOS_OK && t != LOGOS_OK) { s = t; keep = last_error_text() ? last_error_text() : ""; }
+    }
     if (close(fd) != 0 && s == LOGOS_OK) s = fail(LOGOS_ERROR, "logos_llm_save_weights: close failed: %s", strerror(errno));
     else if (s != LOGOS_OK) set_last_error(keep);
     return s;

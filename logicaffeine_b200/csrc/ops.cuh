@@ -17,6 +17,14 @@ logos_status_t launch_q8_quantize(bool generate, const float* w, int8_t* q, floa
                                   int64_t out_row_add, uint64_t seed, uint64_t stream, float std, int device,
                                   cudaStream_t st);
 
+// int8 [n][k] row-major <-> tile-major (128 x 128 tiles of 16 contiguous KB, ordered (row tile, K tile),
+// ceil128(n) rows; K a multiple of 128): the layout a model keeps its GEMM weights in.  in != out.
+logos_status_t launch_q8_retile(const int8_t* in, int8_t* out, int64_t n, int64_t k, bool to_tiled, int device,
+                                cudaStream_t st);
+// and their scales: f32 [n][k/32] row-major <-> [row tile][K tile][128 rows][4 scales]
+logos_status_t launch_q8_retile_scales(const float* in, float* out, int64_t n, int64_t k, bool to_tiled, int device,
+                                       cudaStream_t st);
+
 logos_status_t launch_synth_kv(__half* cache, uint64_t seed, uint64_t stream, int64_t b, int64_t hkv_local, int64_t h0,
                                int64_t hkv_total, int64_t l_max, int64_t d, int64_t t, int device, cudaStream_t st);
 
@@ -36,7 +44,8 @@ struct GemmArgs {
   const __half* a_lo = nullptr;  // second fp16 plane (see act.cuh); only with a_dtype LOGOS_F16
   int           a_dtype = LOGOS_BF16;  // LOGOS_F16 plane(s), LOGOS_BF16 or LOGOS_F32
   int64_t       lda = 0;
-  const int8_t* q = nullptr;   // [N][K]
+  const int8_t* q = nullptr;   // [N][K] row-major, or tile-major when q_tiled (launch_q8_retile)
+  int           q_tiled = 0;   // tcgen05 kernel only; s is then tile-major too (launch_q8_retile_scales)
   const float*  s = nullptr;   // [N][K/32]
   void*         c = nullptr;   // [M][N] (or [M][N/2] for EPI_SWIGLU), row stride ldc elements
   int           c_dtype = LOGOS_BF16;  // LOGOS_BF16, LOGOS_F16, LOGOS_F32 or LOGOS_ACT_PLANES
@@ -115,8 +124,9 @@ logos_status_t launch_rmsnorm_f32(const float* x, const float* g, float* y, int6
                                   cudaStream_t st);
 logos_status_t launch_swiglu_f32(const float* gate, const float* up, float* y, int64_t count, cudaStream_t st);
 // h[row] = dequantised embedding row tokens[row]
+// (q tile-major when `tiled`: see launch_q8_retile)
 logos_status_t launch_embed(const int32_t* tokens, const int8_t* q, const float* s, float* h, int64_t rows,
-                            int64_t hidden, cudaStream_t st);
+                            int64_t hidden, int tiled, cudaStream_t st);
 // h += sum over `parts` partial deltas (each [rows][hidden] f32, spaced
 // part_stride floats, added in ascending order; parts may be 0), then
 // xn = act16( h * rsqrt(mean(h^2)+eps) * g ).

@@ -156,6 +156,7 @@ logos_status_t launch_q8_gemm(const GemmArgs& g, cudaStream_t st) {
   if (g.splits > 1 && (!g.partials || g.epilogue != EPI_NONE))
     return fail(LOGOS_ERROR, "q8_gemm: split-K writes raw partials; the caller reduces them");
   if (!g.force_simt && gemm_tc_applicable(g)) return launch_q8_gemm_tc(g, st);
+  if (g.q_tiled) return fail(LOGOS_ERROR, "q8_gemm: tile-major weights need the tensor-core kernel, which does not take this call");
   dim3 grid((unsigned)((g.n + SIMT_TN - 1) / SIMT_TN), (unsigned)((g.m + SIMT_TM - 1) / SIMT_TM),
             (unsigned)(g.splits > 1 ? g.splits : 1));
   q8_gemm_simt_kernel<<<grid, 256, 0, st>>>(g.a, g.a_lo, g.a_dtype, g.lda, g.q, g.s, g.c, g.c_dtype, g.c_act, g.ldc,

@@ -97,6 +97,7 @@ struct TcParams {
   int stages_total;
   int items;        // work items: row tiles x splits
   int store_mode;
+  int tiled;        // weights are tile-major: the map is [row tiles x K tiles x 128][128 B]
   int* status;
 #ifdef LOGOS_TC_TRACE
   long long* trace;  // SM-clock timestamps of CTA (0,0,0), first item, [stage][16]
@@ -280,12 +281,18 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           if (!mbar_wait(&raw_empty[st], ph ^ 1u)) { ok = false; tc_report(p.status, 2010, i, nst); break; }
           TC_TRACE(i, 0);
           mbar_arrive_expect_tx(&raw_full[st], RAW_BYTES);
-          tma_load_2d_hint(raw + st * RAW_BYTES, &map_q, &raw_full[st], (st_begin + i) * TC_KSTAGE, n0, pol);
+          // row-major weights: tile (n0, stage) of a [N][K] map; tile-major: 128 rows of 128 bytes at
+          // row ((tile * stages + stage) * 128) of a [tiles * stages * 128][128 B] map
+          const int tbase = it.tile * p.stages_total + st_begin;
+          if (p.tiled) tma_load_2d_hint(raw + st * RAW_BYTES, &map_q, &raw_full[st], 0, (tbase + i) * TC_ROWS, pol);
+          else tma_load_2d_hint(raw + st * RAW_BYTES, &map_q, &raw_full[st], (st_begin + i) * TC_KSTAGE, n0, pol);
           if (i + 1 >= RAW_STAGES) {
             // after the first fill: stages RAW_STAGES .. RAW_PREFETCH in one go, then one per stage
             const int first = (i + 1 == RAW_STAGES) ? RAW_STAGES : i + RAW_PREFETCH;
-            for (int j = first; j <= i + RAW_PREFETCH && j < nst; ++j)
-              tma_prefetch_l2_2d(&map_q, (st_begin + j) * TC_KSTAGE, n0);
+            for (int j = first; j <= i + RAW_PREFETCH && j < nst; ++j) {
+              if (p.tiled) tma_prefetch_l2_2d(&map_q, 0, (tbase + j) * TC_ROWS);
+              else tma_prefetch_l2_2d(&map_q, (st_begin + j) * TC_KSTAGE, n0);
+            }
           }
         }
       }
@@ -450,24 +457,37 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       TC_TRACE_ITEM(w);
       const int64_t n = n0 + nl;
       const bool n_ok = n < p.n;
-      const float* srow = p.s + (n_ok ? n : 0) * kb_per_row;
       uint64_t acc2[HC / 2];  // packed f32 pairs: the drain arithmetic uses two-wide f32 FMAs
 #pragma unroll
       for (int j = 0; j < HC / 2; ++j) acc2[j] = 0ull;
-      // The four scales of a stage are one 16-byte load per row.  Their latency (L2, or HBM
-      // once per 128-byte line, i.e. every eight stages) must not sit between the TMEM load and
-      // the arithmetic: registers hold the scales two stages ahead, and the line after next
-      // is prefetched into L2.
+      // The four scales of a stage are one 16-byte load per row.  Their latency (L2, or HBM)
+      // must not sit between the TMEM load and the arithmetic: registers hold the scales two
+      // stages ahead, and a line further on is prefetched into L2.  Row-major scales: stage i of
+      // row n is float4 i of the row (a 128-byte line serves eight stages).  Tile-major: the 128
+      // rows' scales of a stage are 2 contiguous KB, consecutive stages follow each other.
       const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-      const float4* sc_src = reinterpret_cast<const float4*>(srow) + st_begin;
-      float4 sc_a = (n_ok && 0 < nst) ? __ldg(sc_src) : zero4;
-      float4 sc_b = (n_ok && 1 < nst) ? __ldg(sc_src + 1) : zero4;
-      if (n_ok && 8 < nst) prefetch_l2(sc_src + 8);
+      const float4* sc_src;
+      int64_t sc_step;       // float4 between consecutive stages
+      int pf_mask, pf_ahead;   // L2 prefetch: at stages with (i & pf_mask) == 0, that many stages ahead
+      if (p.tiled) {
+        sc_src = reinterpret_cast<const float4*>(p.s) + ((int64_t)it.tile * p.stages_total + st_begin) * TC_ROWS + nl;
+        sc_step = TC_ROWS;
+        pf_mask = 0; pf_ahead = 8;    // this thread's 16 bytes of the stage: the warp's lanes cover 512 bytes
+      } else {
+        sc_src = reinterpret_cast<const float4*>(p.s + (n_ok ? n : 0) * kb_per_row) + st_begin;
+        sc_step = 1;
+        pf_mask = 7; pf_ahead = 16;
+      }
+      const bool s_ok = n_ok || p.tiled;   // tile-major scales are padded to whole tiles (zeros)
+      float4 sc_a = (s_ok && 0 < nst) ? __ldg(sc_src) : zero4;
+      float4 sc_b = (s_ok && 1 < nst) ? __ldg(sc_src + sc_step) : zero4;
+      if (s_ok && 8 < nst) prefetch_l2(sc_src + 8 * sc_step);
       for (int i = 0; i < nst && ok; ++i, ++gs) {
         const float4 sc4 = sc_a;
         sc_a = sc_b;
-        sc_b = (n_ok && i + 2 < nst) ? __ldg(sc_src + i + 2) : zero4;
-        if (n_ok && (i & 7) == 0 && i + 16 < nst) prefetch_l2(sc_src + i + 16);
+        sc_b = (s_ok && i + 2 < nst) ? __ldg(sc_src + (i + 2) * sc_step) : zero4;
+        if (s_ok && (i & pf_mask) == 0 && i + pf_ahead < nst && (!p.tiled || (lane & 7) == 0))
+          prefetch_l2(sc_src + (i + pf_ahead) * sc_step);
         const float scs[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
         const uint32_t fph = (uint32_t)gs & 1u;
 #pragma unroll
@@ -667,7 +687,12 @@ template <int MT, int LIMBS>
 logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
   using Cfg = TcCfg<MT, LIMBS>;
   CUtensorMap mq, mhi, mlo, mo0, mo1;
-  LOGOS_TRY(cached_map(&mq, g.q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)g.k, (uint64_t)g.n, (uint64_t)g.k, TC_KSTAGE, TC_ROWS));
+  if (g.q_tiled) {
+    const uint64_t rows = (uint64_t)((g.n + TC_ROWS - 1) / TC_ROWS) * (uint64_t)(g.k / TC_KSTAGE) * TC_ROWS;
+    LOGOS_TRY(cached_map(&mq, g.q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, TC_KSTAGE, rows, TC_KSTAGE, TC_KSTAGE, TC_ROWS));
+  } else {
+    LOGOS_TRY(cached_map(&mq, g.q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)g.k, (uint64_t)g.n, (uint64_t)g.k, TC_KSTAGE, TC_ROWS));
+  }
   LOGOS_TRY(cached_map(&mhi, g.a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)g.k, (uint64_t)g.m, (uint64_t)g.lda * 2, 64, MT));
   if (LIMBS == 2)
     LOGOS_TRY(cached_map(&mlo, g.a_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)g.k, (uint64_t)g.m, (uint64_t)g.lda * 2, 64, MT));
@@ -677,6 +702,7 @@ logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
   p.s = g.s; p.n = g.n; p.k = g.k; p.m = g.m;
   p.c = g.c; p.c_dtype = g.c_dtype; p.c_act = g.c_act; p.ldc = g.ldc; p.aux = g.aux; p.epilogue = g.epilogue;
   p.partials = g.partials;
+  p.tiled = g.q_tiled;
   p.splits = g.splits > 1 ? g.splits : 1;
   p.stages_total = (int)(g.k / TC_KSTAGE);
   const int64_t tiles = (g.n + TC_ROWS - 1) / TC_ROWS;

@@ -98,6 +98,72 @@ __global__ void q8_quantize_kernel(const float* __restrict__ w, int8_t* __restri
   }
 }
 
+// Row-major int8 [n][k] <-> the tile-major layout the tcgen05 GEMM streams: tiles of 128 rows x
+// 128 columns, each 16 KB contiguous, ordered (row tile, K tile), so that the stages a CTA reads
+// one after the other form one contiguous run in HBM instead of 128 lines a row pitch apart.
+// Rows n .. ceil128(n) of the tiled form are zero.  One thread moves 16 bytes.
+__global__ void q8_retile_kernel(const int8_t* __restrict__ in, int8_t* __restrict__ out, int64_t n, int64_t k,
+                                 int to_tiled) {
+  const int64_t ktiles = k >> 7, rtiles = (n + 127) >> 7;
+  const int64_t total = rtiles * ktiles * 128 * 8;  // 16-byte chunks of the tiled form
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t c16 = i & 7, r = (i >> 3) & 127, ts = i >> 10;
+    const int64_t t = ts / ktiles, st = ts - t * ktiles;
+    const int64_t row = t * 128 + r;
+    const int64_t rm = row * k + st * 128 + c16 * 16;   // offset in the row-major form
+    if (to_tiled) {
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (row < n) v = *reinterpret_cast<const uint4*>(in + rm);
+      *reinterpret_cast<uint4*>(out + i * 16) = v;
+    } else if (row < n) {
+      *reinterpret_cast<uint4*>(out + rm) = *reinterpret_cast<const uint4*>(in + i * 16);
+    }
+  }
+}
+
+// The scales of the same tiles: f32 [n][k/32] row-major <-> [row tile][K tile][128 rows][4], so the
+// 128 rows' scales of one GEMM stage are 2 contiguous KB.  One thread moves one row's four scales.
+__global__ void q8_retile_scales_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t n, int64_t k,
+                                        int to_tiled) {
+  const int64_t ktiles = k >> 7, rtiles = (n + 127) >> 7, kb_per_row = k >> 5;
+  const int64_t total = rtiles * ktiles * 128;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i & 127, ts = i >> 7;
+    const int64_t t = ts / ktiles, st = ts - t * ktiles;
+    const int64_t row = t * 128 + r;
+    const int64_t rm = row * kb_per_row + st * 4;
+    if (to_tiled) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (row < n) v = *reinterpret_cast<const float4*>(in + rm);
+      *reinterpret_cast<float4*>(out + i * 4) = v;
+    } else if (row < n) {
+      *reinterpret_cast<float4*>(out + rm) = *reinterpret_cast<const float4*>(in + i * 4);
+    }
+  }
+}
+
+logos_status_t launch_q8_retile_scales(const float* in, float* out, int64_t n, int64_t k, bool to_tiled, int device,
+                                       cudaStream_t st) {
+  if (n == 0 || k == 0) return LOGOS_OK;
+  if (k % 128) return fail(LOGOS_ERROR, "q8_retile: K=%lld is not a multiple of 128", (long long)k);
+  const int64_t total = ((n + 127) / 128) * (k / 128) * 128;
+  const int64_t want = (total + 255) / 256, cap = (int64_t)sm_count(device) * 32;
+  q8_retile_scales_kernel<<<(int)(want < cap ? want : cap), 256, 0, st>>>(in, out, n, k, to_tiled ? 1 : 0);
+  count_launch(LK_SYNTH);
+  return check_launch("q8_retile_scales_kernel");
+}
+
+logos_status_t launch_q8_retile(const int8_t* in, int8_t* out, int64_t n, int64_t k, bool to_tiled, int device,
+                                cudaStream_t st) {
+  if (n == 0 || k == 0) return LOGOS_OK;
+  if (k % 128) return fail(LOGOS_ERROR, "q8_retile: K=%lld is not a multiple of 128", (long long)k);
+  const int64_t total = ((n + 127) / 128) * (k / 128) * 1024;
+  const int64_t want = (total + 255) / 256, cap = (int64_t)sm_count(device) * 32;
+  q8_retile_kernel<<<(int)(want < cap ? want : cap), 256, 0, st>>>(in, out, n, k, to_tiled ? 1 : 0);
+  count_launch(LK_SYNTH);
+  return check_launch("q8_retile_kernel");
+}
+
 logos_status_t launch_synth_fill(void* dst, int dtype, int kind, uint64_t seed, uint64_t stream, int64_t first,
                                  int64_t count, float a, float b, int device, cudaStream_t st) {
   if (count == 0) return LOGOS_OK;
