@@ -232,11 +232,16 @@ LOGOS_API logos_status_t logos_gqa_decode_attn(logos_handle_t q, logos_handle_t 
  * call an operator: a serving process that hands the whole GPU to its own KV-cache and
  * weight arena at start-up (a later cudaMalloc from inside the library would fail or
  * fragment that arena), or a decode loop with a latency budget that an allocation's
- * device-wide synchronisation would break.  The split-KV partial results go to a fixed
- * 16 MiB array inside the library image instead of library-allocated scratch, so every GPU
- * that loads the library holds those 16 MiB until the process exits.  A shape whose
- * partials need more (b * h_q * ceil(l_max / unit) * (d + 2) * 4 bytes) is refused with
- * LOGOS_OUT_OF_BOUNDS and a message giving both sizes.  The call itself makes no
+ * device-wide synchronisation would break.  The partial results of (sequence, KV head) pairs
+ * that the kernel's persistent grid cuts go to a fixed 6 MiB array inside the library image
+ * instead of library-allocated scratch, so every GPU that loads the library holds those 6 MiB
+ * until the process exits.  What the kernel needs depends on the GPU, not on the shape: two
+ * slots of 16 * (d + 2) floats and a 16-byte descriptor per CTA, two CTAs per SM (4.7 MiB on a
+ * 148-SM B200 at d = 128);
+ * a GPU with so many SMs that this exceeds the array is refused with LOGOS_OUT_OF_BOUNDS and
+ * a message giving both sizes, and so is a call with more than 2048 sequences (the limit of
+ * both attention entry points: a CTA keeps one tile count per sequence in shared memory).
+ * The call itself makes no
  * cudaMalloc / cudaFree.  The first call on a device looks up the array's device address;
  * make that first call outside any stream capture.  All calls share the one array and one
  * status word.  Nothing is cleared between calls: the partials are always written before

@@ -3,20 +3,25 @@
 //
 // HBM-bound: every step streams the whole K and V history once (512 bytes per
 // position per KV head at D=128), so the kernel is built around that stream:
-//   * a (sequence, KV head) pair is cut into units of `unit_len` positions;
-//     one CTA per unit, sized so the grid is several waves of the SM count;
-//   * a producer thread moves 64-position K and V tiles into a 3-stage shared
-//     memory ring with TMA tile loads (128-byte swizzle, no multicast) signalled
-//     on mbarriers; four consumer warps each own 16 positions of every tile;
+//   * the work is the sequence of 64-position K/V tiles of all (sequence, KV head)
+//     pairs, in order; the grid is persistent (two CTAs per SM) and CTA c takes the
+//     c-th equal share of that sequence, whatever pairs it crosses: every CTA streams
+//     the same number of tiles, and a pair is cut only where a share ends;
+//   * a producer thread moves the tiles into a 3-stage shared-memory ring with TMA
+//     tile loads (128-byte swizzle, no multicast) signalled on mbarriers; the ring
+//     keeps running across pairs, so the loads of the next pair are in flight while
+//     the consumers finish and write out the previous one; four consumer warps each
+//     own 16 positions of every tile;
 //   * all query heads that share the KV head (up to 16) form the M side of
 //     m16n8k16 tensor-core MMAs, so a K/V tile is read from shared memory once
 //     for the whole group; scores, softmax and the running output stay in f32
 //     registers; the probabilities enter the second MMA as an fp16 high part
 //     plus an fp16 residual so the product keeps f32-class accuracy;
-//   * the CTA that owns the position being appended rotates the new key
+//   * the CTA whose share holds the position being appended rotates the new key
 //     (f32 multiply and add rounded separately, fp16 store), writes the new
 //     K/V row to the cache and patches it into its own shared-memory tile;
-//   * units are merged by a second small kernel in a fixed order.
+//   * a pair that lies inside one share is normalised and written by that CTA; the
+//     parts of a pair that was cut are merged by a second small kernel in a fixed order.
 #include "ops.cuh"
 #include "ptx.cuh"
 
@@ -33,8 +38,10 @@ using namespace ptx;
 constexpr int ATT_TILE = 64;
 constexpr int ATT_STAGES = 3;
 constexpr int ATT_CWARPS = 4;
+constexpr int ATT_CTHREADS = ATT_CWARPS * 32;
 constexpr int ATT_THREADS = (ATT_CWARPS + 1) * 32;
 constexpr int ATT_BOX_BYTES = 64 * 128;  // 64 rows x 128 bytes
+constexpr int ATT_MAX_BATCH = 2048;      // sequences whose tile counts a CTA keeps in shared memory
 
 struct AttnParams {
   const __half* q_f16;
@@ -56,9 +63,20 @@ struct AttnParams {
   __half*       v_cache;
   const float*  rope;
   const int32_t* seq_len;
-  float*        part_o;   // [B][Hq][max_splits][D]
-  float*        part_ml;  // [B][Hq][max_splits][2]
-  int           b, h_q, h_kv, l_max, unit_len, max_splits;
+  // Parts of cut pairs.  Only the first and the last pair of a share can be cut, so a share writes
+  // at most two: slot 0 for a part that begins at the share's first tile, slot 1 otherwise.
+  float*        part_o;   // [shares][2][16][D]   unnormalised outputs
+  float*        part_ml;  // [shares][2][16][2]   their (max, sum)
+  // [shares][2] descriptors, rewritten by every launch: the slot that holds the FIRST part of a
+  // cut pair names the pair and its shares {b, kvh, first share, last share}; every other slot
+  // says -1.  The merge kernel runs one CTA per slot and query row and acts on the named ones.
+  int4*         part_desc;
+  int64_t*      tiles_total;   // [1] the launch's tile count, for the merge kernel's share arithmetic
+  void*         o;        // [B][Hq][D]
+  int           o_dtype;
+  ActOut        o_act;
+  int           b, h_q, h_kv, l_max;
+  int           shares;   // the persistent grid's size: the tile sequence is cut into this many shares
   float         scale_log2;
   int*          status;
 };
@@ -66,6 +84,26 @@ struct AttnParams {
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
   __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ int attn_len_eff(const AttnParams& p, int len0) {
+  int len_eff = p.fused ? len0 + 1 : len0;
+  if (len_eff > p.l_max) len_eff = p.l_max;
+  return len_eff < 0 ? 0 : len_eff;
+}
+
+// Share c of `shares` takes tiles [c * total / shares, (c + 1) * total / shares); the share that
+// holds tile g is the largest c whose first tile is <= g.
+__device__ __forceinline__ int64_t share_begin(int64_t c, int64_t total, int shares) { return c * total / shares; }
+__device__ __forceinline__ int share_of_tile(int64_t g, int64_t total, int shares) {
+  return (int)(((g + 1) * shares - 1) / total);
+}
+
+__device__ __forceinline__ void store_out(const AttnParams& p, int64_t oi, float v) {
+  if (p.o_dtype == LOGOS_ACT_PLANES) act_store(p.o_act, oi, v);
+  else if (p.o_dtype == LOGOS_F16) reinterpret_cast<__half*>(p.o)[oi] = __float2half_rn(v);
+  else if (p.o_dtype == LOGOS_BF16) reinterpret_cast<__nv_bfloat16*>(p.o)[oi] = __float2bfloat16_rn(v);
+  else reinterpret_cast<float*>(p.o)[oi] = v;
 }
 
 template <int D>
@@ -76,6 +114,7 @@ gqa_decode_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   constexpr int STAGE_BYTES = 2 * NBOX * ATT_BOX_BYTES;
   constexpr int QS_STRIDE = D + 8;  // halfs; +16 bytes keeps ldmatrix rows on distinct banks
   constexpr int KSTEPS = D / 16;
+  static_assert(STAGE_BYTES >= ATT_CWARPS * 16 * D * 4, "a ring stage doubles as the scratch that combines the warps");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -83,38 +122,26 @@ gqa_decode_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   __half* qs = reinterpret_cast<__half*>(stages + ATT_STAGES * STAGE_BYTES);  // [16][QS_STRIDE]
   __half* new_k = qs + 16 * QS_STRIDE;                               // [D]
   __half* new_v = new_k + D;                                         // [D]
-  uint64_t* bar_full = reinterpret_cast<uint64_t*>(new_v + D);
+  float* mml = reinterpret_cast<float*>(new_v + D);                  // [warp][16][2]
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(mml + ATT_CWARPS * 16 * 2);
   uint64_t* bar_empty = bar_full + ATT_STAGES;
+  int32_t* s_tiles = reinterpret_cast<int32_t*>(bar_empty + ATT_STAGES);  // [B] tiles of a sequence
+  int32_t* s_pref = s_tiles + p.b;                                         // [B + 1] tiles before it
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int G = p.h_q / p.h_kv;
 
   // The lengths, the query and the new K/V rows come from kernels of the same step: wait for
   // them (the launch may have let this kernel start early), and read them past L1.
   pdl_wait();
   pdl_trigger();
-  const int len0 = __ldcg(p.seq_len + b);
-  const bool append = p.fused && len0 < p.l_max;
-  int len_eff = p.fused ? len0 + 1 : len0;
-  if (len_eff > p.l_max) len_eff = p.l_max;
-  const int unit_start = split * p.unit_len;
-  if (unit_start >= len_eff) return;
   // a kernel that gave up earlier left a code behind: do not start new work on top of it
   // (one thread reads, everyone takes the same decision)
   __shared__ int prior_status;
-  if (tid == 0) prior_status = *reinterpret_cast<volatile int*>(p.status);
-  __syncthreads();
-  if (prior_status != 0) return;
-  const int unit_end = min(unit_start + p.unit_len, len_eff);
-  const int ntiles = (unit_end - unit_start + ATT_TILE - 1) / ATT_TILE;
-  const int64_t row_base = ((int64_t)b * p.h_kv + kvh) * p.l_max;
-  const int pos_new = len0;  // where the appended row goes
-  const bool owns_new = append && pos_new >= unit_start && pos_new < unit_start + p.unit_len;
-
   if (tid == 0) {
+    prior_status = *reinterpret_cast<volatile int*>(p.status);
     for (int i = 0; i < ATT_STAGES; ++i) {
       mbar_init(&bar_full[i], 1);
       mbar_init(&bar_empty[i], ATT_CWARPS);
@@ -123,334 +150,439 @@ gqa_decode_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     prefetch_tensormap(&map_k);
     prefetch_tensormap(&map_v);
   }
-
-  // ---- stage the query heads (rotated when asked), zero the padding rows
-  {
-    const int half_d = D / 2;
-    int pos_q = len0 < p.l_max ? len0 : p.l_max - 1;
-    if (pos_q < 0) pos_q = 0;
-    const float* tab = p.rope + (int64_t)pos_q * half_d * 2;
-    for (int i = tid; i < 16 * half_d; i += ATT_THREADS) {
-      int g = i / half_d, e = i - g * half_d;
-      float x1 = 0.f, x2 = 0.f;
-      if (g < G) {
-        int hq = kvh * G + g;
-        if (p.q_f16) {
-          const __half* qp = p.q_f16 + ((int64_t)b * p.h_q + hq) * D;
-          x1 = __half2float(__ldcg(qp + e));
-          x2 = __half2float(__ldcg(qp + e + half_d));
-        } else {
-          const float* qp = p.q_f32 + (int64_t)b * p.q_ld + (int64_t)hq * D;
-          x1 = __ldcg(qp + e);
-          x2 = __ldcg(qp + e + half_d);
-          for (int sp = 1; sp < p.f32_parts; ++sp) {
-            x1 = __fadd_rn(x1, __ldcg(qp + sp * p.f32_part_stride + e));
-            x2 = __fadd_rn(x2, __ldcg(qp + sp * p.f32_part_stride + e + half_d));
-          }
-          if (p.q_bias) {
-            x1 = __fadd_rn(x1, __ldg(p.q_bias + hq * D + e));
-            x2 = __fadd_rn(x2, __ldg(p.q_bias + hq * D + e + half_d));
-          }
-        }
-        if (p.rotate_q) {
-          float c = tab[2 * e], s = tab[2 * e + 1];
-          float r1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s));
-          float r2 = __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s));
-          x1 = r1;
-          x2 = r2;
-        }
-      }
-      qs[g * QS_STRIDE + e] = __float2half_rn(x1);
-      qs[g * QS_STRIDE + e + half_d] = __float2half_rn(x2);
+  for (int b = tid; b < p.b; b += ATT_THREADS)
+    s_tiles[b] = (attn_len_eff(p, __ldcg(p.seq_len + b)) + ATT_TILE - 1) / ATT_TILE;
+  if (tid < 2) p.part_desc[blockIdx.x * 2 + tid] = make_int4(-1, -1, -1, -1);
+  __syncthreads();
+  if (prior_status != 0) return;
+  // a sequence without any position to attend to has no tile, hence no CTA: its output rows are zero
+  for (int b = blockIdx.x; b < p.b; b += gridDim.x)
+    if (s_tiles[b] == 0)
+      for (int e = tid; e < p.h_q * D; e += ATT_THREADS) store_out(p, (int64_t)b * p.h_q * D + e, 0.f);
+  if (warp == 0) {  // exclusive prefix over the sequences: lane l sums a contiguous run, then a warp scan
+    const int per = (p.b + 31) / 32;
+    int run = 0;
+    for (int i = 0; i < per; ++i) {
+      const int b = lane * per + i;
+      if (b < p.b) run += s_tiles[b];
     }
-    // ---- the appended row: rotate k, round to fp16, write the cache, keep a copy
-    if (owns_new) {
-      const float* tabn = p.rope + (int64_t)pos_new * half_d * 2;
-      for (int e = tid; e < half_d; e += ATT_THREADS) {
-        float k1, k2, v1, v2;
-        if (p.k_new_f16) {
-          const __half* kp = p.k_new_f16 + ((int64_t)b * p.h_kv + kvh) * D;
-          const __half* vp = p.v_new_f16 + ((int64_t)b * p.h_kv + kvh) * D;
-          k1 = __half2float(__ldcg(kp + e)); k2 = __half2float(__ldcg(kp + e + half_d));
-          v1 = __half2float(__ldcg(vp + e)); v2 = __half2float(__ldcg(vp + e + half_d));
-        } else {
-          const float* kp = p.k_new_f32 + (int64_t)b * p.kv_ld + (int64_t)kvh * D;
-          const float* vp = p.v_new_f32 + (int64_t)b * p.kv_ld + (int64_t)kvh * D;
-          k1 = __ldcg(kp + e); k2 = __ldcg(kp + e + half_d);
-          v1 = __ldcg(vp + e); v2 = __ldcg(vp + e + half_d);
-          for (int sp = 1; sp < p.f32_parts; ++sp) {
-            const int64_t o = sp * p.f32_part_stride;
-            k1 = __fadd_rn(k1, __ldcg(kp + o + e)); k2 = __fadd_rn(k2, __ldcg(kp + o + e + half_d));
-            v1 = __fadd_rn(v1, __ldcg(vp + o + e)); v2 = __fadd_rn(v2, __ldcg(vp + o + e + half_d));
-          }
-          if (p.k_bias) {
-            k1 = __fadd_rn(k1, __ldg(p.k_bias + kvh * D + e)); k2 = __fadd_rn(k2, __ldg(p.k_bias + kvh * D + e + half_d));
-          }
-          if (p.v_bias) {
-            v1 = __fadd_rn(v1, __ldg(p.v_bias + kvh * D + e)); v2 = __fadd_rn(v2, __ldg(p.v_bias + kvh * D + e + half_d));
-          }
-        }
-        float c = tabn[2 * e], s = tabn[2 * e + 1];
-        __half r1 = __float2half_rn(__fsub_rn(__fmul_rn(k1, c), __fmul_rn(k2, s)));
-        __half r2 = __float2half_rn(__fadd_rn(__fmul_rn(k2, c), __fmul_rn(k1, s)));
-        __half h1 = __float2half_rn(v1), h2 = __float2half_rn(v2);
-        new_k[e] = r1; new_k[e + half_d] = r2;
-        new_v[e] = h1; new_v[e + half_d] = h2;
-        __half* kd = p.k_cache + (row_base + pos_new) * D;
-        __half* vd = p.v_cache + (row_base + pos_new) * D;
-        kd[e] = r1; kd[e + half_d] = r2;
-        vd[e] = h1; vd[e + half_d] = h2;
+    int incl = run;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    int acc = incl - run;
+    for (int i = 0; i < per; ++i) {
+      const int b = lane * per + i;
+      if (b < p.b) {
+        s_pref[b] = acc;
+        acc += s_tiles[b];
       }
     }
+    if (lane == 31) s_pref[p.b] = incl;
   }
   __syncthreads();
+  const int64_t total = (int64_t)p.h_kv * s_pref[p.b];
+  if (blockIdx.x == 0 && tid == 0) *p.tiles_total = total;
+  if (total == 0) return;
+  const int64_t g_lo = share_begin(blockIdx.x, total, p.shares), g_hi = share_begin(blockIdx.x + 1, total, p.shares);
+  if (g_lo >= g_hi) return;
+
+  // Both roles walk the share the same way: tile g belongs to sequence b (the one with
+  // h_kv * pref[b] <= g < h_kv * pref[b + 1]), KV head (g - h_kv * pref[b]) / tiles[b], tile
+  // (g - h_kv * pref[b]) % tiles[b] of that pair.
+  int b_cur = 0;
+  {
+    int lo = 0, hi = p.b;  // last b with h_kv * pref[b] <= g_lo
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if ((int64_t)p.h_kv * s_pref[mid] <= g_lo) lo = mid; else hi = mid;
+    }
+    b_cur = lo;
+  }
 
   bool ok = true;
 
   if (warp == ATT_CWARPS) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
-      for (int t = 0; t < ntiles && ok; ++t) {
-        int st = t % ATT_STAGES;
-        uint32_t ph = (uint32_t)(t / ATT_STAGES) & 1u;
-        ok = mbar_wait(&bar_empty[st], ph ^ 1u);
-        if (!ok) break;
-        uint8_t* sb = stages + st * STAGE_BYTES;
-        mbar_arrive_expect_tx(&bar_full[st], STAGE_BYTES);
-        int y = (int)(row_base + unit_start + t * ATT_TILE);
+      int t_ring = 0;
+      int b = b_cur;
+      for (int64_t g = g_lo; g < g_hi && ok;) {
+        while ((int64_t)p.h_kv * s_pref[b + 1] <= g) ++b;
+        const int tiles_b = s_tiles[b];
+        const int64_t within = g - (int64_t)p.h_kv * s_pref[b];
+        const int kvh = (int)(within / tiles_b), t0 = (int)(within - (int64_t)kvh * tiles_b);
+        const int t1 = (int)min((int64_t)tiles_b, t0 + (g_hi - g));
+        const int64_t row_base = ((int64_t)b * p.h_kv + kvh) * p.l_max;
+        for (int t = t0; t < t1 && ok; ++t, ++t_ring) {
+          const int st = t_ring % ATT_STAGES;
+          const uint32_t ph = (uint32_t)(t_ring / ATT_STAGES) & 1u;
+          ok = mbar_wait(&bar_empty[st], ph ^ 1u);
+          if (!ok) break;
+          uint8_t* sb = stages + st * STAGE_BYTES;
+          mbar_arrive_expect_tx(&bar_full[st], STAGE_BYTES);
+          const int y = (int)(row_base + (int64_t)t * ATT_TILE);
 #pragma unroll
-        for (int j = 0; j < NBOX; ++j) {
-          tma_load_2d(sb + j * ATT_BOX_BYTES, &map_k, &bar_full[st], j * 64, y);
-          tma_load_2d(sb + (NBOX + j) * ATT_BOX_BYTES, &map_v, &bar_full[st], j * 64, y);
+          for (int j = 0; j < NBOX; ++j) {
+            tma_load_2d(sb + j * ATT_BOX_BYTES, &map_k, &bar_full[st], j * 64, y);
+            tma_load_2d(sb + (NBOX + j) * ATT_BOX_BYTES, &map_v, &bar_full[st], j * 64, y);
+          }
         }
+        g += t1 - t0;
       }
       if (!ok) atomicExch(p.status, 101);
     }
   } else {
     // ---------------------------------------------------------------- consumers
     const int g4 = lane >> 2, t4 = lane & 3;
-    uint32_t qa[KSTEPS][4];
-    {
-      int row = (lane & 7) + 8 * ((lane >> 3) & 1);
-      int colh = 8 * (lane >> 4);
-#pragma unroll
-      for (int ks = 0; ks < KSTEPS; ++ks) {
-        uint32_t addr = smem_u32(qs + row * QS_STRIDE + ks * 16 + colh);
-        ldmatrix_x4(qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], addr);
-      }
-    }
-    float m_run[2] = {-INFINITY, -INFINITY};
-    float l_run[2] = {0.f, 0.f};
-    float o[D / 8][4];
-#pragma unroll
-    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    const int ctid = tid;  // 0 .. ATT_CTHREADS - 1
+    int t_ring = 0;
+    int b = b_cur;
+    for (int64_t g = g_lo; g < g_hi && ok;) {
+      while ((int64_t)p.h_kv * s_pref[b + 1] <= g) ++b;
+      const int tiles_b = s_tiles[b];
+      const int64_t pair0 = (int64_t)p.h_kv * s_pref[b];
+      const int64_t within = g - pair0;
+      const int kvh = (int)(within / tiles_b), t0 = (int)(within - (int64_t)kvh * tiles_b);
+      const int t1 = (int)min((int64_t)tiles_b, t0 + (g_hi - g));
+      const int64_t pair_g0 = pair0 + (int64_t)kvh * tiles_b;  // first tile of the pair in the whole sequence
+      const int share_first = share_of_tile(pair_g0, total, p.shares);
+      const int share_last = share_of_tile(pair_g0 + tiles_b - 1, total, p.shares);
+      const bool whole = share_first == share_last;   // the pair lies inside this share: write the result itself
+      const int slot = g == g_lo ? 0 : 1;
+      const int len0 = __ldcg(p.seq_len + b);
+      const int len_eff = attn_len_eff(p, len0);
+      const int64_t row_base = ((int64_t)b * p.h_kv + kvh) * p.l_max;
+      const int pos_new = len0;  // where the appended row goes
+      const bool append = p.fused && len0 < p.l_max;
+      const bool owns_new = append && pos_new >= t0 * ATT_TILE && pos_new < t1 * ATT_TILE;
 
-    for (int t = 0; t < ntiles; ++t) {
-      int st = t % ATT_STAGES;
-      uint32_t ph = (uint32_t)(t / ATT_STAGES) & 1u;
-      if (!mbar_wait(&bar_full[st], ph)) {
-        ok = false;
-        break;
+      // ---- stage the query heads (rotated when asked), zero the padding rows
+      {
+        const int half_d = D / 2;
+        int pos_q = len0 < p.l_max ? len0 : p.l_max - 1;
+        if (pos_q < 0) pos_q = 0;
+        const float* tab = p.rope + (int64_t)pos_q * half_d * 2;
+        for (int i = ctid; i < 16 * half_d; i += ATT_CTHREADS) {
+          int g = i / half_d, e = i - g * half_d;
+          float x1 = 0.f, x2 = 0.f;
+          if (g < G) {
+            int hq = kvh * G + g;
+            if (p.q_f16) {
+              const __half* qp = p.q_f16 + ((int64_t)b * p.h_q + hq) * D;
+              x1 = __half2float(__ldcg(qp + e));
+              x2 = __half2float(__ldcg(qp + e + half_d));
+            } else {
+              const float* qp = p.q_f32 + (int64_t)b * p.q_ld + (int64_t)hq * D;
+              x1 = __ldcg(qp + e);
+              x2 = __ldcg(qp + e + half_d);
+              for (int sp = 1; sp < p.f32_parts; ++sp) {
+                x1 = __fadd_rn(x1, __ldcg(qp + sp * p.f32_part_stride + e));
+                x2 = __fadd_rn(x2, __ldcg(qp + sp * p.f32_part_stride + e + half_d));
+              }
+              if (p.q_bias) {
+                x1 = __fadd_rn(x1, __ldg(p.q_bias + hq * D + e));
+                x2 = __fadd_rn(x2, __ldg(p.q_bias + hq * D + e + half_d));
+              }
+            }
+            if (p.rotate_q) {
+              float c = tab[2 * e], s = tab[2 * e + 1];
+              float r1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s));
+              float r2 = __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s));
+              x1 = r1;
+              x2 = r2;
+            }
+          }
+          qs[g * QS_STRIDE + e] = __float2half_rn(x1);
+          qs[g * QS_STRIDE + e + half_d] = __float2half_rn(x2);
+        }
+        // ---- the appended row: rotate k, round to fp16, write the cache, keep a copy
+        if (owns_new) {
+          const float* tabn = p.rope + (int64_t)pos_new * half_d * 2;
+          for (int e = ctid; e < half_d; e += ATT_CTHREADS) {
+            float k1, k2, v1, v2;
+            if (p.k_new_f16) {
+              const __half* kp = p.k_new_f16 + ((int64_t)b * p.h_kv + kvh) * D;
+              const __half* vp = p.v_new_f16 + ((int64_t)b * p.h_kv + kvh) * D;
+              k1 = __half2float(__ldcg(kp + e)); k2 = __half2float(__ldcg(kp + e + half_d));
+              v1 = __half2float(__ldcg(vp + e)); v2 = __half2float(__ldcg(vp + e + half_d));
+            } else {
+              const float* kp = p.k_new_f32 + (int64_t)b * p.kv_ld + (int64_t)kvh * D;
+              const float* vp = p.v_new_f32 + (int64_t)b * p.kv_ld + (int64_t)kvh * D;
+              k1 = __ldcg(kp + e); k2 = __ldcg(kp + e + half_d);
+              v1 = __ldcg(vp + e); v2 = __ldcg(vp + e + half_d);
+              for (int sp = 1; sp < p.f32_parts; ++sp) {
+                const int64_t o = sp * p.f32_part_stride;
+                k1 = __fadd_rn(k1, __ldcg(kp + o + e)); k2 = __fadd_rn(k2, __ldcg(kp + o + e + half_d));
+                v1 = __fadd_rn(v1, __ldcg(vp + o + e)); v2 = __fadd_rn(v2, __ldcg(vp + o + e + half_d));
+              }
+              if (p.k_bias) {
+                k1 = __fadd_rn(k1, __ldg(p.k_bias + kvh * D + e)); k2 = __fadd_rn(k2, __ldg(p.k_bias + kvh * D + e + half_d));
+              }
+              if (p.v_bias) {
+                v1 = __fadd_rn(v1, __ldg(p.v_bias + kvh * D + e)); v2 = __fadd_rn(v2, __ldg(p.v_bias + kvh * D + e + half_d));
+              }
+            }
+            float c = tabn[2 * e], s = tabn[2 * e + 1];
+            __half r1 = __float2half_rn(__fsub_rn(__fmul_rn(k1, c), __fmul_rn(k2, s)));
+            __half r2 = __float2half_rn(__fadd_rn(__fmul_rn(k2, c), __fmul_rn(k1, s)));
+            __half h1 = __float2half_rn(v1), h2 = __float2half_rn(v2);
+            new_k[e] = r1; new_k[e + half_d] = r2;
+            new_v[e] = h1; new_v[e + half_d] = h2;
+            __half* kd = p.k_cache + (row_base + pos_new) * D;
+            __half* vd = p.v_cache + (row_base + pos_new) * D;
+            kd[e] = r1; kd[e + half_d] = r2;
+            vd[e] = h1; vd[e + half_d] = h2;
+          }
+        }
       }
-      uint8_t* kb = stages + st * STAGE_BYTES;
-      uint8_t* vb = kb + NBOX * ATT_BOX_BYTES;
-      const int tile_pos0 = unit_start + t * ATT_TILE;
-      const int my_pos0 = tile_pos0 + 16 * warp;
+      asm volatile("bar.sync 1, %0;" ::"n"(ATT_CTHREADS));
 
-      // patch the appended row / clear rows past the end (only this warp reads its 16 rows)
-      if (my_pos0 + 16 > len_eff || (owns_new && pos_new >= my_pos0 && pos_new < my_pos0 + 16)) {
-        for (int r = 0; r < 16; ++r) {
-          int pos = my_pos0 + r;
-          uint32_t row = 16 * warp + r;
-          if (owns_new && pos == pos_new) {
-            for (int c = lane; c < 2 * (D / 8); c += 32) {
-              bool is_v = c >= D / 8;
-              int cc = is_v ? c - D / 8 : c;
-              const uint4 val = *reinterpret_cast<const uint4*>((is_v ? new_v : new_k) + cc * 8);
-              uint8_t* base = (is_v ? vb : kb) + (cc >> 3) * ATT_BOX_BYTES;
-              *reinterpret_cast<uint4*>(base + swz128(row, cc & 7)) = val;
+      uint32_t qa[KSTEPS][4];
+      {
+        int row = (lane & 7) + 8 * ((lane >> 3) & 1);
+        int colh = 8 * (lane >> 4);
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+          uint32_t addr = smem_u32(qs + row * QS_STRIDE + ks * 16 + colh);
+          ldmatrix_x4(qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], addr);
+        }
+      }
+      float m_run[2] = {-INFINITY, -INFINITY};
+      float l_run[2] = {0.f, 0.f};
+      float o[D / 8][4];
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+      int st = 0;
+      for (int t = t0; t < t1; ++t, ++t_ring) {
+        st = t_ring % ATT_STAGES;
+        uint32_t ph = (uint32_t)(t_ring / ATT_STAGES) & 1u;
+        if (!mbar_wait(&bar_full[st], ph)) {
+          ok = false;
+          break;
+        }
+        uint8_t* kb = stages + st * STAGE_BYTES;
+        uint8_t* vb = kb + NBOX * ATT_BOX_BYTES;
+        const int tile_pos0 = t * ATT_TILE;
+        const int my_pos0 = tile_pos0 + 16 * warp;
+
+        // patch the appended row / clear rows past the end (only this warp reads its 16 rows)
+        if (my_pos0 + 16 > len_eff || (owns_new && pos_new >= my_pos0 && pos_new < my_pos0 + 16)) {
+          for (int r = 0; r < 16; ++r) {
+            int pos = my_pos0 + r;
+            uint32_t row = 16 * warp + r;
+            if (owns_new && pos == pos_new) {
+              for (int c = lane; c < 2 * (D / 8); c += 32) {
+                bool is_v = c >= D / 8;
+                int cc = is_v ? c - D / 8 : c;
+                const uint4 val = *reinterpret_cast<const uint4*>((is_v ? new_v : new_k) + cc * 8);
+                uint8_t* base = (is_v ? vb : kb) + (cc >> 3) * ATT_BOX_BYTES;
+                *reinterpret_cast<uint4*>(base + swz128(row, cc & 7)) = val;
+              }
+            } else if (pos >= len_eff) {
+              for (int c = lane; c < D / 8; c += 32) {
+                uint8_t* base = vb + (c >> 3) * ATT_BOX_BYTES;
+                *reinterpret_cast<uint4*>(base + swz128(row, c & 7)) = make_uint4(0, 0, 0, 0);
+              }
             }
-          } else if (pos >= len_eff) {
-            for (int c = lane; c < D / 8; c += 32) {
-              uint8_t* base = vb + (c >> 3) * ATT_BOX_BYTES;
-              *reinterpret_cast<uint4*>(base + swz128(row, c & 7)) = make_uint4(0, 0, 0, 0);
-            }
+          }
+          __syncwarp();
+        }
+
+        // ---- S = Q K^T for 16 positions
+        float s[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+        {
+          uint32_t row = 16 * warp + (lane & 7) + 8 * (lane >> 4);
+          int ch = (lane >> 3) & 1;
+#pragma unroll
+          for (int ks = 0; ks < KSTEPS; ++ks) {
+            int chunk = ks * 2 + ch;
+            uint32_t addr = smem_u32(kb + (chunk >> 3) * ATT_BOX_BYTES + swz128(row, chunk & 7));
+            uint32_t r0, r1, r2, r3;
+            ldmatrix_x4(r0, r1, r2, r3, addr);
+            mma_f16_16816(s[0], qa[ks], r0, r1);
+            mma_f16_16816(s[1], qa[ks], r2, r3);
+          }
+        }
+        // ---- mask, scale, online softmax
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            int pos = my_pos0 + nt * 8 + 2 * t4 + (j & 1);
+            float v = (pos < len_eff) ? s[nt][j] * p.scale_log2 : -INFINITY;
+            s[nt][j] = v;
+            mx[j >> 1] = fmaxf(mx[j >> 1], v);
+          }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+          mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        }
+        float corr[2], m_use[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          float m_new = fmaxf(m_run[r], mx[r]);
+          m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;
+          corr[r] = exp2f(m_run[r] - m_use[r]);
+          m_run[r] = m_new;
+        }
+        float pr[2][4];
+        float psum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float e = exp2f(s[nt][j] - m_use[j >> 1]);
+            pr[nt][j] = e;
+            psum[j >> 1] += e;
+          }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * corr[r] + psum[r];
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+          o[i][0] *= corr[0]; o[i][1] *= corr[0];
+          o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        // ---- P as fp16 high part + fp16 residual
+        uint32_t a_hi[4], a_lo[4];
+        {
+          const float (*q)[4] = pr;
+          float h[8] = {q[0][0], q[0][1], q[0][2], q[0][3], q[1][0], q[1][1], q[1][2], q[1][3]};
+          float lo[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float hi = __half2float(__float2half_rn(h[i]));
+            lo[i] = h[i] - hi;
+          }
+          a_hi[0] = pack_half2(h[0], h[1]); a_hi[1] = pack_half2(h[2], h[3]);
+          a_hi[2] = pack_half2(h[4], h[5]); a_hi[3] = pack_half2(h[6], h[7]);
+          a_lo[0] = pack_half2(lo[0], lo[1]); a_lo[1] = pack_half2(lo[2], lo[3]);
+          a_lo[2] = pack_half2(lo[4], lo[5]); a_lo[3] = pack_half2(lo[6], lo[7]);
+        }
+        // ---- O += P V
+        {
+          uint32_t row = 16 * warp + (lane & 7) + 8 * ((lane >> 3) & 1);
+          int ch = lane >> 4;
+#pragma unroll
+          for (int dn = 0; dn < D / 16; ++dn) {
+            int chunk = dn * 2 + ch;
+            uint32_t addr = smem_u32(vb + (chunk >> 3) * ATT_BOX_BYTES + swz128(row, chunk & 7));
+            uint32_t r0, r1, r2, r3;
+            ldmatrix_x4_trans(r0, r1, r2, r3, addr);
+            mma_f16_16816(o[2 * dn], a_hi, r0, r1);
+            mma_f16_16816(o[2 * dn], a_lo, r0, r1);
+            mma_f16_16816(o[2 * dn + 1], a_hi, r2, r3);
+            mma_f16_16816(o[2 * dn + 1], a_lo, r2, r3);
           }
         }
         __syncwarp();
+        // the last tile of this part keeps its ring stage: it is the scratch the warps are combined in
+        if (t + 1 < t1 && lane == 0) mbar_arrive(&bar_empty[st]);
       }
-
-      // ---- S = Q K^T for 16 positions
-      float s[2][4];
+      // ---- combine the four warps in the ring stage of the part's last tile (every warp has
+      // read its rows of it once all four have passed the barrier), then hand the stage back.
+      // The barrier also carries the verdict: a warp whose wait gave up takes the others with it.
 #pragma unroll
-      for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+      for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+      }
       {
-        uint32_t row = 16 * warp + (lane & 7) + 8 * (lane >> 4);
-        int ch = (lane >> 3) & 1;
-#pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) {
-          int chunk = ks * 2 + ch;
-          uint32_t addr = smem_u32(kb + (chunk >> 3) * ATT_BOX_BYTES + swz128(row, chunk & 7));
-          uint32_t r0, r1, r2, r3;
-          ldmatrix_x4(r0, r1, r2, r3, addr);
-          mma_f16_16816(s[0], qa[ks], r0, r1);
-          mma_f16_16816(s[1], qa[ks], r2, r3);
+        int all_ok;
+        asm volatile(
+            "{\n\t.reg .pred q, r;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred r, 1, %2, q;\n\tselp.u32 %0, 1, 0, r;\n\t}"
+            : "=r"(all_ok)
+            : "r"((uint32_t)ok), "n"(ATT_CTHREADS)
+            : "memory");
+        if (!all_ok) {
+          if (!ok && lane == 0) atomicExch(p.status, 102);
+          ok = false;
+          break;
         }
       }
-      // ---- mask, scale, online softmax
-      float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          int pos = my_pos0 + nt * 8 + 2 * t4 + (j & 1);
-          float v = (pos < len_eff) ? s[nt][j] * p.scale_log2 : -INFINITY;
-          s[nt][j] = v;
-          mx[j >> 1] = fmaxf(mx[j >> 1], v);
-        }
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-      }
-      float corr[2], m_use[2];
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        float m_new = fmaxf(m_run[r], mx[r]);
-        m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;
-        corr[r] = exp2f(m_run[r] - m_use[r]);
-        m_run[r] = m_new;
-      }
-      float pr[2][4];
-      float psum[2] = {0.f, 0.f};
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float e = exp2f(s[nt][j] - m_use[j >> 1]);
-          pr[nt][j] = e;
-          psum[j >> 1] += e;
-        }
-#pragma unroll
-      for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * corr[r] + psum[r];
+      float* mo = reinterpret_cast<float*>(stages + st * STAGE_BYTES);   // [warp][16][D]
 #pragma unroll
       for (int i = 0; i < D / 8; ++i) {
-        o[i][0] *= corr[0]; o[i][1] *= corr[0];
-        o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        int col = i * 8 + 2 * t4;
+        float* r0p = mo + ((warp * 16 + g4) * D) + col;
+        float* r1p = mo + ((warp * 16 + g4 + 8) * D) + col;
+        r0p[0] = o[i][0]; r0p[1] = o[i][1];
+        r1p[0] = o[i][2]; r1p[1] = o[i][3];
       }
-      // ---- P as fp16 high part + fp16 residual
-      uint32_t a_hi[4], a_lo[4];
-      {
-        const float (*q)[4] = pr;
-        float h[8] = {q[0][0], q[0][1], q[0][2], q[0][3], q[1][0], q[1][1], q[1][2], q[1][3]};
-        float lo[8];
+      if (t4 == 0) {
+        mml[(warp * 16 + g4) * 2 + 0] = m_run[0];
+        mml[(warp * 16 + g4) * 2 + 1] = l_run[0];
+        mml[(warp * 16 + g4 + 8) * 2 + 0] = m_run[1];
+        mml[(warp * 16 + g4 + 8) * 2 + 1] = l_run[1];
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(ATT_CTHREADS));
+      const int64_t pi = ((int64_t)blockIdx.x * 2 + slot) * 16;   // row 0 of this part's slot
+      for (int e = ctid; e < G * D; e += ATT_CTHREADS) {
+        int r = e / D, d = e - r * D;
+        float mstar = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float hi = __half2float(__float2half_rn(h[i]));
-          lo[i] = h[i] - hi;
-        }
-        a_hi[0] = pack_half2(h[0], h[1]); a_hi[1] = pack_half2(h[2], h[3]);
-        a_hi[2] = pack_half2(h[4], h[5]); a_hi[3] = pack_half2(h[6], h[7]);
-        a_lo[0] = pack_half2(lo[0], lo[1]); a_lo[1] = pack_half2(lo[2], lo[3]);
-        a_lo[2] = pack_half2(lo[4], lo[5]); a_lo[3] = pack_half2(lo[6], lo[7]);
-      }
-      // ---- O += P V
-      {
-        uint32_t row = 16 * warp + (lane & 7) + 8 * ((lane >> 3) & 1);
-        int ch = lane >> 4;
+        for (int w = 0; w < ATT_CWARPS; ++w) mstar = fmaxf(mstar, mml[(w * 16 + r) * 2]);
+        float muse = (mstar == -INFINITY) ? 0.f : mstar;
+        float acc = 0.f, L = 0.f;
 #pragma unroll
-        for (int dn = 0; dn < D / 16; ++dn) {
-          int chunk = dn * 2 + ch;
-          uint32_t addr = smem_u32(vb + (chunk >> 3) * ATT_BOX_BYTES + swz128(row, chunk & 7));
-          uint32_t r0, r1, r2, r3;
-          ldmatrix_x4_trans(r0, r1, r2, r3, addr);
-          mma_f16_16816(o[2 * dn], a_hi, r0, r1);
-          mma_f16_16816(o[2 * dn], a_lo, r0, r1);
-          mma_f16_16816(o[2 * dn + 1], a_hi, r2, r3);
-          mma_f16_16816(o[2 * dn + 1], a_lo, r2, r3);
+        for (int w = 0; w < ATT_CWARPS; ++w) {
+          float wgt = exp2f(mml[(w * 16 + r) * 2] - muse);
+          acc = fmaf(mo[(w * 16 + r) * D + d], wgt, acc);
+          L = fmaf(mml[(w * 16 + r) * 2 + 1], wgt, L);
+        }
+        if (whole) {
+          store_out(p, ((int64_t)b * p.h_q + kvh * G + r) * D + d, __fdiv_rn(acc, L));
+        } else {
+          if (e == 0 && t0 == 0) p.part_desc[blockIdx.x * 2 + slot] = make_int4(b, kvh, share_first, share_last);
+          p.part_o[(pi + r) * D + d] = acc;
+          if (d == 0) {
+            p.part_ml[(pi + r) * 2 + 0] = mstar;
+            p.part_ml[(pi + r) * 2 + 1] = L;
+          }
         }
       }
-      __syncwarp();
+      asm volatile("bar.sync 1, %0;" ::"n"(ATT_CTHREADS));   // everyone has read the scratch and qs
       if (lane == 0) mbar_arrive(&bar_empty[st]);
-    }
-    if (!ok && lane == 0) atomicExch(p.status, 102);
-
-    // ---- combine the four warps (stage memory is free now: every load landed and was read)
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(ATT_CWARPS * 32));
-    float* mo = reinterpret_cast<float*>(stages);            // [warp][16][D]
-    float* mml = mo + ATT_CWARPS * 16 * D;                   // [warp][16][2]
-#pragma unroll
-    for (int i = 0; i < D / 8; ++i) {
-      int col = i * 8 + 2 * t4;
-      float* r0p = mo + ((warp * 16 + g4) * D) + col;
-      float* r1p = mo + ((warp * 16 + g4 + 8) * D) + col;
-      r0p[0] = o[i][0]; r0p[1] = o[i][1];
-      r1p[0] = o[i][2]; r1p[1] = o[i][3];
-    }
-    if (t4 == 0) {
-      mml[(warp * 16 + g4) * 2 + 0] = m_run[0];
-      mml[(warp * 16 + g4) * 2 + 1] = l_run[0];
-      mml[(warp * 16 + g4 + 8) * 2 + 0] = m_run[1];
-      mml[(warp * 16 + g4 + 8) * 2 + 1] = l_run[1];
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(ATT_CWARPS * 32));
-    for (int e = tid; e < G * D; e += ATT_CWARPS * 32) {
-      int r = e / D, d = e - r * D;
-      float mstar = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < ATT_CWARPS; ++w) mstar = fmaxf(mstar, mml[(w * 16 + r) * 2]);
-      float muse = (mstar == -INFINITY) ? 0.f : mstar;
-      float acc = 0.f, L = 0.f;
-#pragma unroll
-      for (int w = 0; w < ATT_CWARPS; ++w) {
-        float wgt = exp2f(mml[(w * 16 + r) * 2] - muse);
-        acc = fmaf(mo[(w * 16 + r) * D + d], wgt, acc);
-        L = fmaf(mml[(w * 16 + r) * 2 + 1], wgt, L);
-      }
-      int hq = kvh * G + r;
-      int64_t pi = ((int64_t)b * p.h_q + hq) * p.max_splits + split;
-      p.part_o[pi * D + d] = acc;
-      if (d == 0) {
-        p.part_ml[pi * 2 + 0] = mstar;
-        p.part_ml[pi * 2 + 1] = L;
-      }
+      g += t1 - t0;
     }
   }
-  __syncthreads();
 }
 
-// One CTA per (sequence, query head): fold the units in ascending order.
+// One CTA per (part slot, query row of the group): where the slot holds the first part of a pair
+// that the main kernel cut, fold the pair's parts in ascending order of their shares.
 template <int D>
-__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                  const int32_t* __restrict__ seq_len, void* __restrict__ o, int o_dtype, ActOut o_act,
-                                  int h_q, int l_max, int unit_len, int max_splits, int fused) {
+__global__ void attn_merge_kernel(const AttnParams p) {
   pdl_wait();
   pdl_trigger();
-  const int hq = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
-  int len_eff = __ldcg(seq_len + b) + (fused ? 1 : 0);
-  if (len_eff > l_max) len_eff = l_max;
-  int ns = len_eff > 0 ? (len_eff + unit_len - 1) / unit_len : 0;
-  int64_t base = ((int64_t)b * h_q + hq) * max_splits;
+  const int4 desc = __ldcg(p.part_desc + blockIdx.x);
+  if (desc.x < 0) return;
+  const int G = p.h_q / p.h_kv, r = blockIdx.y, d = threadIdx.x;
+  const int b = desc.x, kvh = desc.y, first = desc.z, last = desc.w;
+  const int64_t total = __ldcg(p.tiles_total);
+  // the first part sits in this very slot; every later share holds its part in slot 0 (it begins
+  // at the share's first tile); with more shares than tiles some shares in between hold no tile
+  auto empty = [&](int c) { return share_begin(c, total, p.shares) == share_begin(c + 1, total, p.shares); };
+  auto row_of = [&](int c) -> int64_t { return (c == first ? (int64_t)blockIdx.x : (int64_t)c * 2) * 16 + r; };
   float mstar = -INFINITY;
-  for (int s = 0; s < ns; ++s) mstar = fmaxf(mstar, __ldcg(part_ml + (base + s) * 2));
+  for (int c = first; c <= last; ++c)
+    if (!empty(c)) mstar = fmaxf(mstar, __ldcg(p.part_ml + row_of(c) * 2));
   float muse = (mstar == -INFINITY) ? 0.f : mstar;
   float acc = 0.f, L = 0.f;
-  for (int s = 0; s < ns; ++s) {
-    float wgt = exp2f(__ldcg(part_ml + (base + s) * 2) - muse);
-    acc = fmaf(__ldcg(part_o + (base + s) * D + d), wgt, acc);
-    L = fmaf(__ldcg(part_ml + (base + s) * 2 + 1), wgt, L);
+  for (int c = first; c <= last; ++c) {
+    if (empty(c)) continue;
+    const int64_t row = row_of(c);
+    float wgt = exp2f(__ldcg(p.part_ml + row * 2) - muse);
+    acc = fmaf(__ldcg(p.part_o + row * D + d), wgt, acc);
+    L = fmaf(__ldcg(p.part_ml + row * 2 + 1), wgt, L);
   }
-  float v = (ns > 0) ? __fdiv_rn(acc, L) : 0.f;
-  int64_t oi = ((int64_t)b * h_q + hq) * D + d;
-  if (o_dtype == LOGOS_ACT_PLANES) act_store(o_act, oi, v);
-  else if (o_dtype == LOGOS_F16) reinterpret_cast<__half*>(o)[oi] = __float2half_rn(v);
-  else if (o_dtype == LOGOS_BF16) reinterpret_cast<__nv_bfloat16*>(o)[oi] = __float2bfloat16_rn(v);
-  else reinterpret_cast<float*>(o)[oi] = v;
+  store_out(p, ((int64_t)b * p.h_q + kvh * G + r) * D + d, __fdiv_rn(acc, L));
 }
 
 __global__ void bump_seq_len_kernel(int32_t* seq_len, int b, int l_max) {
@@ -483,55 +615,45 @@ __global__ void kv_append_rope_kernel(__half* k_cache, __half* v_cache, const __
 }
 
 template <int D>
-constexpr size_t attn_smem_bytes() {
+size_t attn_smem_bytes(int64_t batch) {
   return 1024 + (size_t)ATT_STAGES * 2 * (D / 64) * ATT_BOX_BYTES + (size_t)16 * (D + 8) * 2 + (size_t)2 * D * 2 +
-         2 * ATT_STAGES * 8 + 64;
+         (size_t)ATT_CWARPS * 16 * 2 * 4 + 2 * ATT_STAGES * 8 + (size_t)(2 * batch + 1) * 4 + 64;
 }
 
-// Unit length and units per (sequence, KV head): a CTA pays about a tile's worth of time for its
-// prologue, its first load and its partial results, so units are at least four tiles where the
-// grid still fills the GPU (two CTAs per SM, a few waves), and at most eight, which keeps the
-// last wave short.
-void attn_plan(const AttnArgs& a, int64_t* unit_len, int* max_splits) {
-  int sms = sm_count(a.device);
-  int64_t total_pos = a.b * a.h_kv * a.l_max;
-  int64_t ul = (total_pos + (int64_t)sms * 5 - 1) / ((int64_t)sms * 5);
-  ul = ((ul + ATT_TILE - 1) / ATT_TILE) * ATT_TILE;
-  if (ul < 4 * ATT_TILE) ul = 4 * ATT_TILE;
-  if (ul > 8 * ATT_TILE) ul = 8 * ATT_TILE;
-  {
-    // same number of units, equal lengths: a context just past a multiple of the unit length
-    // would otherwise add one almost empty unit per (sequence, KV head), a CTA that is all prologue
-    const int64_t units = (a.l_max + ul - 1) / ul;
-    ul = (((a.l_max + units - 1) / units + ATT_TILE - 1) / ATT_TILE) * ATT_TILE;
-  }
-  *unit_len = ul;
-  *max_splits = (int)((a.l_max + ul - 1) / ul);
+// The persistent grid: the tile sequence is cut into this many shares, one per CTA.
+int attn_shares(const AttnArgs& a) {
+  const int sms = sm_count(a.device);
+  const int64_t tiles_max = (a.l_max + ATT_TILE - 1) / ATT_TILE;
+  int64_t g = 2ll * sms;   // two CTAs of about 113 KB of shared memory fit an SM
+  const int64_t most = a.b * a.h_kv * tiles_max;
+  if (g > most) g = most > 0 ? most : 1;
+  return (int)g;
 }
 
 template <int D>
 logos_status_t launch_attn_t(const AttnArgs& a, cudaStream_t st) {
+  if (a.b > ATT_MAX_BATCH)
+    return fail(LOGOS_OUT_OF_BOUNDS, "attention: batch %lld exceeds %d sequences per call", (long long)a.b, ATT_MAX_BATCH);
   const int64_t rows_total = a.b * a.h_kv * a.l_max;
   CUtensorMap mk, mv;
   LOGOS_TRY(make_tensor_map_2d(&mk, a.k_cache, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, D, rows_total, D * 2, 64, ATT_TILE,
                                CU_TENSOR_MAP_SWIZZLE_128B));
   LOGOS_TRY(make_tensor_map_2d(&mv, a.v_cache, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, D, rows_total, D * 2, 64, ATT_TILE,
                                CU_TENSOR_MAP_SWIZZLE_128B));
-  int64_t ul = 0;
-  int max_splits = 0;
-  attn_plan(a, &ul, &max_splits);
+  const int shares = attn_shares(a);
 
   void* scratch = nullptr;
-  int64_t po_bytes = a.b * a.h_q * max_splits * D * (int64_t)sizeof(float);
-  int64_t pml_bytes = a.b * a.h_q * max_splits * 2 * (int64_t)sizeof(float);
+  const int64_t po_bytes = (int64_t)shares * 2 * 16 * D * (int64_t)sizeof(float);
+  const int64_t pml_bytes = (int64_t)shares * 2 * 16 * 2 * (int64_t)sizeof(float);
+  const int64_t desc_bytes = (int64_t)shares * 2 * (int64_t)sizeof(int4) + 16;
   if (a.ext_scratch) {
-    if (po_bytes + pml_bytes > a.ext_scratch_bytes)
+    if (po_bytes + pml_bytes + desc_bytes > a.ext_scratch_bytes)
       return fail(LOGOS_OUT_OF_BOUNDS,
                   "attention: this shape needs %lld bytes of split-KV scratch, the fixed scratch holds %lld",
-                  (long long)(po_bytes + pml_bytes), (long long)a.ext_scratch_bytes);
+                  (long long)(po_bytes + pml_bytes + desc_bytes), (long long)a.ext_scratch_bytes);
     scratch = a.ext_scratch;
   } else {
-    LOGOS_TRY(scratch_get(a.device, 1, po_bytes + pml_bytes, &scratch));
+    LOGOS_TRY(scratch_get(a.device, 1, po_bytes + pml_bytes + desc_bytes, &scratch));
   }
 
   AttnParams p{};
@@ -545,22 +667,22 @@ logos_status_t launch_attn_t(const AttnArgs& a, cudaStream_t st) {
   p.k_cache = a.k_cache; p.v_cache = a.v_cache; p.rope = a.rope; p.seq_len = a.seq_len;
   p.part_o = reinterpret_cast<float*>(scratch);
   p.part_ml = reinterpret_cast<float*>(static_cast<char*>(scratch) + po_bytes);
+  p.part_desc = reinterpret_cast<int4*>(static_cast<char*>(scratch) + po_bytes + pml_bytes);
+  p.tiles_total = reinterpret_cast<int64_t*>(static_cast<char*>(scratch) + po_bytes + pml_bytes + desc_bytes - 16);
+  p.o = a.o; p.o_dtype = a.o_dtype; p.o_act = a.o_act;
   p.b = (int)a.b; p.h_q = (int)a.h_q; p.h_kv = (int)a.h_kv; p.l_max = (int)a.l_max;
-  p.unit_len = (int)ul; p.max_splits = max_splits;
+  p.shares = shares;
   p.scale_log2 = a.scale * 1.4426950408889634f;
   p.status = a.ext_status ? a.ext_status : kernel_status_ptr(a.device);
   if (!p.status) return fail(LOGOS_ERROR, "attention: no kernel status word");
 
-  constexpr size_t smem = attn_smem_bytes<D>();
+  const size_t smem = attn_smem_bytes<D>(a.b);
   LOGOS_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_attn_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dim3 grid(max_splits, (unsigned)a.h_kv, (unsigned)a.b);
-  LOGOS_CUDA_TRY(launch_kernel(gqa_decode_attn_kernel<D>, grid, dim3(ATT_THREADS), smem, st, mk, mv, p));
+  LOGOS_CUDA_TRY(launch_kernel(gqa_decode_attn_kernel<D>, dim3((unsigned)shares), dim3(ATT_THREADS), smem, st, mk, mv, p));
   count_launch(LK_ATTN);
   LOGOS_TRY(check_launch("gqa_decode_attn_kernel"));
-  dim3 mgrid((unsigned)a.h_q, (unsigned)a.b);
-  LOGOS_CUDA_TRY(launch_kernel(attn_merge_kernel<D>, mgrid, dim3(D), 0, st, (const float*)p.part_o,
-                               (const float*)p.part_ml, (const int32_t*)a.seq_len, a.o, a.o_dtype, a.o_act, (int)a.h_q,
-                               (int)a.l_max, (int)ul, (int)max_splits, (int)p.fused));
+  dim3 mgrid((unsigned)(2 * shares), (unsigned)(a.h_q / a.h_kv));
+  LOGOS_CUDA_TRY(launch_kernel(attn_merge_kernel<D>, mgrid, dim3(D), 0, st, p));
   count_launch(LK_ATTN_MERGE);
   LOGOS_TRY(check_launch("attn_merge_kernel"));
   if (a.bump_seq_len) {
@@ -585,10 +707,7 @@ void rope_table_host(float* out, int64_t l_max, int64_t d, double theta) {
 }
 
 int64_t attn_scratch_bytes(const AttnArgs& a) {
-  int64_t ul = 0;
-  int max_splits = 0;
-  attn_plan(a, &ul, &max_splits);
-  return a.b * a.h_q * max_splits * (a.d + 2) * (int64_t)sizeof(float);
+  return (int64_t)attn_shares(a) * 2 * (16 * (a.d + 2) * (int64_t)sizeof(float) + (int64_t)sizeof(int4)) + 16;
 }
 
 logos_status_t launch_gqa_decode_attn(const AttnArgs& a, cudaStream_t st) {
@@ -615,8 +734,10 @@ logos_status_t launch_kv_append_rope(__half* k_cache, __half* v_cache, const __h
 
 // ---------------------------------------------------------------- fixed-scratch variant
 // Scratch that lives in the library image instead of coming from cudaMalloc: every GPU
-// that loads the library holds these 16 MiB (+ one status word) until the process exits.
-constexpr int64_t kStaticScratchBytes = 16ll << 20;
+// that loads the library holds these 6 MiB (+ one status word) until the process exits.
+// The kernel needs two part slots of 16 x (D + 2) floats per CTA of its persistent grid (two
+// CTAs per SM): 4.7 MiB on a 148-SM B200 at D = 128; 6 MiB provide for 189 SMs.
+constexpr int64_t kStaticScratchBytes = 6ll << 20;
 static __device__ __align__(256) unsigned char g_static_attn_scratch[kStaticScratchBytes];
 static __device__ __align__(256) int g_static_attn_status[8];
 

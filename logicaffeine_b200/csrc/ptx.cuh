@@ -59,32 +59,6 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar_addr, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-#ifdef LOGOS_EXP_WAIT_HINT
-// try_wait with a suspend-time hint: the thread may sleep in hardware until the phase completes
-// or the hint (nanoseconds) runs out, instead of coming back to poll
-__device__ __forceinline__ bool mbar_try_hint(uint32_t bar_addr, uint32_t parity, uint32_t ns) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar_addr), "r"(parity), "r"(ns)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t a = smem_u32(bar);
-  if (mbar_try(a, parity)) return true;  // fast path: no clock read
-  const long long start = clock64();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 16; ++i)
-      if (mbar_try_hint(a, parity, LOGOS_EXP_WAIT_HINT)) return true;
-    if (clock64() - start > kWaitCycles) return false;
-  }
-}
-#else
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   const uint32_t a = smem_u32(bar);
   if (mbar_try(a, parity)) return true;  // fast path: no clock read
@@ -94,7 +68,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (clock64() - start > kWaitCycles) return false;
   }
 }
-#endif
 
 // ------------------------------------------------------------ TMA (tile mode, no multicast)
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {

@@ -3,10 +3,10 @@
 Some hosts cannot afford a device allocation inside an operator call: a server that gave
 the whole GPU to its own arena at start-up, or a decode loop whose latency budget has no
 room for the device-wide synchronisation an allocation implies.  For them
-logos_gqa_decode_attn_fixed_scratch keeps its split-KV partial results in a fixed 16 MiB
-array inside the library.  It runs the same kernels as logos_gqa_decode_attn, so on the
+logos_gqa_decode_attn_fixed_scratch keeps the partial results of the (sequence, KV head)
+pairs its persistent grid cuts in a fixed 6 MiB array inside the library.  It runs the same kernels as logos_gqa_decode_attn, so on the
 same inputs the two must agree bit for bit, call after call (the array keeps the previous
-call's contents), and a shape that does not fit must be refused, not truncated.
+call's contents), and a call beyond the stated maximum must be refused, not truncated.
 
 This file sorts last on purpose: if it fails under `pytest -x`, every other test has
 already run."""
@@ -59,15 +59,14 @@ def test_fixed_scratch_attention_matches_the_allocating_entry_point_twice(llm, o
 
 
 def test_fixed_scratch_refuses_what_does_not_fit(llm):
-    # 64 sequences x 128 query heads x 4 splits x 130 floats: 16.25 MiB of partials, more than the 16 MiB array
-    b, hq, hkv, d, lmax = 64, 128, 8, 128, 2048
-    tiny = llm.DeviceBuffer(16)
-    big_q = llm.DeviceBuffer(b * hq * d * 2)
+    # the most sequences one call takes is 2048 (a CTA keeps one tile count per sequence in shared memory)
+    b, hq, hkv, d, lmax = 2049, 2, 1, 64, 64
+    q = llm.DeviceBuffer(b * hq * d * 2)
     cache = llm.DeviceBuffer(b * hkv * lmax * d * 2)
     seq = llm.DeviceBuffer(b * 4)
     seq.memset(0)
     with pytest.raises(llm.LogosError) as e:
-        llm.gqaDecodeAttnFixedScratch(big_q, cache, cache, seq, big_q, b, hq, hkv, d, lmax, 0.1)
-    assert e.value.status == 4 and "fixed scratch" in str(e.value)
-    for x in (tiny, big_q, cache, seq):
+        llm.gqaDecodeAttnFixedScratch(q, cache, cache, seq, q, b, hq, hkv, d, lmax, 0.1)
+    assert e.value.status == 4 and "2048" in str(e.value)
+    for x in (q, cache, seq):
         x.free()
