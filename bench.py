@@ -521,9 +521,26 @@ def main():
     out_pinned = torch.empty(B, dtype=torch.int32).pin_memory()
     rng = np.random.default_rng(0)
     first_tokens = rng.integers(0, w["vocab"], B).astype(np.int32)
+    prefill_info = None
     if args.prefill == "prompt":
         prompts = rng.integers(0, w["vocab"], (B, ctx)).astype(np.int32)
-        model.prefill(prompts)
+        torch.cuda.synchronize()
+        t_pf = time.perf_counter()
+        model.prefill(prompts)      # returns after the device has finished
+        pf_s = max_over_ranks(time.perf_counter() - t_pf)
+        # useful arithmetic: 2 FLOP per weight and token; the tensor cores issue twice that (two fp16
+        # activation planes keep f32-class accuracy); attention's share is small and left out
+        weights = gemm_weight_bytes(dict(w), 1) / 1.125
+        useful = 2.0 * weights * B * ctx
+        bf16_sustained = None
+        pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(pk):
+            with open(pk) as f:
+                bf16_sustained = float(json.load(f).get("bf16_tflops_sustained", 0)) or None
+        prefill_info = {"tokens": int(B * ctx), "seconds": pf_s, "tokens_per_s": B * ctx / pf_s,
+                        "useful_tflops": useful / pf_s / 1e12, "issued_tflops": 2 * useful / pf_s / 1e12,
+                        "tensor_frac_of_bf16_sustained": (2 * useful / pf_s / 1e12 / bf16_sustained) if bf16_sustained else None,
+                        "how": "chunks of positions through every layer (rows = batch x chunk), host wall clock around the call"}
         first_tokens = model.decodeStep()
         ctx = ctx + 1
     else:
@@ -631,7 +648,7 @@ def main():
         "kernels_ms_per_step": cls,
         "attention": {"achieved": attn_gbs, "unit": "GB/s", "frac": attn_gbs / peak, "context": mid_len},
         "clocks": clocks, "setup_s": setup_s, "launch_counts": llm.launchCounts(),
-        "tokens_crc": tokens_crc, "tokens_check": tokens_check, "tp_parity": tp_parity,
+        "tokens_crc": tokens_crc, "tokens_check": tokens_check, "tp_parity": tp_parity, "prefill": prefill_info,
     }
 
     if rank == 0 and world == 1 and not args.no_extras:

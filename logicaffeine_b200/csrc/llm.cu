@@ -51,6 +51,19 @@ struct Layer {
   __half *kc = nullptr, *vc = nullptr;
 };
 
+// Buffers of the chunked prompt pass: one row per (sequence, position of the chunk).
+struct PrefillWs {
+  int64_t rows = 0;          // capacity
+  float*  h = nullptr;       // [rows][H] residual stream
+  float*  delta = nullptr;   // [rows][H] output of the last row-parallel GEMM, folded in by the next norm
+  ActOut  xn;                // [rows][H]
+  float*  qkv = nullptr;     // [rows][nqkv]
+  __half* q16 = nullptr;     // [rows][nq] rotated queries
+  ActOut  att;               // [rows][nq]
+  ActOut  ffn;               // [rows][f_local]
+  int32_t* tok = nullptr;    // [rows]
+};
+
 struct Model {
   logos_llm_config_t cfg;
   int device = 0;
@@ -95,6 +108,7 @@ struct Model {
   int64_t launches_per_step = 0;
   int64_t launch_counter = 0;
   std::vector<void*> allocs;
+  PrefillWs pf;
   // per-class device timing of one step (logos_llm_profile_step)
   bool profiling = false;
   std::vector<cudaEvent_t> prof_events;
@@ -476,6 +490,39 @@ logos_status_t norm_step(Model* m, int parts, int64_t gain_row) {
   return launch_residual_rmsnorm(m->h, m->partials, parts, B * H, g, m->xn, B, H, c.rms_eps, m->stream);
 }
 
+// The end of a step: final norm (folding `parts` pending partial sums), lm_head, token choice (when
+// `sample`), then the lengths advance.
+logos_status_t step_tail(Model* m, int parts, bool sample, bool log_tokens, const int32_t* prompt_len, int prompt_step) {
+  const logos_llm_config_t& c = m->cfg;
+  const int64_t B = c.batch, H = c.hidden;
+  cudaStream_t st = m->stream;
+  if (sample) {
+    LOGOS_TRY(norm_step(m, parts, 2 * c.layers));
+    GemmArgs g;
+    g.a = m->xn.hi; g.a_lo = m->xn.lo; g.a_dtype = LOGOS_F16; g.lda = H;
+    g.q = m->head.q; g.s = m->head.s; g.q_tiled = m->head.tiled;
+    g.c = m->logits; g.c_dtype = LOGOS_F32; g.ldc = c.vocab;
+    g.m = B; g.n = c.vocab; g.k = H;
+    g.device = m->device;
+    {
+      ProfScope ps(m, PROF_GEMM);
+      LOGOS_TRY(launch_q8_gemm(g, st));
+    }
+    ProfScope ps(m, PROF_ELEMWISE);
+    // seq_len still holds the position of the token this step consumed (bump_len_kernel runs last)
+    LOGOS_TRY(launch_argmax(m->logits, m->tokens, log_tokens ? m->history : nullptr, m->step_counter, m->history_cap, B,
+                            c.vocab, m->sampling, m->seq_len, prompt_len, prompt_step, st));
+    m->launch_counter += 3;
+  }
+  ProfScope ps_tail(m, PROF_ELEMWISE);
+  LOGOS_CUDA_TRY(launch_kernel(bump_len_kernel, dim3((unsigned)((B + 127) / 128)), dim3(128), 0, st, m->seq_len,
+                               m->step_counter, (int)B, (int)c.l_max, prompt_len, prompt_step));
+  LOGOS_TRY(check_launch("bump_len_kernel"));
+  m->launch_counter += 1;
+  m->launches_per_step = m->launch_counter;
+  return LOGOS_OK;
+}
+
 // One lock-step decode step on the model's stream.  tokens_in: [B] device.
 // prompt_len ([B] device, ragged prompts only) with prompt_step: sequences whose prompt is over
 // (prompt_step >= prompt_len[i]) run through the step without advancing - their K/V row lands at
@@ -550,30 +597,147 @@ logos_status_t step(Model* m, const int32_t* tokens_in, bool sample, bool log_to
     LOGOS_TRY(gemm_partials(m, m->ffn, L.wd, &parts));
     LOGOS_TRY(debug_check(m, "down_proj gemm", l));
   }
-  if (sample) {
-    LOGOS_TRY(norm_step(m, parts, 2 * c.layers));
-    GemmArgs g;
-    g.a = m->xn.hi; g.a_lo = m->xn.lo; g.a_dtype = LOGOS_F16; g.lda = H;
-    g.q = m->head.q; g.s = m->head.s; g.q_tiled = m->head.tiled;
-    g.c = m->logits; g.c_dtype = LOGOS_F32; g.ldc = c.vocab;
-    g.m = B; g.n = c.vocab; g.k = H;
-    g.device = m->device;
-    {
-      ProfScope ps(m, PROF_GEMM);
-      LOGOS_TRY(launch_q8_gemm(g, st));
+  return step_tail(m, parts, sample, log_tokens, prompt_len, prompt_step);
+}
+
+// h[b] = ws.h[row(b)] + ws.delta[row(b)] for the last prompt position of every sequence: the rows the
+// end of the step (final norm, lm_head, token choice) runs on.
+__global__ void gather_last_rows_kernel(float* __restrict__ h, const float* __restrict__ src, const float* __restrict__ delta,
+                                        int64_t hidden, int64_t chunk) {
+  pdl_wait();
+  pdl_trigger();
+  const int64_t b = blockIdx.x, row = b * chunk + chunk - 1;
+  for (int64_t e = threadIdx.x; e < hidden; e += blockDim.x)
+    h[b * hidden + e] = __fadd_rn(__ldcg(src + row * hidden + e), __ldcg(delta + row * hidden + e));
+}
+
+bool chunked_prefill_enabled() {
+  const char* e = getenv("LOGOS_B200_PREFILL");
+  return !(e && (e[0] == 'l' || e[0] == '0'));   // "loop" or "0": prompts run through the decode step token by token
+}
+
+logos_status_t prefill_workspace(Model* m, int64_t rows) {
+  PrefillWs& w = m->pf;
+  if (w.rows >= rows) return LOGOS_OK;
+  const logos_llm_config_t& c = m->cfg;
+  const int64_t H = c.hidden;
+  auto planes = [&](ActOut* a, int64_t elems) -> logos_status_t {
+    a->mode = c.act_dtype;
+    LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&a->hi), elems * 2));
+    if (c.act_dtype == LOGOS_F32) LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&a->lo), elems * 2));
+    return LOGOS_OK;
+  };
+  // (a model is given one workspace, sized by the first prompt pass: later passes use chunks that fit it)
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&w.h), rows * H * 4));
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&w.delta), rows * H * 4));
+  LOGOS_TRY(planes(&w.xn, rows * H));
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&w.qkv), rows * m->nqkv * 4));
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&w.q16), rows * m->nq * 2));
+  LOGOS_TRY(planes(&w.att, rows * m->nq));
+  LOGOS_TRY(planes(&w.ffn, rows * m->f_local));
+  LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&w.tok), rows * 4));
+  w.rows = rows;
+  return LOGOS_OK;
+}
+
+// The prompt pass proper: chunks of positions, every sequence's chunk at once (rows = batch x chunk),
+// so that each weight matrix is streamed once per chunk instead of once per token.  Per layer:
+// norm -> qkv GEMM -> RoPE + KV write + causal attention -> o_proj GEMM -> norm -> gate/up GEMM
+// with SwiGLU -> down GEMM, the same kernels and the same arithmetic as a decode step, on more rows.
+// tokens_host: [B][t].  Leaves the cache filled for positions [0, t), the lengths at t and the
+// token chosen after the last prompt position as the current token.
+logos_status_t prefill_chunked(Model* m, const int32_t* tokens_host, int64_t t) {
+  const logos_llm_config_t& c = m->cfg;
+  const int64_t B = c.batch, H = c.hidden, D = c.head_dim;
+  cudaStream_t st = m->stream;
+  // rows per chunk: enough token tiles that the GEMMs fill the GPU several times over while the
+  // chunk's activations stay inside L2 (LOGOS_B200_PREFILL_ROWS overrides: tests use small chunks)
+  int64_t target_rows = 4096;
+  if (const char* e = getenv("LOGOS_B200_PREFILL_ROWS")) target_rows = std::max<int64_t>(1, atoll(e));
+  int64_t chunk = std::max<int64_t>(1, target_rows / B);
+  if (m->pf.rows > 0 && chunk * B > m->pf.rows) chunk = std::max<int64_t>(1, m->pf.rows / B);
+  if (chunk > t) chunk = t;
+  if (chunk < 1) chunk = 1;
+  LOGOS_TRY(prefill_workspace(m, B * chunk));
+  PrefillWs& w = m->pf;
+  PdlScope pdl(pdl_enabled());
+  LOGOS_CUDA_TRY(cudaMemsetAsync(m->seq_len, 0, (size_t)B * 4, st));
+  std::vector<int32_t> rows_tok;
+  for (int64_t p0 = 0; p0 < t; p0 += chunk) {
+    const int64_t cn = std::min(chunk, t - p0), M = B * cn;
+    rows_tok.assign((size_t)M, 0);
+    for (int64_t b = 0; b < B; ++b)
+      for (int64_t j = 0; j < cn; ++j) rows_tok[(size_t)(b * cn + j)] = tokens_host[b * t + p0 + j];
+    LOGOS_CUDA_TRY(cudaMemcpyAsync(w.tok, rows_tok.data(), (size_t)M * 4, cudaMemcpyHostToDevice, st));
+    LOGOS_CUDA_TRY(cudaStreamSynchronize(st));   // rows_tok is reused by the next chunk
+    LOGOS_TRY(launch_embed(w.tok, m->embed.q, m->embed.s, w.h, M, H, m->embed.tiled ? 1 : 0, st));
+    auto gemm = [&](const ActOut& a, const Q8Mat& wt, int64_t k, GemmArgs g) -> logos_status_t {
+      g.a = a.hi; g.a_lo = a.lo; g.a_dtype = LOGOS_F16; g.lda = k;
+      g.q = wt.q; g.s = wt.s; g.q_tiled = wt.tiled;
+      g.m = M; g.n = wt.n; g.k = k;
+      g.device = m->device;
+      return launch_q8_gemm(g, st);
+    };
+    auto reduce_delta = [&]() -> logos_status_t {
+      if (m->tp.degree > 1) return tp_allreduce_sum_f32(&m->tp, w.delta, M * H, st);
+      return LOGOS_OK;
+    };
+    for (int64_t l = 0; l < c.layers; ++l) {
+      Layer& L = m->layers[(size_t)l];
+      LOGOS_TRY(launch_residual_rmsnorm(w.h, w.delta, l == 0 ? 0 : 1, M * H, m->gains + (2 * l) * H, w.xn, M, H, c.rms_eps, st));
+      {
+        GemmArgs g;
+        g.c = w.qkv; g.c_dtype = LOGOS_F32; g.ldc = m->nqkv;
+        LOGOS_TRY(gemm(w.xn, L.wqkv, H, g));
+      }
+      {
+        PrefillAttnArgs a;
+        a.qkv = w.qkv; a.qkv_ld = m->nqkv; a.qkv_bias = L.bqkv; a.rope = m->rope; a.q16 = w.q16;
+        a.k_cache = L.kc; a.v_cache = L.vc; a.o = w.att;
+        a.b = B; a.h_q = m->hq_local; a.h_kv = m->hkv_local; a.d = D; a.l_max = c.l_max; a.chunk = cn; a.pos0 = p0;
+        a.scale = 1.0f / sqrtf((float)D);
+        a.device = m->device;
+        LOGOS_TRY(launch_prefill_attn(a, st));
+      }
+      {
+        GemmArgs g;
+        g.c = w.delta; g.c_dtype = LOGOS_F32; g.ldc = H;
+        LOGOS_TRY(gemm(w.att, L.wo, m->nq, g));
+        LOGOS_TRY(reduce_delta());
+      }
+      LOGOS_TRY(launch_residual_rmsnorm(w.h, w.delta, 1, M * H, m->gains + (2 * l + 1) * H, w.xn, M, H, c.rms_eps, st));
+      {
+        GemmArgs g;
+        g.c_dtype = LOGOS_ACT_PLANES; g.c_act = w.ffn; g.ldc = m->f_local;
+        g.epilogue = EPI_SWIGLU;
+        LOGOS_TRY(gemm(w.xn, L.wgu, H, g));
+      }
+      {
+        GemmArgs g;
+        g.c = w.delta; g.c_dtype = LOGOS_F32; g.ldc = H;
+        LOGOS_TRY(gemm(w.ffn, L.wd, m->f_local, g));
+        LOGOS_TRY(reduce_delta());
+      }
+      LOGOS_TRY(debug_check(m, "prefill layer", l));
     }
-    ProfScope ps(m, PROF_ELEMWISE);
-    // seq_len still holds the position of the token this step consumed (bump_len_kernel runs last)
-    LOGOS_TRY(launch_argmax(m->logits, m->tokens, log_tokens ? m->history : nullptr, m->step_counter, m->history_cap, B,
-                            c.vocab, m->sampling, m->seq_len, prompt_len, prompt_step, st));
-    m->launch_counter += 3;
+    if (p0 + cn >= t) {
+      // the last position of every sequence: fold the pending delta, then the ordinary end of a step
+      LOGOS_CUDA_TRY(launch_kernel(gather_last_rows_kernel, dim3((unsigned)B), dim3(256), 0, st, m->h, (const float*)w.h,
+                                   (const float*)w.delta, H, cn));
+      LOGOS_TRY(check_launch("gather_last_rows_kernel"));
+    }
   }
-  ProfScope ps_tail(m, PROF_ELEMWISE);
-  LOGOS_CUDA_TRY(launch_kernel(bump_len_kernel, dim3((unsigned)((B + 127) / 128)), dim3(128), 0, st, m->seq_len,
-                               m->step_counter, (int)B, (int)c.l_max, prompt_len, prompt_step));
-  LOGOS_TRY(check_launch("bump_len_kernel"));
-  m->launch_counter += 1;
-  m->launches_per_step = m->launch_counter;
+  {
+    std::vector<int32_t> len((size_t)B, (int32_t)(t - 1));   // the position the last prompt token sits at
+    LOGOS_CUDA_TRY(cudaMemcpyAsync(m->seq_len, len.data(), (size_t)B * 4, cudaMemcpyHostToDevice, st));
+    LOGOS_CUDA_TRY(cudaStreamSynchronize(st));
+  }
+  m->launch_counter = 0;
+  LOGOS_TRY(step_tail(m, 0, true, false, nullptr, 0));
+  LOGOS_CUDA_TRY(cudaStreamSynchronize(st));
+  int code = 0;
+  LOGOS_TRY(kernel_status_read(m->device, &code, false));
+  if (code != 0) return fail(LOGOS_ERROR, "a device-side wait gave up during the prompt pass (kernel status %d)", code);
   return LOGOS_OK;
 }
 
@@ -849,6 +1013,7 @@ logos_status_t logos_llm_prefill(logos_handle_t model, const int32_t* tokens_hos
     for (int64_t i = 0; i < B * t; ++i)
       if (tokens_host[i] < 0 || tokens_host[i] >= m->cfg.vocab)
         return fail(LOGOS_OUT_OF_BOUNDS, "logos_llm_prefill: token id %d outside the vocabulary", tokens_host[i]);
+    if (chunked_prefill_enabled()) return prefill_chunked(m, tokens_host, t);
     if (m->prompt_cap < B * t) {
       LOGOS_TRY(dmalloc(m, reinterpret_cast<void**>(&m->prompt), B * t * 4));
       m->prompt_cap = B * t;

@@ -119,6 +119,23 @@ logos_status_t launch_kv_append_rope(__half* k_cache, __half* v_cache, const __h
                                      int64_t l_max, int device, cudaStream_t st);
 void rope_table_host(float* out, int64_t l_max, int64_t d, double theta);
 
+// ---- prompt processing (prefill.cu): RoPE + KV write + causal attention for a chunk of prompt
+// positions [pos0, pos0 + chunk) of every sequence; rows are ordered (sequence, position).
+struct PrefillAttnArgs {
+  const float*  qkv = nullptr;       // [b * chunk][qkv_ld] f32: q | k | v heads of a row, un-rotated
+  int64_t       qkv_ld = 0;
+  const float*  qkv_bias = nullptr;  // f32 [(Hq + 2 Hkv) * D] or null
+  const float*  rope = nullptr;      // [Lmax][D/2][2]
+  __half*       q16 = nullptr;       // scratch [b * chunk][Hq * D]: the rotated queries
+  __half*       k_cache = nullptr;   // [B][Hkv][Lmax][D]
+  __half*       v_cache = nullptr;
+  ActOut        o;                   // planes [b * chunk][Hq * D]
+  int64_t       b = 0, h_q = 0, h_kv = 0, d = 0, l_max = 0, chunk = 0, pos0 = 0;
+  float         scale = 1.f;
+  int           device = 0;
+};
+logos_status_t launch_prefill_attn(const PrefillAttnArgs& a, cudaStream_t st);
+
 // ---- norms and element-wise (elementwise.cu)
 logos_status_t launch_rmsnorm_f32(const float* x, const float* g, float* y, int64_t rows, int64_t h, float eps,
                                   cudaStream_t st);

@@ -115,12 +115,12 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partials, int spl
 }  // namespace
 
 int gemm_pick_splits(int64_t m, int64_t n, int64_t k, int device) {
-  (void)m;
   // Work units are (tile of 128 weight rows) x (K split); a CTA's time is a fixed part (pipeline
   // fill, epilogue: about twelve stage times, measured) plus its K stages, and CTAs run in
   // rounds of one per SM.  Take the split count with the smallest rounds x (fixed + stages);
   // ties go to fewer splits (fewer partials to write and fold).
-  const int64_t tiles = (n + 127) / 128;
+  // (a row tile for each token tile of 64 is a unit of its own: with many tokens there are enough)
+  const int64_t tiles = ((n + 127) / 128) * ((m + 63) / 64 > 0 ? (m + 63) / 64 : 1);
   const int64_t stages = k / 128;
   const int sms = sm_count(device);
   if (tiles >= sms || stages < 8) return 1;

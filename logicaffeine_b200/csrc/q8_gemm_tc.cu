@@ -95,7 +95,8 @@ struct TcParams {
   float* partials;
   int splits;
   int stages_total;
-  int items;        // work items: row tiles x splits
+  int items;        // (row tile, K split) pairs
+  int mtiles;       // token tiles of MT rows; a work unit is (item, token tile), token tile fastest
   int store_mode;
   int tiled;        // weights are tile-major: the map is [row tiles x K tiles x 128][128 B]
   int* status;
@@ -214,10 +215,12 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const int64_t m0 = (int64_t)blockIdx.z * MT;
-  const int items = p.items;
+  // Work units u = item * mtiles + token tile: CTAs that run side by side hold consecutive units,
+  // i.e. the same weight tile for neighbouring token tiles, so with many tokens (prefill) a
+  // weight tile crosses HBM once and is served to the other token tiles by L2.
+  const int units = p.items * p.mtiles;
 #ifdef LOGOS_TC_TRACE
-  const bool cta0 = p.trace && blockIdx.x == 0 && blockIdx.z == 0;
+  const bool cta0 = p.trace && blockIdx.x == 0;
   bool trace_on = cta0;
 #endif
 
@@ -268,7 +271,8 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     if (lane == 0) {
       const uint64_t pol = policy_evict_first();
       int gs = 0;
-      for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
+      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        const int w = u / p.mtiles;
         const TcItem it = tc_item(p, w);
         const int n0 = it.tile * TC_ROWS, nst = it.nst, st_begin = it.st_begin;
         TC_TRACE_ITEM(w);
@@ -303,7 +307,9 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       pdl_wait();  // the activations are the previous kernel's output
       const uint64_t pol = policy_evict_last();
       int gs = 0;
-      for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
+      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        const int w = u / p.mtiles;
+        const int m0 = (u - w * p.mtiles) * MT;
         const TcItem it = tc_item(p, w);
         const int nst = it.nst, st_begin = it.st_begin;
         TC_TRACE_ITEM(w);
@@ -339,7 +345,8 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     static_assert(ACC_PAIRS == 2, "one accumulator ring entry per MMA warp");
     const int pr = warp - 2;
     int gs = 0;
-    for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
+    for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+      const int w = u / p.mtiles;
       const int nst = tc_item(p, w).nst;
       TC_TRACE_ITEM(w);
       for (int i = 0; i < nst && ok; ++i, ++gs) {
@@ -397,7 +404,8 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const uint32_t row = qd * 32 + lane;
     const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16);
     int gs = 0;
-    for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
+    for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+      const int w = u / p.mtiles;
       const int nst = tc_item(p, w).nst;
       TC_TRACE_ITEM(w);
       for (int i = 0; i < nst; ++i, ++gs) {
@@ -446,11 +454,13 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16) + ACC_COL0 + half * HC;
     const int64_t kb_per_row = p.k >> 5;
     const int et = tid - DRAIN_WARP0 * 32;  // 0..255 among the drain warps
-    const int64_t rows_here = (p.m - m0 < MT) ? (p.m - m0) : MT;
     pdl_wait();  // before any write to global memory (nothing to drain before the activations are in anyway)
     bool stored = false;  // thread et == 0: a TMA store of this CTA may still be reading the staging tile
     int gs = 0;
-    for (int w = blockIdx.x; w < items; w += gridDim.x) {
+    for (int u = blockIdx.x; u < units; u += gridDim.x) {
+      const int w = u / p.mtiles;
+      const int64_t m0 = (int64_t)(u - w * p.mtiles) * MT;
+      const int64_t rows_here = (p.m - m0 < MT) ? (p.m - m0) : MT;
       const TcItem it = tc_item(p, w);
       const int nst = it.nst, st_begin = it.st_begin;
       const int64_t n0 = (int64_t)it.tile * TC_ROWS;
@@ -758,9 +768,13 @@ logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
   }
 
   LOGOS_CUDA_TRY(cudaFuncSetAttribute(q8_gemm_tc_kernel<MT, LIMBS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
-  // persistent CTAs: one per SM at most, each takes items blockIdx.x, blockIdx.x + gridDim.x, ...
+  // persistent CTAs: one per SM at most, each takes units blockIdx.x, blockIdx.x + gridDim.x, ...
   const int sms = sm_count(g.device);
-  dim3 grid((unsigned)(p.items < sms ? p.items : sms), 1u, (unsigned)((g.m + MT - 1) / MT));
+  const int64_t mtiles = (g.m + MT - 1) / MT;
+  if ((int64_t)p.items * mtiles > INT32_MAX) return fail(LOGOS_OUT_OF_BOUNDS, "q8_gemm: too many work units");
+  p.mtiles = (int)mtiles;
+  const int64_t units = (int64_t)p.items * mtiles;
+  dim3 grid((unsigned)(units < sms ? units : sms), 1u, 1u);
   LOGOS_CUDA_TRY(launch_kernel(q8_gemm_tc_kernel<MT, LIMBS>, grid, dim3(TC_THREADS), Cfg::SMEM, st, mq, mhi, mlo, mo0, mo1, p));
   count_launch(LK_GEMM_TC);
   return check_launch("q8_gemm_tc_kernel");

@@ -270,3 +270,60 @@ def test_captured_step_survives_a_larger_stand_alone_call(llm, oracle):
     assert llm.kernelStatus() == 0
     gpu.free()
     ref.close()
+
+
+@pytest.mark.parametrize("rows", ["20", "loop"])
+def test_prompt_pass_in_chunks_and_token_by_token_agree_with_the_oracle(llm, oracle, rows, monkeypatch):
+    """The prompt pass runs chunks of positions of every sequence at once (rows = batch x chunk).  With
+    20 rows per chunk a 13-token prompt of 4 sequences takes chunks of 5, 5 and 3 positions, so the
+    later chunks attend over K/V rows the earlier ones wrote; "loop" is the token-by-token pass
+    through the decode step.  Both must give the oracle's logits, tokens and KV cache."""
+    O = oracle
+    if rows == "loop":
+        monkeypatch.setenv("LOGOS_B200_PREFILL", "loop")
+    else:
+        monkeypatch.setenv("LOGOS_B200_PREFILL_ROWS", rows)
+    cfg = dict(SMALL, seed=12)
+    t, steps = 13, 12
+    toks = O.synth_fill(O.I32, 3, cfg["seed"], 999, 0, cfg["batch"] * t, 0.0, float(cfg["vocab"])).reshape(cfg["batch"], t)
+    ref = O.Llm(tp_degree=1, tp_rank=0, device=0, act_dtype=O.F32, **cfg)
+    ref.prefill(toks)
+    gpu = llm.Llm(**cfg)
+    gpu.prefill(toks)
+    assert rel_l2(gpu.readLogits(), ref.read_logits()) < 1e-4
+    assert (gpu.readSeqLen() == t).all()
+    for layer in (0, cfg["layers"] - 1):
+        k, v = gpu.readKv(layer)
+        kr, vr = ref.read_kv(layer)
+        assert not k[:, :, t:].any() and not v[:, :, t:].any()          # nothing written past the prompt
+        assert rel_l2(O.f16_to_f32(k), O.f16_to_f32(kr)) < 2e-4
+        assert rel_l2(O.f16_to_f32(v), O.f16_to_f32(vr)) < 2e-4
+        frac = max(np.mean(k[:, :, :t] != kr[:, :, :t]), np.mean(v[:, :, :t] != vr[:, :, :t]))
+        assert frac < (0.01 if layer == 0 else 0.25)                      # fp16 last-place flips only
+    want = np.array([ref.decode_step().copy() for _ in range(steps)])
+    assert np.array_equal(gpu.decodeSteps(steps), want)
+    assert llm.kernelStatus() == 0
+    gpu.free()
+    ref.close()
+
+
+def test_prompt_pass_with_seven_query_heads_per_kv_head_and_a_second_prompt(llm, oracle, monkeypatch):
+    """Config 3's head grouping (14 query / 2 KV heads: 7 per group, two positions and two padding
+    rows per MMA tile) in several chunks; then a second, shorter prompt on the same model (the
+    workspace of the first pass is reused, the cache is overwritten from position 0)."""
+    O = oracle
+    monkeypatch.setenv("LOGOS_B200_PREFILL_ROWS", "33")
+    cfg = dict(layers=2, hidden=896, h_q=14, h_kv=2, head_dim=64, ffn=512, vocab=1024, l_max=160, batch=3,
+               rms_eps=1e-6, rope_theta=1e6, tied_embeddings=1, seed=3, init_std=0.02)
+    gpu = llm.Llm(**cfg)
+    for t in (70, 9):
+        toks = O.synth_fill(O.I32, 3, cfg["seed"], 900 + t, 0, cfg["batch"] * t, 0.0, float(cfg["vocab"])).reshape(cfg["batch"], t)
+        ref = O.Llm(tp_degree=1, tp_rank=0, device=0, act_dtype=O.F32, **cfg)
+        ref.prefill(toks)
+        gpu.prefill(toks)
+        assert rel_l2(gpu.readLogits(), ref.read_logits()) < 1e-4
+        want = np.array([ref.decode_step().copy() for _ in range(6)])
+        assert np.array_equal(gpu.decodeSteps(6), want)
+        ref.close()
+    assert llm.kernelStatus() == 0
+    gpu.free()
