@@ -48,8 +48,13 @@ __device__ __forceinline__ int xs4_index(int chunk, int j) { return (chunk >> 5)
 // A warp owns one row.  For each super-chunk of 4096 columns a lane first issues
 // all of its eight 128-bit weight loads (and the eight scales), and only then
 // waits for x to be staged, so the HBM stream starts at the first instruction.
+// What decides the speed is the bytes an SM keeps in flight: the launch bound caps the
+// kernel at 64 registers so that four CTAs share an SM (128 KB of loads in flight, and the
+// 512 CTAs of a 4096-row matrix are one wave); with three CTAs per SM the same code
+// measured 3.2 instead of 3.4 TB/s at 4096 x 4096 and 4.05 instead of 4.3 TB/s at
+// 152064 x 5120.
 template <bool X_IN_SMEM>
-__global__ void __launch_bounds__(GEMV_WARPS * 32)
+__global__ void __launch_bounds__(GEMV_WARPS * 32, 4)
 q8_gemv_kernel(const int8_t* __restrict__ q, const float* __restrict__ s, const float* __restrict__ x,
                float* __restrict__ y, int64_t n, int64_t k) {
   extern __shared__ float4 xs4[];
