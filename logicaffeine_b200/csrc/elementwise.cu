@@ -80,13 +80,17 @@ __global__ void embed_kernel(const int32_t* __restrict__ tokens, const int8_t* _
 }
 
 // One CTA per row, 128-bit accesses: fold the split-K partials into the residual
-// stream in ascending order, keep the updated row in shared memory, reduce the
-// sum of squares, then write the normalised row as activation planes.
+// stream in ascending order, keep the updated row on chip, reduce the sum of squares,
+// then write the normalised row as activation planes.  Rows of up to 8192 floats stay in
+// registers (IN_REGS): the kernel then uses no dynamic shared memory, so under a dependent
+// launch the next GEMM's CTAs, which take nearly a whole SM's shared memory, can start beside
+// it and fetch their first weights while the norm finishes.  Longer rows go through shared memory.
+template <bool IN_REGS>
 __global__ void __launch_bounds__(512)
 residual_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int parts, int64_t part_stride,
                         const float* __restrict__ g, ActOut xn, int64_t hidden, float eps) {
   __shared__ float red[32];
-  extern __shared__ float4 row_cache4[];  // hidden floats
+  extern __shared__ float4 row_cache4[];  // hidden floats (not IN_REGS)
   float* row_cache = reinterpret_cast<float*>(row_cache4);
   // h and the partials come from kernels of the same step: wait for them, and read them past L1
   pdl_wait();
@@ -94,6 +98,48 @@ residual_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, 
   const int64_t row = blockIdx.x;
   float* hr = h + row * hidden;
   float ss = 0.f;
+  if (IN_REGS) {
+    constexpr int PER = 4;   // float4 per thread: 512 threads x 4 x 4 floats = 8192
+    const int64_t n4 = hidden >> 2;
+    float4* hr4 = reinterpret_cast<float4*>(hr);
+    float4 v[PER];
+#pragma unroll
+    for (int u = 0; u < PER; ++u) {
+      const int64_t i = threadIdx.x + (int64_t)u * 512;
+      v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < n4) {
+        v[u] = __ldcg(hr4 + i);
+        for (int p = 0; p < parts; ++p) {
+          const float4 d = __ldcg(reinterpret_cast<const float4*>(delta + (int64_t)p * part_stride + row * hidden) + i);
+          v[u].x = __fadd_rn(v[u].x, d.x); v[u].y = __fadd_rn(v[u].y, d.y);
+          v[u].z = __fadd_rn(v[u].z, d.z); v[u].w = __fadd_rn(v[u].w, d.w);
+        }
+        if (parts > 0) hr4[i] = v[u];
+      }
+    }
+    // the same order of additions as the strided loop over the row: element i of thread t is t + 512 u
+#pragma unroll
+    for (int u = 0; u < PER; ++u) {
+      ss = fmaf(v[u].x, v[u].x, ss); ss = fmaf(v[u].y, v[u].y, ss);
+      ss = fmaf(v[u].z, v[u].z, ss); ss = fmaf(v[u].w, v[u].w, ss);
+    }
+    ss = block_sum(ss, red);
+    const float inv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hidden), eps)));
+    const float4* g4 = reinterpret_cast<const float4*>(g);
+#pragma unroll
+    for (int u = 0; u < PER; ++u) {
+      const int64_t i = threadIdx.x + (int64_t)u * 512;
+      if (i < n4) {
+        const float4 gg = g4[i];
+        const int64_t e = row * hidden + 4 * i;
+        act_store(xn, e + 0, __fmul_rn(__fmul_rn(v[u].x, inv), gg.x));
+        act_store(xn, e + 1, __fmul_rn(__fmul_rn(v[u].y, inv), gg.y));
+        act_store(xn, e + 2, __fmul_rn(__fmul_rn(v[u].z, inv), gg.z));
+        act_store(xn, e + 3, __fmul_rn(__fmul_rn(v[u].w, inv), gg.w));
+      }
+    }
+    return;
+  }
   if ((hidden & 3) == 0) {
     const int64_t n4 = hidden >> 2;
     float4* hr4 = reinterpret_cast<float4*>(hr);
@@ -453,11 +499,16 @@ logos_status_t launch_residual_rmsnorm(float* h, const float* delta, int parts, 
                                        const float* g, ActOut xn, int64_t rows, int64_t hidden, float eps,
                                        cudaStream_t st) {
   if (rows == 0) return LOGOS_OK;
-  size_t smem = sizeof(float) * (size_t)hidden;
-  if (smem > 48 * 1024)
-    LOGOS_CUDA_TRY(cudaFuncSetAttribute(residual_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  LOGOS_CUDA_TRY(launch_kernel(residual_rmsnorm_kernel, dim3((unsigned)rows), dim3(512), smem, st, h, delta, parts,
-                               part_stride, g, xn, hidden, eps));
+  if ((hidden & 3) == 0 && hidden <= 8192) {
+    LOGOS_CUDA_TRY(launch_kernel(residual_rmsnorm_kernel<true>, dim3((unsigned)rows), dim3(512), 0, st, h, delta, parts,
+                                 part_stride, g, xn, hidden, eps));
+  } else {
+    size_t smem = sizeof(float) * (size_t)hidden;
+    if (smem > 48 * 1024)
+      LOGOS_CUDA_TRY(cudaFuncSetAttribute(residual_rmsnorm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LOGOS_CUDA_TRY(launch_kernel(residual_rmsnorm_kernel<false>, dim3((unsigned)rows), dim3(512), smem, st, h, delta, parts,
+                                 part_stride, g, xn, hidden, eps));
+  }
   count_launch(LK_ELEMWISE);
   return check_launch("residual_rmsnorm_kernel");
 }
