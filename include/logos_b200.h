@@ -289,8 +289,16 @@ typedef struct {
 LOGOS_API logos_status_t logos_tp_unique_id(void* out_128_bytes);
 LOGOS_API logos_status_t logos_llm_create(const logos_llm_config_t* cfg, const void* nccl_unique_id_or_null,
                                 logos_handle_t* out);
+/* The configuration the model was created with (a host that holds only the handle learns the
+ * batch size, the vocabulary, ... from here). */
+LOGOS_API logos_status_t logos_llm_get_config(logos_handle_t model, logos_llm_config_t* cfg_out);
 /* Process t prompt tokens per sequence ([B][T] row-major, host) and fill the KV
- * cache; sequence lengths become t.  Starts from an empty cache. */
+ * cache; sequence lengths become t.  Starts from an empty cache.  The prompt runs in chunks of
+ * positions, every sequence's chunk through a layer at once (rows = batch x chunk; the first call
+ * allocates the chunk's workspace, about 4096 rows), with the decode step's arithmetic: weights
+ * are streamed once per chunk, not once per token.  LOGOS_B200_PREFILL=loop in the environment
+ * selects the token-by-token pass through the decode step instead (what
+ * logos_llm_prefill_ragged always uses). */
 LOGOS_API logos_status_t logos_llm_prefill(logos_handle_t model, const int32_t* tokens_host, int64_t t);
 /* Prompts of different lengths: sequence b consumes tokens_host[b][0 .. lens_host[b]) of a
  * [B][t_max] array, 0 <= lens_host[b] <= t_max.  Afterwards its length is lens_host[b] and its

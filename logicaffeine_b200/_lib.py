@@ -91,6 +91,7 @@ _SIGNATURES = {
     "logos_swiglu": (None, [H, H, H, I64, PTR]),
     "logos_tp_unique_id": (None, [PTR]),
     "logos_llm_create": (None, [C.POINTER(LlmConfig), PTR, C.POINTER(H)]),
+    "logos_llm_get_config": (None, [H, C.POINTER(LlmConfig)]),
     "logos_llm_prefill": (None, [H, PTR, I64]),
     "logos_llm_prefill_ragged": (None, [H, PTR, I64, PTR]),
     "logos_llm_synth_kv": (None, [H, I64, U64]),

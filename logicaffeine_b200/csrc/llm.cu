@@ -1261,6 +1261,15 @@ logos_status_t logos_llm_last_timing(logos_handle_t model, double* ms_out, int64
   });
 }
 
+logos_status_t logos_llm_get_config(logos_handle_t model, logos_llm_config_t* cfg_out) {
+  return guarded([&]() -> logos_status_t {
+    MODEL_OR_FAIL(m, model, "logos_llm_get_config");
+    if (!cfg_out) return fail(LOGOS_NULL_POINTER, "logos_llm_get_config: cfg_out is null");
+    *cfg_out = m->cfg;
+    return LOGOS_OK;
+  });
+}
+
 logos_status_t logos_llm_tp_exchange(logos_handle_t model, int32_t* mode_out) {
   return guarded([&]() -> logos_status_t {
     MODEL_OR_FAIL(m, model, "logos_llm_tp_exchange");

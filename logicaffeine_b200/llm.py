@@ -319,6 +319,12 @@ class Llm:
         call("logos_llm_last_timing", self.handle, C.byref(ms), C.byref(launches))
         return ms.value, launches.value
 
+    def config(self):
+        """The logos_llm_config_t the model was created with, as a dict."""
+        cfg = LlmConfig()
+        call("logos_llm_get_config", self.handle, C.byref(cfg))
+        return {name: getattr(cfg, name) for name, _ in LlmConfig._fields_}
+
     def tpExchange(self):
         """0 = no TP group, 1 = NCCL all-reduce, 2 = exchange folded into residual + RMSNorm over peer memory."""
         mode = C.c_int32()

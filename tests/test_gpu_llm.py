@@ -64,6 +64,8 @@ def test_decode_is_repeatable_after_rewind(llm, oracle):
     O = oracle
     toks = np.arange(SMALL["batch"] * 6, dtype=np.int32).reshape(SMALL["batch"], 6) % SMALL["vocab"]
     gpu = llm.Llm(**SMALL)
+    got = gpu.config()
+    assert all(got[k] == v for k, v in SMALL.items() if k in got and not isinstance(v, float))
     gpu.prefill(toks)
     first = gpu.decodeStep()
     a = gpu.decodeSteps(8)
