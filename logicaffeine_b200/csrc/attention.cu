@@ -555,34 +555,38 @@ gqa_decode_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   }
 }
 
-// One CTA per (part slot, query row of the group): where the slot holds the first part of a pair
-// that the main kernel cut, fold the pair's parts in ascending order of their shares.
+// One CTA per part slot: where the slot holds the first part of a pair that the main kernel cut,
+// fold the pair's parts in ascending order of their shares, for every query row of the group.
+// (Most slots name no pair: the grid is small and those CTAs leave after one load.)
 template <int D>
-__global__ void attn_merge_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(256) attn_merge_kernel(const AttnParams p) {
   pdl_wait();
   pdl_trigger();
   const int4 desc = __ldcg(p.part_desc + blockIdx.x);
   if (desc.x < 0) return;
-  const int G = p.h_q / p.h_kv, r = blockIdx.y, d = threadIdx.x;
+  const int G = p.h_q / p.h_kv;
   const int b = desc.x, kvh = desc.y, first = desc.z, last = desc.w;
   const int64_t total = __ldcg(p.tiles_total);
   // the first part sits in this very slot; every later share holds its part in slot 0 (it begins
   // at the share's first tile); with more shares than tiles some shares in between hold no tile
   auto empty = [&](int c) { return share_begin(c, total, p.shares) == share_begin(c + 1, total, p.shares); };
-  auto row_of = [&](int c) -> int64_t { return (c == first ? (int64_t)blockIdx.x : (int64_t)c * 2) * 16 + r; };
-  float mstar = -INFINITY;
-  for (int c = first; c <= last; ++c)
-    if (!empty(c)) mstar = fmaxf(mstar, __ldcg(p.part_ml + row_of(c) * 2));
-  float muse = (mstar == -INFINITY) ? 0.f : mstar;
-  float acc = 0.f, L = 0.f;
-  for (int c = first; c <= last; ++c) {
-    if (empty(c)) continue;
-    const int64_t row = row_of(c);
-    float wgt = exp2f(__ldcg(p.part_ml + row * 2) - muse);
-    acc = fmaf(__ldcg(p.part_o + row * D + d), wgt, acc);
-    L = fmaf(__ldcg(p.part_ml + row * 2 + 1), wgt, L);
+  for (int e = threadIdx.x; e < G * D; e += blockDim.x) {
+    const int r = e / D, d = e - r * D;
+    auto row_of = [&](int c) -> int64_t { return (c == first ? (int64_t)blockIdx.x : (int64_t)c * 2) * 16 + r; };
+    float mstar = -INFINITY;
+    for (int c = first; c <= last; ++c)
+      if (!empty(c)) mstar = fmaxf(mstar, __ldcg(p.part_ml + row_of(c) * 2));
+    float muse = (mstar == -INFINITY) ? 0.f : mstar;
+    float acc = 0.f, L = 0.f;
+    for (int c = first; c <= last; ++c) {
+      if (empty(c)) continue;
+      const int64_t row = row_of(c);
+      float wgt = exp2f(__ldcg(p.part_ml + row * 2) - muse);
+      acc = fmaf(__ldcg(p.part_o + row * D + d), wgt, acc);
+      L = fmaf(__ldcg(p.part_ml + row * 2 + 1), wgt, L);
+    }
+    store_out(p, ((int64_t)b * p.h_q + kvh * G + r) * D + d, __fdiv_rn(acc, L));
   }
-  store_out(p, ((int64_t)b * p.h_q + kvh * G + r) * D + d, __fdiv_rn(acc, L));
 }
 
 __global__ void bump_seq_len_kernel(int32_t* seq_len, int b, int l_max) {
@@ -681,8 +685,7 @@ logos_status_t launch_attn_t(const AttnArgs& a, cudaStream_t st) {
   LOGOS_CUDA_TRY(launch_kernel(gqa_decode_attn_kernel<D>, dim3((unsigned)shares), dim3(ATT_THREADS), smem, st, mk, mv, p));
   count_launch(LK_ATTN);
   LOGOS_TRY(check_launch("gqa_decode_attn_kernel"));
-  dim3 mgrid((unsigned)(2 * shares), (unsigned)(a.h_q / a.h_kv));
-  LOGOS_CUDA_TRY(launch_kernel(attn_merge_kernel<D>, mgrid, dim3(D), 0, st, p));
+  LOGOS_CUDA_TRY(launch_kernel(attn_merge_kernel<D>, dim3((unsigned)(2 * shares)), dim3(256), 0, st, p));
   count_launch(LK_ATTN_MERGE);
   LOGOS_TRY(check_launch("attn_merge_kernel"));
   if (a.bump_seq_len) {
