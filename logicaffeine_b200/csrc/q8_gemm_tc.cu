@@ -10,6 +10,7 @@
 // Data flow per 128-column K stage (4 Q8 blocks):
 //   TMA  int8 weights [128 rows][128 B], 128-byte swizzle  -> smem ring   (warp 0)
 //   TMA  fp16 activation planes [MT][64] x 2 halves x limbs -> smem ring   (warp 1)
+//   TMA  the stage's f32 scales [128 rows][4]               -> smem ring   (warp 0)
 //   8 converter warps: smem int8 -> fp16 (exact: 0x6400|b trick) -> tcgen05.st
 //        into a TMEM operand ring; the weights never go back to shared memory
 //   2 MMA warps (alternate stages): per Q8 block two tcgen05.mma kind::f16 (K=16
@@ -17,7 +18,8 @@
 //        accumulator: first q*lo', then q*hi + D*2^-11 through the MMA's own
 //        accumulator scaling, so hi + lo*2^-11 is recombined on the tensor core
 //   8 drain warps: tcgen05.ld the block's partial sums (two blocks per wait),
-//        acc += s * partial in f32 registers, then the epilogue.
+//        acc += s * partial in f32 registers (scales from the shared-memory ring: a global load
+//        under this kernel's own traffic takes several stage times), then the epilogue.
 // A CTA is persistent: it takes work items (tile of 128 weight rows x K split) in turn,
 // and the rings keep running across items, so the next item's weights stream in, are
 // converted and multiplied while the drain warps finish the previous item's epilogue.
@@ -48,7 +50,7 @@ constexpr int TC_ROWS = 128;     // weight rows per CTA (MMA M)
 constexpr int TC_KSTAGE = 128;   // K per stage
 constexpr int RAW_STAGES = 4;
 constexpr int RAW_PREFETCH = 12;  // L2 prefetch distance of the weight stream, in stages
-constexpr int ACT_STAGES = 4;
+constexpr int ACT_STAGES = 3;
 constexpr int TA_STAGES = 4;
 constexpr int TA_LIMB_COLS = 64; // TMEM columns per converted stage and copy: 128 fp16 per row
 constexpr int CONV_WARPS = 4;     // one per TMEM lane quarter
@@ -57,6 +59,8 @@ constexpr int TC_THREADS = (DRAIN_WARP0 + 8) * 32;  // 4 single-role warps, conv
 constexpr int ACC_PAIRS = 2;     // TMEM accumulator ring: each entry holds two Q8 blocks
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int RAW_BYTES = TC_ROWS * TC_KSTAGE;  // 16 KB
+constexpr int SC_STAGES = 12;                   // scale ring: longer than the way from the producer to the drain
+constexpr int SC_BYTES = TC_ROWS * 16;          // four f32 per row and stage
 
 template <int MT, int LIMBS>
 struct TcCfg {
@@ -67,7 +71,7 @@ struct TcCfg {
   static constexpr int ACT_BYTES = 2 * ACT_ATOM_BYTES;
   static constexpr int EPI_BYTES = MT * TC_ROWS * 4;    // output tile staged for the store: [MT][128] f32 at most
   static constexpr size_t SMEM_NEED =
-      1024 + (size_t)RAW_STAGES * RAW_BYTES + (size_t)ACT_STAGES * ACT_BYTES + EPI_BYTES + 512;
+      1024 + (size_t)RAW_STAGES * RAW_BYTES + (size_t)ACT_STAGES * ACT_BYTES + EPI_BYTES + SC_STAGES * SC_BYTES + 1024;
   // the CTA allocates all of tensor memory, so ask for enough shared memory that only one CTA fits an SM
   static constexpr size_t SMEM = SMEM_NEED > 120 * 1024 ? SMEM_NEED : 120 * 1024;
   static_assert(SMEM <= 227 * 1024, "shared memory budget");
@@ -172,6 +176,14 @@ __device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
   return d;
 }
 
+// 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier; both addresses and the
+// size are multiples of 16
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
 template <int N>
 __device__ __forceinline__ void tc_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
   if constexpr (N == 32) tc_ld_32x32b_x32(taddr, r);
@@ -191,7 +203,8 @@ template <int MT, int LIMBS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_ahi,
                   const __grid_constant__ CUtensorMap map_alo, const __grid_constant__ CUtensorMap map_o0,
-                  const __grid_constant__ CUtensorMap map_o1, const TcParams p) {
+                  const __grid_constant__ CUtensorMap map_o1, const __grid_constant__ CUtensorMap map_s,
+                  const TcParams p) {
   using Cfg = TcCfg<MT, LIMBS>;
   constexpr int TA_COLS = Cfg::TA_COLS;
   constexpr int ACC_COL0 = Cfg::ACC_COL0;
@@ -201,7 +214,8 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   uint8_t* raw = smem;
   uint8_t* act = raw + RAW_STAGES * RAW_BYTES;
   uint8_t* epi = act + ACT_STAGES * Cfg::ACT_BYTES;  // 1024-aligned: all sizes before it are multiples of 1024
-  uint64_t* bars = reinterpret_cast<uint64_t*>(epi + Cfg::EPI_BYTES);
+  uint8_t* scl = epi + Cfg::EPI_BYTES;               // scale ring
+  uint64_t* bars = reinterpret_cast<uint64_t*>(scl + SC_STAGES * SC_BYTES);
   uint64_t* raw_full = bars;                    // [RAW_STAGES]
   uint64_t* raw_empty = raw_full + RAW_STAGES;  // [RAW_STAGES]
   uint64_t* act_full = raw_empty + RAW_STAGES;  // [ACT_STAGES]
@@ -210,7 +224,9 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   uint64_t* ta_empty = ta_full + TA_STAGES;     // [TA_STAGES]
   uint64_t* acc_full = ta_empty + TA_STAGES;    // [ACC_PAIRS]
   uint64_t* acc_empty = acc_full + ACC_PAIRS;   // [ACC_PAIRS]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_PAIRS);
+  uint64_t* sc_full = acc_empty + ACC_PAIRS;    // [SC_STAGES]
+  uint64_t* sc_empty = sc_full + SC_STAGES;     // [SC_STAGES]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sc_empty + SC_STAGES);
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -240,12 +256,14 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     for (int i = 0; i < ACT_STAGES; ++i) { mbar_init(&act_full[i], 1); mbar_init(&act_empty[i], 2); }
     for (int i = 0; i < TA_STAGES; ++i) { mbar_init(&ta_full[i], CONV_WARPS); mbar_init(&ta_empty[i], 2); }
     for (int i = 0; i < ACC_PAIRS; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 8); }
+    for (int i = 0; i < SC_STAGES; ++i) { mbar_init(&sc_full[i], 1); mbar_init(&sc_empty[i], 8); }
     fence_barrier_init();
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_ahi);
     if (LIMBS == 2) prefetch_tensormap(&map_alo);
     if (p.store_mode != STORE_GENERIC) prefetch_tensormap(&map_o0);
     if (p.store_mode == STORE_TMA_SWIGLU) prefetch_tensormap(&map_o1);
+    if (!p.tiled) prefetch_tensormap(&map_s);
   }
   if (warp == 3) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -280,6 +298,17 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         // L2 prefetches run RAW_PREFETCH stages ahead of the TMA loads.  They start only after
         // the item's first loads are on their way, so that nothing queues in front of those.
         for (int i = 0; i < nst; ++i, ++gs) {
+          {
+            // the stage's scales, four per row: tile-major they are 2 contiguous KB, row-major a
+            // [128 rows][4] box of the [N][K/32] matrix (rows past N read as zero)
+            const int ss = gs % SC_STAGES;
+            if (!mbar_wait(&sc_empty[ss], ((uint32_t)(gs / SC_STAGES) & 1u) ^ 1u)) { ok = false; tc_report(p.status, 2011, i, nst); break; }
+            mbar_arrive_expect_tx(&sc_full[ss], SC_BYTES);
+            if (p.tiled)
+              bulk_load(scl + ss * SC_BYTES, p.s + ((int64_t)it.tile * p.stages_total + st_begin + i) * TC_ROWS * 4, SC_BYTES, &sc_full[ss]);
+            else
+              tma_load_2d(scl + ss * SC_BYTES, &map_s, &sc_full[ss], (st_begin + i) * 4, n0);
+          }
           const int st = gs % RAW_STAGES;
           const uint32_t ph = (uint32_t)(gs / RAW_STAGES) & 1u;
           if (!mbar_wait(&raw_empty[st], ph ^ 1u)) { ok = false; tc_report(p.status, 2010, i, nst); break; }
@@ -452,7 +481,6 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     constexpr int HC = MT / 2;  // token columns per drain warp
     const int nl = qd * 32 + lane;  // row of the tile this thread drains
     const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16) + ACC_COL0 + half * HC;
-    const int64_t kb_per_row = p.k >> 5;
     const int et = tid - DRAIN_WARP0 * 32;  // 0..255 among the drain warps
     pdl_wait();  // before any write to global memory (nothing to drain before the activations are in anyway)
     bool stored = false;  // thread et == 0: a TMA store of this CTA may still be reading the staging tile
@@ -462,42 +490,19 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       const int64_t m0 = (int64_t)(u - w * p.mtiles) * MT;
       const int64_t rows_here = (p.m - m0 < MT) ? (p.m - m0) : MT;
       const TcItem it = tc_item(p, w);
-      const int nst = it.nst, st_begin = it.st_begin;
+      const int nst = it.nst;
       const int64_t n0 = (int64_t)it.tile * TC_ROWS;
       TC_TRACE_ITEM(w);
-      const int64_t n = n0 + nl;
-      const bool n_ok = n < p.n;
       uint64_t acc2[HC / 2];  // packed f32 pairs: the drain arithmetic uses two-wide f32 FMAs
 #pragma unroll
       for (int j = 0; j < HC / 2; ++j) acc2[j] = 0ull;
-      // The four scales of a stage are one 16-byte load per row.  Their latency (L2, or HBM)
-      // must not sit between the TMEM load and the arithmetic: registers hold the scales two
-      // stages ahead, and a line further on is prefetched into L2.  Row-major scales: stage i of
-      // row n is float4 i of the row (a 128-byte line serves eight stages).  Tile-major: the 128
-      // rows' scales of a stage are 2 contiguous KB, consecutive stages follow each other.
-      const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-      const float4* sc_src;
-      int64_t sc_step;       // float4 between consecutive stages
-      int pf_mask, pf_ahead;   // L2 prefetch: at stages with (i & pf_mask) == 0, that many stages ahead
-      if (p.tiled) {
-        sc_src = reinterpret_cast<const float4*>(p.s) + ((int64_t)it.tile * p.stages_total + st_begin) * TC_ROWS + nl;
-        sc_step = TC_ROWS;
-        pf_mask = 0; pf_ahead = 8;    // this thread's 16 bytes of the stage: the warp's lanes cover 512 bytes
-      } else {
-        sc_src = reinterpret_cast<const float4*>(p.s + (n_ok ? n : 0) * kb_per_row) + st_begin;
-        sc_step = 1;
-        pf_mask = 7; pf_ahead = 16;
-      }
-      const bool s_ok = n_ok || p.tiled;   // tile-major scales are padded to whole tiles (zeros)
-      float4 sc_a = (s_ok && 0 < nst) ? __ldg(sc_src) : zero4;
-      float4 sc_b = (s_ok && 1 < nst) ? __ldg(sc_src + sc_step) : zero4;
-      if (s_ok && 8 < nst) prefetch_l2(sc_src + 8 * sc_step);
       for (int i = 0; i < nst && ok; ++i, ++gs) {
-        const float4 sc4 = sc_a;
-        sc_a = sc_b;
-        sc_b = (s_ok && i + 2 < nst) ? __ldg(sc_src + (i + 2) * sc_step) : zero4;
-        if (s_ok && (i & pf_mask) == 0 && i + pf_ahead < nst && (!p.tiled || (lane & 7) == 0))
-          prefetch_l2(sc_src + (i + pf_ahead) * sc_step);
+        // the stage's four scales of this row, from the ring
+        const int ss = gs % SC_STAGES;
+        if (!mbar_wait(&sc_full[ss], (uint32_t)(gs / SC_STAGES) & 1u)) { ok = false; if (lane == 0) tc_report(p.status, 2051, i, nst); break; }
+        const float4 sc4 = *reinterpret_cast<const float4*>(scl + ss * SC_BYTES + nl * 16);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sc_empty[ss]);
         const float scs[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
         const uint32_t fph = (uint32_t)gs & 1u;
 #pragma unroll
@@ -665,13 +670,14 @@ struct MapKeyHash {
   }
 };
 
+}  // namespace
+
 // Tensor maps are pure functions of (address, shape, box): encode once, reuse.  d2 == 0 asks
 // for a 2-D map [d1][d0] with the given swizzle; otherwise a 3-D map [d2][d1][d0], box depth 1,
 // no swizzle.
 logos_status_t cached_map(CUtensorMap* out, const void* base, CUtensorMapDataType dt, uint32_t elem, uint64_t d0,
-                          uint64_t d1, uint64_t pitch1, uint32_t box0, uint32_t box1,
-                          CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B, uint64_t d2 = 0,
-                          uint64_t pitch2 = 0) {
+                          uint64_t d1, uint64_t pitch1, uint32_t box0, uint32_t box1, CUtensorMapSwizzle swizzle,
+                          uint64_t d2, uint64_t pitch2) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   MapKey key{base, d0, d1, d2, pitch1, pitch2, box0, box1, elem, (uint32_t)swizzle};
@@ -691,12 +697,14 @@ logos_status_t cached_map(CUtensorMap* out, const void* base, CUtensorMapDataTyp
   return LOGOS_OK;
 }
 
+namespace {
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <int MT, int LIMBS>
 logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
   using Cfg = TcCfg<MT, LIMBS>;
-  CUtensorMap mq, mhi, mlo, mo0, mo1;
+  CUtensorMap mq, mhi, mlo, mo0, mo1, ms;
   if (g.q_tiled) {
     const uint64_t rows = (uint64_t)((g.n + TC_ROWS - 1) / TC_ROWS) * (uint64_t)(g.k / TC_KSTAGE) * TC_ROWS;
     LOGOS_TRY(cached_map(&mq, g.q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, TC_KSTAGE, rows, TC_KSTAGE, TC_KSTAGE, TC_ROWS));
@@ -708,6 +716,10 @@ logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
     LOGOS_TRY(cached_map(&mlo, g.a_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)g.k, (uint64_t)g.m, (uint64_t)g.lda * 2, 64, MT));
   else
     mlo = mhi;
+  ms = mhi;
+  if (!g.q_tiled)
+    LOGOS_TRY(cached_map(&ms, g.s, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)(g.k / 32), (uint64_t)g.n, (uint64_t)(g.k / 32) * 4, 4,
+                         TC_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE));
   TcParams p{};
   p.s = g.s; p.n = g.n; p.k = g.k; p.m = g.m;
   p.c = g.c; p.c_dtype = g.c_dtype; p.c_act = g.c_act; p.ldc = g.ldc; p.aux = g.aux; p.epilogue = g.epilogue;
@@ -775,7 +787,7 @@ logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
   p.mtiles = (int)mtiles;
   const int64_t units = (int64_t)p.items * mtiles;
   dim3 grid((unsigned)(units < sms ? units : sms), 1u, 1u);
-  LOGOS_CUDA_TRY(launch_kernel(q8_gemm_tc_kernel<MT, LIMBS>, grid, dim3(TC_THREADS), Cfg::SMEM, st, mq, mhi, mlo, mo0, mo1, p));
+  LOGOS_CUDA_TRY(launch_kernel(q8_gemm_tc_kernel<MT, LIMBS>, grid, dim3(TC_THREADS), Cfg::SMEM, st, mq, mhi, mlo, mo0, mo1, ms, p));
   count_launch(LK_GEMM_TC);
   return check_launch("q8_gemm_tc_kernel");
 }
