@@ -11,9 +11,9 @@
 //   TMA  int8 weights [128 rows][128 B], 128-byte swizzle  -> smem ring   (warp 0)
 //   TMA  fp16 activation planes [MT][64] x 2 halves x limbs -> smem ring   (warp 1)
 //   TMA  the stage's f32 scales [128 rows][4]               -> smem ring   (warp 0)
-//   8 converter warps: smem int8 -> fp16 (exact: 0x6400|b trick) -> tcgen05.st
-//        into a TMEM operand ring; the weights never go back to shared memory
-//   2 MMA warps (alternate stages): per Q8 block two tcgen05.mma kind::f16 (K=16
+//   4 converter warps (one per TMEM lane quarter): smem int8 -> fp16 (exact: 0x6400|b trick)
+//        -> tcgen05.st into a TMEM operand ring; the weights never go back to shared memory
+//   2 MMA warps (one per half of a stage): per Q8 block two tcgen05.mma kind::f16 (K=16
 //        each) per plane, A from TMEM, B = activations from smem, into a fresh TMEM
 //        accumulator: first q*lo', then q*hi + D*2^-11 through the MMA's own
 //        accumulator scaling, so hi + lo*2^-11 is recombined on the tensor core
