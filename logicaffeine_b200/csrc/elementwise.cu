@@ -70,7 +70,8 @@ __global__ void embed_kernel(const int32_t* __restrict__ tokens, const int8_t* _
     const int8_t* base = q + tile0 * 128;
     const float* sbase = s + tile0 * 4;
     for (int64_t e = threadIdx.x; e < hidden; e += blockDim.x)
-      h[row * hidden + e] = __fmul_rn(sbase[(e >> 7) * 512 + ((e & 127) >> 5)], (float)base[(e >> 7) * 16384 + (e & 127)]);
+      h[row * hidden + e] = __fmul_rn(sbase[(e >> 7) * 512 + ((e & 127) >> 5)],
+                                      (float)((int)(uint8_t)base[(e >> 7) * 16384 + (e & 127)] - 128));  // bytes hold q + 128
     return;
   }
   const float* sr = s + t * (hidden / 32);

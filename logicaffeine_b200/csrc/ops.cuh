@@ -18,7 +18,9 @@ logos_status_t launch_q8_quantize(bool generate, const float* w, int8_t* q, floa
                                   cudaStream_t st);
 
 // int8 [n][k] row-major <-> tile-major (128 x 128 tiles of 16 contiguous KB, ordered (row tile, K tile),
-// ceil128(n) rows; K a multiple of 128): the layout a model keeps its GEMM weights in.  in != out.
+// ceil128(n) rows; K a multiple of 128): the layout a model keeps its GEMM weights in.  The tiled
+// bytes hold q + 128 (top bit flipped), the form the GEMM's int8 -> fp16 conversion starts from.
+// in != out.
 logos_status_t launch_q8_retile(const int8_t* in, int8_t* out, int64_t n, int64_t k, bool to_tiled, int device,
                                 cudaStream_t st);
 // and their scales: f32 [n][k/32] row-major <-> [row tile][K tile][128 rows][4 scales]

@@ -154,7 +154,8 @@ __device__ __forceinline__ float load_aux(const TcParams& p, int64_t i) {
   return reinterpret_cast<const float*>(p.aux)[i];
 }
 
-// two int8 (bytes sel_lo / sel_hi of w ^ 0x80808080) -> packed fp16 pair, exact
+// two int8 (bytes sel_lo / sel_hi of w ^ 0x80808080, i.e. of q + 128 as unsigned bytes) -> packed
+// fp16 pair, exact
 __device__ __forceinline__ uint32_t cvt_pair(uint32_t w_xor80, uint32_t selector) {
   uint32_t bits = __byte_perm(w_xor80, 0x64646464u, selector);   // 0x64bb = 1024 + (q + 128)
   __half2 h = *reinterpret_cast<__half2*>(&bits);
@@ -199,7 +200,7 @@ __device__ __forceinline__ void act_split_planes(int mode, float x, __half* h, _
   *l = __float2half_rn((x - __half2float(*h)) * 2048.f);
 }
 
-template <int MT, int LIMBS>
+template <int MT, int LIMBS, bool TILED>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_ahi,
                   const __grid_constant__ CUtensorMap map_alo, const __grid_constant__ CUtensorMap map_o0,
@@ -263,7 +264,7 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     if (LIMBS == 2) prefetch_tensormap(&map_alo);
     if (p.store_mode != STORE_GENERIC) prefetch_tensormap(&map_o0);
     if (p.store_mode == STORE_TMA_SWIGLU) prefetch_tensormap(&map_o1);
-    if (!p.tiled) prefetch_tensormap(&map_s);
+    if (!TILED) prefetch_tensormap(&map_s);
   }
   if (warp == 3) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -304,7 +305,7 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             const int ss = gs % SC_STAGES;
             if (!mbar_wait(&sc_empty[ss], ((uint32_t)(gs / SC_STAGES) & 1u) ^ 1u)) { ok = false; tc_report(p.status, 2011, i, nst); break; }
             mbar_arrive_expect_tx(&sc_full[ss], SC_BYTES);
-            if (p.tiled)
+            if (TILED)
               bulk_load(scl + ss * SC_BYTES, p.s + ((int64_t)it.tile * p.stages_total + st_begin + i) * TC_ROWS * 4, SC_BYTES, &sc_full[ss]);
             else
               tma_load_2d(scl + ss * SC_BYTES, &map_s, &sc_full[ss], (st_begin + i) * 4, n0);
@@ -317,13 +318,13 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           // row-major weights: tile (n0, stage) of a [N][K] map; tile-major: 128 rows of 128 bytes at
           // row ((tile * stages + stage) * 128) of a [tiles * stages * 128][128 B] map
           const int tbase = it.tile * p.stages_total + st_begin;
-          if (p.tiled) tma_load_2d_hint(raw + st * RAW_BYTES, &map_q, &raw_full[st], 0, (tbase + i) * TC_ROWS, pol);
+          if (TILED) tma_load_2d_hint(raw + st * RAW_BYTES, &map_q, &raw_full[st], 0, (tbase + i) * TC_ROWS, pol);
           else tma_load_2d_hint(raw + st * RAW_BYTES, &map_q, &raw_full[st], (st_begin + i) * TC_KSTAGE, n0, pol);
           if (i + 1 >= RAW_STAGES) {
             // after the first fill: stages RAW_STAGES .. RAW_PREFETCH in one go, then one per stage
             const int first = (i + 1 == RAW_STAGES) ? RAW_STAGES : i + RAW_PREFETCH;
             for (int j = first; j <= i + RAW_PREFETCH && j < nst; ++j) {
-              if (p.tiled) tma_prefetch_l2_2d(&map_q, 0, (tbase + j) * TC_ROWS);
+              if (TILED) tma_prefetch_l2_2d(&map_q, 0, (tbase + j) * TC_ROWS);
               else tma_prefetch_l2_2d(&map_q, (st_begin + j) * TC_KSTAGE, n0);
             }
           }
@@ -374,13 +375,15 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     static_assert(ACC_PAIRS == 2, "one accumulator ring entry per MMA warp");
     const int pr = warp - 2;
     int gs = 0;
+    int as = 0;           // slot and phase of the activation ring, counted
+    uint32_t aph = 0;
     for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
       const int w = u / p.mtiles;
       const int nst = tc_item(p, w).nst;
       TC_TRACE_ITEM(w);
       for (int i = 0; i < nst && ok; ++i, ++gs) {
-        const int ts = gs % TA_STAGES, as = gs % ACT_STAGES;
-        const uint32_t tph = (uint32_t)(gs / TA_STAGES) & 1u, aph = (uint32_t)(gs / ACT_STAGES) & 1u;
+        const int ts = gs % TA_STAGES;
+        const uint32_t tph = (uint32_t)(gs / TA_STAGES) & 1u;
         if (!mbar_wait(&ta_full[ts], tph)) { ok = false; if (lane == 0) tc_report(p.status, 2031, i, nst); break; }
         if (lane == 0 && pr == 0) TC_TRACE(i, 2);
         if (!mbar_wait(&act_full[as], aph)) { ok = false; if (lane == 0) tc_report(p.status, 2032, i, nst); break; }
@@ -421,6 +424,7 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         }
         __syncwarp();
         if (lane == 0 && pr == 0) TC_TRACE(i, 4);
+        if (++as == ACT_STAGES) { as = 0; aph ^= 1u; }
       }
     }
 
@@ -452,11 +456,20 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           const uint4 wv = *reinterpret_cast<const uint4*>(rb + swz128(row, c));
           uint32_t r[8];
           const uint32_t ws[4] = {wv.x, wv.y, wv.z, wv.w};
+          if (TILED) {  // tile-major weights are stored as q + 128 already (compile-time branch: two
+                        // copies of this loop in one kernel cost 10 % of its speed)
 #pragma unroll
-          for (int wi = 0; wi < 4; ++wi) {
-            uint32_t u = ws[wi] ^ 0x80808080u;
-            r[2 * wi] = cvt_pair(u, 0x4140);
-            r[2 * wi + 1] = cvt_pair(u, 0x4342);
+            for (int wi = 0; wi < 4; ++wi) {
+              r[2 * wi] = cvt_pair(ws[wi], 0x4140);
+              r[2 * wi + 1] = cvt_pair(ws[wi], 0x4342);
+            }
+          } else {
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+              const uint32_t u = ws[wi] ^ 0x80808080u;
+              r[2 * wi] = cvt_pair(u, 0x4140);
+              r[2 * wi + 1] = cvt_pair(u, 0x4342);
+            }
           }
           tc_st_32x32b_x8(t_lane + ts * TA_COLS + c * 8, r);
         }
@@ -485,6 +498,8 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     pdl_wait();  // before any write to global memory (nothing to drain before the activations are in anyway)
     bool stored = false;  // thread et == 0: a TMA store of this CTA may still be reading the staging tile
     int gs = 0;
+    int ss = 0;           // slot and phase of the scale ring (SC_STAGES is not a power of two: counted, not divided)
+    uint32_t sph = 0;
     for (int u = blockIdx.x; u < units; u += gridDim.x) {
       const int w = u / p.mtiles;
       const int64_t m0 = (int64_t)(u - w * p.mtiles) * MT;
@@ -498,11 +513,11 @@ q8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       for (int j = 0; j < HC / 2; ++j) acc2[j] = 0ull;
       for (int i = 0; i < nst && ok; ++i, ++gs) {
         // the stage's four scales of this row, from the ring
-        const int ss = gs % SC_STAGES;
-        if (!mbar_wait(&sc_full[ss], (uint32_t)(gs / SC_STAGES) & 1u)) { ok = false; if (lane == 0) tc_report(p.status, 2051, i, nst); break; }
+        if (!mbar_wait(&sc_full[ss], sph)) { ok = false; if (lane == 0) tc_report(p.status, 2051, i, nst); break; }
         const float4 sc4 = *reinterpret_cast<const float4*>(scl + ss * SC_BYTES + nl * 16);
         __syncwarp();
         if (lane == 0) mbar_arrive(&sc_empty[ss]);
+        if (++ss == SC_STAGES) { ss = 0; sph ^= 1u; }
         const float scs[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
         const uint32_t fph = (uint32_t)gs & 1u;
 #pragma unroll
@@ -779,7 +794,8 @@ logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
     }
   }
 
-  LOGOS_CUDA_TRY(cudaFuncSetAttribute(q8_gemm_tc_kernel<MT, LIMBS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
+  auto kernel = g.q_tiled ? q8_gemm_tc_kernel<MT, LIMBS, true> : q8_gemm_tc_kernel<MT, LIMBS, false>;
+  LOGOS_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
   // persistent CTAs: one per SM at most, each takes units blockIdx.x, blockIdx.x + gridDim.x, ...
   const int sms = sm_count(g.device);
   const int64_t mtiles = (g.m + MT - 1) / MT;
@@ -787,7 +803,7 @@ logos_status_t launch_t(const GemmArgs& g, cudaStream_t st) {
   p.mtiles = (int)mtiles;
   const int64_t units = (int64_t)p.items * mtiles;
   dim3 grid((unsigned)(units < sms ? units : sms), 1u, 1u);
-  LOGOS_CUDA_TRY(launch_kernel(q8_gemm_tc_kernel<MT, LIMBS>, grid, dim3(TC_THREADS), Cfg::SMEM, st, mq, mhi, mlo, mo0, mo1, ms, p));
+  LOGOS_CUDA_TRY(launch_kernel(kernel, grid, dim3(TC_THREADS), Cfg::SMEM, st, mq, mhi, mlo, mo0, mo1, ms, p));
   count_launch(LK_GEMM_TC);
   return check_launch("q8_gemm_tc_kernel");
 }

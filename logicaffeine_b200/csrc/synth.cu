@@ -101,7 +101,7 @@ __global__ void q8_quantize_kernel(const float* __restrict__ w, int8_t* __restri
 // Row-major int8 [n][k] <-> the tile-major layout the tcgen05 GEMM streams: tiles of 128 rows x
 // 128 columns, each 16 KB contiguous, ordered (row tile, K tile), so that the stages a CTA reads
 // one after the other form one contiguous run in HBM instead of 128 lines a row pitch apart.
-// Rows n .. ceil128(n) of the tiled form are zero.  One thread moves 16 bytes.
+// Rows n .. ceil128(n) of the tiled form hold the value zero.  One thread moves 16 bytes.
 __global__ void q8_retile_kernel(const int8_t* __restrict__ in, int8_t* __restrict__ out, int64_t n, int64_t k,
                                  int to_tiled) {
   const int64_t ktiles = k >> 7, rtiles = (n + 127) >> 7;
@@ -111,12 +111,16 @@ __global__ void q8_retile_kernel(const int8_t* __restrict__ in, int8_t* __restri
     const int64_t t = ts / ktiles, st = ts - t * ktiles;
     const int64_t row = t * 128 + r;
     const int64_t rm = row * k + st * 128 + c16 * 16;   // offset in the row-major form
+    // the tiled form holds q + 128 as unsigned bytes (every byte's top bit flipped): the GEMM's
+    // int8 -> fp16 conversion wants that form and then needs no flip of its own
+    const uint32_t f = 0x80808080u;
     if (to_tiled) {
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
       if (row < n) v = *reinterpret_cast<const uint4*>(in + rm);
-      *reinterpret_cast<uint4*>(out + i * 16) = v;
+      *reinterpret_cast<uint4*>(out + i * 16) = make_uint4(v.x ^ f, v.y ^ f, v.z ^ f, v.w ^ f);
     } else if (row < n) {
-      *reinterpret_cast<uint4*>(out + rm) = *reinterpret_cast<const uint4*>(in + i * 16);
+      const uint4 v = *reinterpret_cast<const uint4*>(in + i * 16);
+      *reinterpret_cast<uint4*>(out + rm) = make_uint4(v.x ^ f, v.y ^ f, v.z ^ f, v.w ^ f);
     }
   }
 }
