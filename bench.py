@@ -218,34 +218,40 @@ def gemv_probe(llm, torch, device):
         for c in range(copies):
             llm.q8Gemv(qs[c], ss[c], x, y, n, k, stream=sp)
         stream.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        # a chain of GEMVs as a batch-1 decode would issue them: the weights of a launch are
-        # fetched while the previous launch finishes (dependent-launch scope), x and y wait
-        prev = llm.dependentLaunchScope(True)
-        try:
-            with torch.cuda.graph(graph, stream=stream):
-                for i in range(launches):
-                    llm.q8Gemv(qs[i % copies], ss[i % copies], x, y, n, k, stream=stream.cuda_stream)
-        finally:
-            llm.dependentLaunchScope(prev)
-        for _ in range(3):
-            graph.replay()
-        stream.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        best = 1e9
-        for _ in range(5):
-            e0.record(stream)
-            graph.replay()
-            e1.record(stream)
+        def timed_graph(dependent):
+            graph = torch.cuda.CUDAGraph()
+            prev = llm.dependentLaunchScope(dependent)
+            try:
+                with torch.cuda.graph(graph, stream=stream):
+                    for i in range(launches):
+                        llm.q8Gemv(qs[i % copies], ss[i % copies], x, y, n, k, stream=stream.cuda_stream)
+            finally:
+                llm.dependentLaunchScope(prev)
+            for _ in range(3):
+                graph.replay()
             stream.synchronize()
-            best = min(best, e0.elapsed_time(e1))
-    us = best * 1e3 / launches
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            best = 1e9
+            for _ in range(5):
+                e0.record(stream)
+                graph.replay()
+                e1.record(stream)
+                stream.synchronize()
+                best = min(best, e0.elapsed_time(e1))
+            return best * 1e3 / launches
+
+        # a chain of GEMVs as a batch-1 decode would issue them: the weights of a launch are
+        # fetched while the previous launch finishes (dependent-launch scope), x and y wait;
+        # and the same chain with ordinary launches, each waiting for the previous one to end
+        us = timed_graph(True)
+        us_plain = timed_graph(False)
     nbytes = n * k + n * (k // 32) * 4 + k * 4 + n * 4
     for b in qs + ss + [x, y]:
         b.free()
     return {"shape": "4096x4096", "us_per_launch": us, "algorithmic_bytes": nbytes, "gbs": nbytes / us / 1e3,
             "timing": "CUDA graph of %d dependent launches (dependent-launch scope: a launch fetches its weights while "
-                      "the previous one finishes) over %d rotating weight copies (> L2)" % (launches, copies)}
+                      "the previous one finishes) over %d rotating weight copies (> L2)" % (launches, copies),
+            "ordinary_launches": {"us_per_launch": us_plain, "gbs": nbytes / us_plain / 1e3}}
 
 
 def op_probe(args):
@@ -656,6 +662,7 @@ def main():
             line["q8_gemv"] = gemv_probe(llm, torch, local_rank)
             line["q8_gemv"]["frac"] = line["q8_gemv"]["gbs"] / peak
             line["q8_gemv"]["frac_of_8000_nominal"] = line["q8_gemv"]["gbs"] / 8000.0
+            line["q8_gemv"]["ordinary_launches"]["frac"] = line["q8_gemv"]["ordinary_launches"]["gbs"] / peak
         except Exception as e:  # the probe is an extra; the headline stands without it
             line["q8_gemv"] = {"error": str(e)}
         c = cpu_sample(dict(w), ctx, warm=1, runs=3)
