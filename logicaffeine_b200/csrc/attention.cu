@@ -558,6 +558,12 @@ gqa_decode_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 // One CTA per part slot: where the slot holds the first part of a pair that the main kernel cut,
 // fold the pair's parts in ascending order of their shares, for every query row of the group.
 // (Most slots name no pair: the grid is small and those CTAs leave after one load.)
+// The parts of a pair are listed once (a lane per share: which shares hold tiles), every row's
+// maximum, weights and normaliser are computed once by a warp, and the threads then sum the
+// parts' output rows with all their loads independent of one another: a fold is three rounds of
+// global loads whatever the number of parts.  A pair cut into more than ATT_MERGE_PARTS parts
+// (more shares than tiles) goes through a plain loop.
+constexpr int ATT_MERGE_PARTS = 64;
 template <int D>
 __global__ void __launch_bounds__(256) attn_merge_kernel(const AttnParams p) {
   pdl_wait();
@@ -567,25 +573,82 @@ __global__ void __launch_bounds__(256) attn_merge_kernel(const AttnParams p) {
   const int G = p.h_q / p.h_kv;
   const int b = desc.x, kvh = desc.y, first = desc.z, last = desc.w;
   const int64_t total = __ldcg(p.tiles_total);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // the first part sits in this very slot; every later share holds its part in slot 0 (it begins
   // at the share's first tile); with more shares than tiles some shares in between hold no tile
   auto empty = [&](int c) { return share_begin(c, total, p.shares) == share_begin(c + 1, total, p.shares); };
-  for (int e = threadIdx.x; e < G * D; e += blockDim.x) {
-    const int r = e / D, d = e - r * D;
-    auto row_of = [&](int c) -> int64_t { return (c == first ? (int64_t)blockIdx.x : (int64_t)c * 2) * 16 + r; };
-    float mstar = -INFINITY;
-    for (int c = first; c <= last; ++c)
-      if (!empty(c)) mstar = fmaxf(mstar, __ldcg(p.part_ml + row_of(c) * 2));
-    float muse = (mstar == -INFINITY) ? 0.f : mstar;
-    float acc = 0.f, L = 0.f;
-    for (int c = first; c <= last; ++c) {
-      if (empty(c)) continue;
-      const int64_t row = row_of(c);
-      float wgt = exp2f(__ldcg(p.part_ml + row * 2) - muse);
-      acc = fmaf(__ldcg(p.part_o + row * D + d), wgt, acc);
-      L = fmaf(__ldcg(p.part_ml + row * 2 + 1), wgt, L);
+  auto row0_of = [&](int c) -> int { return (c == first ? (int)blockIdx.x : c * 2) * 16; };
+  const int span = last - first + 1;
+  if (span > ATT_MERGE_PARTS) {
+    for (int e = tid; e < G * D; e += blockDim.x) {
+      const int r = e / D, d = e - r * D;
+      float mstar = -INFINITY;
+      for (int c = first; c <= last; ++c)
+        if (!empty(c)) mstar = fmaxf(mstar, __ldcg(p.part_ml + (int64_t)(row0_of(c) + r) * 2));
+      float muse = (mstar == -INFINITY) ? 0.f : mstar;
+      float acc = 0.f, L = 0.f;
+      for (int c = first; c <= last; ++c) {
+        if (empty(c)) continue;
+        const int64_t row = row0_of(c) + r;
+        float wgt = exp2f(__ldcg(p.part_ml + row * 2) - muse);
+        acc = fmaf(__ldcg(p.part_o + row * D + d), wgt, acc);
+        L = fmaf(__ldcg(p.part_ml + row * 2 + 1), wgt, L);
+      }
+      store_out(p, ((int64_t)b * p.h_q + kvh * G + r) * D + d, __fdiv_rn(acc, L));
     }
-    store_out(p, ((int64_t)b * p.h_q + kvh * G + r) * D + d, __fdiv_rn(acc, L));
+    return;
+  }
+  __shared__ int s_row0[ATT_MERGE_PARTS];       // first of the 16 rows of each part that holds tiles
+  __shared__ float s_w[ATT_MERGE_PARTS][16];    // weight of a part for a query row
+  __shared__ float s_l[16];                     // the row's normaliser
+  __shared__ int s_np;
+  if (warp == 0) {  // list the parts in ascending order of their shares
+    int np = 0;
+    for (int c0 = first; c0 <= last; c0 += 32) {
+      const int c = c0 + lane;
+      const bool has = c <= last && !empty(c);
+      const uint32_t m = __ballot_sync(0xffffffffu, has);
+      if (has) s_row0[np + __popc(m & ((1u << lane) - 1u))] = row0_of(c);
+      np += __popc(m);
+    }
+    if (lane == 0) s_np = np;
+  }
+  __syncthreads();
+  const int np = s_np;
+  // per query row (a warp each): maximum, weights in part order, normaliser summed in part order
+  for (int r = warp; r < G; r += 8) {
+    float mloc = -INFINITY;
+    for (int pi = lane; pi < np; pi += 32) mloc = fmaxf(mloc, __ldcg(p.part_ml + (int64_t)(s_row0[pi] + r) * 2));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
+    const float muse = (mloc == -INFINITY) ? 0.f : mloc;
+    for (int pi = lane; pi < np; pi += 32)
+      s_w[pi][r] = exp2f(__ldcg(p.part_ml + (int64_t)(s_row0[pi] + r) * 2) - muse);
+    __syncwarp();
+    if (lane == 0) {
+      float L = 0.f;
+      for (int pi = 0; pi < np; ++pi) L = fmaf(__ldcg(p.part_ml + (int64_t)(s_row0[pi] + r) * 2 + 1), s_w[pi][r], L);
+      s_l[r] = L;
+    }
+  }
+  __syncthreads();
+  // a thread's elements (tid + 256 k) together, so that a part costs one round of loads for all of them
+  constexpr int EPT = 16 * D / 256;
+  float acc[EPT];
+#pragma unroll
+  for (int k = 0; k < EPT; ++k) acc[k] = 0.f;
+  for (int pi = 0; pi < np; ++pi) {
+    const float* po = p.part_o + (int64_t)s_row0[pi] * D;
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+      const int e = tid + k * 256;   // row e / D, column e % D: the part's rows are contiguous
+      if (e < G * D) acc[k] = fmaf(__ldcg(po + e), s_w[pi][e / D], acc[k]);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < EPT; ++k) {
+    const int e = tid + k * 256;
+    if (e < G * D) store_out(p, ((int64_t)b * p.h_q + kvh * G) * D + e, __fdiv_rn(acc[k], s_l[e / D]));
   }
 }
 
