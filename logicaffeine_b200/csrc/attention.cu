@@ -488,7 +488,7 @@ gqa_decode_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       }
       // ---- combine the four warps in the ring stage of the part's last tile (every warp has
       // read its rows of it once all four have passed the barrier), then hand the stage back.
-      // The barrier also carries the verdict: a warp whose wait gave up takes the others with it.
+      // The barrier also carries the outcome: a warp whose wait gave up takes the others with it.
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);

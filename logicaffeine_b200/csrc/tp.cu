@@ -111,7 +111,7 @@ logos_status_t tp_symm_alloc(TpGroup* g, size_t bytes, TpSymm* out, cudaStream_t
   cudaIpcMemHandle_t mine;
   bool good = cudaIpcGetMemHandle(&mine, local) == cudaSuccess;
   if (!good) cudaGetLastError();
-  // exchange the handles (and each rank's verdict so far) through the group's own all-gather
+  // exchange the handles (and each rank's outcome so far) through the group's own all-gather
   struct Slot { cudaIpcMemHandle_t h; int32_t good; int32_t pad[15]; };
   static_assert(sizeof(Slot) == 128, "exchange slot");
   Slot send_h;

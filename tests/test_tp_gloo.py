@@ -86,7 +86,7 @@ def test_two_rank_sharding_matches_unsharded(oracle, tmp_path):
     assert rel(r[0]["o"], o) < 1e-6 and rel(r[0]["d"], d) < 1e-6
 
 
-def test_bench_byte_model_matches_the_survey_figures():
+def test_bench_byte_model_matches_the_workload_arithmetic():
     sys.path.insert(0, ROOT)
     import bench
     w = dict(bench.WORKLOADS["qwen32b-b64"])
